@@ -1,0 +1,370 @@
+// K-GEMM: persistent, warp-specialised bf16 GEMM on the 5th-generation tensor cores.
+//
+//   C[M,N] = epilogue( alpha * A[M,K] * B[N,K]^T )        fp32 accumulation in tensor memory
+//
+// One CTA per SM walks output tiles of 128 x BN. Roles inside the CTA (192 threads):
+//   warp 0      TMA producer: fills a ring of shared-memory stages (A 128x64, B BNx64)
+//   warp 1      allocates tensor memory and issues tcgen05.mma (one thread)
+//   warps 2..5  epilogue: tcgen05.ld the accumulator, apply bias / GELU / gate+residual /
+//               accumulate, store bf16 or fp32
+// Two accumulator buffers in tensor memory let the epilogue of tile i overlap the
+// main loop of tile i+1.
+//
+// Either operand may be "K-major" (reduction dim contiguous, e.g. activations [M,K] and
+// nn.Linear weights [N,K]) or "MN-major" (output dim contiguous). That covers, without
+// any transpose pass:
+//   forward   Y  = X  W^T     A K-major,  B K-major
+//   dgrad     dX = dY W       A K-major,  B MN-major   (W is [N,K] = [Kred, Nout])
+//   wgrad     dW = dY^T X     A MN-major, B MN-major   (reduction over tokens)
+// It replaces the cuBLAS calls behind nn.Linear in the reference
+// (teletron/models/wan/wan_model.py:144-147,225-226).
+#include "tt_common.cuh"
+
+using namespace tt;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int A_BYTES = BM * BK * 2;
+
+enum Epi : int { EPI_NONE = 0, EPI_GELU = 1, EPI_GATE_RES = 2, EPI_ACCUM = 3, EPI_SILU = 4 };
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  int c_fp32;
+  const bf16* bias;
+  int epi;
+  const bf16* residual;
+  long long ldr;
+  const float* gate;
+  long long gate_ld;
+  int rows_per_gate;
+  bf16* aux_out;  // optional pre-activation copy (same ld as C)
+  float alpha;
+  unsigned* status;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = BN * 2 < 32 ? 32 : BN * 2;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+};
+
+template <int BN, int A_MN, int B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const GemmParams p) {
+  using C_ = Cfg<BN>;
+  constexpr int STAGES = C_::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * C_::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C_::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * BM;
+        const int n0 = (tile % tiles_n) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, TT_ST_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * C_::STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full[s], C_::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, &tmA, &full[s], m0 + i * 64, k0);
+          } else {
+            tma_load_2d(sa, &tmA, &full[s], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, &tmB, &full[s], n0 + i * 64, k0);
+          } else {
+            tma_load_2d(sb, &tmB, &full[s], k0, n0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BM, BN, A_MN, B_MN);
+      int it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+        const int a = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tempty[a], aph ^ 1, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 1)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + a * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 2)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + s * C_::STAGE_BYTES);
+          const uint32_t b_base = a_base + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? umma_desc(a_base + k * 2048, 8192, 1024)
+                                        : umma_desc(a_base + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_desc(b_base + k * 2048, 8192, 1024)
+                                        : umma_desc(b_base + k * 32, 16, 1024);
+            umma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[s]);
+        }
+        if (ok) tc_commit(&tfull[a]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    int tcount = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+      const int a = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      if (!mbar_wait(&tfull[a], aph, abort_flag, p.status, TT_ST_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      const int m0 = (tile / tiles_n) * BM;
+      const int n0 = (tile % tiles_n) * BN;
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const float* gate_row = nullptr;
+      if (p.epi == EPI_GATE_RES && row_ok)
+        gate_row = p.gate + (long long)(row / p.rows_per_gate) * p.gate_ld;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c * 32), r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int col = col0 + g * 8;
+          if (!row_ok || col >= p.N) break;
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
+          if (p.bias) {
+            uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+            const uint32_t* bu = reinterpret_cast<const uint32_t*>(&bv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float2 f = unpack_bf16(bu[j]);
+              v[2 * j] += f.x;
+              v[2 * j + 1] += f.y;
+            }
+          }
+          if (p.epi == EPI_GELU || p.epi == EPI_SILU) {
+            if (p.aux_out) {
+              uint4 o;
+              o.x = pack_bf16(v[0], v[1]);
+              o.y = pack_bf16(v[2], v[3]);
+              o.z = pack_bf16(v[4], v[5]);
+              o.w = pack_bf16(v[6], v[7]);
+              *reinterpret_cast<uint4*>(p.aux_out + (long long)row * p.ldc + col) = o;
+            }
+            if (p.epi == EPI_GELU) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = silu(v[j]);
+            }
+          } else if (p.epi == EPI_GATE_RES) {
+            uint4 rv = *reinterpret_cast<const uint4*>(p.residual + (long long)row * p.ldr + col);
+            const uint32_t* ru = reinterpret_cast<const uint32_t*>(&rv);
+            float4 g0 = *reinterpret_cast<const float4*>(gate_row + col);
+            float4 g1 = *reinterpret_cast<const float4*>(gate_row + col + 4);
+            const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float2 f = unpack_bf16(ru[j]);
+              v[2 * j] = f.x + gg[2 * j] * v[2 * j];
+              v[2 * j + 1] = f.y + gg[2 * j + 1] * v[2 * j + 1];
+            }
+          } else if (p.epi == EPI_ACCUM) {
+            if (p.c_fp32) {
+              const float* cp = reinterpret_cast<const float*>(p.C) + (long long)row * p.ldc + col;
+              float4 c0 = *reinterpret_cast<const float4*>(cp);
+              float4 c1 = *reinterpret_cast<const float4*>(cp + 4);
+              v[0] += c0.x; v[1] += c0.y; v[2] += c0.z; v[3] += c0.w;
+              v[4] += c1.x; v[5] += c1.y; v[6] += c1.z; v[7] += c1.w;
+            } else {
+              uint4 cv = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.C) +
+                                                         (long long)row * p.ldc + col);
+              const uint32_t* cu = reinterpret_cast<const uint32_t*>(&cv);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16(cu[j]);
+                v[2 * j] += f.x;
+                v[2 * j + 1] += f.y;
+              }
+            }
+          }
+          if (p.c_fp32) {
+            float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
+            *reinterpret_cast<float4*>(cp) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(cp + 4) = make_float4(v[4], v[5], v[6], v[7]);
+          } else {
+            uint4 o;
+            o.x = pack_bf16(v[0], v[1]);
+            o.y = pack_bf16(v[2], v[3]);
+            o.z = pack_bf16(v[4], v[5]);
+            o.w = pack_bf16(v[6], v[7]);
+            *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.C) + (long long)row * p.ldc + col) = o;
+          }
+        }
+        __syncwarp();  // tcgen05.ld is warp-collective: reconverge before the next chunk
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[a]);
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag) {
+    // let copies that are still in flight land before the CTA's shared memory goes away
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, C_::TMEM_COLS);
+}
+
+template <int BN, int A_MN, int B_MN>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms,
+           cudaStream_t stream) {
+  using C_ = Cfg<BN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    TT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES));
+    attr_done = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, 192, C_::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  TT_LAUNCH_CHECK();
+  return 0;
+}
+
+template <int BN>
+int dispatch_major(int a_mn, int b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                   const GemmParams& p, int sms, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch<BN, 0, 0>(tmA, tmB, p, sms, stream);
+  if (!a_mn && b_mn) return launch<BN, 0, 1>(tmA, tmB, p, sms, stream);
+  if (a_mn && b_mn) return launch<BN, 1, 1>(tmA, tmB, p, sms, stream);
+  return launch<BN, 1, 0>(tmA, tmB, p, sms, stream);
+}
+
+}  // namespace
+
+// A: K-major -> memory [M, K] with row stride lda;  MN-major -> memory [K, M] with row stride lda.
+// B: K-major -> memory [N, K] with row stride ldb;  MN-major -> memory [K, N] with row stride ldb.
+// gate is fp32 [*, gate_ld]; row r uses gate row r / rows_per_gate.
+TT_API int tt_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
+                        void* C, long long ldc, int c_fp32, int M, int N, int K, const void* bias,
+                        int epi, const void* residual, long long ldr, const float* gate,
+                        long long gate_ld, int rows_per_gate, void* aux_out, float alpha,
+                        unsigned* status, int max_ctas, cudaStream_t stream) {
+  TT_CHECK(M > 0 && N > 0 && K > 0, "gemm: empty problem %d x %d x %d", M, N, K);
+  TT_CHECK(N % 8 == 0, "gemm: N (%d) must be a multiple of 8", N);
+  TT_CHECK(lda % 8 == 0 && ldb % 8 == 0, "gemm: lda/ldb must be multiples of 8 elements");
+  TT_CHECK(ldc % (c_fp32 ? 4 : 8) == 0, "gemm: ldc (%lld) breaks 16-byte row alignment", ldc);
+  TT_CHECK(((uintptr_t)C & 15) == 0, "gemm: C is not 16-byte aligned");
+  TT_CHECK(epi >= 0 && epi <= 4, "gemm: unknown epilogue %d", epi);
+  if (epi == EPI_GATE_RES) {
+    TT_CHECK(residual && gate && rows_per_gate > 0, "gemm: gate/residual epilogue needs both tensors");
+    TT_CHECK(ldr % 8 == 0 && gate_ld % 4 == 0, "gemm: residual/gate leading dims misaligned");
+    TT_CHECK((((uintptr_t)residual | (uintptr_t)gate) & 15) == 0, "gemm: residual/gate misaligned");
+  }
+  if (bias) TT_CHECK(((uintptr_t)bias & 15) == 0, "gemm: bias is not 16-byte aligned");
+  const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[2], str[1];
+    uint32_t box[2];
+    if (a_mn) { dims[0] = (uint64_t)M; dims[1] = (uint64_t)K; box[0] = 64; box[1] = 64; }
+    else      { dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = 64; box[1] = BM; }
+    str[0] = (uint64_t)lda * 2;
+    if (tt_make_tmap(&tmA, A, 2, 2, dims, str, box, 1)) return -1;
+    if (b_mn) { dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 64; box[1] = 64; }
+    else      { dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = 64; box[1] = (uint32_t)BN; }
+    str[0] = (uint64_t)ldb * 2;
+    if (tt_make_tmap(&tmB, B, 2, 2, dims, str, box, 1)) return -1;
+  }
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32;
+  p.bias = (const bf16*)bias; p.epi = epi;
+  p.residual = (const bf16*)residual; p.ldr = ldr;
+  p.gate = gate; p.gate_ld = gate_ld; p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1;
+  p.aux_out = (bf16*)aux_out; p.alpha = alpha; p.status = status;
+  int dev = 0, sms = 0;
+  TT_CUDA(cudaGetDevice(&dev));
+  TT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  if (BN == 256) return dispatch_major<256>(a_mn, b_mn, tmA, tmB, p, sms, stream);
+  if (BN == 128) return dispatch_major<128>(a_mn, b_mn, tmA, tmB, p, sms, stream);
+  return dispatch_major<64>(a_mn, b_mn, tmA, tmB, p, sms, stream);
+}

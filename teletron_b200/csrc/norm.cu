@@ -1,0 +1,532 @@
+// K-ADALN, K-RMSNORM (+K-ROPE3D): row-normalisation kernels, bf16 in/out, fp32 math.
+//
+// adaln:  y = LN(x) * m + a   with  m = (plus_one ? 1 + mul : mul), per-sample rows of
+//         mul/add (timestep modulation) or one shared row (affine LayerNorm); mul/add
+//         may be null (plain LayerNorm).  Saves mean and rstd per row.
+//         Backward returns dx and, per CTA, fp32 partial column sums of dy*xhat and dy,
+//         which tt_colsum_partials folds into [batch, C] gradients of mul / add.
+// rmsrope: y = rope(x * rsqrt(mean(x^2) + eps) * w) over the whole row (Wan q/k norm) or
+//         per head of D elements (HunyuanVideo), followed by the rotary embedding on
+//         interleaved (even, odd) pairs with a per-token table of (cos, sin).  Either
+//         stage can be switched off.  Backward is computed from the saved input and
+//         rstd (never from y / w).
+//
+// Successors of teletron_op/fused_adaln/{adaln_forward,adaln_backward,scale_shift_backward}.cu
+// and teletron_op/fused_rmsnorm/{rms_forward,rms_backward,weight_backward}.cu; unlike those,
+// any C that is a multiple of 8 up to 6144 is accepted, modulation is per sample, launches
+// go to the caller's stream and every argument is validated.
+#include "tt_common.cuh"
+
+using namespace tt;
+
+namespace {
+
+constexpr int NT = 256;  // threads per CTA; one row per CTA iteration
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < NT / 32; ++i) t += red[i];
+  return t;
+}
+__device__ __forceinline__ float2 block_sum2(float2 v, float2* red) {
+  v.x = warp_sum(v.x);
+  v.y = warp_sum(v.y);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float2 t = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < NT / 32; ++i) {
+    t.x += red[i].x;
+    t.y += red[i].y;
+  }
+  return t;
+}
+
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 f = unpack_bf16(w[j]);
+    v[2 * j] = f.x;
+    v[2 * j + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
+  uint4 o;
+  o.x = pack_bf16(v[0], v[1]);
+  o.y = pack_bf16(v[2], v[3]);
+  o.z = pack_bf16(v[4], v[5]);
+  o.w = pack_bf16(v[6], v[7]);
+  *reinterpret_cast<uint4*>(p) = o;
+}
+__device__ __forceinline__ void loadf8(const float* p, float (&v)[8]) {
+  float4 a = *reinterpret_cast<const float4*>(p);
+  float4 b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// ------------------------------------------------------------------ AdaLN forward
+template <int VPT>
+__global__ void __launch_bounds__(NT)
+adaln_fwd_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, long long ldy,
+                 const float* __restrict__ mul, const float* __restrict__ add, long long mod_ld,
+                 int plus_one, int rows, int C, int rows_per_batch, float eps,
+                 float* __restrict__ mean_out, float* __restrict__ rstd_out) {
+  __shared__ float red[NT / 32];
+  const int nvec = C >> 3;
+  const float invC = 1.f / (float)C;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    float v[VPT][8];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int vec = threadIdx.x + k * NT;
+      if (vec < nvec) {
+        load8(x + (long long)row * ldx + vec * 8, v[k]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += v[k][j];
+      }
+    }
+    const float mean = block_sum(s, red) * invC;
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int vec = threadIdx.x + k * NT;
+      if (vec < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = v[k][j] - mean;
+          s2 += d * d;
+        }
+      }
+    }
+    const float rstd = rsqrtf(block_sum(s2, red) * invC + eps);
+    if (threadIdx.x == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    const long long mrow = (long long)(row / rows_per_batch) * mod_ld;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int vec = threadIdx.x + k * NT;
+      if (vec < nvec) {
+        float m[8], a[8], o[8];
+        if (mul) {
+          loadf8(mul + mrow + vec * 8, m);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) m[j] = plus_one ? 0.f : 1.f;
+        }
+        if (add) {
+          loadf8(add + mrow + vec * 8, a);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float mm = plus_one ? 1.f + m[j] : m[j];
+          o[j] = (v[k][j] - mean) * rstd * mm + a[j];
+        }
+        store8(y + (long long)row * ldy + vec * 8, o);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ AdaLN backward
+// grid = (chunks, batch). CTA (chunk, b) owns rows [b*rpb + chunk*rpc, min(.. + rpc, (b+1)*rpb)).
+template <int VPT>
+__global__ void __launch_bounds__(NT)
+adaln_bwd_kernel(const bf16* __restrict__ dy, long long lddy, const bf16* __restrict__ x,
+                 long long ldx, const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                 const float* __restrict__ mul, long long mod_ld, int plus_one, bf16* __restrict__ dx,
+                 long long lddx, const bf16* __restrict__ dx_add, long long ldadd,
+                 float* __restrict__ partial, int C, int rows_per_batch, int rows_per_chunk) {
+  __shared__ float2 red[NT / 32];
+  const int nvec = C >> 3;
+  const float invC = 1.f / (float)C;
+  const int b = blockIdx.y;
+  const int chunk = blockIdx.x;
+  const int r0 = chunk * rows_per_chunk;
+  const int r1 = min(r0 + rows_per_chunk, rows_per_batch);
+  float m[VPT][8], acc_mul[VPT][8], acc_add[VPT][8];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int vec = threadIdx.x + k * NT;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      acc_mul[k][j] = 0.f;
+      acc_add[k][j] = 0.f;
+      m[k][j] = plus_one ? 0.f : 1.f;
+    }
+    if (vec < nvec && mul) loadf8(mul + (long long)b * mod_ld + vec * 8, m[k]);
+    if (plus_one) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m[k][j] += 1.f;
+    }
+  }
+  for (int r = r0; r < r1; ++r) {
+    const long long row = (long long)b * rows_per_batch + r;
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float g[VPT][8], xh[VPT][8];
+    float2 s = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int vec = threadIdx.x + k * NT;
+      if (vec < nvec) {
+        float d[8], xv[8];
+        load8(dy + row * lddy + vec * 8, d);
+        load8(x + row * ldx + vec * 8, xv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[k][j] = (xv[j] - mean) * rstd;
+          acc_mul[k][j] += d[j] * xh[k][j];
+          acc_add[k][j] += d[j];
+          g[k][j] = d[j] * m[k][j];
+          s.x += g[k][j];
+          s.y += g[k][j] * xh[k][j];
+        }
+      }
+    }
+    s = block_sum2(s, red);
+    const float c1 = s.x * invC, c2 = s.y * invC;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int vec = threadIdx.x + k * NT;
+      if (vec < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[k][j] - c1 - xh[k][j] * c2);
+        if (dx_add) {  // fold the residual-branch gradient into the same pass
+          float e[8];
+          load8(dx_add + row * ldadd + vec * 8, e);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += e[j];
+        }
+        store8(dx + row * lddx + vec * 8, o);
+      }
+    }
+  }
+  if (partial) {
+    float* pm = partial + ((long long)(b * gridDim.x + chunk) * 2) * C;
+    float* pa = pm + C;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int vec = threadIdx.x + k * NT;
+      if (vec < nvec) {
+        *reinterpret_cast<float4*>(pm + vec * 8) = make_float4(acc_mul[k][0], acc_mul[k][1], acc_mul[k][2], acc_mul[k][3]);
+        *reinterpret_cast<float4*>(pm + vec * 8 + 4) = make_float4(acc_mul[k][4], acc_mul[k][5], acc_mul[k][6], acc_mul[k][7]);
+        *reinterpret_cast<float4*>(pa + vec * 8) = make_float4(acc_add[k][0], acc_add[k][1], acc_add[k][2], acc_add[k][3]);
+        *reinterpret_cast<float4*>(pa + vec * 8 + 4) = make_float4(acc_add[k][4], acc_add[k][5], acc_add[k][6], acc_add[k][7]);
+      }
+    }
+  }
+}
+
+// out[g, c] (+)= sum_{i < n} partial[g*stride_g + i*stride_n + c]  (fixed order => deterministic)
+__global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                       int groups, int n, int width, long long stride_g,
+                                       long long stride_n, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int g = blockIdx.y;
+  if (c >= width || g >= groups) return;
+  const float* p = partial + (long long)g * stride_g + c;
+  float s = 0.f;
+  for (int i = 0; i < n; ++i) s += p[(long long)i * stride_n];
+  float* o = out + (long long)g * width + c;
+  *o = accumulate ? *o + s : s;
+}
+
+// ------------------------------------------------------------------ RMSNorm + RoPE
+// norm_dim == C : statistics over the whole row; norm_dim == D : per head (16 threads own
+// one head of 128). w may be null (no norm), freqs may be null (no rotary).
+template <int VPT, bool BWD>
+__global__ void __launch_bounds__(NT)
+rmsrope_kernel(const bf16* __restrict__ in, long long ldi, const bf16* __restrict__ xsave,
+               long long ldx, bf16* __restrict__ out, long long ldo, const float* __restrict__ w,
+               const float2* __restrict__ freqs, int freq_rows, float* __restrict__ rstd_io,
+               float* __restrict__ partial, int rows, int C, int D, int per_head, float eps,
+               int rows_per_cta) {
+  __shared__ float red[NT / 32];
+  const int nvec = C >> 3;
+  const int vec_per_head = D >> 3;
+  const int H = C / D;
+  float accw[VPT][8];
+  float wv[VPT][8];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int vec = threadIdx.x + k * NT;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      accw[k][j] = 0.f;
+      wv[k][j] = 1.f;
+    }
+    if (w && vec < nvec) loadf8(w + (per_head ? (vec % vec_per_head) * 8 : vec * 8), wv[k]);
+  }
+  const int r0 = blockIdx.x * rows_per_cta;
+  const int r1 = min(r0 + rows_per_cta, rows);
+  for (int row = r0; row < r1; ++row) {
+    float v[VPT][8];  // forward: x ; backward: dy then g
+    float cs[VPT][8];
+    const float2* frow = freqs ? freqs + (long long)(row % freq_rows) * (D >> 1) : nullptr;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int vec = threadIdx.x + k * NT;
+      if (vec < nvec) {
+        load8(in + (long long)row * ldi + vec * 8, v[k]);
+        if (frow) loadf8(reinterpret_cast<const float*>(frow + (vec % vec_per_head) * 4), cs[k]);
+      }
+    }
+    if (!BWD) {
+      float rs[VPT];
+      if (w) {
+        float ss[VPT];
+        float tot = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          ss[k] = 0.f;
+          if (threadIdx.x + k * NT < nvec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss[k] += v[k][j] * v[k][j];
+          }
+          tot += ss[k];
+        }
+        if (per_head) {
+#pragma unroll
+          for (int k = 0; k < VPT; ++k) {
+            float t = ss[k];
+            for (int o = vec_per_head >> 1; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+            rs[k] = rsqrtf(t / (float)D + eps);
+            const int vec = threadIdx.x + k * NT;
+            if (vec < nvec && (vec % vec_per_head) == 0 && rstd_io)
+              rstd_io[(long long)row * H + vec / vec_per_head] = rs[k];
+          }
+        } else {
+          const float r = rsqrtf(block_sum(tot, red) / (float)C + eps);
+#pragma unroll
+          for (int k = 0; k < VPT; ++k) rs[k] = r;
+          if (threadIdx.x == 0 && rstd_io) rstd_io[row] = r;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) rs[k] = 1.f;
+      }
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int vec = threadIdx.x + k * NT;
+        if (vec < nvec) {
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = v[k][j] * rs[k] * wv[k][j];
+          if (frow) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float c = cs[k][2 * j], s = cs[k][2 * j + 1];
+              const float a = o[2 * j], b = o[2 * j + 1];
+              o[2 * j] = a * c - b * s;
+              o[2 * j + 1] = a * s + b * c;
+            }
+          }
+          store8(out + (long long)row * ldo + vec * 8, o);
+        }
+      }
+    } else {
+      // backward: v = dy. un-rotate, then norm backward from saved x and rstd.
+      float xh[VPT][8];
+      float dot[VPT];
+      float tot = 0.f;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        dot[k] = 0.f;
+        const int vec = threadIdx.x + k * NT;
+        if (vec < nvec) {
+          if (frow) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float c = cs[k][2 * j], s = cs[k][2 * j + 1];
+              const float a = v[k][2 * j], b = v[k][2 * j + 1];
+              v[k][2 * j] = a * c + b * s;
+              v[k][2 * j + 1] = -a * s + b * c;
+            }
+          }
+          if (w) {
+            float xv[8];
+            load8(xsave + (long long)row * ldx + vec * 8, xv);
+            const float r = per_head ? rstd_io[(long long)row * H + vec / vec_per_head] : rstd_io[row];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              xh[k][j] = xv[j] * r;
+              accw[k][j] += v[k][j] * xh[k][j];
+              v[k][j] *= wv[k][j];
+              dot[k] += v[k][j] * xh[k][j];
+            }
+          }
+        }
+        tot += dot[k];
+      }
+      if (w) {
+        float full = 0.f;
+        if (!per_head) full = block_sum(tot, red) / (float)C;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          const int vec = threadIdx.x + k * NT;
+          float sdot;
+          if (per_head) {
+            float t = dot[k];
+            for (int o = vec_per_head >> 1; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+            sdot = t / (float)D;
+          } else {
+            sdot = full;
+          }
+          if (vec < nvec) {
+            const float r = per_head ? rstd_io[(long long)row * H + vec / vec_per_head] : rstd_io[row];
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = r * (v[k][j] - xh[k][j] * sdot);
+            store8(out + (long long)row * ldo + vec * 8, o);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          const int vec = threadIdx.x + k * NT;
+          if (vec < nvec) store8(out + (long long)row * ldo + vec * 8, v[k]);
+        }
+      }
+    }
+  }
+  if (BWD && partial && w) {
+    float* pw = partial + (long long)blockIdx.x * C;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int vec = threadIdx.x + k * NT;
+      if (vec < nvec) {
+        *reinterpret_cast<float4*>(pw + vec * 8) = make_float4(accw[k][0], accw[k][1], accw[k][2], accw[k][3]);
+        *reinterpret_cast<float4*>(pw + vec * 8 + 4) = make_float4(accw[k][4], accw[k][5], accw[k][6], accw[k][7]);
+      }
+    }
+  }
+}
+
+int vpt_for(int C) { return (C / 8 + NT - 1) / NT; }
+bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+}  // namespace
+
+#define TT_DISPATCH_VPT(vpt, ...)            \
+  switch (vpt) {                             \
+    case 1: { constexpr int VPT = 1; __VA_ARGS__; } break; \
+    case 2: { constexpr int VPT = 2; __VA_ARGS__; } break; \
+    case 3: { constexpr int VPT = 3; __VA_ARGS__; } break; \
+    default: tt_set_error("row width too large (max 6144)"); return -1; \
+  }
+
+TT_API int tt_adaln_fwd(const void* x, long long ldx, void* y, long long ldy, const float* mul,
+                        const float* add, long long mod_ld, int plus_one, int rows, int C,
+                        int rows_per_batch, float eps, float* mean_out, float* rstd_out,
+                        cudaStream_t stream) {
+  TT_CHECK(rows > 0 && C > 0 && C % 8 == 0 && C <= 6144, "adaln_fwd: bad shape rows=%d C=%d", rows, C);
+  TT_CHECK(ldx % 8 == 0 && ldy % 8 == 0 && mod_ld % 4 == 0, "adaln_fwd: leading dims misaligned");
+  TT_CHECK(aligned16(x) && aligned16(y) && aligned16(mul) && aligned16(add), "adaln_fwd: misaligned pointer");
+  TT_CHECK(rows_per_batch > 0, "adaln_fwd: rows_per_batch must be positive");
+  const int grid = rows < 148 * 16 ? rows : 148 * 16;
+  TT_DISPATCH_VPT(vpt_for(C), adaln_fwd_kernel<VPT><<<grid, NT, 0, stream>>>(
+      (const bf16*)x, ldx, (bf16*)y, ldy, mul, add, mod_ld, plus_one, rows, C, rows_per_batch, eps,
+      mean_out, rstd_out));
+  TT_LAUNCH_CHECK();
+  return 0;
+}
+
+// partial: fp32 [batch, chunks, 2, C] scratch (may be null when no mul/add gradient is wanted).
+// dmul / dadd: fp32 [batch, C] (either may be null). accumulate: add into them.
+TT_API int tt_adaln_bwd(const void* dy, long long lddy, const void* x, long long ldx,
+                        const float* mean, const float* rstd, const float* mul, long long mod_ld,
+                        int plus_one, void* dx, long long lddx, const void* dx_add, long long ldadd,
+                        float* partial, int chunks, float* dmul, float* dadd, int accumulate,
+                        int batch, int rows_per_batch, int C, cudaStream_t stream) {
+  TT_CHECK(batch > 0 && rows_per_batch > 0 && C % 8 == 0 && C <= 6144, "adaln_bwd: bad shape");
+  TT_CHECK(chunks > 0, "adaln_bwd: chunks must be positive");
+  TT_CHECK(lddy % 8 == 0 && ldx % 8 == 0 && lddx % 8 == 0 && mod_ld % 4 == 0 && ldadd % 8 == 0,
+           "adaln_bwd: leading dims misaligned");
+  TT_CHECK(aligned16(dy) && aligned16(x) && aligned16(dx) && aligned16(mul) && aligned16(partial) &&
+               aligned16(dx_add),
+           "adaln_bwd: misaligned pointer");
+  const int rpc = (rows_per_batch + chunks - 1) / chunks;
+  dim3 grid(chunks, batch);
+  TT_DISPATCH_VPT(vpt_for(C), adaln_bwd_kernel<VPT><<<grid, NT, 0, stream>>>(
+      (const bf16*)dy, lddy, (const bf16*)x, ldx, mean, rstd, mul, mod_ld, plus_one, (bf16*)dx, lddx,
+      (const bf16*)dx_add, ldadd, partial, C, rows_per_batch, rpc));
+  TT_LAUNCH_CHECK();
+  if (partial && (dmul || dadd)) {
+    dim3 g2((C + 255) / 256, batch);
+    const long long sg = (long long)chunks * 2 * C, sn = 2ll * C;
+    if (dmul) colsum_partials_kernel<<<g2, 256, 0, stream>>>(partial, dmul, batch, chunks, C, sg, sn, accumulate);
+    if (dadd) colsum_partials_kernel<<<g2, 256, 0, stream>>>(partial + C, dadd, batch, chunks, C, sg, sn, accumulate);
+    TT_LAUNCH_CHECK();
+  }
+  return 0;
+}
+
+TT_API int tt_colsum_partials(const float* partial, float* out, int groups, int n, int width,
+                              int accumulate, cudaStream_t stream) {
+  TT_CHECK(groups > 0 && n > 0 && width > 0, "colsum_partials: bad shape");
+  dim3 grid((width + 255) / 256, groups);
+  colsum_partials_kernel<<<grid, 256, 0, stream>>>(partial, out, groups, n, width, (long long)n * width, (long long)width, accumulate);
+  TT_LAUNCH_CHECK();
+  return 0;
+}
+
+// Forward: in = x. Saves rstd ([rows] or [rows, H]) when w != null.
+TT_API int tt_rmsrope_fwd(const void* x, long long ldx, void* y, long long ldy, const float* w,
+                          const void* freqs, int freq_rows, float* rstd, int rows, int C, int D,
+                          int per_head, float eps, cudaStream_t stream) {
+  TT_CHECK(rows > 0 && C % 8 == 0 && C <= 6144 && D > 0 && C % D == 0, "rmsrope_fwd: bad shape");
+  TT_CHECK(!per_head || (D == 128 || D == 64), "rmsrope_fwd: per-head norm supports D = 64 or 128");
+  TT_CHECK(freqs == nullptr || (D % 8 == 0 && freq_rows > 0), "rmsrope_fwd: bad rotary table");
+  TT_CHECK(ldx % 8 == 0 && ldy % 8 == 0, "rmsrope_fwd: leading dims misaligned");
+  TT_CHECK(aligned16(x) && aligned16(y) && aligned16(w) && aligned16(freqs), "rmsrope_fwd: misaligned pointer");
+  const int rpc = rows > 148 * 32 ? (rows + 148 * 16 - 1) / (148 * 16) : 1;
+  const int grid = (rows + rpc - 1) / rpc;
+  TT_DISPATCH_VPT(vpt_for(C), rmsrope_kernel<VPT, false><<<grid, NT, 0, stream>>>(
+      (const bf16*)x, ldx, nullptr, 0, (bf16*)y, ldy, w, (const float2*)freqs, freq_rows, rstd,
+      nullptr, rows, C, D, per_head, eps, rpc));
+  TT_LAUNCH_CHECK();
+  return 0;
+}
+
+// Backward: dy -> dx, with x (saved forward input) and rstd. partial: fp32 [ctas, C] scratch for
+// the weight gradient, ctas = tt_rmsrope_bwd_ctas(rows); fold it with tt_colsum_partials.
+TT_API int tt_rmsrope_bwd_ctas(int rows) {
+  const int rpc = (rows + 592 - 1) / 592;
+  return (rows + rpc - 1) / rpc;
+}
+TT_API int tt_rmsrope_bwd(const void* dy, long long lddy, const void* x, long long ldx, void* dx,
+                          long long lddx, const float* w, const void* freqs, int freq_rows,
+                          float* rstd, float* partial, int rows, int C, int D, int per_head,
+                          cudaStream_t stream) {
+  TT_CHECK(rows > 0 && C % 8 == 0 && C <= 6144 && D > 0 && C % D == 0, "rmsrope_bwd: bad shape");
+  TT_CHECK(!per_head || (D == 128 || D == 64), "rmsrope_bwd: per-head norm supports D = 64 or 128");
+  TT_CHECK(lddy % 8 == 0 && ldx % 8 == 0 && lddx % 8 == 0, "rmsrope_bwd: leading dims misaligned");
+  TT_CHECK(aligned16(dy) && aligned16(x) && aligned16(dx) && aligned16(w) && aligned16(freqs) &&
+               aligned16(partial),
+           "rmsrope_bwd: misaligned pointer");
+  TT_CHECK(w == nullptr || (x != nullptr && rstd != nullptr), "rmsrope_bwd: norm backward needs x and rstd");
+  const int rpc = (rows + 592 - 1) / 592;
+  const int grid = (rows + rpc - 1) / rpc;
+  TT_DISPATCH_VPT(vpt_for(C), rmsrope_kernel<VPT, true><<<grid, NT, 0, stream>>>(
+      (const bf16*)dy, lddy, (const bf16*)x, ldx, (bf16*)dx, lddx, w, (const float2*)freqs, freq_rows,
+      rstd, partial, rows, C, D, per_head, 0.f, rpc));
+  TT_LAUNCH_CHECK();
+  return 0;
+}

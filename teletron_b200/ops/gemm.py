@@ -1,0 +1,98 @@
+"""bf16 GEMM on tcgen05 tensor cores (csrc/gemm.cu) and the autograd Linear built on it.
+
+``gemm`` computes ``C[M,N] = epilogue(alpha * A @ B^T)`` where either operand may be
+stored transposed ("MN-major"), so forward, dgrad and wgrad of a Linear layer need no
+transpose pass.  ``gemm_ref`` is the fp32 PyTorch statement of the same contract and is
+what runs on CPU.  Replaces cuBLAS behind ``nn.Linear`` in the reference
+(teletron/models/wan/wan_model.py:144-147).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+EPI_NONE, EPI_GELU, EPI_GATE_RES, EPI_ACCUM, EPI_SILU = 0, 1, 2, 3, 4
+
+
+def _logical(a: torch.Tensor, mn_major: bool) -> torch.Tensor:
+    return a.t() if mn_major else a
+
+
+def gemm_ref(a, b, *, a_mn=False, b_mn=False, bias=None, epi=EPI_NONE, residual=None, gate=None,
+             rows_per_gate=1, out=None, out_dtype=torch.bfloat16, alpha=1.0, want_aux=False):
+    """fp32 reference. A logical [M,K], B logical [N,K]."""
+    A = _logical(a, a_mn).float()
+    B = _logical(b, b_mn).float()
+    acc = alpha * (A @ B.t())
+    if bias is not None:
+        acc = acc + bias.float()
+    aux = None
+    if epi == EPI_GELU:
+        aux = acc.to(torch.bfloat16) if want_aux else None
+        acc = torch.nn.functional.gelu(acc, approximate="tanh")
+    elif epi == EPI_SILU:
+        aux = acc.to(torch.bfloat16) if want_aux else None
+        acc = torch.nn.functional.silu(acc)
+    elif epi == EPI_GATE_RES:
+        g = gate.float().repeat_interleave(rows_per_gate, dim=0)[: acc.shape[0]]
+        acc = residual.float() + g * acc
+    elif epi == EPI_ACCUM:
+        acc = out.float() + acc
+    if out is not None:
+        out.copy_(acc.to(out.dtype))
+        res = out
+    else:
+        res = acc.to(out_dtype)
+    return (res, aux) if want_aux else res
+
+
+def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, epi=EPI_NONE, residual=None, gate=None,
+         rows_per_gate=1, out=None, out_dtype=torch.bfloat16, alpha=1.0, want_aux=False, max_ctas=0):
+    """C = epilogue(alpha * A @ B^T).
+
+    a: [M,K] (or [K,M] when a_mn)   b: [N,K] (or [K,N] when b_mn); both bf16 with a
+    contiguous last dim.  ``epi``: EPI_GELU / EPI_SILU (optionally returning the
+    pre-activation as aux), EPI_GATE_RES (``residual + gate[row // rows_per_gate] * acc``,
+    gate fp32), EPI_ACCUM (``out += acc``).
+    """
+    if not a.is_cuda:
+        return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, epi=epi, residual=residual, gate=gate,
+                        rows_per_gate=rows_per_gate, out=out, out_dtype=out_dtype, alpha=alpha,
+                        want_aux=want_aux)
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "gemm operands must be bf16"
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"reduction dims differ: {K} vs {Kb}"
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    else:
+        assert out.shape == (M, N) and out.stride(1) == 1
+    aux = None
+    if want_aux:
+        aux = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+        assert out.stride(0) == aux.stride(0)
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == N
+    if epi == EPI_GATE_RES:
+        assert residual.dtype == torch.bfloat16 and gate.dtype == torch.float32
+        assert residual.shape == (M, N) and residual.stride(1) == 1 and gate.stride(-1) == 1
+    L = _lib.lib()
+    rc = L.tt_gemm_bf16(
+        _lib.ptr(a), _lib.c_ll(a.stride(0)), _lib.c_int(int(a_mn)),
+        _lib.ptr(b), _lib.c_ll(b.stride(0)), _lib.c_int(int(b_mn)),
+        _lib.ptr(out), _lib.c_ll(out.stride(0)), _lib.c_int(int(out.dtype == torch.float32)),
+        _lib.c_int(M), _lib.c_int(N), _lib.c_int(K), _lib.ptr(bias), _lib.c_int(epi),
+        _lib.ptr(residual), _lib.c_ll(residual.stride(0) if residual is not None else 0),
+        _lib.ptr(gate), _lib.c_ll(gate.stride(0) if gate is not None else 0),
+        _lib.c_int(rows_per_gate), _lib.ptr(aux), _lib.c_float(alpha),
+        _lib.ptr(_lib.status_word(a.device)), _lib.c_int(max_ctas), _lib.stream())
+    _lib.check(rc, "tt_gemm_bf16")
+    return (out, aux) if want_aux else out
