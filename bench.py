@@ -1,0 +1,311 @@
+#!/usr/bin/env python
+"""Headline benchmark: Wan2.1-1.3B t2v training throughput (tokens/s) at 480P x 81 frames.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched under torchrun)
+    python bench.py --impl reference ...                     (the reference's own model code)
+
+One step = one optimizer step over a global batch of 8 samples (32,760 tokens each), bf16,
+synthetic latents / text embeddings, random-init weights, AdamW.  The same global batch is
+used at every N (strong scaling): DP over the ranks that are not used for Ulysses CP, gradient
+accumulation when fewer than 8 replicas exist.  Rank 0 prints one JSON line.
+
+`value` is timed on the device with CUDA events with inputs already resident; `e2e` repeats
+the measurement through ``Trainer.train_step`` with every step's inputs copied from pinned host
+memory and the loss read back to the host.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "wan2.1_1.3b_t2v_480p81f_train_tokens_per_s"
+FRAMES, HEIGHT, WIDTH = 81, 480, 832
+TOKENS_PER_SAMPLE = 21 * 30 * 52  # 32,760
+GLOBAL_BATCH = 8
+PUBLISHED_TOKENS_PER_S_PER_GPU = 1090.0  # 21.6 FPS/node on 16 x H800, read off ComparativeGraph.jpg
+
+
+def clock_sampler_start(path: str):
+    q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    try:
+        f = open(path, "w")
+        return subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                stdout=f, stderr=subprocess.DEVNULL), f
+    except Exception:
+        return None, None
+
+
+def clock_sampler_stop(proc, f, path: str, device_index: int = 0):
+    out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+    if proc is None:
+        return out
+    proc.terminate()
+    try:
+        proc.wait(timeout=5)
+    except Exception:
+        proc.kill()
+    f.close()
+    sm, mx, reasons = [], [], set()
+    try:
+        for line in open(path):
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9 or not c[0].isdigit() or int(c[0]) != device_index:
+                continue
+            try:
+                sm.append(float(c[1]))
+                mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+    except FileNotFoundError:
+        return out
+    if sm:
+        busy = [s for s in sm if s > 0.5 * max(sm)] or sm
+        out["sm_mhz"] = statistics.median(busy)
+        out["sm_max_mhz"] = max(mx)
+        out["reasons"] = sorted(reasons)
+        out["samples"] = len(sm)
+    return out
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+
+
+# ------------------------------------------------------------------------------ ours
+def run_ours(a):
+    import torch
+    import torch.distributed as dist
+
+    from teletron_b200.data import SyntheticLatentDataset
+    from teletron_b200.ops import _lib
+    from teletron_b200.train import Trainer, make_forward_step, parse_args
+
+    rank, world, local = dist_env()
+    assert world == a.gpus, f"WORLD_SIZE {world} != --gpus {a.gpus} (launch N > 1 under torchrun)"
+    cp = a.cp
+    dp = world // cp
+    argv = ["--model", "ParallelWanModel", "--model-preset", a.model, "--bf16", "--micro-batch-size", "1",
+            "--global-batch-size", str(GLOBAL_BATCH), "--train-iters", "1000000", "--lr", "1e-5",
+            "--weight-decay", "1e-2", "--clip-grad", "1.0", "--context-parallel-size", str(cp),
+            "--num-frames", str(FRAMES), "--video-resolution", str(HEIGHT), str(WIDTH), "--synthetic-latents",
+            "--log-interval", "1000000", "--seed", "1234"]
+    if world > 1:
+        argv.append("--use-distributed-optimizer")
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if a.recompute:
+        argv += ["--recompute-granularity", "full", "--recompute-method", "block", "--recompute-num-layers", "30"]
+    if a.layers:
+        argv += ["--num-layers", str(a.layers)]
+    targs = parse_args(argv=argv)
+    trainer = Trainer(targs, build_data=False)
+    dev = trainer.device
+    fwd = make_forward_step()
+    n_mb = targs.num_micro_batches
+
+    # a small pool of distinct samples, kept both in pinned host memory and on the device
+    ds = SyntheticLatentDataset(FRAMES, HEIGHT, WIDTH, seed=1234 + rank)
+    pool_host = []
+    for i in range(max(n_mb, 2)):
+        it = ds[i]
+        pool_host.append({k: v.unsqueeze(0).pin_memory() for k, v in it.items()})
+    pool_dev = [{k: v.to(dev) for k, v in b.items()} for b in pool_host]
+    bytes_h2d_per_mb = sum(v.numel() * v.element_size() for v in pool_host[0].values())
+
+    def cycle(pool):
+        i = 0
+        while True:
+            yield pool[i % len(pool)]
+            i += 1
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(pool, steps, read_loss):
+        it = cycle(pool)
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = _lib.launch_count()
+        e0.record()
+        last = None
+        for _ in range(steps):
+            loss_dict, _, _, _ = trainer.train_step(fwd, it)
+            if read_loss:
+                last = float(loss_dict["loss"])  # device -> host read of the step's result
+        e1.record()
+        sync_all()
+        ms = e0.elapsed_time(e1)
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), _lib.launch_count() - l0, last
+
+    for _ in range(a.warmup):
+        trainer.train_step(fwd, cycle(pool_dev))
+    sync_all()
+    _lib.check_status()
+    clk_path = str(ROOT / "gpurun_out" / f"bench_clocks_rank{rank}.csv")
+    os.makedirs(os.path.dirname(clk_path), exist_ok=True)
+    proc, fh = clock_sampler_start(clk_path) if rank == 0 else (None, None)
+    ms_dev, launches, _ = timed(pool_dev, a.steps, read_loss=False)
+    clocks = clock_sampler_stop(proc, fh, clk_path, local) if rank == 0 else {}
+    ms_e2e, _, last_loss = timed(pool_host, a.steps, read_loss=True)
+    _lib.check_status()
+    tokens = GLOBAL_BATCH * TOKENS_PER_SAMPLE * a.steps
+    value = tokens / (ms_dev * 1e-3)
+    e2e = tokens / (ms_e2e * 1e-3)
+    if rank == 0:
+        res = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+            "warmup": a.warmup, "ms_per_step": ms_dev / a.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": value / (PUBLISHED_TOKENS_PER_S_PER_GPU * world), "dtype": "bf16", "data": "synthetic",
+            "impl": "teletron_b200",
+            "config": {"model": "Wan2.1-1.3B t2v (30 layers, dim 1536, 12x128 heads, ffn 8960)" if not a.layers
+                       else f"Wan2.1-1.3B t2v truncated to {a.layers} layers (NOT the named config)",
+                       "global_batch": GLOBAL_BATCH, "seq_len": TOKENS_PER_SAMPLE,
+                       "parallelism": f"dp{dp}" + (f"xcp{cp}" if cp > 1 else ""), "micro_batches_per_step": n_mb,
+                       "optimizer": "AdamW fp32 master" + (" (sharded)" if world > 1 else ""),
+                       "recompute": "full" if a.recompute else "none",
+                       "l2": "inputs and working set far larger than L2 (each step touches > 50 GB)",
+                       "baseline_note": "vs_baseline divides by 1.09k tokens/s/GPU read off the reference's H800 chart"},
+            "clocks": clocks,
+            "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps,
+                    "h2d_bytes_per_step": bytes_h2d_per_mb * GLOBAL_BATCH, "d2h_bytes_per_step": 4 * world,
+                    "last_loss": last_loss},
+            "gpu_launches": launches,
+        }
+        print(json.dumps(res), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------ reference
+def run_reference(a):
+    """The reference's own DiT code from baseline/_ref, driven directly: its Trainer needs
+    megatron-core / apex / yunchang, none of which can be installed offline."""
+    rank, world, local = dist_env()
+
+    def unavailable(why):
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+        return 0
+
+    ref_file = ROOT / "baseline" / "_ref" / "teletron" / "models" / "wan" / "wan_model.py"
+    if not ref_file.exists():
+        return unavailable("reference not installed under baseline/_ref (pip --no-deps install missing)")
+    if world > 1 or a.gpus > 1:
+        return unavailable("multi-GPU reference path needs megatron-core 0.6.0 + yunchang (parallel_state, DDP, "
+                           "Ulysses all-to-all); neither is in the offline wheelhouse, so only N=1 runs")
+    import importlib.util
+    from types import SimpleNamespace
+
+    import torch
+
+    spec = importlib.util.spec_from_file_location("ref_wan_model", ref_file)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    fm_spec = importlib.util.spec_from_file_location("ref_flow_match", ref_file.parent.parent / "flow_match.py")
+    fm = importlib.util.module_from_spec(fm_spec)
+    fm_spec.loader.exec_module(fm)
+    P = ref.WanParams  # model shape is class-level configuration in the reference
+    P.in_channels, P.ffn_dim, P.has_image_input = 16, 8960, False
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    torch.manual_seed(1234)
+    n_layers = a.layers or 30
+    model = ref.WanModel(SimpleNamespace(hidden_size=1536, num_attention_heads=12, num_layers=n_layers))
+    model = model.to(dev).to(torch.bfloat16).train()
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-5, weight_decay=1e-2, fused=True)
+    sched = fm.FlowMatchScheduler(shift=5, sigma_min=0.0, extra_one_step=True)
+    sched.set_timesteps(1000, training=True)
+    f, h, w = 21, 60, 104
+    pool = [dict(latents=torch.randn(1, 16, f, h, w, device=dev, dtype=torch.bfloat16),
+                 context=torch.randn(1, 512, 4096, device=dev, dtype=torch.bfloat16)) for _ in range(GLOBAL_BATCH)]
+    use_ckpt = not a.ref_no_recompute
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        for mb in range(GLOBAL_BATCH):
+            b = pool[mb]
+            latents = b["latents"]
+            noise = torch.randn_like(latents)
+            tid = torch.randint(0, sched.num_train_timesteps, (1,))
+            timestep = sched.timesteps[tid].to(dtype=torch.bfloat16, device=dev)
+            target = sched.training_target(latents, noise, timestep)
+            noisy = sched.add_noise(latents, noise, timestep)
+            out = model(x=noisy, timestep=timestep, context=b["context"], use_gradient_checkpointing=use_ckpt)
+            loss = torch.nn.functional.mse_loss(out.float(), target.float()) * sched.training_weight(timestep)
+            (loss / GLOBAL_BATCH).backward()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        opt.step()
+        return loss
+
+    try:
+        for _ in range(a.warmup):
+            step()
+    except torch.cuda.OutOfMemoryError:
+        return unavailable("reference model ran out of memory in warm-up")
+    torch.cuda.synchronize()
+    clk_path = str(ROOT / "gpurun_out" / "bench_clocks_reference.csv")
+    os.makedirs(os.path.dirname(clk_path), exist_ok=True)
+    proc, fh = clock_sampler_start(clk_path)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        loss = step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = clock_sampler_stop(proc, fh, clk_path, local)
+    ms = e0.elapsed_time(e1)
+    tokens = GLOBAL_BATCH * TOKENS_PER_SAMPLE * a.steps
+    value = tokens / (ms * 1e-3)
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": value / PUBLISHED_TOKENS_PER_S_PER_GPU, "dtype": "bf16", "data": "synthetic",
+        "impl": "reference",
+        "config": {"model": "Wan2.1-1.3B t2v" if not a.layers else f"truncated to {a.layers} layers",
+                   "global_batch": GLOBAL_BATCH, "seq_len": TOKENS_PER_SAMPLE, "parallelism": "dp1",
+                   "recompute": "per-block checkpointing (the reference's shipped setting)" if use_ckpt else "none",
+                   "note": "unmodified teletron/models/wan/wan_model.py + flow_match.py from baseline/_ref, flash_attn 2 "
+                           "attention, torch fused AdamW on bf16 parameters; the reference Trainer itself cannot be "
+                           "imported offline (megatron-core, apex, yunchang missing)"},
+        "clocks": clocks, "last_loss": float(loss)}), flush=True)
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", type=str, default="wan2.1-1.3b-t2v")
+    ap.add_argument("--cp", type=int, default=1, help="Ulysses context-parallel size (rest is DP)")
+    ap.add_argument("--recompute", action="store_true", help="full activation recompute (not needed at 1.3B)")
+    ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (invalid as a result)")
+    ap.add_argument("--ref-no-recompute", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        sys.exit(run_reference(a) or 0)
+    run_ours(a)
+
+
+if __name__ == "__main__":
+    main()

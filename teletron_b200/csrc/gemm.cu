@@ -229,6 +229,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               for (int j = 0; j < 8; ++j) v[j] = silu(v[j]);
             }
           } else if (p.epi == EPI_GATE_RES) {
+            if (p.aux_out) {  // keep the un-gated branch output: its gradient needs it
+              uint4 o;
+              o.x = pack_bf16(v[0], v[1]);
+              o.y = pack_bf16(v[2], v[3]);
+              o.z = pack_bf16(v[4], v[5]);
+              o.w = pack_bf16(v[6], v[7]);
+              *reinterpret_cast<uint4*>(p.aux_out + (long long)row * p.ldc + col) = o;
+            }
             uint4 rv = *reinterpret_cast<const uint4*>(p.residual + (long long)row * p.ldr + col);
             const uint32_t* ru = reinterpret_cast<const uint32_t*>(&rv);
             float4 g0 = *reinterpret_cast<const float4*>(gate_row + col);

@@ -471,9 +471,14 @@ TT_API int tt_adaln_bwd(const void* dy, long long lddy, const void* x, long long
   if (partial && (dmul || dadd)) {
     dim3 g2((C + 255) / 256, batch);
     const long long sg = (long long)chunks * 2 * C, sn = 2ll * C;
-    if (dmul) colsum_partials_kernel<<<g2, 256, 0, stream>>>(partial, dmul, batch, chunks, C, sg, sn, accumulate);
-    if (dadd) colsum_partials_kernel<<<g2, 256, 0, stream>>>(partial + C, dadd, batch, chunks, C, sg, sn, accumulate);
-    TT_LAUNCH_CHECK();
+    if (dmul) {
+      colsum_partials_kernel<<<g2, 256, 0, stream>>>(partial, dmul, batch, chunks, C, sg, sn, accumulate);
+      TT_LAUNCH_CHECK();
+    }
+    if (dadd) {
+      colsum_partials_kernel<<<g2, 256, 0, stream>>>(partial + C, dadd, batch, chunks, C, sg, sn, accumulate);
+      TT_LAUNCH_CHECK();
+    }
   }
   return 0;
 }

@@ -42,7 +42,14 @@ void tt_set_error(const char* fmt, ...);
       return -2;                                                              \
     }                                                                         \
   } while (0)
-#define TT_LAUNCH_CHECK() TT_CUDA(cudaGetLastError())
+// every kernel launch is followed by one TT_LAUNCH_CHECK(): it also counts launches so that
+// callers can report how many of this library's kernels ran (tt_launch_count()).
+void tt_count_launch();
+#define TT_LAUNCH_CHECK()          \
+  do {                             \
+    tt_count_launch();             \
+    TT_CUDA(cudaGetLastError());   \
+  } while (0)
 
 // Builds a tiled TMA descriptor for a row-major bf16/fp32 tensor of up to 4 dims.
 // dims[0] is the innermost (contiguous) extent; strides_bytes[i] is the stride of

@@ -3,6 +3,7 @@
 // device queries.
 #include "tt_common.cuh"
 #include <stdarg.h>
+#include <atomic>
 #include <mutex>
 
 static thread_local char g_err[1024] = "";
@@ -15,6 +16,11 @@ void tt_set_error(const char* fmt, ...) {
 }
 
 TT_API const char* tt_last_error() { return g_err; }
+
+static std::atomic<long long> g_launches{0};
+void tt_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+// Number of kernels this library has launched in this process.
+TT_API long long tt_launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,

@@ -1,0 +1,4 @@
+from .registry import DATASETS, build_dataset  # noqa: F401
+from .fake import FakeDataset, SyntheticLatentDataset, latent_grid  # noqa: F401
+from .samplers import (PretrainingRandomSampler, PretrainingSampler, RandomSeedDataset,  # noqa: F401
+                       build_data_loader)

@@ -56,6 +56,7 @@ def lib() -> ctypes.CDLL:
                     )
             L = ctypes.CDLL(str(path))
             L.tt_last_error.restype = ctypes.c_char_p
+            L.tt_launch_count.restype = ctypes.c_longlong
             _LIB = L
     return _LIB
 
@@ -91,3 +92,8 @@ def check_status(device: torch.device | None = None) -> None:
     if code != 0:
         t.zero_()
         raise RuntimeError(f"a device-side wait timed out (status 0x{code:x}); results are invalid")
+
+
+def launch_count() -> int:
+    """Kernels launched by the native library in this process so far."""
+    return int(lib().tt_launch_count()) if lib_file().exists() else 0

@@ -35,6 +35,7 @@ def gemm_ref(a, b, *, a_mn=False, b_mn=False, bias=None, epi=EPI_NONE, residual=
         aux = acc.to(torch.bfloat16) if want_aux else None
         acc = torch.nn.functional.silu(acc)
     elif epi == EPI_GATE_RES:
+        aux = acc.to(torch.bfloat16) if want_aux else None
         g = gate.float().repeat_interleave(rows_per_gate, dim=0)[: acc.shape[0]]
         acc = residual.float() + g * acc
     elif epi == EPI_ACCUM:

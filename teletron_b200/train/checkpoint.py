@@ -1,0 +1,209 @@
+"""Checkpoint save / load in the Megatron directory layout the reference uses
+(teletron/train/checkpoint/utils.py:47-113, teletron/train/checkpoint/checkpoint.py:46-398):
+
+    <save>/latest_checkpointed_iteration.txt            integer iteration or "release"
+    <save>/iter_0000100/mp_rank_00/model_optim_rng.pt   one directory per tensor-parallel rank
+    <save>/iter_0000100/mp_rank_00/distrib_optim.pt     fp32 optimizer state when it is sharded
+
+``model_optim_rng.pt`` is a ``torch.save`` dict with the keys ``args`` (argparse.Namespace),
+``checkpoint_version`` (3.0), ``iteration``, ``model`` (bare parameter names such as
+``blocks.0.self_attn.q.weight``, bf16), ``optimizer``, ``opt_param_scheduler``, ``rng_state`` and
+``num_floating_point_operations_so_far``.  The file is written by data-parallel rank 0 of each
+tensor-parallel rank through a temporary file and ``os.replace``; rank 0 updates the tracker
+after a barrier.  Loading honours ``--finetune``, ``--no-load-optim``, ``--no-load-rng``,
+``--ckpt-step``, ``--pretrained-checkpoint`` and ``--exit-on-missing-checkpoint``.
+"""
+from __future__ import annotations
+
+import os
+import random
+import sys
+from argparse import Namespace
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..parallel import state as mpu
+
+TRACKER = "latest_checkpointed_iteration.txt"
+MODEL_FILE = "model_optim_rng.pt"
+DISTOPT_FILE = "distrib_optim.pt"
+
+
+# ----------------------------------------------------------------------------- naming
+def checkpoint_dir(root: str, iteration, release: bool = False) -> str:
+    return os.path.join(root, "release" if release else f"iter_{int(iteration):07d}")
+
+
+def checkpoint_name(root: str, iteration, release=False, tp_rank: Optional[int] = None,
+                    pp_rank: Optional[int] = None, pp_size: int = 1, filename: str = MODEL_FILE) -> str:
+    tp_rank = mpu.get_tensor_model_parallel_rank() if tp_rank is None else tp_rank
+    sub = f"mp_rank_{tp_rank:02d}"
+    if pp_size > 1:
+        sub += f"_{(pp_rank or 0):03d}"
+    return os.path.join(checkpoint_dir(root, iteration, release), sub, filename)
+
+
+def tracker_filename(root: str) -> str:
+    return os.path.join(root, TRACKER)
+
+
+def read_tracker(root: str) -> Tuple[int, bool]:
+    """(iteration, release). Raises FileNotFoundError when there is no tracker."""
+    with open(tracker_filename(root)) as f:
+        txt = f.read().strip()
+    if txt == "release":
+        return 0, True
+    try:
+        it = int(txt)
+    except ValueError as e:
+        raise ValueError(f"invalid tracker content {txt!r} in {tracker_filename(root)}") from e
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        grp = mpu.get_transformer_model_group()
+        dev = "cuda" if (torch.cuda.is_available() and dist.get_backend(grp) == "nccl") else "cpu"
+        t = torch.tensor([it], dtype=torch.long, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=grp)
+        it = int(t.item())
+    return it, False
+
+
+# ----------------------------------------------------------------------------- rng
+def get_rng_state():
+    st = dict(random_rng_state=random.getstate(), np_rng_state=np.random.get_state(),
+              torch_rng_state=torch.get_rng_state(),
+              cuda_rng_state=torch.cuda.get_rng_state() if torch.cuda.is_available() else None,
+              rng_tracker_states={})
+    return [st]
+
+
+def set_rng_state(states, dp_rank: int = 0):
+    st = states[dp_rank] if len(states) > dp_rank else states[0]
+    random.setstate(st["random_rng_state"])
+    np.random.set_state(st["np_rng_state"])
+    torch.set_rng_state(st["torch_rng_state"])
+    if st.get("cuda_rng_state") is not None and torch.cuda.is_available():
+        torch.cuda.set_rng_state(st["cuda_rng_state"])
+
+
+def _atomic_save(obj, path: str):
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    tmp = path + ".tmp"
+    torch.save(obj, tmp)
+    os.replace(tmp, path)
+
+
+def _barrier():
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier(group=mpu.get_transformer_model_group())
+
+
+def _plain_namespace(args) -> Namespace:
+    keep = {}
+    for k, v in vars(args).items():
+        if isinstance(v, (int, float, str, bool, type(None), list, tuple, dict)):
+            keep[k] = v
+    return Namespace(**keep)
+
+
+# ----------------------------------------------------------------------------- save
+def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
+                    num_floating_point_operations_so_far: float = 0.0) -> Optional[str]:
+    root = args.save
+    assert root, "--save is not set"
+    dp_rank = mpu.get_data_parallel_rank(with_context_parallel=True)
+    sharded_opt = optimizer is not None and getattr(optimizer, "sharded", False) and not args.no_save_optim
+    full_opt = optimizer.gather_full_state() if sharded_opt else None  # collective: every rank calls it
+    path = None
+    if dp_rank == 0:
+        sd = dict(args=_plain_namespace(args), checkpoint_version=3.0, iteration=iteration,
+                  num_floating_point_operations_so_far=num_floating_point_operations_so_far)
+        inner = model.module if hasattr(model, "module") else model
+        sd["model"] = {k: v.detach().cpu() for k, v in inner.state_dict().items()}
+        if not args.no_save_optim:
+            if optimizer is not None and not sharded_opt:
+                sd["optimizer"] = optimizer.state_dict()
+            elif optimizer is not None:
+                sd["optimizer"] = dict(step=optimizer.step_count, param_groups=optimizer.param_groups,
+                                       sharded=True)
+            if opt_param_scheduler is not None:
+                sd["opt_param_scheduler"] = opt_param_scheduler.state_dict()
+        if not args.no_save_rng:
+            sd["rng_state"] = get_rng_state()
+        path = checkpoint_name(root, iteration)
+        _atomic_save(sd, path)
+        if sharded_opt and full_opt is not None:
+            _atomic_save(full_opt, checkpoint_name(root, iteration, filename=DISTOPT_FILE))
+    _barrier()
+    if (not dist.is_initialized()) or dist.get_rank() == 0:
+        os.makedirs(root, exist_ok=True)
+        tmp = tracker_filename(root) + ".tmp"
+        with open(tmp, "w") as f:
+            f.write(str(iteration))
+        os.replace(tmp, tracker_filename(root))
+    _barrier()
+    return path
+
+
+# ----------------------------------------------------------------------------- load
+def load_checkpoint(model, optimizer, opt_param_scheduler, args, strict: bool = True) -> Tuple[int, float]:
+    """Returns (iteration, num_floating_point_operations_so_far); (0, 0) when nothing was loaded."""
+    root = args.load
+    finetune = args.finetune
+    if (not root or not os.path.exists(tracker_filename(root))) and args.pretrained_checkpoint:
+        root, finetune = args.pretrained_checkpoint, True
+    if not root:
+        return 0, 0.0
+    try:
+        iteration, release = read_tracker(root)
+    except FileNotFoundError:
+        if args.exit_on_missing_checkpoint:
+            print(f">> no checkpoint tracker in {root}; exiting as requested", flush=True)
+            _barrier()
+            sys.exit(0)
+        print(f"WARNING: no checkpoint tracker in {root}; starting from scratch", flush=True)
+        return 0, 0.0
+    if args.ckpt_step is not None:
+        iteration, release = args.ckpt_step, False
+    path = checkpoint_name(root, iteration, release)
+    if not os.path.exists(path):
+        raise FileNotFoundError(f"checkpoint file {path} is missing or incomplete")
+    try:
+        sd = torch.load(path, map_location="cpu", weights_only=False)
+    except Exception as e:
+        raise RuntimeError(f"could not read checkpoint {path}: {e}") from e
+    inner = model.module if hasattr(model, "module") else model
+    inner.load_state_dict(sd["model"], strict=strict)
+    flops = float(sd.get("num_floating_point_operations_so_far", 0.0))
+    if finetune or release:
+        iteration = 0
+        if optimizer is not None:
+            optimizer.reload_model_params()
+    else:
+        iteration = sd.get("iteration", sd.get("total_iters", 0))
+        saved = sd.get("args")
+        if saved is not None:
+            args.consumed_train_samples = getattr(saved, "consumed_train_samples", 0)
+            args.consumed_valid_samples = getattr(saved, "consumed_valid_samples", 0)
+        if optimizer is not None:
+            if not args.no_load_optim and "optimizer" in sd:
+                if getattr(optimizer, "sharded", False) and sd["optimizer"].get("sharded"):
+                    full = torch.load(checkpoint_name(root, iteration, filename=DISTOPT_FILE),
+                                      map_location="cpu", weights_only=False)
+                    optimizer.scatter_full_state(full)
+                    optimizer.step_count = sd["optimizer"]["step"]
+                    optimizer.param_groups[0].update(sd["optimizer"]["param_groups"][0])
+                elif "master" in sd["optimizer"] and not getattr(optimizer, "sharded", False):
+                    optimizer.load_state_dict(sd["optimizer"])
+                else:
+                    raise RuntimeError("optimizer layout (sharded vs. replicated) differs from the checkpoint; "
+                                       "use --no-load-optim")
+            else:
+                optimizer.reload_model_params()
+        if opt_param_scheduler is not None and not args.no_load_optim and "opt_param_scheduler" in sd:
+            opt_param_scheduler.load_state_dict(sd["opt_param_scheduler"])
+        if not args.no_load_rng and "rng_state" in sd:
+            set_rng_state(sd["rng_state"], 0)
+    _barrier()
+    return iteration, flops

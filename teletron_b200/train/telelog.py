@@ -1,0 +1,117 @@
+"""Training-loop logging: loss accumulation between log intervals, skipped / NaN iteration
+counters, TensorBoard scalars on the last rank and one console line per interval
+(teletron/train/telelogger.py:18-262).  In addition it reports device-timed throughput in
+tokens/s, which the reference never logs.
+"""
+from __future__ import annotations
+
+import math
+import time
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+
+class TrainLogger:
+    ADV, SKIP, NAN = "advanced iterations", "skipped iterations", "nan iterations"
+
+    def __init__(self, args, writer=None):
+        self.args = args
+        self.writer = writer
+        self.totals: Dict[str, float] = {}
+        self.counts = {self.ADV: 0, self.SKIP: 0, self.NAN: 0}
+        self.t_last = time.time()
+        self.tokens_since = 0
+        self.device_ms_since = 0.0
+        self.reported_memory = False
+
+    @staticmethod
+    def make_writer(args):
+        """SummaryWriter on the last rank only (teletron/utils/config.py:59-70)."""
+        if not args.tensorboard_dir or args.rank != args.world_size - 1:
+            return None
+        try:
+            from torch.utils.tensorboard import SummaryWriter
+
+            return SummaryWriter(log_dir=args.tensorboard_dir, max_queue=args.tensorboard_queue_size)
+        except Exception as e:  # tensorboard missing: keep training
+            print(f"WARNING: TensorBoard unavailable ({e})", flush=True)
+            return None
+
+    def log(self, loss_dict, iteration, lr, loss_scale, grad_norm, skipped_iter, params_norm=None,
+            tokens: int = 0, device_ms: float = 0.0) -> bool:
+        a = self.args
+        self.counts[self.SKIP if skipped_iter else self.ADV] += 1
+        got_nan = False
+        for k, v in loss_dict.items():
+            val = float(v)
+            if not skipped_iter:
+                self.totals[k] = self.totals.get(k, 0.0) + val
+            got_nan |= math.isnan(val) or math.isinf(val)
+        self.counts[self.NAN] += int(got_nan)
+        self.tokens_since += tokens
+        self.device_ms_since += device_ms
+        w = self.writer
+        if w is not None and iteration % a.tensorboard_log_interval == 0:
+            samples = a.consumed_train_samples
+            w.add_scalar("learning-rate", lr, iteration)
+            w.add_scalar("learning-rate vs samples", lr, samples)
+            w.add_scalar("batch-size", a.global_batch_size, iteration)
+            for k, v in loss_dict.items():
+                w.add_scalar(k, float(v), iteration)
+                w.add_scalar(k + " vs samples", float(v), samples)
+            w.add_scalar("loss-scale", float(loss_scale), iteration)
+            w.add_scalar("world-size", a.world_size, iteration)
+            if grad_norm is not None:
+                w.add_scalar("grad-norm", float(grad_norm), iteration)
+            if params_norm is not None:
+                w.add_scalar("params-norm", float(params_norm), iteration)
+            if a.log_memory_to_tensorboard and torch.cuda.is_available():
+                ms = torch.cuda.memory_stats()
+                w.add_scalar("mem-reserved-bytes", ms["reserved_bytes.all.current"], iteration)
+                w.add_scalar("mem-allocated-bytes", ms["allocated_bytes.all.current"], iteration)
+        if iteration % a.log_interval != 0:
+            return False
+        n_adv = max(self.counts[self.ADV], 1)
+        elapsed = time.time() - self.t_last
+        parts = [f"iteration {iteration:8d}/{a.train_iters or 0:8d}",
+                 f"consumed samples: {a.consumed_train_samples:12d}",
+                 f"elapsed time per iteration (ms): {elapsed * 1000.0 / max(self.counts[self.ADV] + self.counts[self.SKIP], 1):.1f}",
+                 f"learning rate: {lr:.3E}", f"global batch size: {a.global_batch_size:5d}"]
+        for k, tot in self.totals.items():
+            parts.append(f"{k}: {tot / n_adv:.6E}")
+        parts.append(f"loss scale: {float(loss_scale):.1f}")
+        if grad_norm is not None:
+            parts.append(f"grad norm: {float(grad_norm):.3f}")
+        if params_norm is not None:
+            parts.append(f"params norm: {float(params_norm):.3f}")
+        if self.device_ms_since > 0:
+            tps = self.tokens_since / (self.device_ms_since * 1e-3)
+            parts.append(f"tokens/s (device-timed): {tps:.1f}")
+            if w is not None:
+                w.add_scalar("tokens-per-second", tps, iteration)
+        parts.append(f"number of skipped iterations: {self.counts[self.SKIP]:3d}")
+        parts.append(f"number of nan iterations: {self.counts[self.NAN]:3d}")
+        if a.rank == a.world_size - 1:
+            print(" | ".join(parts), flush=True)
+        report_mem = not self.reported_memory and torch.cuda.is_available()
+        if report_mem:
+            self.reported_memory = True
+            if a.rank == a.world_size - 1:
+                mb = 1024.0 * 1024.0
+                print(f"[rank {a.rank}] memory (MB) | allocated: {torch.cuda.memory_allocated() / mb:.0f}"
+                      f" | max allocated: {torch.cuda.max_memory_allocated() / mb:.0f}"
+                      f" | reserved: {torch.cuda.memory_reserved() / mb:.0f}", flush=True)
+        self.totals = {}
+        self.counts = {k: 0 for k in self.counts}
+        self.tokens_since, self.device_ms_since = 0, 0.0
+        self.t_last = time.time()
+        return report_mem
+
+    def log_validation(self, loss_dict, iteration):
+        if self.writer is None:
+            return
+        for k, v in loss_dict.items():
+            self.writer.add_scalar(f"{k} validation", float(v), iteration)
+            self.writer.add_scalar(f"{k} validation vs samples", float(v), self.args.consumed_train_samples)

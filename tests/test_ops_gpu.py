@@ -1,0 +1,213 @@
+"""Numerics of every CUDA kernel against its plain PyTorch fp32 reference (needs a B200)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from teletron_b200 import ops
+from teletron_b200.ops import _lib
+import importlib
+
+G = importlib.import_module("teletron_b200.ops.gemm")
+N = importlib.import_module("teletron_b200.ops.norm")
+from teletron_b200.ops.attention import attention_bwd, attention_fwd, attention_ref
+
+DEV = "cuda"
+
+
+def rel(a, b):
+    a, b = a.float(), b.float()
+    return (0.5 * (a - b).norm() / (a.norm() + b.norm() + 1e-30)).item()
+
+
+@pytest.fixture(autouse=True)
+def _seed_and_status():
+    torch.manual_seed(0)
+    yield
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])
+@pytest.mark.parametrize("M,N_,K", [(256, 256, 128), (1000, 1536, 328), (130, 72, 1000)])
+def test_gemm_layouts(a_mn, b_mn, M, N_, K):
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((K, N_) if b_mn else (N_, K), device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N_, device=DEV, dtype=torch.bfloat16)
+    kw = dict(a_mn=bool(a_mn), b_mn=bool(b_mn), bias=bias, alpha=1.0 / math.sqrt(K))
+    assert rel(G.gemm(a, b, **kw), G.gemm_ref(a, b, **kw)) < 2e-3
+
+
+@pytest.mark.parametrize("epi", [G.EPI_GELU, G.EPI_SILU, G.EPI_GATE_RES, G.EPI_ACCUM])
+def test_gemm_epilogues(epi):
+    M, N_, K = 520, 384, 256
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N_, K, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N_, device=DEV, dtype=torch.bfloat16)
+    kw = dict(bias=bias, epi=epi, alpha=1.0 / math.sqrt(K))
+    if epi == G.EPI_GATE_RES:
+        kw.update(residual=torch.randn(M, N_, device=DEV, dtype=torch.bfloat16),
+                  gate=torch.randn(2, N_, device=DEV), rows_per_gate=260)
+    if epi == G.EPI_ACCUM:
+        base = torch.randn(M, N_, device=DEV, dtype=torch.float32)
+        got = G.gemm(a, b, out=base.clone(), **kw)
+        ref = G.gemm_ref(a, b, out=base.clone(), **kw)
+        assert rel(got, ref) < 1e-4
+        return
+    got, aux = G.gemm(a, b, want_aux=True, **kw)
+    ref, aux_ref = G.gemm_ref(a, b, want_aux=True, **kw)
+    assert rel(got, ref) < 3e-3
+    assert rel(aux, aux_ref) < 3e-3
+
+
+@pytest.mark.parametrize("C", [256, 1536, 3072, 5120])
+def test_adaln_fwd_bwd(C):
+    B, S = 2, 77
+    x = torch.randn(B * S, C, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    mod = (0.3 * torch.randn(B, 6, C, device=DEV)).requires_grad_(True)
+    scale, shift = mod[:, 1], mod[:, 0]
+    y = N.adaln(x, scale, shift, S)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(True)
+    modr = mod.detach().clone().requires_grad_(True)
+    yr = N.adaln_ref(xr, modr[:, 1], modr[:, 0], S)
+    yr.backward(dy.float())
+    assert rel(y, yr) < 3e-3
+    assert rel(x.grad, xr.grad) < 5e-3
+    assert rel(mod.grad, modr.grad) < 5e-3
+
+
+def test_layernorm_affine():
+    rows, C = 300, 1536
+    x = torch.randn(rows, C, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    w = torch.randn(C, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(C, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    y = N.layernorm_affine(x, w, b)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.layer_norm(xr, (C,), wr, br, 1e-6)
+    yr.backward(dy.float())
+    assert rel(y, yr) < 3e-3 and rel(x.grad, xr.grad) < 5e-3
+    assert rel(w.grad, wr.grad) < 1e-2 and rel(b.grad, br.grad) < 1e-2
+
+
+@pytest.mark.parametrize("per_head,C", [(False, 1536), (True, 3072), (False, 5120)])
+@pytest.mark.parametrize("with_rope", [True, False])
+def test_rmsnorm_rope(per_head, C, with_rope):
+    D, S, B = 128, 50, 2
+    qkv = torch.randn(B * S, 3 * C, device=DEV).to(torch.bfloat16)
+    x = qkv[:, C:2 * C].detach().requires_grad_(True)  # strided view, like a fused projection slice
+    w = (1 + 0.1 * torch.randn(D if per_head else C, device=DEV)).to(torch.bfloat16).requires_grad_(True)
+    ang = torch.rand(S, D // 2, device=DEV) * 6.28
+    freqs = torch.stack([ang.cos(), ang.sin()], -1).contiguous() if with_rope else None
+    y = N.rmsnorm_rope(x, w, freqs, D, per_head)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = N.rmsnorm_rope_ref(xr, wr, freqs, D, per_head)
+    yr.backward(dy.float())
+    assert rel(y, yr) < 3e-3
+    assert rel(x.grad, xr.grad) < 5e-3
+    assert rel(w.grad, wr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("B,Sq,Skv,H,kvl", [(1, 256, 256, 1, None), (2, 300, 1000, 3, None),
+                                            (1, 1000, 520, 2, None), (2, 384, 512, 2, [257, 512]),
+                                            (1, 64, 77, 1, None)])
+def test_attention_fwd_bwd(B, Sq, Skv, H, kvl):
+    D = 128
+    q = torch.randn(B, Sq, H, D, device=DEV).to(torch.bfloat16)
+    k = torch.randn(B, Skv, H, D, device=DEV).to(torch.bfloat16)
+    v = torch.randn(B, Skv, H, D, device=DEV).to(torch.bfloat16)
+    do = torch.randn(B, Sq, H, D, device=DEV).to(torch.bfloat16)
+    kv_lens = torch.tensor(kvl, dtype=torch.int32, device=DEV) if kvl else None
+    o, lse = attention_fwd(q, k, v, kv_lens=kv_lens)
+    dq, dk, dv = attention_bwd(q, k, v, o, lse, do, kv_lens=kv_lens)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    oref, lref = attention_ref(qf, kf, vf, kv_lens=kv_lens)
+    oref.backward(do.float())
+    assert rel(o, oref) < 2e-3 and (lse - lref).abs().max().item() < 1e-3
+    assert rel(dq, qf.grad) < 3e-3 and rel(dk, kf.grad) < 3e-3 and rel(dv, vf.grad) < 3e-3
+
+
+def test_attention_is_deterministic():
+    q, k, v = (torch.randn(1, 512, 2, 128, device=DEV).to(torch.bfloat16) for _ in range(3))
+    o1, l1 = attention_fwd(q, k, v)
+    o2, l2 = attention_fwd(q, k, v)
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    do = torch.randn_like(o1)
+    g1 = attention_bwd(q, k, v, o1, l1, do)
+    g2 = attention_bwd(q, k, v, o1, l1, do)
+    assert all(torch.equal(a, b) for a, b in zip(g1, g2))
+
+
+@pytest.mark.parametrize("act", [None, "gelu", "silu"])
+def test_linear_autograd(act):
+    rows, K, N_ = 333, 256, 384
+    x = (torch.randn(rows, K, device=DEV) / 4).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(N_, K, device=DEV) / 16).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(N_, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    y = ops.linear(x, w, b, act)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    if act == "gelu":
+        yr = torch.nn.functional.gelu(yr, approximate="tanh")
+    elif act == "silu":
+        yr = torch.nn.functional.silu(yr)
+    yr.backward(dy.float())
+    assert rel(y, yr) < 3e-3 and rel(x.grad, xr.grad) < 5e-3
+    assert rel(w.grad, wr.grad) < 5e-3 and rel(b.grad, br.grad) < 5e-3
+
+
+def test_linear_residual_gate_and_main_grad():
+    B, S, K, N_ = 2, 100, 256, 384
+    rows = B * S
+    x = (torch.randn(rows, K, device=DEV) / 4).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(N_, K, device=DEV) / 16).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(N_, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    res = torch.randn(rows, N_, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    gate = torch.randn(B, N_, device=DEV).requires_grad_(True)
+    w.main_grad = torch.full((N_, K), 0.5, device=DEV)
+    y = ops.linear_residual(x, w, b, res, gate, S)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr, br, rr, gr = (t.detach().float().requires_grad_(True) for t in (x, w, b, res, gate))
+    z = torch.nn.functional.linear(xr, wr, br)
+    yr = rr + gr.repeat_interleave(S, 0) * z
+    yr.backward(dy.float())
+    assert rel(y, yr) < 3e-3 and rel(x.grad, xr.grad) < 6e-3 and rel(res.grad, rr.grad) < 1e-6
+    assert rel(gate.grad, gr.grad) < 6e-3 and rel(b.grad, br.grad) < 6e-3
+    assert w.grad is None and rel(w.main_grad - 0.5, wr.grad) < 6e-3
+
+
+def test_flow_ops_and_adamw():
+    B = 2
+    x0, nz, pred = (torch.randn(B, 16, 3, 8, 8, device=DEV).to(torch.bfloat16) for _ in range(3))
+    sig = torch.tensor([0.3, 0.9], device=DEV)
+    assert rel(ops.add_noise(x0, nz, sig), ops.add_noise_ref(x0, nz, sig)) < 3e-3
+    w = torch.tensor([0.7, 1.4], device=DEV)
+    p = pred.clone().requires_grad_(True)
+    loss = ops.flow_mse(p, x0, nz, w, scale=0.5)
+    loss.backward()
+    pr = pred.float().requires_grad_(True)
+    lr_ = ops.flow_mse_ref(pr, x0, nz, w) * 0.5
+    lr_.backward()
+    assert abs(loss.item() - lr_.item()) < 1e-4 * abs(lr_.item()) + 1e-6
+    assert rel(p.grad, pr.grad) < 5e-3
+    n = 4096 + 64
+    p32 = torch.randn(n, device=DEV); p16 = p32.to(torch.bfloat16)
+    m = torch.zeros(n, device=DEV); v = torch.zeros(n, device=DEV); g = torch.randn(n, device=DEV)
+    rp, rm, rv = p32.clone(), m.clone(), v.clone()
+    for step in (1, 2, 3):
+        ops.adamw_step(p32, p16, m, v, g, lr=1e-2, wd=0.1, step=step, grad_scale=0.5)
+        ops.adamw_ref(rp, None, rm, rv, g, 1e-2, 0.9, 0.999, 1e-8, 0.1, step, 0.5)
+    assert rel(p32, rp) < 1e-6 and rel(m, rm) < 1e-6 and rel(v, rv) < 1e-6
+    assert torch.equal(p16, p32.to(torch.bfloat16))
+    gn = ops.grad_norm(g, 1.0)
+    assert abs(gn[0].item() - g.norm().item()) < 1e-3 * g.norm().item()
