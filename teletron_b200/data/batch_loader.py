@@ -1,0 +1,176 @@
+"""Consumer side of the encoder service: the iterator a DiT rank trains from when encoders run
+on dedicated ranks (teletron/train/consumer_dataloader.py:18-282).
+
+The TP x CP leader receives (header, payload) from its producer with a watchdog (timed polling
+of the receive, producer heartbeat and failure keys in the store, so a dead encoder raises an
+error instead of hanging the job), prefetches the next sample while the current one trains, and
+fans the sample out to its TP x CP group with two broadcasts (header, flat payload) instead of
+pickled metadata plus one broadcast per tensor.  ``timestep_range`` is attached for
+timestep-expert replicas from ``--moe-step-factor-list``.
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..parallel import state as mpu
+from .base_encoder import FLAG_LAST, HEADER_INTS, decode_header, numel_of, unpack_tensors
+from .encoder_service import store, store_has
+
+WAN_SCHEMA = ["context", "clip_feature", "image_emb_y", "latents", "noise"]
+HUNYUAN_SCHEMA = ["prompt_embeds", "clip_text_embed", "first_ref_image", "latents"]
+
+
+class EncoderTimeout(RuntimeError):
+    pass
+
+
+class DistBatchLoader:
+    schema: List[str] = WAN_SCHEMA
+
+    def __init__(self, args, timeout_s: float = 600.0, heartbeat_stale_s: float = 120.0):
+        self.args = args
+        self.timeout_s, self.heartbeat_stale_s = timeout_s, heartbeat_stale_s
+        self.backend = dist.get_backend()
+        self.dev = (torch.device("cuda", torch.cuda.current_device()) if self.backend == "nccl"
+                    else torch.device("cpu"))
+        self.rank = dist.get_rank()
+        pairs = [p for p in mpu.get_comm_pair() if p.consumer == self.rank]
+        self.pair = pairs[0] if pairs else None
+        self.is_leader = self.pair is not None
+        self.group = mpu.get_tensor_context_parallel_group()
+        self.group_size = mpu.get_tensor_context_parallel_world_size()
+        self.src = mpu.get_tensor_context_parallel_src_rank()
+        self.received = 0
+        self.finished = False
+        self._pending = None
+        factors = getattr(args, "moe_step_factor_list", None)
+        self.timestep_range = None
+        if factors and len(factors) >= 2:
+            rep = mpu.get_topology().coords(self.rank)["replica"]
+            if rep + 1 < len(factors):
+                self.timestep_range = (float(factors[rep]), float(factors[rep + 1]))
+        if self.is_leader:
+            info = torch.tensor([args.iteration, args.consumed_train_samples, args.consumed_valid_samples],
+                                dtype=torch.int64, device=self.dev)
+            dist.isend(info, dst=self.pair.producer).wait()
+            self._post_header()
+
+    # ---- leader-side receive with watchdog ------------------------------------------------
+    def _post_header(self):
+        hdr = torch.zeros(HEADER_INTS, dtype=torch.int32, device=self.dev)
+        self._pending = (dist.irecv(hdr, src=self.pair.producer), hdr)
+
+    def _wait(self, work, what: str):
+        t0 = time.time()
+        prod = self.pair.producer
+        while not work.is_completed():
+            if store_has(f"tt_failed_{prod}"):
+                raise EncoderTimeout(f"encoder rank {prod} reported a failure: "
+                                     f"{store().get(f'tt_failed_{prod}').decode(errors='replace')[-500:]}")
+            now = time.time()
+            if now - t0 > self.timeout_s:
+                raise EncoderTimeout(f"timed out after {self.timeout_s:.0f}s waiting for {what} from encoder rank {prod}")
+            if store_has(f"tt_hb_{prod}") and now - t0 > 5.0:
+                hb = float(store().get(f"tt_hb_{prod}").decode())
+                if now - hb > self.heartbeat_stale_s:
+                    raise EncoderTimeout(f"encoder rank {prod} stopped sending heartbeats {now - hb:.0f}s ago")
+            time.sleep(0.001)
+        work.wait()
+
+    def _receive(self):
+        work, hdr = self._pending
+        self._wait(work, "a sample header")
+        shapes, seq, flags = decode_header(hdr.cpu())
+        if seq != (self.received & 0x7FFFFFFF):
+            raise ValueError(f"encoder stream out of order: got sample {seq}, expected {self.received}")
+        blob = torch.empty(numel_of(shapes), dtype=torch.bfloat16, device=self.dev)
+        self._wait(dist.irecv(blob, src=self.pair.producer), "a sample payload")
+        self.received += 1
+        if flags & FLAG_LAST:
+            self.finished = True
+            self._pending = None
+        else:
+            self._post_header()  # prefetch: the next header is already in flight while we train
+        return hdr, blob, shapes
+
+    # ---- iterator -------------------------------------------------------------------------------
+    def __iter__(self):
+        return self
+
+    def __next__(self) -> Dict[str, torch.Tensor]:
+        if self.is_leader:
+            if self.finished and self._pending is None and self.received > 0 and self._exhausted():
+                raise StopIteration
+            hdr, blob, shapes = self._receive()
+        else:
+            hdr = torch.zeros(HEADER_INTS, dtype=torch.int32, device=self.dev)
+            blob, shapes = None, None
+        if self.group_size > 1:
+            dist.broadcast(hdr, self.src, group=self.group)
+            if not self.is_leader:
+                shapes, _, _ = decode_header(hdr.cpu())
+                blob = torch.empty(numel_of(shapes), dtype=torch.bfloat16, device=self.dev)
+            dist.broadcast(blob, self.src, group=self.group)
+        tensors = unpack_tensors(blob, shapes)
+        batch = {}
+        for name, t in zip(self.schema, tensors):
+            if t.numel() > 0:
+                batch[name] = t
+        if self.timestep_range is not None:
+            batch["timestep_range"] = self.timestep_range
+        return batch
+
+    def _exhausted(self) -> bool:
+        return self.finished and self._pending is None
+
+    def close(self):
+        """Early stop: ask producers to stop and drain what they already issued."""
+        if not self.is_leader or self.finished:
+            return
+        st = store()
+        st.set("tt_stop", "1")
+        key = f"tt_issued_{self.pair.producer}_{self.rank}"
+        t0 = time.time()
+        while not store_has(key):
+            if time.time() - t0 > self.timeout_s:
+                raise EncoderTimeout("producer did not acknowledge the stop request")
+            if self._pending is not None and self._pending[0].is_completed():
+                self._receive()
+            time.sleep(0.005)
+        issued = int(st.get(key).decode())
+        while self.received < issued:
+            self._receive()
+        self.finished = True
+
+
+class WanDistBatchLoader(DistBatchLoader):
+    schema = WAN_SCHEMA
+
+
+class HunyuanDistBatchLoader(DistBatchLoader):
+    schema = HUNYUAN_SCHEMA
+
+
+class OriginBatchLoader:
+    """Plain passthrough of a local data iterator (the reference's 'hunyuan origin' loader)."""
+
+    def __init__(self, iterator):
+        self.iterator = iterator
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        return next(self.iterator)
+
+
+def create_batch_loader(model_name: str, args, iterator=None):
+    if iterator is not None and not args.distributed_vae:
+        return OriginBatchLoader(iterator)
+    if "Hunyuan" in model_name:
+        return HunyuanDistBatchLoader(args)
+    return WanDistBatchLoader(args)

@@ -1,0 +1,158 @@
+"""Producer loop of the distributed multimodal encoders: what an encoder rank runs instead of
+training (teletron/core/distributed/distributed_encoder.py:59-192).
+
+Each encoder rank serves the TP x CP leaders assigned to it by ``Topology.comm_pairs``:
+  1. receive ``int64[3] = (iteration, consumed_train, consumed_valid)`` from every consumer, so
+     the data iterators resume where training stopped;
+  2. merge consumers that must see identical data (same producer, dp_rank, dp_size — the same
+     DP rank in different timestep-expert replicas);
+  3. loop: reap completed sends, keep up to ``QUEUE_DEPTH`` encoded samples per consumer
+     group, send header then payload with at most one sample in flight per consumer, publish a
+     heartbeat in the rendezvous store.
+Both sides know how many samples the run needs, so the stream ends without dangling sends; an
+early stop is negotiated through the store (``stop`` key, then the producer publishes how many
+samples it issued and the consumer drains them).  A failure in the encoder is reported in the
+store so consumers raise instead of waiting forever (the reference aborts the world group).
+"""
+from __future__ import annotations
+
+import collections
+import time
+import traceback
+from typing import Dict, List
+
+import torch
+import torch.distributed as dist
+
+from ..models.registry import encoder_for_model, get_encoder
+from ..parallel import state as mpu
+from ..parallel.state import CommPair
+from .base_encoder import FLAG_LAST, pack_tensors
+
+QUEUE_DEPTH = 2
+MAX_OUTSTANDING_SENDS = 1
+POLL_SECONDS = 0.002
+
+
+def store():
+    from torch.distributed.distributed_c10d import _get_default_store
+
+    return _get_default_store()
+
+
+def store_has(key: str) -> bool:
+    try:
+        return bool(store().check([key]))
+    except Exception:
+        return False
+
+
+def merge_comm_pairs(pairs: List[CommPair]) -> List[Dict]:
+    """Group consumers that share (producer, dp_rank, dp_size): they receive identical samples."""
+    groups: Dict[tuple, Dict] = collections.OrderedDict()
+    for p in pairs:
+        key = (p.producer, p.dp_rank, p.dp_size)
+        g = groups.setdefault(key, dict(producer=p.producer, dp_rank=p.dp_rank, dp_size=p.dp_size, consumers=[]))
+        g["consumers"].append(p.consumer)
+    return list(groups.values())
+
+
+def items_needed(args, iteration: int) -> int:
+    """Samples one consumer will request from `iteration` to the end of training."""
+    remaining = max((args.train_iters or 0) - iteration, 0)
+    return remaining * args.num_micro_batches * args.micro_batch_size
+
+
+def _comm_device(backend: str):
+    return torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+
+
+def producer_process(args, encoder=None, dataset=None):
+    rank = dist.get_rank()
+    backend = dist.get_backend()
+    dev = _comm_device(backend)
+    st = store()
+    try:
+        pairs = [p for p in mpu.get_comm_pair() if p.producer == rank]
+        if not pairs:
+            dist.barrier()
+            return 0
+        if encoder is None:
+            encoder = get_encoder(getattr(args, "encoder_name", None) or encoder_for_model(args.model), device=dev,
+                                  args=args)
+        encoder.setup()
+        # 1. resume counters
+        info = torch.zeros((len(pairs), 3), dtype=torch.int64, device=dev)
+        for req in [dist.irecv(info[i], src=p.consumer) for i, p in enumerate(pairs)]:
+            req.wait()
+        iteration, consumed_train = int(info[0, 0]), int(info[0, 1])
+        total = items_needed(args, iteration)
+        # 2. one data iterator per group of consumers that share data
+        groups = merge_comm_pairs(pairs)
+        if dataset is None:
+            from . import build_dataset
+
+            h, w = args.video_resolution
+            dataset = build_dataset(args.dataset_type, num_frames=args.num_frames, height=h, width=w, seed=args.seed)
+        from .samplers import build_data_loader
+
+        iters = []
+        for g in groups:
+            dl = build_data_loader(dataset, consumed_train, args.micro_batch_size, g["dp_rank"], g["dp_size"],
+                                   args.dataloader_type, 0, args.seed, pin_memory=False,
+                                   collate_fn=lambda b: b[0] if len(b) == 1 else b)
+            iters.append(iter(dl))
+        queues = {p.consumer: collections.deque() for p in pairs}
+        issued = {p.consumer: 0 for p in pairs}
+        inflight = []  # (work, consumer, keepalive tensors)
+        prof = None
+        if getattr(args, "producer_profile", False):
+            from ..train.profiling import make_torch_profiler
+
+            prof = make_torch_profiler(args, "producer")
+            prof.__enter__()
+        stopping = False
+        while True:
+            st.set(f"tt_hb_{rank}", str(time.time()))
+            inflight = [x for x in inflight if not x[0].is_completed()]
+            if not stopping and store_has("tt_stop"):
+                stopping = True
+            done = all(issued[c] >= total for c in issued) or stopping
+            if done and not inflight:
+                break
+            if not stopping:
+                for g, it in zip(groups, iters):
+                    first = g["consumers"][0]
+                    if issued[first] + len(queues[first]) < total and len(queues[first]) < QUEUE_DEPTH:
+                        tensors, _ = encoder.encode(next(it))
+                        blob = pack_tensors(tensors).to(dev)
+                        shapes = [tuple(t.shape) for t in tensors]
+                        for c in g["consumers"]:
+                            queues[c].append((shapes, blob))
+                for p in pairs:
+                    c = p.consumer
+                    if queues[c] and sum(1 for x in inflight if x[1] == c) < MAX_OUTSTANDING_SENDS * 2:
+                        shapes, blob = queues[c].popleft()
+                        last = FLAG_LAST if issued[c] + 1 >= total else 0
+                        from .base_encoder import encode_header
+
+                        hdr = encode_header(shapes, issued[c], last).to(dev)
+                        inflight.append((dist.isend(hdr, dst=c), c, hdr))
+                        inflight.append((dist.isend(blob, dst=c), c, blob))
+                        issued[c] += 1
+            if prof is not None:
+                prof.step()
+            time.sleep(POLL_SECONDS)
+        for c, n in issued.items():
+            st.set(f"tt_issued_{rank}_{c}", str(n))
+        if prof is not None:
+            prof.__exit__(None, None, None)
+        return sum(issued.values())
+    except Exception:
+        msg = traceback.format_exc()
+        try:
+            st.set(f"tt_failed_{rank}", msg[-2000:])
+        except Exception:
+            pass
+        print(f"[encoder rank {rank}] failed:\n{msg}", flush=True)
+        raise

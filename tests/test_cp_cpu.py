@@ -1,0 +1,115 @@
+"""Ulysses context parallelism on CPU/gloo: a 2-rank CP=2 training step of the tiny Wan DiT
+(2 blocks, dim 128, 4 heads x 32, FFN 512, 192 tokens) must reproduce the single-rank step —
+loss, reduced gradients and parameters after one AdamW step."""
+import pytest
+import torch
+
+from dist_utils import run_distributed
+from teletron_b200 import ops
+from teletron_b200.models import WanModel, wan_config
+from teletron_b200.parallel import state as mpu
+from teletron_b200.parallel.ddp import DistributedOptimizer, ParamBuffer
+from teletron_b200.parallel.ulysses import UlyssesContext
+
+
+def _problem():
+    g = torch.Generator().manual_seed(0)
+    x0 = torch.randn(1, 16, 3, 16, 16, generator=g)
+    noise = torch.randn(1, 16, 3, 16, 16, generator=g)
+    ctx = torch.randn(1, 32, 64, generator=g)
+    t = torch.rand(1, generator=g)
+    return x0, noise, ctx, t
+
+
+def _model(cp=None):
+    torch.manual_seed(0)
+    return WanModel(wan_config("wan-tiny"), cp)
+
+
+def _step(model, group, grad_scale, local_loss, sharded=False):
+    x0, noise, ctx, t = _problem()
+    sigma = t
+    xt = (1 - sigma) * x0 + sigma * noise
+    buf = ParamBuffer(model, shard_world=(2 if sharded else 1))
+    opt = DistributedOptimizer(buf, group, lr=1e-4, weight_decay=0.01, clip_grad=0.0, sharded=sharded,
+                               grad_scale=grad_scale)
+    opt.zero_grad()
+    model.return_local_shard = local_loss
+    pred = model(xt, t * 1000.0, ctx)
+    if local_loss:
+        loss = ops.flow_mse(pred, model.local_target_tokens(x0), model.local_target_tokens(noise),
+                            scale=1.0 / model.cp.size)
+    else:
+        loss = ops.flow_mse(pred, x0, noise)
+    loss.backward()
+    opt.reduce_gradients()
+    grads = buf.grads.clone()
+    opt.step()
+    return loss.detach(), grads, buf.params.clone(), {n: i for n, i in buf.index.items()}
+
+
+def _worker(rank, world, local_loss, sharded):
+    mpu.initialize_model_parallel(context_parallel_size=world)
+    cp = UlyssesContext(mpu.get_context_parallel_group(), world, rank)
+    model = _model(cp)
+    loss, grads, params, _ = _step(model, mpu.get_data_parallel_group(with_context_parallel=True), 1.0,
+                                   local_loss, sharded)
+    if local_loss:
+        torch.distributed.all_reduce(loss)
+    return loss, grads, params
+
+
+@pytest.mark.parametrize("local_loss,sharded", [(True, False), (False, False), (True, True)])
+def test_cp2_step_matches_single_rank(local_loss, sharded):
+    ref_loss, ref_grads, ref_params, index = _step(_model(), None, 1.0, False)
+    outs = run_distributed(_worker, 2, local_loss, sharded)
+    for loss, grads, params in outs:
+        assert abs(loss.item() - ref_loss.item()) < 1e-5 * max(1.0, abs(ref_loss.item()))
+        if not sharded:
+            worst = max(((grads[o:o + n] - ref_grads[o:o + n]).norm() / (ref_grads[o:o + n].norm() + 1e-12)).item()
+                        for _, (o, n, _) in index.items())
+            assert worst < 2e-4, worst
+        assert (params - ref_params).abs().max().item() < 2e-6
+
+
+def _split_gather_worker(rank, world):
+    mpu.initialize_model_parallel(context_parallel_size=world)
+    cp = UlyssesContext(mpu.get_context_parallel_group(), world, rank)
+    x = torch.arange(2 * 98 * 3, dtype=torch.float32).view(2, 98, 3).requires_grad_(True)  # 98 % 4 != 0
+    loc = cp.split_tokens(x)
+    assert loc.shape[1] == 25
+    full = cp.gather_tokens(loc)
+    assert torch.equal(full, x.detach())
+    (full * (rank + 1)).sum().backward()
+    expect = torch.zeros_like(x)
+    lo, hi = rank * 25, min((rank + 1) * 25, 98)
+    expect[:, lo:hi] = rank + 1
+    assert torch.equal(x.grad, expect)
+    # attention: 16 heads, sequence not divisible by the group size, against single-device attention
+    g = torch.Generator().manual_seed(1)
+    q, k, v = (torch.randn(1, 98, 16, 8, generator=g) for _ in range(3))
+    ref = ops.attention_ref(q, k, v)[0]
+    out = cp.attention(cp.split_tokens(q).contiguous(), cp.split_tokens(k).contiguous(),
+                       cp.split_tokens(v).contiguous())
+    got = cp.gather_tokens(out, 98)
+    assert (got - ref).abs().max().item() < 1e-5
+    return True
+
+
+def test_split_gather_and_ulysses_attention_with_padding():
+    assert all(run_distributed(_split_gather_worker, 4))
+
+
+def _heads_not_divisible_worker(rank, world):
+    mpu.initialize_model_parallel(context_parallel_size=world)
+    cp = UlyssesContext(mpu.get_context_parallel_group(), world, rank)
+    g = torch.Generator().manual_seed(2)
+    q, k, v = (torch.randn(1, 64, 3, 8, generator=g) for _ in range(3))  # 3 heads on 2 ranks
+    ref = ops.attention_ref(q, k, v)[0]
+    out = cp.attention(*(cp.split_tokens(t).contiguous() for t in (q, k, v)))
+    assert (cp.gather_tokens(out, 64) - ref).abs().max().item() < 1e-5
+    return True
+
+
+def test_ulysses_pads_heads():
+    assert all(run_distributed(_heads_not_divisible_worker, 2))
