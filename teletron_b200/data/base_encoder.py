@@ -80,6 +80,9 @@ def pack_tensors(tensors: Sequence[torch.Tensor], dtype=torch.bfloat16) -> torch
 
 
 def unpack_tensors(blob: torch.Tensor, shapes) -> List[torch.Tensor]:
+    want = numel_of(shapes)
+    if want != blob.numel():
+        raise ValueError(f"payload has {blob.numel()} elements but the header describes {want}")
     out, pos = [], 0
     for s in shapes:
         n = 1
@@ -87,8 +90,6 @@ def unpack_tensors(blob: torch.Tensor, shapes) -> List[torch.Tensor]:
             n *= d
         out.append(blob[pos:pos + n].view(*s))
         pos += n
-    if pos != blob.numel():
-        raise ValueError(f"payload has {blob.numel()} elements but the header describes {pos}")
     return out
 
 

@@ -18,7 +18,7 @@ import torch.distributed as dist
 
 from ..parallel import state as mpu
 from .base_encoder import FLAG_LAST, HEADER_INTS, decode_header, numel_of, unpack_tensors
-from .encoder_service import store, store_has
+from .encoder_service import PolledWork, store, store_has
 
 WAN_SCHEMA = ["context", "clip_feature", "image_emb_y", "latents", "noise"]
 HUNYUAN_SCHEMA = ["prompt_embeds", "clip_text_embed", "first_ref_image", "latents"]
@@ -56,18 +56,19 @@ class DistBatchLoader:
         if self.is_leader:
             info = torch.tensor([args.iteration, args.consumed_train_samples, args.consumed_valid_samples],
                                 dtype=torch.int64, device=self.dev)
-            dist.isend(info, dst=self.pair.producer).wait()
+            self._wait(dist.isend(info, dst=self.pair.producer), "the resume handshake")
             self._post_header()
 
     # ---- leader-side receive with watchdog ------------------------------------------------
     def _post_header(self):
         hdr = torch.zeros(HEADER_INTS, dtype=torch.int32, device=self.dev)
-        self._pending = (dist.irecv(hdr, src=self.pair.producer), hdr)
+        self._pending = (PolledWork(dist.irecv(hdr, src=self.pair.producer), self.backend), hdr)
 
     def _wait(self, work, what: str):
         t0 = time.time()
         prod = self.pair.producer
-        while not work.is_completed():
+        polled = work if isinstance(work, PolledWork) else PolledWork(work, self.backend)
+        while not polled.done():
             if store_has(f"tt_failed_{prod}"):
                 raise EncoderTimeout(f"encoder rank {prod} reported a failure: "
                                      f"{store().get(f'tt_failed_{prod}').decode(errors='replace')[-500:]}")
@@ -79,7 +80,8 @@ class DistBatchLoader:
                 if now - hb > self.heartbeat_stale_s:
                     raise EncoderTimeout(f"encoder rank {prod} stopped sending heartbeats {now - hb:.0f}s ago")
             time.sleep(0.001)
-        work.wait()
+        if polled.thread is None:
+            polled.work.wait()
 
     def _receive(self):
         work, hdr = self._pending
@@ -138,7 +140,7 @@ class DistBatchLoader:
         while not store_has(key):
             if time.time() - t0 > self.timeout_s:
                 raise EncoderTimeout("producer did not acknowledge the stop request")
-            if self._pending is not None and self._pending[0].is_completed():
+            if self._pending is not None and self._pending[0].done():
                 self._receive()
             time.sleep(0.005)
         issued = int(st.get(key).decode())

@@ -47,6 +47,37 @@ def store_has(key: str) -> bool:
         return False
 
 
+class PolledWork:
+    """Non-blocking completion test for a p2p request on any backend.  NCCL requests answer
+    ``is_completed()`` truthfully; gloo send/recv requests only flip it inside ``wait()``, so for
+    those a helper thread blocks in ``wait()`` and the caller polls the thread."""
+
+    def __init__(self, work, backend: str):
+        self.work = work
+        self.error = None
+        self.thread = None
+        if backend != "nccl":
+            import threading
+
+            self.thread = threading.Thread(target=self._block, daemon=True)
+            self.thread.start()
+
+    def _block(self):
+        try:
+            self.work.wait()
+        except Exception as e:  # surfaced by done()
+            self.error = e
+
+    def done(self) -> bool:
+        if self.thread is None:
+            return self.work.is_completed()
+        if self.thread.is_alive():
+            return False
+        if self.error is not None:
+            raise self.error
+        return True
+
+
 def merge_comm_pairs(pairs: List[CommPair]) -> List[Dict]:
     """Group consumers that share (producer, dp_rank, dp_size): they receive identical samples."""
     groups: Dict[tuple, Dict] = collections.OrderedDict()
@@ -114,7 +145,7 @@ def producer_process(args, encoder=None, dataset=None):
         stopping = False
         while True:
             st.set(f"tt_hb_{rank}", str(time.time()))
-            inflight = [x for x in inflight if not x[0].is_completed()]
+            inflight = [x for x in inflight if not x[0].done()]
             if not stopping and store_has("tt_stop"):
                 stopping = True
             done = all(issued[c] >= total for c in issued) or stopping
@@ -137,8 +168,8 @@ def producer_process(args, encoder=None, dataset=None):
                         from .base_encoder import encode_header
 
                         hdr = encode_header(shapes, issued[c], last).to(dev)
-                        inflight.append((dist.isend(hdr, dst=c), c, hdr))
-                        inflight.append((dist.isend(blob, dst=c), c, blob))
+                        inflight.append((PolledWork(dist.isend(hdr, dst=c), backend), c, hdr))
+                        inflight.append((PolledWork(dist.isend(blob, dst=c), backend), c, blob))
                         issued[c] += 1
             if prof is not None:
                 prof.step()

@@ -37,6 +37,10 @@ def free_port() -> int:
 
 
 def _entry(rank, world, port, backend, fn, args, queue):
+    import faulthandler
+
+    if os.environ.get("TT_TEST_HANG_DUMP"):
+        faulthandler.dump_traceback_later(float(os.environ["TT_TEST_HANG_DUMP"]), exit=True)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
     try:

@@ -207,7 +207,7 @@ def test_flow_ops_and_adamw():
     for step in (1, 2, 3):
         ops.adamw_step(p32, p16, m, v, g, lr=1e-2, wd=0.1, step=step, grad_scale=0.5)
         ops.adamw_ref(rp, None, rm, rv, g, 1e-2, 0.9, 0.999, 1e-8, 0.1, step, 0.5)
-    assert rel(p32, rp) < 1e-6 and rel(m, rm) < 1e-6 and rel(v, rv) < 1e-6
+    assert rel(p32, rp) < 1e-6 and rel(m, rm) < 1e-6 and rel(v, rv) < 1e-5
     assert torch.equal(p16, p32.to(torch.bfloat16))
     gn = ops.grad_norm(g, 1.0)
     assert abs(gn[0].item() - g.norm().item()) < 1e-3 * g.norm().item()
