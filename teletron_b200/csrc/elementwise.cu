@@ -407,3 +407,58 @@ TT_API int tt_flow_mse(const void* pred, const void* x0, const void* noise, void
   TT_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------- allocation-free column sums
+// See tt_noalloc.h for who needs this and for the rules.  The partial sums of the two-stage
+// reduction live in this fixed device array instead of caller scratch.
+#include "tt_noalloc.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_colsum_noalloc_scratch[TT_COLSUM_NOALLOC_CHUNKS * TT_COLSUM_NOALLOC_MAX_C];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device. In host code the array's name is
+// only a handle; the address kernels may use comes from cudaGetSymbolAddress, looked up once
+// per device while that device is current.
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  TT_CUDA(cudaGetDevice(&dev));
+  TT_CHECK(dev >= 0 && dev < kMaxDevices, "colsum_noalloc: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    TT_CUDA(cudaGetSymbolAddress((void**)&p, g_colsum_noalloc_scratch));
+    TT_CHECK(p != nullptr, "colsum_noalloc: scratch symbol has no device address");
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+TT_API int tt_colsum_noalloc(const void* x, long long ldx, void* out, int out_fp32, int accumulate,
+                             int rows, int C, cudaStream_t stream) {
+  TT_CHECK(rows > 0 && C > 0 && C % 8 == 0, "colsum_noalloc: bad shape rows=%d C=%d", rows, C);
+  TT_CHECK(C <= TT_COLSUM_NOALLOC_MAX_C,
+           "colsum_noalloc: C=%d exceeds the built-in scratch (max %d columns); use tt_colsum with "
+           "caller-provided scratch instead",
+           C, TT_COLSUM_NOALLOC_MAX_C);
+  TT_CHECK(ldx % 8 == 0 && al16(x), "colsum_noalloc: input misaligned");
+  TT_CHECK(out != nullptr, "colsum_noalloc: null output");
+  float* partial = nullptr;
+  if (noalloc_scratch(&partial)) return -2;
+  const int chunks = rows < TT_COLSUM_NOALLOC_CHUNKS ? rows : TT_COLSUM_NOALLOC_CHUNKS;
+  const int rpc = (rows + chunks - 1) / chunks;
+  dim3 g1((C / 8 + 255) / 256, chunks);
+  // stage 1 writes partial[chunk, 0..C) for every chunk < chunks: exactly what stage 2 reads,
+  // so stale contents from an earlier call are never observed.
+  colsum_stage1_kernel<<<g1, 256, 0, stream>>>((const bf16*)x, ldx, partial, rows, C, rpc);
+  TT_LAUNCH_CHECK();
+  colsum_stage2_kernel<<<(C + 255) / 256, 256, 0, stream>>>(partial, out, chunks, C, out_fp32, accumulate);
+  TT_LAUNCH_CHECK();
+  return 0;
+}
