@@ -40,6 +40,8 @@ struct BwdParams {
   long long ld0, bs0, ld1, bs1;
   const int* kv_lens;
   unsigned* status;
+  TTScatter sc0;  // mode 2: out0 (dK or dQ) is stored into the owning peer's [B, S_l, H, D] buffer
+  TTScatter sc1;  // likewise for out1 (dV)
 };
 
 // plain (untiled) bulk copy global -> shared, completion counted on an mbarrier
@@ -253,9 +255,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const bool live = row < kv_len;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {  // 0: dV, 1: dK
-        bf16* dst = which == 0
-                        ? p.out1 + (long long)b * p.bs1 + (long long)row * p.ld1 + h * 128
-                        : p.out0 + (long long)b * p.bs0 + (long long)row * p.ld0 + h * 128;
+        bf16* dst;
+        if (which == 0)
+          dst = (p.sc1.mode == 2 && row < p.Skv) ? scatter_dst(p.sc1, b, row, h)
+                                                 : p.out1 + (long long)b * p.bs1 + (long long)row * p.ld1 + h * 128;
+        else
+          dst = (p.sc0.mode == 2 && row < p.Skv) ? scatter_dst(p.sc0, b, row, h)
+                                                 : p.out0 + (long long)b * p.bs0 + (long long)row * p.ld0 + h * 128;
         const float mul = which == 0 ? 1.f : p.scale;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -475,7 +481,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
-      bf16* dst = p.out0 + (long long)b * p.bs0 + (long long)row * p.ld0 + h * 128;
+      bf16* dst = (p.sc0.mode == 2 && row < p.Sq) ? scatter_dst(p.sc0, b, row, h)
+                                                  : p.out0 + (long long)b * p.bs0 + (long long)row * p.ld0 + h * 128;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
@@ -557,19 +564,21 @@ TT_API long long tt_attn_bwd_scratch_floats(int B, int H, int Sq) {
   return 2ll * B * H * ((Sq + 63) / 64 * 64);
 }
 
-TT_API int tt_attn_bwd(const void* q, long long ldq, long long q_bs, const void* k, long long ldk,
+static int attn_bwd_impl(const void* q, long long ldq, long long q_bs, const void* k, long long ldk,
                        long long k_bs, const void* v, long long ldv, long long v_bs, const void* o,
                        long long ldo, long long o_bs, const void* dout, long long lddo, long long do_bs,
                        const float* lse, float* scratch, void* dq, long long lddq, long long dq_bs,
                        void* dk, long long lddk, long long dk_bs, void* dv, long long lddv,
                        long long dv_bs, const int* kv_lens, int B, int H, int Sq, int Skv, int D,
-                       float scale, unsigned* status, cudaStream_t stream) {
+                       float scale, unsigned* status, const TTScatter* scq, const TTScatter* sck,
+                       const TTScatter* scv, cudaStream_t stream) {
   TT_CHECK(D == 128, "attn_bwd: head_dim must be 128 (got %d)", D);
   TT_CHECK(B > 0 && H > 0 && Sq > 0 && Skv > 0, "attn_bwd: empty problem");
   const long long lds[] = {ldq, ldk, ldv, ldo, lddo, lddq, lddk, lddv, q_bs, k_bs, v_bs, o_bs, do_bs, dq_bs, dk_bs, dv_bs};
   for (long long x : lds) TT_CHECK(x % 8 == 0, "attn_bwd: strides must be multiples of 8 elements");
   TT_CHECK((((uintptr_t)dq | (uintptr_t)dk | (uintptr_t)dv | (uintptr_t)o | (uintptr_t)dout) & 15) == 0,
            "attn_bwd: misaligned pointer");
+  TT_CHECK(scq != nullptr || (dq && dk && dv), "attn_bwd: output pointers missing");
   TT_CHECK(((uintptr_t)scratch & 15) == 0, "attn_bwd: scratch misaligned");
   const int Sq_pad = (Sq + 63) / 64 * 64;
   float* lse2 = scratch;
@@ -586,6 +595,8 @@ TT_API int tt_attn_bwd(const void* q, long long ldq, long long q_bs, const void*
   p.Sq = Sq; p.Skv = Skv; p.H = H; p.B = B; p.Sq_pad = Sq_pad;
   p.scale = scale; p.scale_log2 = scale * LOG2E;
   p.lse2 = lse2; p.delta = delta; p.kv_lens = kv_lens; p.status = status;
+  memset(&p.sc0, 0, sizeof(p.sc0));
+  memset(&p.sc1, 0, sizeof(p.sc1));
   static bool attr_done = false;
   if (!attr_done) {
     TT_CUDA(cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A_SMEM));
@@ -600,6 +611,8 @@ TT_API int tt_attn_bwd(const void* q, long long ldq, long long q_bs, const void*
     if (make_map(&tmV, v, ldv, v_bs, Skv, H, B, 128)) return -1;
     p.out0 = (bf16*)dk; p.ld0 = lddk; p.bs0 = dk_bs;
     p.out1 = (bf16*)dv; p.ld1 = lddv; p.bs1 = dv_bs;
+    if (sck) p.sc0 = *sck;
+    if (scv) p.sc1 = *scv;
     dim3 grid((Skv + 127) / 128, H, B);
     attn_bwd_dkdv_kernel<<<grid, NTHREADS, A_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, p);
     TT_LAUNCH_CHECK();
@@ -612,9 +625,51 @@ TT_API int tt_attn_bwd(const void* q, long long ldq, long long q_bs, const void*
     if (make_map(&tmV, v, ldv, v_bs, Skv, H, B, 64)) return -1;
     p.out0 = (bf16*)dq; p.ld0 = lddq; p.bs0 = dq_bs;
     p.out1 = nullptr; p.ld1 = 0; p.bs1 = 0;
+    memset(&p.sc0, 0, sizeof(p.sc0));
+    memset(&p.sc1, 0, sizeof(p.sc1));
+    if (scq) p.sc0 = *scq;
     dim3 grid((Sq + 127) / 128, H, B);
     attn_bwd_dq_kernel<<<grid, NTHREADS, B_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, p);
     TT_LAUNCH_CHECK();
   }
   return 0;
+}
+
+TT_API int tt_attn_bwd(const void* q, long long ldq, long long q_bs, const void* k, long long ldk,
+                       long long k_bs, const void* v, long long ldv, long long v_bs, const void* o,
+                       long long ldo, long long o_bs, const void* dout, long long lddo, long long do_bs,
+                       const float* lse, float* scratch, void* dq, long long lddq, long long dq_bs,
+                       void* dk, long long lddk, long long dk_bs, void* dv, long long lddv,
+                       long long dv_bs, const int* kv_lens, int B, int H, int Sq, int Skv, int D,
+                       float scale, unsigned* status, cudaStream_t stream) {
+  return attn_bwd_impl(q, ldq, q_bs, k, ldk, k_bs, v, ldv, v_bs, o, ldo, o_bs, dout, lddo, do_bs, lse, scratch,
+                       dq, lddq, dq_bs, dk, lddk, dk_bs, dv, lddv, dv_bs, kv_lens, B, H, Sq, Skv, D, scale,
+                       status, nullptr, nullptr, nullptr, stream);
+}
+
+// Backward over head-parallel tensors [B, S_pad, Hl, D]; dQ, dK, dV are stored with the Ulysses
+// head -> seq pattern into every peer's [B, S_l, H_total, D] buffers (three peer tables).
+TT_API int tt_attn_bwd_scatter(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                               const float* lse, float* scratch, const long long* dq_peers,
+                               const long long* dk_peers, const long long* dv_peers, const int* kv_lens,
+                               int B, int Hl, int S_pad, int D, float scale, int world, int rank,
+                               unsigned* status, cudaStream_t stream) {
+  TT_CHECK(world >= 1 && world <= TT_MAX_PEERS && rank >= 0 && rank < world, "attn_bwd_scatter: bad world/rank");
+  TT_CHECK(S_pad % world == 0, "attn_bwd_scatter: padded sequence must divide by the group size");
+  TTScatter sc[3];
+  const long long* tabs[3] = {dq_peers, dk_peers, dv_peers};
+  for (int t = 0; t < 3; ++t) {
+    memset(&sc[t], 0, sizeof(TTScatter));
+    for (int i = 0; i < world; ++i) {
+      sc[t].peer[i] = reinterpret_cast<void*>(tabs[t][i]);
+      TT_CHECK(sc[t].peer[i] && ((uintptr_t)sc[t].peer[i] & 15) == 0, "attn_bwd_scatter: bad peer pointer");
+    }
+    sc[t].mode = 2; sc[t].S_l = S_pad / world; sc[t].S_pad = S_pad; sc[t].Hl = Hl; sc[t].H = Hl * world;
+    sc[t].D = D; sc[t].rank = rank; sc[t].world = world;
+  }
+  const long long ld = (long long)Hl * D, bs = (long long)S_pad * Hl * D;
+  // dq/dk/dv local pointers are unused in scatter mode; pass q as an aligned placeholder
+  return attn_bwd_impl(q, ld, bs, k, ld, bs, v, ld, bs, o, ld, bs, dout, ld, bs, lse, scratch,
+                       const_cast<void*>(q), ld, bs, const_cast<void*>(q), ld, bs, const_cast<void*>(q), ld, bs,
+                       kv_lens, B, Hl, S_pad, S_pad, D, scale, status, &sc[0], &sc[1], &sc[2], stream);
 }

@@ -41,6 +41,7 @@ struct AttnParams {
   float* lse;  // [B, H, Sq]
   const int* kv_lens;  // optional [B]
   unsigned* status;
+  TTScatter sc;  // mode 2: also store O into the owning peer's [B, S_l, H, D] buffer (head -> seq)
 };
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -277,6 +278,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int row = q0 + t * TILE + r;
       const float inv = 1.f / l;
       bf16* orow = p.O + (long long)b * p.o_batch_stride + (long long)row * p.ldo + h * 128;
+      bf16* prow = (p.sc.mode == 2 && row < p.Sq) ? scatter_dst(p.sc, b, row, h) : nullptr;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
@@ -291,6 +293,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             pk.z = pack_bf16(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
             pk.w = pack_bf16(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
             *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = pk;
+            if (prow) *reinterpret_cast<uint4*>(prow + c * 32 + g * 8) = pk;
           }
         }
         __syncwarp();
@@ -322,10 +325,11 @@ int make_qkv_map(CUtensorMap* tm, const void* ptr, long long ld, long long batch
 // q: [B, Sq, H, 128] with token stride ldq and batch stride q_bs (elements); k, v likewise
 // with Skv tokens; o: [B, Sq, H*128] with token stride ldo; lse: fp32 [B, H, Sq] (may be null).
 // kv_lens: optional int32 [B], keys at or beyond kv_lens[b] are masked.
-TT_API int tt_attn_fwd(const void* q, long long ldq, long long q_bs, const void* k, long long ldk,
-                       long long k_bs, const void* v, long long ldv, long long v_bs, void* o,
-                       long long ldo, long long o_bs, float* lse, const int* kv_lens, int B, int H,
-                       int Sq, int Skv, int D, float scale, unsigned* status, cudaStream_t stream) {
+static int attn_fwd_impl(const void* q, long long ldq, long long q_bs, const void* k, long long ldk,
+                         long long k_bs, const void* v, long long ldv, long long v_bs, void* o,
+                         long long ldo, long long o_bs, float* lse, const int* kv_lens, int B, int H,
+                         int Sq, int Skv, int D, float scale, unsigned* status, const TTScatter& sc,
+                         cudaStream_t stream) {
   TT_CHECK(D == 128, "attn_fwd: head_dim must be 128 (got %d)", D);
   TT_CHECK(B > 0 && H > 0 && Sq > 0 && Skv > 0, "attn_fwd: empty problem");
   TT_CHECK(ldq % 8 == 0 && ldk % 8 == 0 && ldv % 8 == 0 && ldo % 8 == 0, "attn_fwd: token strides must be multiples of 8");
@@ -340,6 +344,7 @@ TT_API int tt_attn_fwd(const void* q, long long ldq, long long q_bs, const void*
   p.scale_log2 = scale * 1.4426950408889634f;
   p.O = (bf16*)o; p.ldo = ldo; p.o_batch_stride = o_bs;
   p.lse = lse; p.kv_lens = kv_lens; p.status = status;
+  p.sc = sc;
   static bool attr_done = false;
   if (!attr_done) {
     TT_CUDA(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -349,4 +354,36 @@ TT_API int tt_attn_fwd(const void* q, long long ldq, long long q_bs, const void*
   attn_fwd_kernel<<<grid, NTHREADS, SMEM_BYTES, stream>>>(tmQ, tmK, tmV, p);
   TT_LAUNCH_CHECK();
   return 0;
+}
+
+TT_API int tt_attn_fwd(const void* q, long long ldq, long long q_bs, const void* k, long long ldk,
+                       long long k_bs, const void* v, long long ldv, long long v_bs, void* o,
+                       long long ldo, long long o_bs, float* lse, const int* kv_lens, int B, int H,
+                       int Sq, int Skv, int D, float scale, unsigned* status, cudaStream_t stream) {
+  TTScatter sc;
+  memset(&sc, 0, sizeof(sc));
+  return attn_fwd_impl(q, ldq, q_bs, k, ldk, k_bs, v, ldv, v_bs, o, ldo, o_bs, lse, kv_lens, B, H, Sq, Skv, D,
+                       scale, status, sc, stream);
+}
+
+// Attention over head-parallel tensors [B, S_pad, Hl, D] whose epilogue also stores O with the
+// Ulysses head -> seq pattern into every peer's [B, S_l, H_total, D] buffer (peer_ptrs), in
+// addition to the local head-layout copy `o` that the backward pass needs.
+TT_API int tt_attn_fwd_scatter(const void* q, long long ldq, long long q_bs, const void* k, long long ldk,
+                               long long k_bs, const void* v, long long ldv, long long v_bs, void* o,
+                               long long ldo, long long o_bs, float* lse, const int* kv_lens, int B, int Hl,
+                               int S_pad, int D, float scale, const long long* peer_ptrs, int world,
+                               int rank, unsigned* status, cudaStream_t stream) {
+  TT_CHECK(world >= 1 && world <= TT_MAX_PEERS && rank >= 0 && rank < world, "attn_fwd_scatter: bad world/rank");
+  TT_CHECK(S_pad % world == 0, "attn_fwd_scatter: padded sequence must divide by the group size");
+  TTScatter sc;
+  memset(&sc, 0, sizeof(sc));
+  for (int i = 0; i < world; ++i) {
+    sc.peer[i] = reinterpret_cast<void*>(peer_ptrs[i]);
+    TT_CHECK(sc.peer[i] && ((uintptr_t)sc.peer[i] & 15) == 0, "attn_fwd_scatter: bad peer pointer %d", i);
+  }
+  sc.mode = 2; sc.S_l = S_pad / world; sc.S_pad = S_pad; sc.Hl = Hl; sc.H = Hl * world; sc.D = D;
+  sc.rank = rank; sc.world = world;
+  return attn_fwd_impl(q, ldq, q_bs, k, ldk, k_bs, v, ldv, v_bs, o, ldo, o_bs, lse, kv_lens, B, Hl, S_pad,
+                       S_pad, D, scale, status, sc, stream);
 }

@@ -257,7 +257,7 @@ rmsrope_kernel(const bf16* __restrict__ in, long long ldi, const bf16* __restric
                long long ldx, bf16* __restrict__ out, long long ldo, const float* __restrict__ w,
                const float2* __restrict__ freqs, int freq_rows, float* __restrict__ rstd_io,
                float* __restrict__ partial, int rows, int C, int D, int per_head, float eps,
-               int rows_per_cta) {
+               int rows_per_cta, const TTScatter sc) {
   __shared__ float red[NT / 32];
   const int nvec = C >> 3;
   const int vec_per_head = D >> 3;
@@ -338,7 +338,13 @@ rmsrope_kernel(const bf16* __restrict__ in, long long ldi, const bf16* __restric
               o[2 * j + 1] = a * s + b * c;
             }
           }
-          store8(out + (long long)row * ldo + vec * 8, o);
+          if (sc.mode == 0) {
+            store8(out + (long long)row * ldo + vec * 8, o);
+          } else {  // all-to-all fused into the store: write straight into the owning peer's buffer
+            const int col = vec * 8;
+            const int hd = col / D;
+            store8(scatter_dst(sc, row / sc.S_l, row % sc.S_l, hd) + (col - hd * D), o);
+          }
         }
       }
     } else {
@@ -493,9 +499,9 @@ TT_API int tt_colsum_partials(const float* partial, float* out, int groups, int 
 }
 
 // Forward: in = x. Saves rstd ([rows] or [rows, H]) when w != null.
-TT_API int tt_rmsrope_fwd(const void* x, long long ldx, void* y, long long ldy, const float* w,
-                          const void* freqs, int freq_rows, float* rstd, int rows, int C, int D,
-                          int per_head, float eps, cudaStream_t stream) {
+static int rmsrope_fwd_impl(const void* x, long long ldx, void* y, long long ldy, const float* w,
+                            const void* freqs, int freq_rows, float* rstd, int rows, int C, int D,
+                            int per_head, float eps, const TTScatter& sc, cudaStream_t stream) {
   TT_CHECK(rows > 0 && C % 8 == 0 && C <= 6144 && D > 0 && C % D == 0, "rmsrope_fwd: bad shape");
   TT_CHECK(!per_head || (D == 128 || D == 64), "rmsrope_fwd: per-head norm supports D = 64 or 128");
   TT_CHECK(freqs == nullptr || (D % 8 == 0 && freq_rows > 0), "rmsrope_fwd: bad rotary table");
@@ -505,9 +511,38 @@ TT_API int tt_rmsrope_fwd(const void* x, long long ldx, void* y, long long ldy, 
   const int grid = (rows + rpc - 1) / rpc;
   TT_DISPATCH_VPT(vpt_for(C), rmsrope_kernel<VPT, false><<<grid, NT, 0, stream>>>(
       (const bf16*)x, ldx, nullptr, 0, (bf16*)y, ldy, w, (const float2*)freqs, freq_rows, rstd,
-      nullptr, rows, C, D, per_head, eps, rpc));
+      nullptr, rows, C, D, per_head, eps, rpc, sc));
   TT_LAUNCH_CHECK();
   return 0;
+}
+
+TT_API int tt_rmsrope_fwd(const void* x, long long ldx, void* y, long long ldy, const float* w,
+                          const void* freqs, int freq_rows, float* rstd, int rows, int C, int D,
+                          int per_head, float eps, cudaStream_t stream) {
+  TTScatter sc;
+  memset(&sc, 0, sizeof(sc));
+  return rmsrope_fwd_impl(x, ldx, y, ldy, w, freqs, freq_rows, rstd, rows, C, D, per_head, eps, sc, stream);
+}
+
+// Same as tt_rmsrope_fwd, but the result is stored into peer memory with the Ulysses seq -> head
+// pattern (TTScatter mode 1): x is this rank's [B*S_l, H*D] shard, the output lands in every
+// peer's [B, S_pad, H/P, D] buffer. peer_ptrs: `world` device addresses of those buffers.
+TT_API int tt_rmsrope_fwd_scatter(const void* x, long long ldx, const float* w, const void* freqs,
+                                  int freq_rows, float* rstd, int rows, int C, int D, int per_head,
+                                  float eps, const long long* peer_ptrs, int world, int rank, int S_l,
+                                  int S_pad, cudaStream_t stream) {
+  TT_CHECK(world >= 1 && world <= TT_MAX_PEERS && rank >= 0 && rank < world, "rmsrope_fwd_scatter: bad world/rank");
+  const int H = C / D;
+  TT_CHECK(H % world == 0, "rmsrope_fwd_scatter: heads (%d) must divide by the group size (%d)", H, world);
+  TT_CHECK(S_l > 0 && S_pad == S_l * world && rows % S_l == 0, "rmsrope_fwd_scatter: bad sequence split");
+  TTScatter sc;
+  memset(&sc, 0, sizeof(sc));
+  for (int i = 0; i < world; ++i) {
+    sc.peer[i] = reinterpret_cast<void*>(peer_ptrs[i]);
+    TT_CHECK(sc.peer[i] && ((uintptr_t)sc.peer[i] & 15) == 0, "rmsrope_fwd_scatter: bad peer pointer %d", i);
+  }
+  sc.mode = 1; sc.S_l = S_l; sc.S_pad = S_pad; sc.Hl = H / world; sc.H = H; sc.D = D; sc.rank = rank; sc.world = world;
+  return rmsrope_fwd_impl(x, ldx, const_cast<void*>(x), ldx, w, freqs, freq_rows, rstd, rows, C, D, per_head, eps, sc, stream);
 }
 
 // Backward: dy -> dx, with x (saved forward input) and rstd. partial: fp32 [ctas, C] scratch for
@@ -531,7 +566,7 @@ TT_API int tt_rmsrope_bwd(const void* dy, long long lddy, const void* x, long lo
   const int grid = (rows + rpc - 1) / rpc;
   TT_DISPATCH_VPT(vpt_for(C), rmsrope_kernel<VPT, true><<<grid, NT, 0, stream>>>(
       (const bf16*)dy, lddy, (const bf16*)x, ldx, (bf16*)dx, lddx, w, (const float2*)freqs, freq_rows,
-      rstd, partial, rows, C, D, per_head, 0.f, rpc));
+      rstd, partial, rows, C, D, per_head, 0.f, rpc, TTScatter{}));
   TT_LAUNCH_CHECK();
   return 0;
 }

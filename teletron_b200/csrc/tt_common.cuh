@@ -68,8 +68,33 @@ enum : unsigned {
   TT_ST_TIMEOUT_PEER = 0x500,
 };
 
+// Ulysses all-to-all as a store pattern: where an element of a local tensor lands in peer memory.
+//   mode 1 (seq -> head): source [B, S_l, H, D] on rank r  ->  peer h / Hl, [B, S_pad, Hl, D] at
+//                         token r*S_l + s, head h % Hl
+//   mode 2 (head -> seq): source [B, S_pad, Hl, D] on rank r ->  peer t / S_l, [B, S_l, H, D] at
+//                         token t % S_l, head r*Hl + hl
+// mode 0 means "no scatter" (store locally).
+#define TT_MAX_PEERS 16
+struct TTScatter {
+  void* peer[TT_MAX_PEERS];
+  int mode;
+  int S_l, S_pad, Hl, H, D, rank, world;
+};
+
 #ifdef __CUDACC__
 namespace tt {
+
+// Destination of element (batch b, token tok, head hd, d = 0) of the source tensor; bf16 elements.
+__device__ __forceinline__ bf16* scatter_dst(const TTScatter& sc, int b, int tok, int hd) {
+  if (sc.mode == 1) {
+    const int p = hd / sc.Hl;
+    const long long idx = ((long long)(b * sc.S_pad + sc.rank * sc.S_l + tok) * sc.Hl + (hd - p * sc.Hl)) * sc.D;
+    return reinterpret_cast<bf16*>(sc.peer[p]) + idx;
+  }
+  const int p = tok / sc.S_l;
+  const long long idx = ((long long)(b * sc.S_l + (tok - p * sc.S_l)) * sc.H + sc.rank * sc.Hl + hd) * sc.D;
+  return reinterpret_cast<bf16*>(sc.peer[p]) + idx;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

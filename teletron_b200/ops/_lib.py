@@ -22,6 +22,7 @@ c_void_p = ctypes.c_void_p
 c_int = ctypes.c_int
 c_ll = ctypes.c_longlong
 c_float = ctypes.c_float
+c_uint = ctypes.c_uint
 
 
 def lib_file() -> Path:

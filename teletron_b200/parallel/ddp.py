@@ -38,7 +38,9 @@ def _no_weight_decay(name: str, p: torch.Tensor) -> bool:
 
 
 class ParamBuffer:
-    def __init__(self, module: torch.nn.Module, shard_world: int = 1, grad_dtype=torch.float32):
+    def __init__(self, module: torch.nn.Module, shard_world: int = 1, grad_dtype=torch.float32, arena=None):
+        """``arena``: a ``dist.SymmetricArena``; when given, both flat buffers live in symmetric peer
+        memory so the fused reduce-scatter / AdamW / all-gather kernels can reach every rank's copy."""
         named = [(n, p) for n, p in module.named_parameters() if p.requires_grad]
         assert named, "module has no trainable parameters"
         dev = named[0][1].device
@@ -58,8 +60,17 @@ class ParamBuffer:
             self.index[n] = (off, p.numel(), p.shape)
             off += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
         self.numel = (off + self.region_align - 1) // self.region_align * self.region_align
-        self.params = torch.zeros(self.numel, dtype=self.param_dtype, device=dev)
-        self.grads = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
+        self.arena = arena
+        self.symm_params = self.symm_grads = None
+        if arena is not None:
+            self.symm_params = arena.alloc(self.numel, self.param_dtype)
+            self.symm_grads = arena.alloc(self.numel, grad_dtype)
+            self.params, self.grads = self.symm_params.tensor, self.symm_grads.tensor
+            self.params.zero_()
+            self.grads.zero_()
+        else:
+            self.params = torch.zeros(self.numel, dtype=self.param_dtype, device=dev)
+            self.grads = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
         self.named = named
         for n, p in named:
             o, cnt, shape = self.index[n]
@@ -121,12 +132,19 @@ class DistributedOptimizer:
         self.exp_avg = [torch.zeros(e - s, dtype=torch.float32, device=dev) for s, e, _ in self.shards]
         self.exp_avg_sq = [torch.zeros(e - s, dtype=torch.float32, device=dev) for s, e, _ in self.shards]
         self._shard_grads: List[Optional[torch.Tensor]] = [None] * len(self.shards)
+        # fused path: peer-memory reduce-scatter + AdamW + parameter scatter (csrc/comm.cu)
+        self.fused = bool(self.sharded and buf.arena is not None and buf.grads.dtype == torch.float32)
+        self._reduced = None
+        self.last_path = "nccl"
 
     # ------------------------------------------------------------------ gradient sync
     def reduce_gradients(self):
         """Sum gradients over the group; afterwards ``_shard_grads`` holds this rank's fp32 slices."""
         self.buf.collect_grads()
         g = self.buf.grads
+        if self.fused:
+            self._shard_grads = ["fused"] * len(self.shards)  # reduction happens inside step()
+            return
         if self.world > 1:
             if self.sharded:
                 for i, ((s, e, _), (rs, re, _)) in enumerate(zip(self.shards, self.buf.regions())):
@@ -148,9 +166,56 @@ class DistributedOptimizer:
 
     # ------------------------------------------------------------------ step
     @torch.no_grad()
+    def _fused_step(self):
+        """K-DP-RS-ADAMW: barrier, pull-reduce of the owned shard from every peer, global norm, AdamW
+        and bf16 parameter scatter to every peer, barrier."""
+        from ..ops import _lib
+
+        L = _lib.lib()
+        buf, arena = self.buf, self.buf.arena
+        dev = buf.params.device
+        self.step_count += 1
+        lr = self.param_groups[0]["lr"]
+        wd_base = self.param_groups[0]["weight_decay"]
+        blocks = L.tt_comm_blocks()
+        need_clip = bool(self.clip_grad and self.clip_grad > 0)
+        partials = torch.zeros((len(self.shards), blocks), dtype=torch.float32, device=dev)
+        if need_clip and self._reduced is None:
+            self._reduced = [torch.empty(e - s, dtype=torch.float32, device=dev) for s, e, _ in self.shards]
+        arena.barrier(0)  # every rank's backward (its writes into its gradient buffer) is complete
+
+        def launch(mode, i, coef):
+            s, e, wd = self.shards[i]
+            rc = L.tt_dp_shard_step(
+                _lib.c_int(mode), buf.symm_grads.c_ptrs(), buf.symm_params.c_ptrs(), _lib.c_int(self.world),
+                _lib.c_int(self.rank), _lib.c_ll(s), _lib.c_ll(e - s),
+                _lib.ptr(self._reduced[i] if self._reduced is not None else None), _lib.ptr(self.master[i]),
+                _lib.ptr(self.exp_avg[i]), _lib.ptr(self.exp_avg_sq[i]), _lib.c_float(self.grad_scale),
+                _lib.ptr(coef), _lib.c_float(lr), _lib.c_float(self.betas[0]), _lib.c_float(self.betas[1]),
+                _lib.c_float(self.eps), _lib.c_float(wd_base if wd else 0.0), _lib.c_int(self.step_count),
+                _lib.ptr(partials[i]), _lib.stream())
+            _lib.check(rc, "tt_dp_shard_step")
+
+        for i in range(len(self.shards)):
+            launch(0 if need_clip else 2, i, None)
+        ss = partials.sum()
+        dist.all_reduce(ss, op=dist.ReduceOp.SUM, group=self.group)
+        norm = ss.sqrt() * self.grad_scale
+        if need_clip:
+            coef = torch.clamp(self.clip_grad / (norm + 1e-6), max=1.0).reshape(1).float()
+            for i in range(len(self.shards)):
+                launch(1, i, coef)
+        arena.barrier(1)  # every rank has written its parameter shard into every peer
+        self._shard_grads = [None] * len(self.shards)
+        self.last_path = "fused"
+        return True, norm, None
+
+    @torch.no_grad()
     def step(self):
         if self._shard_grads[0] is None:
             self.reduce_gradients()
+        if self.fused:
+            return self._fused_step()
         self.step_count += 1
         lr = self.param_groups[0]["lr"]
         wd_base = self.param_groups[0]["weight_decay"]

@@ -124,7 +124,21 @@ class Trainer:
         inner = model.module if isinstance(model, Float16Module) else model
         group = mpu.get_data_parallel_group(with_context_parallel=True)
         world = mpu.get_data_parallel_world_size(with_context_parallel=True)
-        self.buffer = ParamBuffer(inner, shard_world=world if a.use_distributed_optimizer else 1)
+        arena = None
+        want_fused = a.fused_comm != "off" and a.use_distributed_optimizer and world > 1 and self.device.type == "cuda"
+        if want_fused:
+            from ..dist import SymmetricArena, symmetric_memory_available
+
+            single_box = a.world_size <= torch.cuda.device_count()
+            if symmetric_memory_available() and (single_box or a.fused_comm == "on"):
+                try:
+                    arena = SymmetricArena(group)
+                except Exception as e:
+                    if a.fused_comm == "on":
+                        raise
+                    print(f"WARNING: symmetric memory unavailable ({e}); using NCCL collectives", flush=True)
+        self.arena = arena
+        self.buffer = ParamBuffer(inner, shard_world=world if a.use_distributed_optimizer else 1, arena=arena)
         self.optimizer = DistributedOptimizer(
             self.buffer, group if world > 1 else None, lr=a.lr, betas=(a.adam_beta1, a.adam_beta2),
             eps=a.adam_eps, weight_decay=a.weight_decay, clip_grad=a.clip_grad,

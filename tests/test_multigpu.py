@@ -1,0 +1,105 @@
+"""Multi-GPU tests (need >= 2 GPUs in one box): peer-memory fused optimizer step vs the NCCL path,
+Ulysses context parallelism through the CUDA kernels vs one GPU."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from dist_utils import run_distributed
+
+needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+
+
+def rel(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return (0.5 * (a - b).norm() / (a.norm() + b.norm() + 1e-30)).item()
+
+
+def _opt_worker(rank, world, fused, clip):
+    import torch.distributed as dist
+
+    from teletron_b200.dist import SymmetricArena
+    from teletron_b200.ops import _lib
+    from teletron_b200.parallel.ddp import DistributedOptimizer, ParamBuffer
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.Linear(512, 264)).cuda().to(torch.bfloat16)
+    arena = SymmetricArena(dist.group.WORLD) if fused else None
+    buf = ParamBuffer(model, shard_world=world, arena=arena)
+    opt = DistributedOptimizer(buf, dist.group.WORLD, lr=1e-2, weight_decay=0.1, clip_grad=clip, sharded=True,
+                               grad_scale=1.0 / world)
+    assert opt.fused == fused
+    norms = []
+    for step in range(3):
+        opt.zero_grad()
+        g = torch.Generator(device="cuda").manual_seed(100 * step + rank)
+        buf.grads.copy_(torch.randn(buf.numel, device="cuda", generator=g))
+        opt.reduce_gradients()
+        _, n, _ = opt.step()
+        norms.append(float(n))
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return buf.params.float().cpu(), torch.cat([m.cpu() for m in opt.master]), norms
+
+
+@needs2
+@pytest.mark.parametrize("clip", [0.0, 1.0])
+def test_fused_dp_optimizer_matches_nccl(clip):
+    ref = run_distributed(_opt_worker, 2, False, clip, backend="nccl")
+    got = run_distributed(_opt_worker, 2, True, clip, backend="nccl")
+    for r in range(2):
+        assert torch.equal(got[r][0], got[0][0])                      # replicas agree bit for bit
+        assert rel(got[r][0], ref[r][0]) < 1e-3                          # bf16 params
+        assert rel(got[r][1], ref[r][1]) < 1e-5                          # fp32 master shard
+        assert all(abs(a - b) < 1e-3 * abs(b) for a, b in zip(got[r][2], ref[r][2]))
+
+
+def _cp_worker(rank, world):
+    from teletron_b200 import ops
+    from teletron_b200.models import WanModel, wan_config
+    from teletron_b200.ops import _lib
+    from teletron_b200.parallel import state as mpu
+    from teletron_b200.parallel.ulysses import UlyssesContext
+
+    mpu.initialize_model_parallel(context_parallel_size=world)
+    cp = UlyssesContext(mpu.get_context_parallel_group(), world, rank)
+    torch.manual_seed(0)
+    cfg = wan_config("wan-tiny", dim=256, num_heads=2, ffn_dim=512, text_dim=64, freq_dim=64, num_layers=2)
+    model = WanModel(cfg, cp).cuda().to(torch.bfloat16)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(1, 16, 3, 16, 20, generator=g).cuda().bfloat16()   # 3*8*10 = 240 tokens
+    ctx = torch.randn(1, 40, 64, generator=g).cuda().bfloat16()
+    t = torch.tensor([400.0]).cuda()
+    out = model(x, t, ctx)
+    out.float().square().mean().backward()
+    grads = {n: p.grad.float() for n, p in model.named_parameters() if p.grad is not None}
+    for v in grads.values():
+        torch.distributed.all_reduce(v)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return out.float().cpu(), {k: v.cpu() for k, v in grads.items()}
+
+
+def _single_gpu_reference():
+    from teletron_b200.models import WanModel, wan_config
+
+    torch.manual_seed(0)
+    cfg = wan_config("wan-tiny", dim=256, num_heads=2, ffn_dim=512, text_dim=64, freq_dim=64, num_layers=2)
+    model = WanModel(cfg).cuda().to(torch.bfloat16)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(1, 16, 3, 16, 20, generator=g).cuda().bfloat16()
+    ctx = torch.randn(1, 40, 64, generator=g).cuda().bfloat16()
+    t = torch.tensor([400.0]).cuda()
+    out = model(x, t, ctx)
+    out.float().square().mean().backward()
+    return out.float().cpu(), {n: p.grad.float().cpu() for n, p in model.named_parameters() if p.grad is not None}
+
+
+@needs2
+def test_ulysses_cp2_matches_single_gpu():
+    ref_out, ref_g = _single_gpu_reference()
+    outs = run_distributed(_cp_worker, 2, backend="nccl")
+    for out, grads in outs:
+        assert rel(out, ref_out) < 1e-3          # same threshold as the reference's model test
+        bad = [(n, rel(grads[n], ref_g[n])) for n in ref_g if ref_g[n].norm() > 2e-4 and rel(grads[n], ref_g[n]) > 2e-2]
+        assert not bad, bad
