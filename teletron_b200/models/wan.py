@@ -185,6 +185,13 @@ class SelfAttention(nn.Module, _FusedStateMixin):
     def forward(self, h2d, freqs, batch, cp: Optional[UlyssesContext], residual, gate, rows_per_batch):
         C, H, D = self.dim, self.num_heads, self.head_dim
         qkv = self.qkv(h2d)  # [rows, 3C]
+        fu = cp.fused if (cp is not None and cp.size > 1) else None
+        if fu is not None and h2d.is_cuda and fu.supports(H, D):
+            # all-to-alls fused into the norm/rope and attention kernels' stores (peer memory)
+            fu.seq_len = cp.seq_len
+            a2d = fu.attention(qkv[:, 0:C], qkv[:, C:2 * C], qkv[:, 2 * C:3 * C], self.norm_q.weight,
+                               self.norm_k.weight, freqs, batch, rows_per_batch, H, D, self.eps)
+            return ops.linear_residual(a2d, self.o.weight, self.o.bias, residual, gate, rows_per_batch)
         q = ops.rmsnorm_rope(qkv[:, 0:C], self.norm_q.weight, freqs, D, False, self.eps)
         k = ops.rmsnorm_rope(qkv[:, C:2 * C], self.norm_k.weight, freqs, D, False, self.eps)
         v = qkv[:, 2 * C:3 * C]
@@ -376,6 +383,13 @@ class WanModel(nn.Module):
         if cp is not None:
             tok = cp.split_tokens(tok.view(B, S, cfg.dim)).reshape(-1, cfg.dim)
             freqs = cp.split_rows(freqs)
+            fu = cp.fused
+            if fu is not None and tok.is_cuda and fu.supports(cfg.num_heads, cfg.head_dim):
+                alive = cfg.num_layers
+                if self.training and cfg.recompute_granularity == "full":
+                    k = cfg.recompute_num_layers or 1
+                    alive = (cfg.num_layers - min(k, cfg.num_layers) + 2) if cfg.recompute_method == "block" else k + 1
+                fu.begin_microbatch(fu.slab_elems(alive, B, cp.padded_len(S), cfg.dim, cp.size))
         tok = rc.run_blocks(self.blocks, tok, (ctx, t_mod, freqs, B, cp), cfg, self.training)
         out = self.head(tok, t, B)  # [B*S_local, 64]
         out = out.view(B, -1, out.shape[-1])

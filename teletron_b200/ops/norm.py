@@ -159,30 +159,35 @@ class _RmsRope(torch.autograd.Function):
     def backward(ctx, dy):
         x, wf, freqs, rstd = ctx.saved_tensors
         D, per_head, wdtype = ctx.meta
-        rows, C = x.shape
-        if dy.stride(1) != 1:
-            dy = dy.contiguous()
-        dx = torch.empty((rows, C), dtype=torch.bfloat16, device=x.device)
-        L = _lib.lib()
-        partial = None
-        ctas = L.tt_rmsrope_bwd_ctas(_lib.c_int(rows))
-        if wf is not None:
-            partial = torch.empty((ctas, C), dtype=torch.float32, device=x.device)
-        rc = L.tt_rmsrope_bwd(
-            _lib.ptr(dy), _lib.c_ll(dy.stride(0)), _lib.ptr(x), _lib.c_ll(x.stride(0)), _lib.ptr(dx),
-            _lib.c_ll(C), _lib.ptr(wf), _lib.ptr(freqs), _lib.c_int(freqs.shape[0] if freqs is not None else 1),
-            _lib.ptr(rstd), _lib.ptr(partial), _lib.c_int(rows), _lib.c_int(C), _lib.c_int(D),
-            _lib.c_int(int(per_head)), _lib.stream())
-        _lib.check(rc, "tt_rmsrope_bwd")
-        dw = None
-        if wf is not None:
-            dwf = torch.empty((1, C), dtype=torch.float32, device=x.device)
-            rc = L.tt_colsum_partials(_lib.ptr(partial), _lib.ptr(dwf), _lib.c_int(1), _lib.c_int(ctas),
-                                      _lib.c_int(C), _lib.c_int(0), _lib.stream())
-            _lib.check(rc, "tt_colsum_partials")
-            dw = dwf.view(C // D, D).sum(0) if per_head else dwf.view(C)
-            dw = dw.to(wdtype)
-        return dx, dw, None, None, None, None
+        dx, dw = rmsrope_bwd_raw(dy, x, wf, freqs, rstd, D, per_head)
+        return dx, (dw.to(wdtype) if dw is not None else None), None, None, None, None
+
+
+def rmsrope_bwd_raw(dy, x, wf, freqs, rstd, D, per_head=False):
+    """Backward of rope(rmsnorm(x) * w) from the saved input and rstd: returns (dx bf16, dw fp32 or None)."""
+    rows, C = x.shape
+    if dy.stride(1) != 1:
+        dy = dy.contiguous()
+    dx = torch.empty((rows, C), dtype=torch.bfloat16, device=x.device)
+    L = _lib.lib()
+    partial = None
+    ctas = L.tt_rmsrope_bwd_ctas(_lib.c_int(rows))
+    if wf is not None:
+        partial = torch.empty((ctas, C), dtype=torch.float32, device=x.device)
+    rc = L.tt_rmsrope_bwd(
+        _lib.ptr(dy), _lib.c_ll(dy.stride(0)), _lib.ptr(x), _lib.c_ll(x.stride(0)), _lib.ptr(dx),
+        _lib.c_ll(C), _lib.ptr(wf), _lib.ptr(freqs), _lib.c_int(freqs.shape[0] if freqs is not None else 1),
+        _lib.ptr(rstd), _lib.ptr(partial), _lib.c_int(rows), _lib.c_int(C), _lib.c_int(D),
+        _lib.c_int(int(per_head)), _lib.stream())
+    _lib.check(rc, "tt_rmsrope_bwd")
+    dw = None
+    if wf is not None:
+        dwf = torch.empty((1, C), dtype=torch.float32, device=x.device)
+        rc = L.tt_colsum_partials(_lib.ptr(partial), _lib.ptr(dwf), _lib.c_int(1), _lib.c_int(ctas),
+                                  _lib.c_int(C), _lib.c_int(0), _lib.stream())
+        _lib.check(rc, "tt_colsum_partials")
+        dw = dwf.view(C // D, D).sum(0) if per_head else dwf.view(C)
+    return dx, dw
 
 
 def rmsnorm_rope(x, weight, freqs, D, per_head=False, eps=1e-6):

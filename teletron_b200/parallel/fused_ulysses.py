@@ -1,0 +1,188 @@
+"""Ulysses attention with the all-to-alls fused into kernel epilogues over NVLink peer memory.
+
+Per self-attention layer, forward:
+  q/k RMSNorm+RoPE kernel and a V copy kernel store their results straight into the owning
+  peer's head-parallel buffers (seq -> head exchange as a store pattern)   -> device barrier
+  flash attention over [B, S, H/P, D]; its epilogue stores O both locally (kept for backward)
+  and into the owning peer's sequence-parallel buffer (head -> seq exchange)  -> device barrier
+backward mirrors it: dO is scattered to the head owners, the attention-backward kernels store
+dQ / dK / dV into the token owners' staging buffers, and the RMSNorm+RoPE backward consumes them.
+
+This replaces four NCCL all-to-alls per direction with no separate communication kernels and no
+pack / unpack copies (reference: teletron/core/context_parallel/context_parallel_mixin.py:87-125).
+Activations that must live until backward (q/k/v in head layout, O in sequence layout) are
+bump-allocated from one symmetric slab that is reset every micro-batch; gradient staging
+buffers are reused across layers.  Ordering across ranks relies on every rank executing the
+same kernel sequence; each exchange is fenced by the bounded flag barrier of csrc/comm.cu.
+Requirements: heads divisible by the group size, head_dim 128, bf16, one NVLink box.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops import _lib
+from ..ops.norm import rmsrope_bwd_raw
+
+_ALIGN = 128  # elements (256 bytes)
+
+
+class SymmSlab:
+    """Bump allocator over one symmetric bf16 buffer; identical call sequences on every rank give
+    identical offsets, so peer addresses are base + offset."""
+
+    def __init__(self, arena, numel: int):
+        self.arena = arena
+        self.buf = arena.alloc(numel, torch.bfloat16)
+        self.numel = numel
+        self.off = 0
+        self.high_water = 0
+
+    def reset(self):
+        self.off = 0
+
+    def take(self, numel: int):
+        n = (numel + _ALIGN - 1) // _ALIGN * _ALIGN
+        if self.off + n > self.numel:
+            raise RuntimeError(
+                f"symmetric activation slab exhausted ({self.off + n} > {self.numel} elements); raise "
+                "slab_bytes (FusedUlysses) or enable activation recompute")
+        t = self.buf.tensor[self.off:self.off + numel]
+        ptrs = self.buf.c_ptrs(self.off)
+        self.off += n
+        self.high_water = max(self.high_water, self.off)
+        return t, ptrs
+
+
+class FusedUlysses:
+    def __init__(self, arena, slab_bytes: int = 0, barrier_slot: int = 2):
+        self.arena = arena
+        self.rank, self.world = arena.rank, arena.world
+        self.slot = barrier_slot
+        self.slab = SymmSlab(arena, slab_bytes // 2) if slab_bytes else None
+        self._staging = {}
+        self.seq_len: Optional[int] = None  # true (un-padded) global sequence length
+
+    def supports(self, H: int, D: int) -> bool:
+        return D == 128 and H % self.world == 0
+
+    def begin_microbatch(self, need_elems: int = 0):
+        """Call before the first layer of every forward pass: makes sure no peer still reads the slab
+        regions of the previous micro-batch, then recycles the slab (growing it when ``need_elems``
+        bf16 elements do not fit; every rank of the group takes the same decision)."""
+        self.arena.barrier(self.slot)
+        if self.slab is None or self.slab.numel < need_elems:
+            torch.cuda.synchronize()
+            self.slab = None
+            self.slab = SymmSlab(self.arena, int(need_elems))
+        self.slab.reset()
+
+    @staticmethod
+    def slab_elems(layers_alive: int, batch: int, s_pad: int, channels: int, world: int) -> int:
+        """bf16 elements one micro-batch needs: per live layer q, k, v in head layout and O in sequence
+        layout (4 tensors of batch * s_pad * channels / world), plus alignment slack."""
+        per_layer = 4 * (batch * s_pad * channels // world + _ALIGN)
+        return int(per_layer * max(layers_alive, 1) * 1.02) + 4 * _ALIGN
+
+    def staging(self, name: str, numel: int):
+        t = self._staging.get(name)
+        if t is None or t.tensor.numel() < numel:
+            t = self.arena.alloc(numel, torch.bfloat16)  # collective; same order on every rank
+            self._staging[name] = t
+        return t
+
+    def attention(self, q_pre, k_pre, v, wq, wk, freqs, B, S_l, H, D, eps, scale=None):
+        """q_pre/k_pre/v: [B*S_l, H*D] bf16 views (row stride free). Returns [B*S_l, H*D]."""
+        return _FusedUlyssesFn.apply(self, q_pre, k_pre, v, wq, wk, freqs, B, S_l, H, D, eps, scale)
+
+
+def _scatter_rows(fu: FusedUlysses, x, w, freqs, rstd, rows, C, D, eps, dst_ptrs, S_l, S_pad):
+    L = _lib.lib()
+    rc = L.tt_rmsrope_fwd_scatter(
+        _lib.ptr(x), _lib.c_ll(x.stride(0)), _lib.ptr(w), _lib.ptr(freqs),
+        _lib.c_int(freqs.shape[0] if freqs is not None else 1), _lib.ptr(rstd), _lib.c_int(rows), _lib.c_int(C),
+        _lib.c_int(D), _lib.c_int(0), _lib.c_float(eps), dst_ptrs, _lib.c_int(fu.world), _lib.c_int(fu.rank),
+        _lib.c_int(S_l), _lib.c_int(S_pad), _lib.stream())
+    _lib.check(rc, "tt_rmsrope_fwd_scatter")
+
+
+class _FusedUlyssesFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, fu: FusedUlysses, q_pre, k_pre, v, wq, wk, freqs, B, S_l, H, D, eps, scale):
+        import math
+
+        P, rank = fu.world, fu.rank
+        C = H * D
+        Hl = H // P
+        S_pad = S_l * P
+        rows = B * S_l
+        dev = q_pre.device
+        scale = scale if scale is not None else 1.0 / math.sqrt(D)
+        n_h = B * S_pad * Hl * D
+        qh, qh_p = fu.slab.take(n_h)
+        kh, kh_p = fu.slab.take(n_h)
+        vh, vh_p = fu.slab.take(n_h)
+        o_s, o_p = fu.slab.take(rows * C)
+        wq_f = wq.float().contiguous()
+        wk_f = wk.float().contiguous()
+        rstd_q = torch.empty(rows, dtype=torch.float32, device=dev)
+        rstd_k = torch.empty(rows, dtype=torch.float32, device=dev)
+        _scatter_rows(fu, q_pre, wq_f, freqs, rstd_q, rows, C, D, eps, qh_p, S_l, S_pad)
+        _scatter_rows(fu, k_pre, wk_f, freqs, rstd_k, rows, C, D, eps, kh_p, S_l, S_pad)
+        _scatter_rows(fu, v, None, None, None, rows, C, D, eps, vh_p, S_l, S_pad)
+        fu.arena.barrier(fu.slot)
+        o_h = torch.empty(n_h, dtype=torch.bfloat16, device=dev)
+        lse = torch.empty((B, Hl, S_pad), dtype=torch.float32, device=dev)
+        kv_lens = None
+        if fu.seq_len is not None and fu.seq_len != S_pad:
+            kv_lens = torch.full((B,), fu.seq_len, dtype=torch.int32, device=dev)
+        ld, bs = Hl * D, S_pad * Hl * D
+        L = _lib.lib()
+        rc = L.tt_attn_fwd_scatter(
+            _lib.ptr(qh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(kh), _lib.c_ll(ld), _lib.c_ll(bs),
+            _lib.ptr(vh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(o_h), _lib.c_ll(ld), _lib.c_ll(bs),
+            _lib.ptr(lse), _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl), _lib.c_int(S_pad), _lib.c_int(D),
+            _lib.c_float(scale), o_p, _lib.c_int(P), _lib.c_int(rank), _lib.ptr(_lib.status_word(dev)),
+            _lib.stream())
+        _lib.check(rc, "tt_attn_fwd_scatter")
+        fu.arena.barrier(fu.slot)
+        ctx.fu = fu
+        ctx.meta = (B, S_l, H, D, scale, kv_lens)
+        ctx.save_for_backward(q_pre, k_pre, wq_f, wk_f, freqs, rstd_q, rstd_k, qh, kh, vh, o_h, lse)
+        ctx.w_dtypes = (wq.dtype, wk.dtype)
+        return o_s.view(rows, C)
+
+    @staticmethod
+    def backward(ctx, do):
+        fu: FusedUlysses = ctx.fu
+        q_pre, k_pre, wq_f, wk_f, freqs, rstd_q, rstd_k, qh, kh, vh, o_h, lse = ctx.saved_tensors
+        B, S_l, H, D, scale, kv_lens = ctx.meta
+        P, rank = fu.world, fu.rank
+        C, Hl, S_pad, rows = H * D, H // P, S_l * P, B * S_l
+        dev = do.device
+        if do.stride(1) != 1:
+            do = do.contiguous()
+        n_h = B * S_pad * Hl * D
+        do_h = fu.staging("do_h", n_h)
+        dq_s = fu.staging("dq_s", rows * C)
+        dk_s = fu.staging("dk_s", rows * C)
+        dv_s = fu.staging("dv_s", rows * C)
+        _scatter_rows(fu, do, None, None, None, rows, C, D, 0.0, do_h.c_ptrs(), S_l, S_pad)
+        fu.arena.barrier(fu.slot)
+        L = _lib.lib()
+        L.tt_attn_bwd_scratch_floats.restype = _lib.c_ll
+        scratch = torch.empty(L.tt_attn_bwd_scratch_floats(_lib.c_int(B), _lib.c_int(Hl), _lib.c_int(S_pad)),
+                              dtype=torch.float32, device=dev)
+        rc = L.tt_attn_bwd_scatter(
+            _lib.ptr(qh), _lib.ptr(kh), _lib.ptr(vh), _lib.ptr(o_h), _lib.ptr(do_h.tensor), _lib.ptr(lse),
+            _lib.ptr(scratch), dq_s.c_ptrs(), dk_s.c_ptrs(), dv_s.c_ptrs(), _lib.ptr(kv_lens), _lib.c_int(B),
+            _lib.c_int(Hl), _lib.c_int(S_pad), _lib.c_int(D), _lib.c_float(scale), _lib.c_int(P),
+            _lib.c_int(rank), _lib.ptr(_lib.status_word(dev)), _lib.stream())
+        _lib.check(rc, "tt_attn_bwd_scatter")
+        fu.arena.barrier(fu.slot)
+        dq_pre, dwq = rmsrope_bwd_raw(dq_s.tensor[:rows * C].view(rows, C), q_pre, wq_f, freqs, rstd_q, D, False)
+        dk_pre, dwk = rmsrope_bwd_raw(dk_s.tensor[:rows * C].view(rows, C), k_pre, wk_f, freqs, rstd_k, D, False)
+        dv = dv_s.tensor[:rows * C].view(rows, C).clone()
+        wdq, wdk = ctx.w_dtypes
+        return (None, dq_pre, dk_pre, dv, dwq.to(wdq), dwk.to(wdk), None, None, None, None, None, None, None)

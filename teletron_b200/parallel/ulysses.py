@@ -96,6 +96,7 @@ class UlyssesContext:
         self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
         self.seq_len = None      # un-padded global sequence length of the current batch
         self.local_len = None
+        self.fused = None        # parallel.fused_ulysses.FusedUlysses when peer-memory kernels are enabled
 
     # ---- sequence split / gather -------------------------------------------------------
     def padded_len(self, S: int) -> int:

@@ -138,6 +138,19 @@ class Trainer:
                         raise
                     print(f"WARNING: symmetric memory unavailable ({e}); using NCCL collectives", flush=True)
         self.arena = arena
+        cp_ctx = getattr(inner, "cp", None)
+        if (a.fused_comm != "off" and cp_ctx is not None and cp_ctx.size > 1 and self.device.type == "cuda"
+                and a.world_size <= torch.cuda.device_count()):
+            from ..dist import SymmetricArena, symmetric_memory_available
+            from ..parallel.fused_ulysses import FusedUlysses
+
+            if symmetric_memory_available():
+                try:
+                    cp_ctx.fused = FusedUlysses(SymmetricArena(mpu.get_context_parallel_group()))
+                except Exception as e:
+                    if a.fused_comm == "on":
+                        raise
+                    print(f"WARNING: fused Ulysses unavailable ({e}); using NCCL all-to-all", flush=True)
         self.buffer = ParamBuffer(inner, shard_world=world if a.use_distributed_optimizer else 1, arena=arena)
         self.optimizer = DistributedOptimizer(
             self.buffer, group if world > 1 else None, lr=a.lr, betas=(a.adam_beta1, a.adam_beta2),

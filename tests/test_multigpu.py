@@ -54,7 +54,7 @@ def test_fused_dp_optimizer_matches_nccl(clip):
         assert all(abs(a - b) < 1e-3 * abs(b) for a, b in zip(got[r][2], ref[r][2]))
 
 
-def _cp_worker(rank, world):
+def _cp_worker(rank, world, fused=False):
     from teletron_b200 import ops
     from teletron_b200.models import WanModel, wan_config
     from teletron_b200.ops import _lib
@@ -63,6 +63,11 @@ def _cp_worker(rank, world):
 
     mpu.initialize_model_parallel(context_parallel_size=world)
     cp = UlyssesContext(mpu.get_context_parallel_group(), world, rank)
+    if fused:
+        from teletron_b200.dist import SymmetricArena
+        from teletron_b200.parallel.fused_ulysses import FusedUlysses
+
+        cp.fused = FusedUlysses(SymmetricArena(mpu.get_context_parallel_group()))
     torch.manual_seed(0)
     cfg = wan_config("wan-tiny", dim=256, num_heads=2, ffn_dim=512, text_dim=64, freq_dim=64, num_layers=2)
     model = WanModel(cfg, cp).cuda().to(torch.bfloat16)
@@ -70,8 +75,10 @@ def _cp_worker(rank, world):
     x = torch.randn(1, 16, 3, 16, 20, generator=g).cuda().bfloat16()   # 3*8*10 = 240 tokens
     ctx = torch.randn(1, 40, 64, generator=g).cuda().bfloat16()
     t = torch.tensor([400.0]).cuda()
-    out = model(x, t, ctx)
-    out.float().square().mean().backward()
+    for _ in range(2 if fused else 1):  # twice: the slab and staging buffers are recycled
+        model.zero_grad(set_to_none=True)
+        out = model(x, t, ctx)
+        out.float().square().mean().backward()
     grads = {n: p.grad.float() for n, p in model.named_parameters() if p.grad is not None}
     for v in grads.values():
         torch.distributed.all_reduce(v)
@@ -96,9 +103,10 @@ def _single_gpu_reference():
 
 
 @needs2
-def test_ulysses_cp2_matches_single_gpu():
+@pytest.mark.parametrize("fused", [False, True])
+def test_ulysses_cp2_matches_single_gpu(fused):
     ref_out, ref_g = _single_gpu_reference()
-    outs = run_distributed(_cp_worker, 2, backend="nccl")
+    outs = run_distributed(_cp_worker, 2, fused, backend="nccl")
     for out, grads in outs:
         assert rel(out, ref_out) < 1e-3          # same threshold as the reference's model test
         bad = [(n, rel(grads[n], ref_g[n])) for n in ref_g if ref_g[n].norm() > 2e-4 and rel(grads[n], ref_g[n]) > 2e-2]
