@@ -106,6 +106,7 @@ def run_ours(a):
     if world > 1:
         argv.append("--use-distributed-optimizer")
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    argv += ["--fused-comm", a.fused_comm]
     if a.recompute:
         argv += ["--recompute-granularity", "full", "--recompute-method", "block", "--recompute-num-layers", "30"]
     if a.layers:
@@ -181,6 +182,9 @@ def run_ours(a):
                        "parallelism": f"dp{dp}" + (f"xcp{cp}" if cp > 1 else ""), "micro_batches_per_step": n_mb,
                        "optimizer": "AdamW fp32 master" + (" (sharded)" if world > 1 else ""),
                        "recompute": "full" if a.recompute else "none",
+                       "comm": ("peer-memory fused kernels" if (getattr(trainer.optimizer, "fused", False) or
+                                getattr(getattr(getattr(trainer.model, "module", trainer.model), "cp", None), "fused", None))
+                                else ("nccl" if world > 1 else "none")),
                        "l2": "inputs and working set far larger than L2 (each step touches > 50 GB)",
                        "baseline_note": "vs_baseline divides by 1.09k tokens/s/GPU read off the reference's H800 chart"},
             "clocks": clocks,
@@ -301,6 +305,8 @@ def main():
     ap.add_argument("--recompute", action="store_true", help="full activation recompute (not needed at 1.3B)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (invalid as a result)")
     ap.add_argument("--ref-no-recompute", action="store_true")
+    ap.add_argument("--fused-comm", type=str, default="auto", choices=["auto", "on", "off"],
+                    help="peer-memory fused collectives (off = NCCL baseline path)")
     a = ap.parse_args()
     if a.impl == "reference":
         sys.exit(run_reference(a) or 0)

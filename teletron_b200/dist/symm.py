@@ -25,8 +25,9 @@ def symmetric_memory_available() -> bool:
     if not torch.cuda.is_available() or not dist.is_initialized():
         return False
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        import importlib
 
+        importlib.import_module("torch.distributed._symmetric_memory")
         return True
     except Exception:
         return False

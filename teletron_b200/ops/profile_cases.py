@@ -1,0 +1,88 @@
+"""Small, self-contained workloads for profiling single kernels (``ncu -k regex:<kernel> -c 1 ...``).
+
+    python -m teletron_b200.ops.profile_cases gemm  [--m 32760 --n 8960 --k 1536 --epi gelu]
+    python -m teletron_b200.ops.profile_cases attn  [--seq 16384 --heads 12] [--bwd]
+    python -m teletron_b200.ops.profile_cases norm  [--rows 32760 --c 1536]
+
+Each case runs one warm-up and then a few timed launches (CUDA events) and prints the achieved
+rate, so the same command serves both as the plain run and as the profiled run.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import _lib
+from .attention import attention_bwd, attention_fwd
+from .gemm import EPI_GELU, EPI_NONE, gemm
+from .norm import adaln
+
+
+def _time(fn, iters=3):
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["gemm", "attn", "norm"])
+    ap.add_argument("--m", type=int, default=32760)
+    ap.add_argument("--n", type=int, default=8960)
+    ap.add_argument("--k", type=int, default=1536)
+    ap.add_argument("--epi", type=str, default="none", choices=["none", "gelu"])
+    ap.add_argument("--a-mn", action="store_true")
+    ap.add_argument("--b-mn", action="store_true")
+    ap.add_argument("--seq", type=int, default=16384)
+    ap.add_argument("--kv", type=int, default=0)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--rows", type=int, default=32760)
+    ap.add_argument("--c", type=int, default=1536)
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args()
+    dev = "cuda"
+    torch.manual_seed(0)
+    res = dict(case=a.case)
+    if a.case == "gemm":
+        A = torch.randn((a.k, a.m) if a.a_mn else (a.m, a.k), device=dev, dtype=torch.bfloat16)
+        B = torch.randn((a.k, a.n) if a.b_mn else (a.n, a.k), device=dev, dtype=torch.bfloat16)
+        bias = torch.randn(a.n, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+        epi = EPI_GELU if a.epi == "gelu" else EPI_NONE
+        ms = _time(lambda: gemm(A, B, a_mn=a.a_mn, b_mn=a.b_mn, bias=bias, epi=epi, out=out), a.iters)
+        res.update(m=a.m, n=a.n, k=a.k, epi=a.epi, ms=ms, tflops=2.0 * a.m * a.n * a.k / ms / 1e9)
+    elif a.case == "attn":
+        kv = a.kv or a.seq
+        q = torch.randn(1, a.seq, a.heads, 128, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(1, kv, a.heads, 128, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(1, kv, a.heads, 128, device=dev, dtype=torch.bfloat16)
+        o, lse = attention_fwd(q, k, v)
+        flops = 4.0 * a.heads * a.seq * kv * 128
+        if a.bwd:
+            do = torch.randn_like(o)
+            ms = _time(lambda: attention_bwd(q, k, v, o, lse, do), a.iters)
+            res.update(seq=a.seq, kv=kv, heads=a.heads, bwd=True, ms=ms, tflops_at_2p5x=2.5 * flops / ms / 1e9,
+                       tflops_executed=3.5 * flops / ms / 1e9)
+        else:
+            ms = _time(lambda: attention_fwd(q, k, v), a.iters)
+            res.update(seq=a.seq, kv=kv, heads=a.heads, bwd=False, ms=ms, tflops=flops / ms / 1e9)
+    else:
+        x = torch.randn(a.rows, a.c, device=dev, dtype=torch.bfloat16)
+        mod = torch.randn(1, 6, a.c, device=dev)
+        ms = _time(lambda: adaln(x, mod[:, 1], mod[:, 0], a.rows), a.iters)
+        res.update(rows=a.rows, c=a.c, ms=ms, gbps=2.0 * a.rows * a.c * 2 / ms / 1e6)
+    _lib.check_status()
+    print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()
