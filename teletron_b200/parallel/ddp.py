@@ -92,6 +92,18 @@ class ParamBuffer:
                 p.main_grad.add_(p.grad.to(p.main_grad.dtype))
                 p.grad = None
 
+    def runs_excluding(self, names) -> List[Tuple[int, int]]:
+        """Contiguous (start, end) element ranges covering every parameter NOT in ``names``."""
+        spans = sorted((o, o + (n + _ALIGN - 1) // _ALIGN * _ALIGN) for k, (o, n, _) in self.index.items()
+                       if k not in names)
+        runs: List[Tuple[int, int]] = []
+        for s, e in spans:
+            if runs and runs[-1][1] == s:
+                runs[-1] = (runs[-1][0], e)
+            else:
+                runs.append((s, e))
+        return runs
+
     def regions(self) -> List[Tuple[int, int, bool]]:
         """(start, end, weight_decay?) of the two regions."""
         out = []
@@ -111,8 +123,14 @@ class DistributedOptimizer:
     """
 
     def __init__(self, buf: ParamBuffer, group=None, *, lr=1e-4, betas=(0.9, 0.999), eps=1e-8,
-                 weight_decay=0.01, clip_grad=0.0, sharded=False, grad_scale=1.0):
+                 weight_decay=0.01, clip_grad=0.0, sharded=False, grad_scale=1.0, tp_group=None,
+                 tp_sharded_names=()):
+        """``tp_group`` / ``tp_sharded_names``: under tensor parallelism the gradients of parameters
+        that are replicated across the TP group (everything not in ``tp_sharded_names``) are partial
+        sums over that group's row shards and are all-reduced over it before the DP x CP reduction."""
         self.buf, self.group = buf, group
+        self.tp_group = tp_group
+        self.tp_runs = buf.runs_excluding(set(tp_sharded_names)) if tp_group is not None else []
         self.world = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.sharded = bool(sharded) and self.world > 1
@@ -142,6 +160,8 @@ class DistributedOptimizer:
         """Sum gradients over the group; afterwards ``_shard_grads`` holds this rank's fp32 slices."""
         self.buf.collect_grads()
         g = self.buf.grads
+        for s_, e_ in self.tp_runs:
+            dist.all_reduce(g[s_:e_], op=dist.ReduceOp.SUM, group=self.tp_group)
         if self.fused:
             self._shard_grads = ["fused"] * len(self.shards)  # reduction happens inside step()
             return

@@ -69,12 +69,30 @@ class ReduceScatterRows(torch.autograd.Function):
         return _ag_rows(g, ctx.group, ctx.world), None, None
 
 
+class GatherRowsKeepLocalGrad(torch.autograd.Function):
+    """all-gather along rows for a result that every rank then uses identically (the model output that
+    feeds a replicated loss): backward keeps this rank's rows of the gradient, no reduction."""
+
+    @staticmethod
+    def forward(ctx, x, group, world, rank):
+        ctx.meta = (rank, x.shape[0])
+        return _ag_rows(x, group, world)
+
+    @staticmethod
+    def backward(ctx, g):
+        rank, n = ctx.meta
+        return g[rank * n:(rank + 1) * n].contiguous(), None, None, None
+
+
 class TPContext:
     def __init__(self, group=None, size: int = 1, rank: int = 0):
         self.group, self.size, self.rank = group, size, rank
 
     def gather_rows(self, x):
         return GatherRows.apply(x, self.group, self.size) if self.size > 1 else x
+
+    def gather_rows_for_output(self, x):
+        return GatherRowsKeepLocalGrad.apply(x, self.group, self.size, self.rank) if self.size > 1 else x
 
     def reduce_scatter_rows(self, x):
         return ReduceScatterRows.apply(x, self.group, self.size) if self.size > 1 else x
@@ -124,13 +142,26 @@ class RowParallelLinear(nn.Module):
 
 
 # ------------------------------------------------------------------------------ checkpoints
-def tp_shard_state_dict(full: Dict[str, torch.Tensor], shard_dims: Dict[str, int], rank: int, world: int):
-    """Slice every tensor named in ``shard_dims`` (name -> dim) for ``rank``; others are copied."""
+def _slice_groups(v, d, groups, rank, world):
+    """Slice dim ``d`` of ``v`` per group: dim d is a concatenation of ``groups`` widths, each sharded."""
+    parts, pos = [], 0
+    for g in groups:
+        n = g // world
+        parts.append(v.narrow(d, pos + rank * n, n))
+        pos += g
+    return torch.cat(parts, dim=d).contiguous()
+
+
+def tp_shard_state_dict(full: Dict[str, torch.Tensor], shard_dims: Dict[str, object], rank: int, world: int):
+    """Slice every tensor named in ``shard_dims`` (name -> dim, or (dim, column groups)) for ``rank``;
+    others are copied."""
     out = {}
     for k, v in full.items():
         d = shard_dims.get(k)
         if d is None or world == 1:
             out[k] = v
+        elif isinstance(d, tuple):
+            out[k] = _slice_groups(v, d[0], d[1], rank, world)
         else:
             n = v.shape[d] // world
             out[k] = v.narrow(d, rank * n, n).contiguous()
@@ -139,9 +170,21 @@ def tp_shard_state_dict(full: Dict[str, torch.Tensor], shard_dims: Dict[str, int
 
 def tp_merge_state_dicts(shards: List[Dict[str, torch.Tensor]], shard_dims: Dict[str, int]):
     out = {}
+    world = len(shards)
     for k in shards[0]:
         d = shard_dims.get(k)
-        out[k] = shards[0][k] if d is None or len(shards) == 1 else torch.cat([s[k] for s in shards], dim=d)
+        if d is None or world == 1:
+            out[k] = shards[0][k]
+        elif isinstance(d, tuple):
+            dim, groups = d
+            pieces, pos = [], 0
+            for g in groups:
+                n = g // world
+                pieces.extend(s[k].narrow(dim, pos, n) for s in shards)
+                pos += n
+            out[k] = torch.cat(pieces, dim=dim)
+        else:
+            out[k] = torch.cat([s[k] for s in shards], dim=d)
     return out
 
 
@@ -149,7 +192,8 @@ def tp_shard_dims(module: nn.Module) -> Dict[str, int]:
     dims = {}
     for name, m in module.named_modules():
         if isinstance(m, (ColumnParallelLinear, RowParallelLinear)):
-            dims[f"{name}.weight"] = m.shard_dim
+            groups = getattr(m, "col_groups", None)
+            dims[f"{name}.weight"] = (m.shard_dim, tuple(groups)) if groups else m.shard_dim
             if isinstance(m, ColumnParallelLinear) and m.bias is not None:
                 dims[f"{name}.bias"] = 0
     return dims

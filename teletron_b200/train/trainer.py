@@ -25,6 +25,7 @@ from ..data import build_data_loader, build_dataset
 from ..models import build_model
 from ..parallel import state as mpu
 from ..parallel.ddp import DistributedOptimizer, ParamBuffer
+from ..parallel.tp import tp_shard_dims
 from . import checkpoint as ckpt
 from .arguments import set_args
 from .schedule import scheduler_from_args
@@ -155,7 +156,9 @@ class Trainer:
         self.optimizer = DistributedOptimizer(
             self.buffer, group if world > 1 else None, lr=a.lr, betas=(a.adam_beta1, a.adam_beta2),
             eps=a.adam_eps, weight_decay=a.weight_decay, clip_grad=a.clip_grad,
-            sharded=a.use_distributed_optimizer, grad_scale=1.0 / max(a.data_parallel_size, 1))
+            sharded=a.use_distributed_optimizer, grad_scale=1.0 / max(a.data_parallel_size, 1),
+            tp_group=mpu.get_tensor_model_parallel_group() if a.tensor_model_parallel_size > 1 else None,
+            tp_sharded_names=tuple(tp_shard_dims(inner)) if a.tensor_model_parallel_size > 1 else ())
         self.opt_param_scheduler = scheduler_from_args(a, self.optimizer) if (a.train_iters or a.train_samples) else None
         if a.load or a.pretrained_checkpoint:
             a.iteration, self.num_floating_point_operations_so_far = ckpt.load_checkpoint(
