@@ -21,7 +21,7 @@ using namespace tt;
 
 namespace {
 
-constexpr int NTHREADS = 192;
+constexpr int NTHREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 elementwise (two per lane quarter)
 constexpr int BIG = 128 * 128 * 2;     // 128 x 128 bf16 tile (two 64-wide halves of 16 KB)
 constexpr int BIG_HALF = 128 * 128;    // 128 rows x 128 B
 constexpr int SMALL = 64 * 128 * 2;    // 64 x 128 bf16 tile (two halves of 8 KB)
@@ -94,7 +94,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 4);
+      mbar_init(&p_full[i], 8);
       mbar_init(&pds_free[i], 1);
     }
     mbar_init(done_bar, 1);
@@ -200,6 +200,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   } else {
     // ------------------------------------------------------------ elementwise warps
     const int q = warp & 3;
+    const int wg = (warp - 2) >> 2;  // 0/1: which half of the 64 query columns (and of the output columns)
     const int r = q * 32 + lane;  // key row in the tile
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const int sw = r & 7;
@@ -215,27 +216,34 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_after();
       uint8_t* prow = smem + A_SM_P + st * 2 * PT + r * 128;
       uint8_t* dsrow = prow + PT;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      {
+        // this warp group's 32 of the 64 query columns
         uint32_t s[32], dp[32];
-        tmem_ld32(tmem_base + lane_addr + st * 64 + c * 32, s);
-        tmem_ld32(tmem_base + lane_addr + 128 + st * 64 + c * 32, dp);
+        tmem_ld32(tmem_base + lane_addr + st * 64 + wg * 32, s);
+        tmem_ld32(tmem_base + lane_addr + 128 + st * 64 + wg * 32, dp);
+        float lv[32], dv_[32];
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          const float4 a = *reinterpret_cast<const float4*>(ls + wg * 32 + e);
+          const float4 d = *reinterpret_cast<const float4*>(dl + wg * 32 + e);
+          lv[e] = a.x; lv[e + 1] = a.y; lv[e + 2] = a.z; lv[e + 3] = a.w;
+          dv_[e] = d.x; dv_[e + 1] = d.y; dv_[e + 2] = d.z; dv_[e + 3] = d.w;
+        }
         tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           float pv[8], dv[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const int col = c * 32 + g * 8 + e;
-            pv[e] = exp2f(fmaf(__uint_as_float(s[g * 8 + e]), p.scale_log2, -ls[col]));
-            dv[e] = pv[e] * (__uint_as_float(dp[g * 8 + e]) - dl[col]);
+            pv[e] = fast_exp2(fmaf(__uint_as_float(s[g * 8 + e]), p.scale_log2, -lv[g * 8 + e]));
+            dv[e] = pv[e] * (__uint_as_float(dp[g * 8 + e]) - dv_[g * 8 + e]);
           }
           uint4 a, d;
           a.x = pack_bf16(pv[0], pv[1]); a.y = pack_bf16(pv[2], pv[3]);
           a.z = pack_bf16(pv[4], pv[5]); a.w = pack_bf16(pv[6], pv[7]);
           d.x = pack_bf16(dv[0], dv[1]); d.y = pack_bf16(dv[2], dv[3]);
           d.z = pack_bf16(dv[4], dv[5]); d.w = pack_bf16(dv[6], dv[7]);
-          const int chunk = c * 4 + g;
+          const int chunk = wg * 4 + g;
           *reinterpret_cast<uint4*>(prow + ((chunk ^ sw) << 4)) = a;
           *reinterpret_cast<uint4*>(dsrow + ((chunk ^ sw) << 4)) = d;
         }
@@ -264,7 +272,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                                                  : p.out0 + (long long)b * p.bs0 + (long long)row * p.ld0 + h * 128;
         const float mul = which == 0 ? 1.f : p.scale;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = wg * 2; c < wg * 2 + 2; ++c) {
           uint32_t o[32];
           tmem_ld32(tmem_base + lane_addr + 256 + which * 128 + c * 32, o);
           tmem_ld_wait();
@@ -335,7 +343,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 4);
+      mbar_init(&p_full[i], 8);
       mbar_init(&ds_free[i], 1);
     }
     mbar_init(done_bar, 1);
@@ -431,6 +439,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else {
     const int q = warp & 3;
+    const int wg = (warp - 2) >> 2;
     const int r = q * 32 + lane;
     const int row = q0 + r;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
@@ -449,26 +458,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       uint8_t* dsrow = smem + B_SM_DS + st * PT + r * 128;
       const int valid = kv_len - i * 64;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      {
         uint32_t s[32], dp[32];
-        tmem_ld32(tmem_base + lane_addr + st * 64 + c * 32, s);
-        tmem_ld32(tmem_base + lane_addr + 128 + st * 64 + c * 32, dp);
+        tmem_ld32(tmem_base + lane_addr + st * 64 + wg * 32, s);
+        tmem_ld32(tmem_base + lane_addr + 128 + st * 64 + wg * 32, dp);
         tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           float dv[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const int col = c * 32 + g * 8 + e;
-            float pe = exp2f(fmaf(__uint_as_float(s[g * 8 + e]), p.scale_log2, -lse2));
+            const int col = wg * 32 + g * 8 + e;
+            float pe = fast_exp2(fmaf(__uint_as_float(s[g * 8 + e]), p.scale_log2, -lse2));
             if (col >= valid) pe = 0.f;
             dv[e] = pe * (__uint_as_float(dp[g * 8 + e]) - del);
           }
           uint4 d;
           d.x = pack_bf16(dv[0], dv[1]); d.y = pack_bf16(dv[2], dv[3]);
           d.z = pack_bf16(dv[4], dv[5]); d.w = pack_bf16(dv[6], dv[7]);
-          const int chunk = c * 4 + g;
+          const int chunk = wg * 4 + g;
           *reinterpret_cast<uint4*>(dsrow + ((chunk ^ sw) << 4)) = d;
         }
       }
@@ -484,7 +492,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       bf16* dst = (p.sc0.mode == 2 && row < p.Sq) ? scatter_dst(p.sc0, b, row, h)
                                                   : p.out0 + (long long)b * p.bs0 + (long long)row * p.ld0 + h * 128;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = wg * 2; c < wg * 2 + 2; ++c) {
         uint32_t o[32];
         tmem_ld32(tmem_base + lane_addr + 256 + c * 32, o);
         tmem_ld_wait();

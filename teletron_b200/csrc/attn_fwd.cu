@@ -224,12 +224,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       const float mx2 = mx * p.scale_log2;
       const bool need = mx2 > m_used + RESCALE_THRESHOLD;
+      const float m_new = need ? mx2 : m_used;
+      const float f = (need && j > 0) ? fast_exp2(m_used - mx2) : 1.f;
+      // probabilities first (bf16, packed in registers): this is the long special-function phase
+      // and it does not depend on the previous P*V, so it overlaps with it on the tensor pipe
+      uint32_t pk[64];
+      float lsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float e0 = fast_exp2(fmaf(__uint_as_float(s[c][i]), p.scale_log2, -m_new));
+          const float e1 = fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), p.scale_log2, -m_new));
+          lsum += e0 + e1;
+          pk[c * 16 + (i >> 1)] = pack_bf16(e0, e1);
+        }
+      }
       if (j > 0) {
+        // P_t's shared buffer and O_t may only be touched once the previous P*V has finished
         if (!mbar_wait(&pv_done[t], (j - 1) & 1, abort_flag, p.status, TT_ST_TIMEOUT_SOFTMAX + 2)) { ok = false; break; }
         __syncwarp();
         tc_fence_after();
         if (__any_sync(0xffffffffu, need)) {
-          const float f = need ? exp2f(m_used - mx2) : 1.f;
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t o[32];
@@ -240,32 +256,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tmem_st32(o_addr + c * 32, o);
           }
           tmem_st_wait();
-          l *= f;
         }
       }
-      if (need) m_used = mx2;
-      // probabilities -> bf16 -> swizzled shared tile (A operand of P*V)
-      float lsum = 0.f;
+      l = l * f + lsum;
+      m_used = m_new;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float e[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            e[i] = exp2f(fmaf(__uint_as_float(s[c][g * 8 + i]), p.scale_log2, -m_used));
-            lsum += e[i];
-          }
-          uint4 pk;
-          pk.x = pack_bf16(e[0], e[1]);
-          pk.y = pack_bf16(e[2], e[3]);
-          pk.z = pack_bf16(e[4], e[5]);
-          pk.w = pack_bf16(e[6], e[7]);
-          const int chunk = c * 4 + g;  // 16-byte chunk index along kv (0..15)
-          *reinterpret_cast<uint4*>(p_row + (chunk >> 3) * HALF_BYTES + (((chunk & 7) ^ sw) << 4)) = pk;
-        }
+      for (int chunk = 0; chunk < 16; ++chunk) {  // 16-byte chunks along kv, 128-byte swizzle
+        uint4 v4 = make_uint4(pk[chunk * 4], pk[chunk * 4 + 1], pk[chunk * 4 + 2], pk[chunk * 4 + 3]);
+        *reinterpret_cast<uint4*>(p_row + (chunk >> 3) * HALF_BYTES + (((chunk & 7) ^ sw) << 4)) = v4;
       }
-      l += lsum;
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();

@@ -2,10 +2,10 @@
 //
 //   C[M,N] = epilogue( alpha * A[M,K] * B[N,K]^T )        fp32 accumulation in tensor memory
 //
-// One CTA per SM walks output tiles of 128 x BN. Roles inside the CTA (192 threads):
+// One CTA per SM walks output tiles of 128 x BN. Roles inside the CTA (320 threads):
 //   warp 0      TMA producer: fills a ring of shared-memory stages (A 128x64, B BNx64)
 //   warp 1      allocates tensor memory and issues tcgen05.mma (one thread)
-//   warps 2..5  epilogue: tcgen05.ld the accumulator, apply bias / GELU / gate+residual /
+//   warps 2..9  epilogue (two warps per tensor-memory lane quarter, half of the columns each): tcgen05.ld the accumulator, apply bias / GELU / gate+residual /
 //               accumulate, store bf16 or fp32
 // Two accumulator buffers in tensor memory let the epilogue of tile i overlap the
 // main loop of tile i+1.
@@ -57,7 +57,7 @@ struct Cfg {
 };
 
 template <int BN, int A_MN, int B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const GemmParams p) {
   using C_ = Cfg<BN>;
@@ -86,7 +86,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 4);
+      mbar_init(&tempty[a], 8);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -176,6 +176,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    const int eg = (warp - 2) >> 2;  // two warps share a quarter and split the tile's columns
     int tcount = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
       const int a = tcount & 1;
@@ -190,7 +191,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (p.epi == EPI_GATE_RES && row_ok)
         gate_row = p.gate + (long long)(row / p.rows_per_gate) * p.gate_ld;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = eg * (BN / 64); c < (eg + 1) * (BN / 64); ++c) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c * 32), r);
         tmem_ld_wait();
@@ -311,7 +312,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, 
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, 192, C_::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  kern<<<grid, 320, C_::SMEM_BYTES, stream>>>(tmA, tmB, p);
   TT_LAUNCH_CHECK();
   return 0;
 }
