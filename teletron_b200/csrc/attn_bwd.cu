@@ -56,11 +56,12 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 // ===================================================================== dK / dV
 constexpr int A_SM_K = 0;
 constexpr int A_SM_V = A_SM_K + BIG;
-constexpr int A_SM_Q = A_SM_V + BIG;            // 2 stages of (Q, dO) 64-row tiles
-constexpr int A_SM_P = A_SM_Q + 2 * 2 * SMALL;  // 2 buffers of (P^T, dS^T)
-constexpr int A_SM_LSE = A_SM_P + 2 * 2 * PT;   // 2 x (64 lse + 64 delta) floats
-constexpr int A_SM_BAR = A_SM_LSE + 2 * 128 * 4;
-constexpr int A_SMEM = A_SM_BAR + 256 + 1024;
+constexpr int A_LST = 3;                        // load stages of (Q, dO, lse, delta): TMA latency stays hidden
+constexpr int A_SM_Q = A_SM_V + BIG;            // A_LST stages of (Q, dO) 64-row tiles
+constexpr int A_SM_P = A_SM_Q + A_LST * 2 * SMALL;  // 2 buffers of (P^T, dS^T)
+constexpr int A_SM_LSE = A_SM_P + 2 * 2 * PT;   // A_LST x (64 lse + 64 delta) floats
+constexpr int A_SM_BAR = A_SM_LSE + A_LST * 128 * 4;
+constexpr int A_SMEM = A_SM_BAR + 128 + 1024;
 
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -71,13 +72,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + A_SM_BAR);
   uint64_t* kv_full = bars;          // 1
-  uint64_t* qdo_full = bars + 1;     // 2
-  uint64_t* qdo_empty = bars + 3;    // 2
-  uint64_t* s_full = bars + 5;       // 2
-  uint64_t* p_full = bars + 7;       // 2
-  uint64_t* pds_free = bars + 9;     // 2
-  uint64_t* done_bar = bars + 11;    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* qdo_full = bars + 1;     // 3
+  uint64_t* qdo_empty = bars + 4;    // 3
+  uint64_t* s_full = bars + 7;       // 2
+  uint64_t* p_full = bars + 9;       // 2
+  uint64_t* pds_free = bars + 11;    // 2
+  uint64_t* done_bar = bars + 13;    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   float* lse_s = reinterpret_cast<float*>(smem + A_SM_LSE);
 
@@ -90,9 +91,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < A_LST; ++i) {
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 8);
       mbar_init(&pds_free[i], 1);
@@ -125,8 +128,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tma_load_3d(smem + A_SM_V + hf * BIG_HALF, &tmV, kv_full, h * 128 + hf * 64, kv0, b);
       }
       for (int i = 0; i < n_it; ++i) {
-        const int st = i & 1;
-        if (!mbar_wait(&qdo_empty[st], ((i >> 1) & 1) ^ 1, abort_flag, p.status, TT_ST_TIMEOUT_PRODUCER)) break;
+        const int st = i % A_LST;
+        if (!mbar_wait(&qdo_empty[st], ((i / A_LST) & 1) ^ 1, abort_flag, p.status, TT_ST_TIMEOUT_PRODUCER)) break;
         mbar_expect_tx(&qdo_full[st], 2 * SMALL + 512);
         uint8_t* dq_ = smem + A_SM_Q + st * 2 * SMALL;
         for (int hf = 0; hf < 2; ++hf) {
@@ -148,10 +151,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const uint32_t p_base = smem_u32(smem + A_SM_P);
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 1);
       auto issue_sdp = [&](int i) -> bool {
-        const int st = i & 1;
-        if (!mbar_wait(&qdo_full[st], (i >> 1) & 1, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 2)) return false;
+        const int st = i & 1, ld = i % A_LST;
+        if (!mbar_wait(&qdo_full[ld], (i / A_LST) & 1, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 2)) return false;
         tc_fence_after();
-        const uint32_t qb = q_base + st * 2 * SMALL;
+        const uint32_t qb = q_base + ld * 2 * SMALL;
         const uint32_t dob = qb + SMALL;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -171,10 +174,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         return true;
       };
       auto issue_dvdk = [&](int i) -> bool {
-        const int st = i & 1;
+        const int st = i & 1, ld = i % A_LST;
         if (!mbar_wait(&p_full[st], (i >> 1) & 1, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 3)) return false;
         tc_fence_after();
-        const uint32_t qb = q_base + st * 2 * SMALL;
+        const uint32_t qb = q_base + ld * 2 * SMALL;
         const uint32_t dob = qb + SMALL;
         const uint32_t pb = p_base + st * 2 * PT;
         const uint32_t dsb = pb + PT;
@@ -187,7 +190,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           umma_ss(tmem_base + 384, umma_desc(dsb + ks * 32, 16, 1024),
                   umma_desc(qb + ks * 2048, SMALL_HALF, 1024), idesc_o, (i > 0 || ks != 0) ? 1u : 0u);
         tc_commit(&pds_free[st]);
-        tc_commit(&qdo_empty[st]);
+        tc_commit(&qdo_empty[ld]);
         return true;
       };
       if (ok) ok = issue_sdp(0);
@@ -206,10 +209,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int sw = r & 7;
     bool ok = true;
     for (int i = 0; i < n_it; ++i) {
-      const int st = i & 1;
-      const float* ls = lse_s + st * 128;
+      const int st = i & 1, ld = i % A_LST;
+      const float* ls = lse_s + ld * 128;
       const float* dl = ls + 64;
-      if (!mbar_wait(&qdo_full[st], (i >> 1) & 1, abort_flag, p.status, TT_ST_TIMEOUT_SOFTMAX + 4)) { ok = false; break; }
+      if (!mbar_wait(&qdo_full[ld], (i / A_LST) & 1, abort_flag, p.status, TT_ST_TIMEOUT_SOFTMAX + 4)) { ok = false; break; }
       if (!mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, p.status, TT_ST_TIMEOUT_SOFTMAX + 1)) { ok = false; break; }
       if (!mbar_wait(&pds_free[st], ((i >> 1) & 1) ^ 1, abort_flag, p.status, TT_ST_TIMEOUT_SOFTMAX + 2)) { ok = false; break; }
       __syncwarp();
@@ -305,8 +308,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 // ===================================================================== dQ
 constexpr int B_SM_Q = 0;
 constexpr int B_SM_DO = B_SM_Q + BIG;
-constexpr int B_SM_KV = B_SM_DO + BIG;             // 2 stages of (K, V) 64-row tiles
-constexpr int B_SM_DS = B_SM_KV + 2 * 2 * SMALL;   // 2 buffers of dS (128 x 64)
+constexpr int B_LST = 4;                           // load stages of (K, V) 64-row tiles
+constexpr int B_SM_KV = B_SM_DO + BIG;
+constexpr int B_SM_DS = B_SM_KV + B_LST * 2 * SMALL;   // 2 buffers of dS (128 x 64)
 constexpr int B_SM_BAR = B_SM_DS + 2 * PT;
 constexpr int B_SMEM = B_SM_BAR + 256 + 1024;
 
@@ -319,13 +323,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + B_SM_BAR);
   uint64_t* q_full = bars;           // 1
-  uint64_t* kv_full = bars + 1;      // 2
-  uint64_t* kv_empty = bars + 3;     // 2
-  uint64_t* s_full = bars + 5;       // 2
-  uint64_t* p_full = bars + 7;       // 2
-  uint64_t* ds_free = bars + 9;      // 2
-  uint64_t* done_bar = bars + 11;    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* kv_full = bars + 1;      // 4
+  uint64_t* kv_empty = bars + 5;     // 4
+  uint64_t* s_full = bars + 9;       // 2
+  uint64_t* p_full = bars + 11;      // 2
+  uint64_t* ds_free = bars + 13;     // 2
+  uint64_t* done_bar = bars + 15;    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -339,9 +343,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < B_LST; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 8);
       mbar_init(&ds_free[i], 1);
@@ -374,8 +380,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_3d(smem + B_SM_DO + hf * BIG_HALF, &tmdO, q_full, h * 128 + hf * 64, q0, b);
       }
       for (int i = 0; i < n_it; ++i) {
-        const int st = i & 1;
-        if (!mbar_wait(&kv_empty[st], ((i >> 1) & 1) ^ 1, abort_flag, p.status, TT_ST_TIMEOUT_PRODUCER)) break;
+        const int st = i % B_LST;
+        if (!mbar_wait(&kv_empty[st], ((i / B_LST) & 1) ^ 1, abort_flag, p.status, TT_ST_TIMEOUT_PRODUCER)) break;
         mbar_expect_tx(&kv_full[st], 2 * SMALL);
         uint8_t* d_ = smem + B_SM_KV + st * 2 * SMALL;
         for (int hf = 0; hf < 2; ++hf) {
@@ -394,10 +400,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t ds_base = smem_u32(smem + B_SM_DS);
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 1);
       auto issue_sdp = [&](int i) -> bool {
-        const int st = i & 1;
-        if (!mbar_wait(&kv_full[st], (i >> 1) & 1, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 2)) return false;
+        const int st = i & 1, ld = i % B_LST;
+        if (!mbar_wait(&kv_full[ld], (i / B_LST) & 1, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 2)) return false;
         tc_fence_after();
-        const uint32_t kb = kv_base + st * 2 * SMALL;
+        const uint32_t kb = kv_base + ld * 2 * SMALL;
         const uint32_t vb = kb + SMALL;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -417,17 +423,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         return true;
       };
       auto issue_dq = [&](int i) -> bool {
-        const int st = i & 1;
+        const int st = i & 1, ld = i % B_LST;
         if (!mbar_wait(&p_full[st], (i >> 1) & 1, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 3)) return false;
         tc_fence_after();
-        const uint32_t kb = kv_base + st * 2 * SMALL;
+        const uint32_t kb = kv_base + ld * 2 * SMALL;
         const uint32_t dsb = ds_base + st * PT;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           umma_ss(tmem_base + 256, umma_desc(dsb + ks * 32, 16, 1024),
                   umma_desc(kb + ks * 2048, SMALL_HALF, 1024), idesc_o, (i > 0 || ks != 0) ? 1u : 0u);
         tc_commit(&ds_free[st]);
-        tc_commit(&kv_empty[st]);
+        tc_commit(&kv_empty[ld]);
         return true;
       };
       if (ok) ok = issue_sdp(0);

@@ -102,7 +102,7 @@ def _barrier():
 def _plain_namespace(args) -> Namespace:
     keep = {}
     for k, v in vars(args).items():
-        if isinstance(v, (int, float, str, bool, type(None), list, tuple, dict)):
+        if isinstance(v, (int, float, str, bool, type(None), list, tuple, dict)) and k != "deferred_rng_state":
             keep[k] = v
     return Namespace(**keep)
 
@@ -147,8 +147,12 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
 
 
 # ----------------------------------------------------------------------------- load
-def load_checkpoint(model, optimizer, opt_param_scheduler, args, strict: bool = True) -> Tuple[int, float]:
-    """Returns (iteration, num_floating_point_operations_so_far); (0, 0) when nothing was loaded."""
+def load_checkpoint(model, optimizer, opt_param_scheduler, args, strict: bool = True,
+                    defer_rng: bool = False) -> Tuple[int, float]:
+    """Returns (iteration, num_floating_point_operations_so_far); (0, 0) when nothing was loaded.
+    With ``defer_rng`` the saved RNG state is left in ``args.deferred_rng_state`` for the caller to
+    apply (``set_rng_state``) once everything that draws random numbers during start-up — data-loader
+    worker seeds, for instance — has been constructed."""
     root = args.load
     finetune = args.finetune
     if (not root or not os.path.exists(tracker_filename(root))) and args.pretrained_checkpoint:
@@ -204,6 +208,9 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, strict: bool = 
         if opt_param_scheduler is not None and not args.no_load_optim and "opt_param_scheduler" in sd:
             opt_param_scheduler.load_state_dict(sd["opt_param_scheduler"])
         if not args.no_load_rng and "rng_state" in sd:
-            set_rng_state(sd["rng_state"], 0)
+            if defer_rng:
+                args.deferred_rng_state = sd["rng_state"]
+            else:
+                set_rng_state(sd["rng_state"], 0)
     _barrier()
     return iteration, flops

@@ -85,6 +85,9 @@ class Trainer:
         self.logger = TrainLogger(args, TrainLogger.make_writer(args))
         if build_data:
             self.build_data_iterators()
+        if getattr(args, "deferred_rng_state", None) is not None:
+            ckpt.set_rng_state(args.deferred_rng_state, 0)   # after everything that consumes start-up randomness
+            args.deferred_rng_state = None
 
     # ------------------------------------------------------------------ distributed
     def _init_distributed(self):
@@ -162,7 +165,7 @@ class Trainer:
         self.opt_param_scheduler = scheduler_from_args(a, self.optimizer) if (a.train_iters or a.train_samples) else None
         if a.load or a.pretrained_checkpoint:
             a.iteration, self.num_floating_point_operations_so_far = ckpt.load_checkpoint(
-                self.model, self.optimizer, self.opt_param_scheduler, a)
+                self.model, self.optimizer, self.opt_param_scheduler, a, defer_rng=True)
         if world > 1 and not (a.load or a.pretrained_checkpoint):
             # identical initial weights on every replica (DDP.broadcast_params in the reference)
             dist.broadcast(self.buffer.params, src=mpu.get_group_ranks("dp_cp")[0], group=group)

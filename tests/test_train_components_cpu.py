@@ -1,0 +1,166 @@
+"""CPU tests of the training stack: flow-matching scheduler vs the reference, LR/WD schedule,
+samplers, arguments, recompute policy (recompute count like the reference's block test),
+checkpoint save / resume in the Megatron layout, and an end-to-end Trainer run with resume."""
+import importlib.util
+import os
+from argparse import Namespace
+
+import pytest
+import torch
+
+from conftest import reference_file
+from teletron_b200.data import PretrainingRandomSampler, PretrainingSampler
+from teletron_b200.models import FlowMatchScheduler
+from teletron_b200.parallel import recompute as rc
+from teletron_b200.train import checkpoint as ckpt
+from teletron_b200.train import make_forward_step, parse_args
+from teletron_b200.train.schedule import OptimizerParamScheduler
+
+
+def test_flow_match_matches_reference():
+    path = reference_file("teletron/models/flow_match.py")
+    if path is None:
+        pytest.skip("reference tree not available")
+    spec = importlib.util.spec_from_file_location("ref_fm", path)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    for kw in (dict(shift=5, sigma_min=0.0, extra_one_step=True), dict(shift=3.0), dict(inverse_timesteps=True)):
+        a, b = FlowMatchScheduler(**kw), ref.FlowMatchScheduler(**kw)
+        a.set_timesteps(1000, training=True)
+        b.set_timesteps(1000, training=True)
+        assert torch.allclose(a.sigmas, b.sigmas) and torch.allclose(a.timesteps, b.timesteps)
+        assert torch.allclose(a.linear_timesteps_weights, b.linear_timesteps_weights)
+        x, n, v = torch.randn(2, 4), torch.randn(2, 4), torch.randn(2, 4)
+        t = a.timesteps[417]
+        assert torch.allclose(a.add_noise(x, n, t), b.add_noise(x, n, t))
+        assert torch.allclose(a.step(v, t, x), b.step(v, t, x))
+        assert torch.allclose(a.training_weight(t), b.training_weight(t))
+        assert torch.equal(a.training_target(x, n, t), b.training_target(x, n, t))
+
+
+def test_lr_wd_schedule():
+    opt = Namespace(param_groups=[dict(lr=0.0, weight_decay=0.0)])
+    s = OptimizerParamScheduler(opt, init_lr=0.0, max_lr=1.0, min_lr=0.1, lr_warmup_steps=10, lr_decay_steps=110,
+                                lr_decay_style="cosine", start_wd=0.0, end_wd=0.2, wd_incr_steps=100,
+                                wd_incr_style="linear")
+    s.step(5)
+    assert abs(opt.param_groups[0]["lr"] - 0.5) < 1e-9 and abs(opt.param_groups[0]["weight_decay"] - 0.01) < 1e-9
+    s.step(55)  # 60: halfway through the cosine
+    assert abs(opt.param_groups[0]["lr"] - 0.55) < 1e-9
+    s.step(1000)
+    assert opt.param_groups[0]["lr"] == 0.1 and opt.param_groups[0]["weight_decay"] == 0.2
+    sd = s.state_dict()
+    s2 = OptimizerParamScheduler(opt, 0.0, 1.0, 0.1, 10, 110, "cosine", 0.0, 0.2, 100, "linear")
+    s2.load_state_dict({"start_lr": sd["max_lr"], "warmup_iter": 10, "end_iter": 110, "decay_style": "cosine",
+                        "num_iters": sd["num_steps"], "min_lr": 0.1})
+    assert s2.num_steps == sd["num_steps"]
+
+
+def test_samplers_resume_and_shard():
+    full = [b for b in PretrainingSampler(20, 0, 2, 1, 2)]
+    assert full[0] == [2, 3] and full[1] == [6, 7] and len(full) == 5
+    resumed = [b for b in PretrainingSampler(20, 8, 2, 1, 2)]
+    assert resumed == full[2:]
+    a = [b for b in PretrainingRandomSampler(32, 0, 2, 0, 2, seed=7)]
+    b = [b for b in PretrainingRandomSampler(32, 0, 2, 1, 2, seed=7)]
+    assert not set(sum(a, [])) & set(sum(b, []))          # data sharding: disjoint buckets
+    again = [x for x in PretrainingRandomSampler(32, 8, 2, 0, 2, seed=7)]
+    assert again == a[2:]                                  # resumable in the middle of an epoch
+
+
+def test_arguments_surface_and_derivations(monkeypatch):
+    monkeypatch.setenv("WORLD_SIZE", "5")
+    monkeypatch.setenv("RANK", "0")
+    argv = ("--num-layers 20 --hidden-size 5120 --num-attention-heads 40 --seq-length 512 --max-position-embeddings 4096 "
+            "--tokenizer-type NullTokenizer --vocab-size 0 --model ParallelWanModel --task-type wan_i2v_prone "
+            "--micro-batch-size 1 --train-iters 10000 --weight-decay 1e-2 --init-method-std 0.006 --clip-grad 0.0 --bf16 "
+            "--lr 1e-5 --lr-decay-style constant --lr-warmup-fraction 0 --recompute-granularity full --recompute-method block "
+            "--activation-offload --use-distributed-optimizer --recompute-num-layers 40 --no-rope-fusion "
+            "--distributed-timeout-minutes 60 --tensor-model-parallel-size 1 --context-parallel-size 2 --distributed-vae "
+            "--distributed-vae-world-size 1 --consumer-models-num 1 --dataset-type FakeDataset --split 949,50,1 "
+            "--dataloader-type single --num-workers 1 --num-frames 9 --tensorboard-queue-size 10 --log-interval 1 "
+            "--save-interval 10000 --eval-interval 10000 --eval-iters 10000").split()
+
+    def extra(p):
+        p.add_argument("--moe-step-factor-list", type=float, action="append")
+        return p
+
+    a = parse_args(extra, argv + ["--moe-step-factor-list", "0.0", "--moe-step-factor-list", "1.0"])
+    assert a.dit_world_size == 4 and a.data_parallel_size == 2 and a.global_batch_size == 2
+    assert a.task_type == "i2v" and a.recompute_method == "block" and a.moe_step_factor_list == [0.0, 1.0]
+    with pytest.raises(ValueError):
+        parse_args(None, ["--context-parallel-size", "3"])
+
+
+class _CountingLinear(torch.nn.Module):
+    calls = 0
+
+    def __init__(self):
+        super().__init__()
+        self.lin = torch.nn.Linear(32, 32)
+
+    def forward(self, x):
+        _CountingLinear.calls += 1
+        return torch.tanh(self.lin(x))
+
+
+@pytest.mark.parametrize("method,k,expect_extra", [("block", 2, 2), ("block", 9, 4), ("uniform", 2, 4), ("uniform", 3, 4)])
+def test_recompute_policy_counts_and_grads(method, k, expect_extra):
+    torch.manual_seed(0)
+    blocks = torch.nn.ModuleList([_CountingLinear() for _ in range(4)])
+    x = torch.randn(3, 32, requires_grad=True)
+    cfg = Namespace(recompute_granularity=None, recompute_method=method, recompute_num_layers=k, activation_offload=False)
+    y0 = rc.run_blocks(blocks, x, (), cfg, True)
+    g0 = torch.autograd.grad(y0.sum(), [x] + list(blocks.parameters()))
+    cfg.recompute_granularity = "full"
+    _CountingLinear.calls = 0
+    y1 = rc.run_blocks(blocks, x, (), cfg, True)
+    assert torch.equal(y0, y1)
+    g1 = torch.autograd.grad(y1.sum(), [x] + list(blocks.parameters()))
+    assert _CountingLinear.calls == 4 + expect_extra      # layers + recomputed layers
+    for a, b in zip(g0, g1):
+        assert torch.allclose(a, b, atol=1e-6)
+    _CountingLinear.calls = 0
+    rc.run_blocks(blocks, x, (), cfg, False)                 # evaluation: no checkpointing
+    assert _CountingLinear.calls == 4
+
+
+def _trainer_args(tmp, extra=""):
+    argv = (f"--model ParallelWanModel --model-preset wan-tiny --train-iters 4 --micro-batch-size 1 --global-batch-size 2 "
+            f"--lr 1e-3 --synthetic-latents --num-frames 5 --video-resolution 64 64 --log-interval 100 --clip-grad 1.0 "
+            f"--save {tmp} --save-interval 2 --seed 11 {extra}").split()
+    a = parse_args(argv=argv)
+    a.text_dim, a.text_len = 64, 16
+    return a
+
+
+def test_trainer_checkpoint_layout_and_exact_resume(tmp_path):
+    from teletron_b200.train import Trainer
+
+    gen = torch.Generator().manual_seed(3)
+    t1 = Trainer(_trainer_args(tmp_path))
+    t1.pretrain(make_forward_step(timestep_generator=gen))
+    ref_params = t1.buffer.params.clone()
+    root = str(tmp_path)
+    assert open(os.path.join(root, "latest_checkpointed_iteration.txt")).read().strip() == "4"
+    f2 = os.path.join(root, "iter_0000002", "mp_rank_00", "model_optim_rng.pt")
+    assert os.path.exists(f2)
+    sd = torch.load(f2, weights_only=False)
+    assert sd["checkpoint_version"] == 3.0 and sd["iteration"] == 2
+    for key in ("args", "model", "optimizer", "opt_param_scheduler", "rng_state", "num_floating_point_operations_so_far"):
+        assert key in sd, key
+    assert "blocks.0.self_attn.q.weight" in sd["model"] and sd["args"].consumed_train_samples == 4
+    # resume from iteration 2 with the same timestep stream -> identical final parameters
+    gen2 = torch.Generator().manual_seed(3)
+    for _ in range(2 * 2):
+        torch.randint(0, 1000, (1,), generator=gen2)       # the draws of the first two iterations
+    a = _trainer_args(tmp_path / "second", f"--load {root} --ckpt-step 2")
+    t2 = Trainer(a)
+    assert a.iteration == 2 and a.consumed_train_samples == 4
+    t2.pretrain(make_forward_step(timestep_generator=gen2))
+    assert torch.allclose(t2.buffer.params, ref_params, atol=1e-6)
+    # corrupted file -> clear error
+    with open(f2, "wb") as fh:
+        fh.write(b"truncated")
+    with pytest.raises(RuntimeError):
+        Trainer(_trainer_args(tmp_path / "third", f"--load {root} --ckpt-step 2"))
