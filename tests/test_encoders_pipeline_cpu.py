@@ -1,0 +1,127 @@
+"""CPU tests: VAE (causality, shapes, tiling), text / image encoders, the wan_encoder bundle, weight
+converter and model-shape detection, and the sampling pipeline end to end on tiny models."""
+from argparse import Namespace
+
+import torch
+
+from teletron_b200.infer import HunyuanVideoPipeline, WanVideoPipeline
+from teletron_b200.models import WanModel, get_encoder, wan_config
+from teletron_b200.models.convert import (convert_wan_state_dict, detect_wan_config, from_diffusers,
+                                          hash_state_dict_keys)
+from teletron_b200.models.encoders import UMT5Encoder, WanImageEncoder, WanVideoVAE, encode_prompt
+from teletron_b200.models.encoders.wan_encoder import HashTokenizer
+from teletron_b200.models.hunyuan import HunyuanVideoModel, hunyuan_config
+
+
+def test_vae_shapes_causality_and_tiling():
+    torch.manual_seed(0)
+    vae = WanVideoVAE(dim=16)
+    v = torch.rand(3, 13, 32, 48) * 2 - 1
+    z = vae.encode([v])
+    assert z.shape == (1, 16, 4, 4, 6)                      # 1 + (13-1)/4 frames, /8 spatially
+    z_prefix = vae.encode([v[:, :5]])
+    assert torch.allclose(z_prefix, z[:, :, :2], atol=1e-5)  # causal in time: a prefix encodes to a prefix
+    rec = vae.decode(z)
+    assert rec.shape == (1, 3, 13, 32, 48) and rec.abs().max() <= 1.0
+    rec_prefix = vae.decode(z[:, :, :2])
+    assert torch.allclose(rec_prefix, rec[:, :, :5], atol=1e-5)
+    zt = vae.encode([v], tiled=True, tile_size=(4, 6), tile_stride=(4, 6))   # one tile covers everything
+    assert torch.allclose(zt, z, atol=1e-5)
+    rt = vae.decode(z, tiled=True, tile_size=(3, 4), tile_stride=(2, 3))
+    assert rt.shape == rec.shape and torch.isfinite(rt).all()
+
+
+def test_text_and_image_encoders():
+    torch.manual_seed(0)
+    t5 = UMT5Encoder(vocab=500, dim=64, dim_attn=64, dim_ffn=128, num_heads=4, num_layers=2)
+    ids = torch.randint(2, 500, (2, 12))
+    mask = torch.ones(2, 12, dtype=torch.long)
+    mask[0, 7:] = 0
+    out = encode_prompt(t5, ids, mask)
+    assert out.shape == (2, 12, 64) and out[0, 7:].abs().max() == 0 and out[1].abs().sum() > 0
+    # padding must not influence valid positions
+    ids2 = ids.clone()
+    ids2[0, 7:] = 3
+    assert torch.allclose(encode_prompt(t5, ids2, mask)[0, :7], out[0, :7], atol=1e-5)
+    # relative position buckets: symmetric offsets land in different halves, far offsets saturate
+    pe = t5.blocks[0].pos_embedding
+    b = pe._bucket(torch.tensor([[-200, -1, 0, 1, 200]]))
+    assert b[0, 2] == 0 and b[0, 0] == 15 and b[0, 4] == 31 and b[0, 1] != b[0, 3]
+    clip = WanImageEncoder(dim=64, layers=3, heads=4)
+    assert clip.encode_image(torch.rand(2, 3, 50, 70) * 2 - 1).shape == (2, 257, 64)
+
+
+def test_wan_encoder_bundle_schema():
+    for task, n in (("t2v", 4), ("i2v", 4)):
+        enc = get_encoder("wan_encoder", device=torch.device("cpu"), small=True, dtype=torch.float32, text_len=16,
+                          args=Namespace(task_type=task, consumer_models_num=2))
+        enc.setup()
+        tensors, hdr = enc.encode(dict(prompts="a red fox runs", images=torch.rand(9, 3, 32, 32) * 2 - 1))
+        assert enc.get_output_schema() == ["context", "clip_feature", "image_emb_y", "latents", "noise"]
+        ctx, clip, y, lat, noise = tensors
+        assert ctx.shape == (1, 16, 64) and lat.shape == (1, 16, 3, 4, 4) and noise.shape == lat.shape
+        if task == "i2v":
+            assert clip.shape == (1, 257, 64) and y.shape == (1, 20, 3, 4, 4)
+            assert y[0, :4, 0].min() == 1 and y[0, :4, 1:].max() == 0
+        else:
+            assert clip.numel() == 0 and y.numel() == 0
+
+
+def _to_diffusers_names(sd):
+    inv = {}
+    for k, v in sd.items():
+        n = k
+        n = n.replace(".self_attn.q.", ".attn1.to_q.").replace(".self_attn.k.", ".attn1.to_k.")
+        n = n.replace(".self_attn.v.", ".attn1.to_v.").replace(".self_attn.o.", ".attn1.to_out.0.")
+        n = n.replace(".self_attn.norm_", ".attn1.norm_")
+        n = n.replace(".cross_attn.q.", ".attn2.to_q.").replace(".cross_attn.k.", ".attn2.to_k.")
+        n = n.replace(".cross_attn.v.", ".attn2.to_v.").replace(".cross_attn.o.", ".attn2.to_out.0.")
+        n = n.replace(".cross_attn.norm_", ".attn2.norm_")
+        n = n.replace(".ffn.0.", ".ffn.net.0.proj.").replace(".ffn.2.", ".ffn.net.2.")
+        n = n.replace(".norm3.", ".norm2.")
+        if n.endswith(".modulation") and n.startswith("blocks."):
+            n = n.replace(".modulation", ".scale_shift_table")
+        n = n.replace("text_embedding.0.", "condition_embedder.text_embedder.linear_1.")
+        n = n.replace("text_embedding.2.", "condition_embedder.text_embedder.linear_2.")
+        n = n.replace("time_embedding.0.", "condition_embedder.time_embedder.linear_1.")
+        n = n.replace("time_embedding.2.", "condition_embedder.time_embedder.linear_2.")
+        n = n.replace("time_projection.1.", "condition_embedder.time_proj.")
+        n = "scale_shift_table" if n == "head.modulation" else n
+        n = n.replace("head.head.", "proj_out.")
+        inv[n] = v
+    return inv
+
+
+def test_converter_round_trip_and_detection():
+    m = WanModel(wan_config("wan-tiny", dim=256, num_heads=2))
+    sd = m.state_dict()
+    diff = _to_diffusers_names(sd)
+    assert "blocks.0.attn1.to_q.weight" in diff and "condition_embedder.time_proj.bias" in diff
+    back, cfg = convert_wan_state_dict(diff)
+    assert set(back) == set(sd) and all(torch.equal(back[k], sd[k]) for k in sd)
+    assert (cfg.dim, cfg.num_heads, cfg.num_layers, cfg.ffn_dim, cfg.in_dim, cfg.has_image_input) == (256, 2, 2, 512, 16, False)
+    pref, cfg2 = convert_wan_state_dict({"model.diffusion_model." + k: v for k, v in sd.items()})
+    assert set(pref) == set(sd) and cfg2.dim == 256
+    assert hash_state_dict_keys(sd) == hash_state_dict_keys(dict(reversed(list(sd.items()))))
+    m2 = WanModel(detect_wan_config(sd))
+    m2.load_state_dict(back)
+
+
+def test_pipelines_run_end_to_end():
+    torch.manual_seed(0)
+    dit = WanModel(wan_config("wan-tiny", in_dim=36, has_image_input=True, text_dim=64)).eval()
+    t5 = UMT5Encoder(vocab=512, dim=64, dim_attn=64, dim_ffn=128, num_heads=4, num_layers=1)
+    pipe = WanVideoPipeline.from_modules(dit, WanVideoVAE(dim=16), t5, WanImageEncoder(dim=1280, layers=1, heads=16),
+                                         HashTokenizer(512, 512), device="cpu", torch_dtype=torch.float32)
+    frames = pipe("a cat", negative_prompt="blurry", input_image=torch.rand(3, 64, 64) * 2 - 1, height=70, width=64,
+                  num_frames=10, num_inference_steps=2, seed=0, tiled=False, output_type="tensor")
+    assert frames.shape == (3, 13, 64, 64)                  # frames rounded to 4k+1, H to a multiple of 16
+    again = pipe("a cat", negative_prompt="blurry", input_image=torch.rand(3, 64, 64) * 2 - 1, height=70, width=64,
+                 num_frames=10, num_inference_steps=2, seed=0, tiled=False, output_type="latent")
+    assert again.shape == (1, 16, 4, 8, 8)
+    hy = HunyuanVideoModel(hunyuan_config("hunyuan-tiny", hidden_size=64, num_attention_heads=4,
+                                          attention_head_dim=16, rope_axes_dim=(4, 6, 6))).eval()
+    hp = HunyuanVideoPipeline(hy, None, device="cpu", torch_dtype=torch.float32)
+    lat = hp(torch.randn(1, 8, 64), torch.ones(1, 8, dtype=torch.long), torch.randn(1, 32), height=32, width=32,
+             num_frames=5, num_inference_steps=2, seed=1)
+    assert lat.shape == (1, 16, 2, 4, 4) and torch.isfinite(lat).all()
