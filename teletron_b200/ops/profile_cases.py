@@ -3,6 +3,7 @@
     python -m teletron_b200.ops.profile_cases gemm  [--m 32760 --n 8960 --k 1536 --epi gelu]
     python -m teletron_b200.ops.profile_cases attn  [--seq 16384 --heads 12] [--bwd]
     python -m teletron_b200.ops.profile_cases norm  [--rows 32760 --c 1536]
+    python -m teletron_b200.ops.profile_cases layers [--layers 2]     Wan2.1-1.3B blocks, one 480P x 81 sample, fwd + bwd
 
 Each case runs one warm-up and then a few timed launches (CUDA events) and prints the achieved
 rate, so the same command serves both as the plain run and as the profiled run.
@@ -34,7 +35,8 @@ def _time(fn, iters=3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "attn", "norm"])
+    ap.add_argument("case", choices=["gemm", "attn", "norm", "layers"])
+    ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--m", type=int, default=32760)
     ap.add_argument("--n", type=int, default=8960)
     ap.add_argument("--k", type=int, default=1536)
@@ -75,6 +77,24 @@ def main():
         else:
             ms = _time(lambda: attention_fwd(q, k, v), a.iters)
             res.update(seq=a.seq, kv=kv, heads=a.heads, bwd=False, ms=ms, tflops=flops / ms / 1e9)
+    elif a.case == "layers":
+        from ..models import WanModel, wan_config
+        from ..parallel.ddp import ParamBuffer
+        from .flow import flow_mse
+
+        model = WanModel(wan_config("wan2.1-1.3b-t2v", num_layers=a.layers)).to(dev).to(torch.bfloat16).train()
+        buf = ParamBuffer(model)
+        x0 = torch.randn(1, 16, 21, 60, 104, device=dev, dtype=torch.bfloat16)
+        nz = torch.randn_like(x0)
+        ctx = torch.randn(1, 512, 4096, device=dev, dtype=torch.bfloat16)
+        t = torch.tensor([500.0], device=dev)
+
+        def step():
+            buf.zero_grads()
+            flow_mse(model(0.5 * x0 + 0.5 * nz, t, ctx), x0, nz).backward()
+
+        ms = _time(step, a.iters)
+        res.update(layers=a.layers, ms=ms, launches_per_step=None)
     else:
         x = torch.randn(a.rows, a.c, device=dev, dtype=torch.bfloat16)
         mod = torch.randn(1, 6, a.c, device=dev)
