@@ -222,8 +222,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       {
         // this warp group's 32 of the 64 query columns
         uint32_t s[32], dp[32];
+#ifdef TT_EXP_SKIP_TMEMLD
+#pragma unroll
+        for (int e = 0; e < 32; ++e) { s[e] = 0u; dp[e] = 0u; }
+#else
         tmem_ld32(tmem_base + lane_addr + st * 64 + wg * 32, s);
         tmem_ld32(tmem_base + lane_addr + 128 + st * 64 + wg * 32, dp);
+#endif
         float lv[32], dv_[32];
 #pragma unroll
         for (int e = 0; e < 32; e += 4) {
@@ -238,8 +243,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           float pv[8], dv[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
+#ifdef TT_EXP_SKIP_MATH
+            pv[e] = __uint_as_float(s[g * 8 + e]);
+            dv[e] = __uint_as_float(dp[g * 8 + e]);
+#else
             pv[e] = fast_exp2(fmaf(__uint_as_float(s[g * 8 + e]), p.scale_log2, -lv[g * 8 + e]));
             dv[e] = pv[e] * (__uint_as_float(dp[g * 8 + e]) - dv_[g * 8 + e]);
+#endif
           }
           uint4 a, d;
           a.x = pack_bf16(pv[0], pv[1]); a.y = pack_bf16(pv[2], pv[3]);
@@ -251,7 +261,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           *reinterpret_cast<uint4*>(dsrow + ((chunk ^ sw) << 4)) = d;
         }
       }
+#ifndef TT_EXP_SKIP_FENCE
       fence_proxy_async_smem();
+#endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[st]);
