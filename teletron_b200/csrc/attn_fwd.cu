@@ -126,20 +126,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t q_base = smem_u32(smem + SM_Q);
       const uint32_t kv_base = smem_u32(smem + SM_KV);
       const uint32_t p_base = smem_u32(smem + SM_P);
+      // descriptors as (low word + constant): one integer add per operand and MMA
+      constexpr uint32_t HI = umma_desc_hi(1024);
       auto issue_s = [&](int t, uint32_t k_addr) {
+        const uint32_t a_lo = umma_desc_lo(q_base + t * TILE_BYTES, 16);
+        const uint32_t b_lo = umma_desc_lo(k_addr, 16);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_ss(tmem_base + t * 128, umma_desc(q_base + t * TILE_BYTES + off, 16, 1024),
-                  umma_desc(k_addr + off, 16, 1024), idesc_qk, ks != 0);
+          const uint32_t off = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
+          umma_ss_lo<HI, HI>(tmem_base + t * 128, a_lo + off, b_lo + off, idesc_qk, ks != 0);
         }
       };
       auto issue_pv = [&](int t, uint32_t v_addr, bool acc) {
+        const uint32_t a_lo = umma_desc_lo(p_base + t * TILE_BYTES, 16);
+        const uint32_t b_lo = umma_desc_lo(v_addr, HALF_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_ss(tmem_base + 256 + t * 128, umma_desc(p_base + t * TILE_BYTES + off, 16, 1024),
-                  umma_desc(v_addr + ks * 2048, HALF_BYTES, 1024), idesc_pv, (acc || ks != 0) ? 1u : 0u);
+          const uint32_t off = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
+          umma_ss_lo<HI, HI>(tmem_base + 256 + t * 128, a_lo + off, b_lo + ks * (2048 >> 4), idesc_pv,
+                             (acc || ks != 0) ? 1u : 0u);
         }
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 1);

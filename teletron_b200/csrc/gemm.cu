@@ -158,16 +158,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             break;
           }
           tc_fence_after();
+          // descriptors as (low word + constant): one integer add per operand and MMA
           const uint32_t a_base = smem_u32(smem + s * C_::STAGE_BYTES);
-          const uint32_t b_base = a_base + A_BYTES;
+          const uint32_t a_lo = umma_desc_lo(a_base, A_MN ? 8192 : 16);
+          const uint32_t b_lo = umma_desc_lo(a_base + A_BYTES, B_MN ? 8192 : 16);
+          constexpr uint32_t HI = umma_desc_hi(1024);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t adesc = A_MN ? umma_desc(a_base + k * 2048, 8192, 1024)
-                                        : umma_desc(a_base + k * 32, 16, 1024);
-            const uint64_t bdesc = B_MN ? umma_desc(b_base + k * 2048, 8192, 1024)
-                                        : umma_desc(b_base + k * 32, 16, 1024);
-            umma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / 16; ++k)
+            umma_ss_lo<HI, HI>(d_tmem, a_lo + k * ((A_MN ? 2048 : 32) >> 4), b_lo + k * ((B_MN ? 2048 : 32) >> 4), idesc,
+                               (kb | k) != 0 ? 1u : 0u);
           tc_commit(&empty[s]);
         }
         if (ok) tc_commit(&tfull[a]);

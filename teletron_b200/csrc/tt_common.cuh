@@ -66,6 +66,7 @@ enum : unsigned {
   TT_ST_TIMEOUT_EPILOGUE = 0x300,
   TT_ST_TIMEOUT_SOFTMAX = 0x400,
   TT_ST_TIMEOUT_PEER = 0x500,
+  TT_ST_BAD_SMEM_ALIGN = 0x600,  // dynamic shared memory did not start on a 1024-byte boundary
 };
 
 // Ulysses all-to-all as a store pattern: where an element of a local tensor lands in peer memory.
@@ -153,6 +154,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     }
   }
   return true;
+}
+
+// The same wait for a whole (converged) warp: lane 0 polls and the outcome is broadcast.  Thirty-two lanes
+// polling one mbarrier are served one after the other (about 200 clocks per wait even when the phase has
+// already completed); the shuffle also orders the other lanes' later reads behind lane 0's acquire.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity,
+                                               volatile uint32_t* abort_flag, unsigned* status,
+                                               unsigned code) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status, code) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ---------------------------------------------------------------- TMA
@@ -251,6 +263,42 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_b
   d |= (uint64_t)2 << 61;  // 128-byte swizzle
   return d;
 }
+// The same descriptor as two 32-bit words.  The high word (stride between 8-row groups, version,
+// swizzle mode) is the same for every k-step of an operand and the low word moves by (bytes >> 4),
+// so an MMA loop costs one integer add per operand instead of rebuilding 64-bit descriptors: the single
+// issuing thread runs a dependent instruction chain, and rebuilding them was measured to cap the issue
+// rate at one tcgen05.mma per 70-100 clocks.
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__host__ __device__ constexpr uint32_t umma_desc_hi(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+// D[tmem] (+)= A[smem] * B[smem]; descriptors given as (low word, shared high word)
+template <uint32_t HI_A, uint32_t HI_B>
+__device__ __forceinline__ void umma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 ad, bd;\n\t"
+      "mov.b64 ad, {%1, %5};\n\t"
+      "mov.b64 bd, {%2, %6};\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "n"(HI_A), "n"(HI_B)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+template <uint32_t HI_B>
+__device__ __forceinline__ void umma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\t"
+      "mov.b64 bd, {%2, %5};\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "n"(HI_B)
+      : "memory");
+}
 // Instruction descriptor: bf16 x bf16 -> fp32, shape M x N (K = 16 per instruction).
 __host__ __device__ constexpr uint32_t umma_idesc(int M, int N, int a_mn_major, int b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) |
@@ -282,6 +330,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
       "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
       "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+// 32 lanes x 16 columns (e.g. 32 packed bf16 per row: an A operand slice for tcgen05.mma)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() {
