@@ -2,13 +2,17 @@
 //
 // One CTA owns 256 query rows of one (batch, head) as two 128-row tiles t = 0,1 and walks
 // the keys in tiles of 128.  Roles (320 threads):
-//   warp 0       TMA producer: Q once, then K_0, V_0, K_1, V_1, ... through a 3-slot ring
+//   warp 0       TMA producer: Q once, then K_0, V_0, K_1, V_1, ... through a 5-slot ring
 //   warp 1       tcgen05.mma issuer: S_t = Q_t K_j^T into tensor memory, O_t += P_t V_j
 //   warps 2..5   softmax group for tile 0, warps 6..9 for tile 1; thread <-> query row
 // Tensor memory: S_0, S_1, O_0, O_1, 128 fp32 columns each (all 512 columns).
+// The bf16 probabilities P_t are written over the first 64 columns of S_t and read from there as the
+// A operand of P*V: with P in shared memory the kernel was bound by shared-memory bandwidth (operand
+// reads of 32 MMAs, 64 KB of bank-conflicted P stores and the TMA writes added up to the measured
+// 4,700 clocks per key tile).  S_t(j+1) therefore follows P_t V_j on the tensor pipe, and the two tiles
+// alternate: while one is in its softmax, the other's two products run.
 // The softmax keeps a running maximum that is only raised when the tile maximum exceeds it
-// by more than 8 (in log2 units), so O in tensor memory is rescaled rarely; probabilities
-// are written as bf16 into a 128-byte-swizzled shared tile that is the A operand of P*V.
+// by more than 8 (in log2 units), so O in tensor memory is rescaled rarely.
 // V is consumed as an MN-major B operand straight from its [token, d] layout.
 // Keys past kv_len (ragged last tile, or a per-batch key length for padded text) are
 // masked to -inf.  Every barrier wait is bounded (see tt_common.cuh).
@@ -24,11 +28,10 @@ namespace {
 constexpr int TILE = 128;
 constexpr int HALF_BYTES = 128 * 128;      // 128 rows x 64 bf16
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 128 x 128 bf16
-constexpr int KV_SLOTS = 3;
+constexpr int KV_SLOTS = 5;
 constexpr int SM_Q = 0;
 constexpr int SM_KV = SM_Q + 2 * TILE_BYTES;
-constexpr int SM_P = SM_KV + KV_SLOTS * TILE_BYTES;
-constexpr int SM_BAR = SM_P + 2 * TILE_BYTES;
+constexpr int SM_BAR = SM_KV + KV_SLOTS * TILE_BYTES;
 constexpr int SMEM_BYTES = SM_BAR + 256 + 1024;
 constexpr int NTHREADS = 320;
 constexpr float RESCALE_THRESHOLD = 8.0f;
@@ -51,14 +54,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM_BAR);
-  uint64_t* q_full = bars;             // 1
-  uint64_t* kv_full = bars + 1;        // 3
-  uint64_t* kv_empty = bars + 4;       // 3
-  uint64_t* s_full = bars + 7;         // 2
-  uint64_t* s_free = bars + 9;         // 2
-  uint64_t* p_full = bars + 11;        // 2
-  uint64_t* pv_done = bars + 13;       // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* q_full = bars;                        // 1
+  uint64_t* kv_full = bars + 1;                   // KV_SLOTS
+  uint64_t* kv_empty = kv_full + KV_SLOTS;        // KV_SLOTS
+  uint64_t* s_full = kv_empty + KV_SLOTS;         // 2
+  uint64_t* p_full = s_full + 2;                  // 2 (4 arrivals)
+  uint64_t* pv_done = p_full + 2;                 // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -78,7 +80,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1);
-      mbar_init(&s_free[t], 4);
       mbar_init(&p_full[t], 4);
       mbar_init(&pv_done[t], 1);
     }
@@ -123,11 +124,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(128, 128, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc(128, 128, 0, 1);
+      constexpr uint32_t HI = umma_desc_hi(1024);
       const uint32_t q_base = smem_u32(smem + SM_Q);
       const uint32_t kv_base = smem_u32(smem + SM_KV);
-      const uint32_t p_base = smem_u32(smem + SM_P);
       // descriptors as (low word + constant): one integer add per operand and MMA
-      constexpr uint32_t HI = umma_desc_hi(1024);
       auto issue_s = [&](int t, uint32_t k_addr) {
         const uint32_t a_lo = umma_desc_lo(q_base + t * TILE_BYTES, 16);
         const uint32_t b_lo = umma_desc_lo(k_addr, 16);
@@ -136,55 +136,51 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const uint32_t off = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
           umma_ss_lo<HI, HI>(tmem_base + t * 128, a_lo + off, b_lo + off, idesc_qk, ks != 0);
         }
+        tc_commit(&s_full[t]);
       };
-      auto issue_pv = [&](int t, uint32_t v_addr, bool acc) {
-        const uint32_t a_lo = umma_desc_lo(p_base + t * TILE_BYTES, 16);
+      // O_t += P_t V: P_t is the packed bf16 copy in the first 64 columns of S_t (8 columns per k-step)
+      auto issue_pv = [&](int t, uint32_t v_addr, uint32_t acc) {
         const uint32_t b_lo = umma_desc_lo(v_addr, HALF_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
-          umma_ss_lo<HI, HI>(tmem_base + 256 + t * 128, a_lo + off, b_lo + ks * (2048 >> 4), idesc_pv,
-                             (acc || ks != 0) ? 1u : 0u);
-        }
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts_lo<HI>(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8, b_lo + ks * (2048 >> 4), idesc_pv,
+                         ks != 0 ? 1u : acc);
+        tc_commit(&pv_done[t]);
       };
+      // ring position (slot, phase) of the next tile to consume: K_0, V_0, K_1, V_1, ...
+      uint32_t slot = 0, ph = 0;
+      auto next_slot = [&]() { if (++slot == KV_SLOTS) { slot = 0; ph ^= 1; } };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 1);
       if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 2);
       if (ok) {
         tc_fence_after();
         issue_s(0, kv_base);
-        tc_commit(&s_full[0]);
         issue_s(1, kv_base);
-        tc_commit(&s_full[1]);
         tc_commit(&kv_empty[0]);
+        next_slot();
       }
+      uint32_t eph = 0;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const uint32_t jph = j & 1;
-        if (j + 1 < n_tiles) {
-          const int i = 2 * (j + 1);
-          const int slot = i % KV_SLOTS;
-          if (!mbar_wait(&kv_full[slot], (i / KV_SLOTS) & 1, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 3)) { ok = false; break; }
-          for (int t = 0; t < 2 && ok; ++t) {
-            if (!mbar_wait(&s_free[t], jph, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 4)) { ok = false; break; }
-            tc_fence_after();
-            issue_s(t, kv_base + slot * TILE_BYTES);
-            tc_commit(&s_full[t]);
-          }
-          if (!ok) break;
-          tc_commit(&kv_empty[slot]);
+        const bool more = j + 1 < n_tiles;
+        // V_j and K_{j+1} were requested slots ago; waiting for them first keeps the waits on the softmax
+        // groups the only ones between groups of MMAs
+        const uint32_t v_slot = slot, v_ph = ph;
+        next_slot();
+        const uint32_t k_slot = slot, k_ph = ph;
+        if (more) next_slot();
+        if (!mbar_wait(&kv_full[v_slot], v_ph, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 5)) { ok = false; break; }
+        if (more && !mbar_wait(&kv_full[k_slot], k_ph, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 3)) { ok = false; break; }
+        const uint32_t acc = j > 0 ? 1u : 0u;
+        for (int t = 0; t < 2; ++t) {
+          if (!mbar_wait(&p_full[t], eph, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 6)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(t, kv_base + v_slot * TILE_BYTES, acc);
+          if (more) issue_s(t, kv_base + k_slot * TILE_BYTES);
         }
-        {
-          const int i = 2 * j + 1;
-          const int slot = i % KV_SLOTS;
-          if (!mbar_wait(&kv_full[slot], (i / KV_SLOTS) & 1, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 5)) { ok = false; break; }
-          for (int t = 0; t < 2 && ok; ++t) {
-            if (!mbar_wait(&p_full[t], jph, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 6)) { ok = false; break; }
-            tc_fence_after();
-            issue_pv(t, kv_base + slot * TILE_BYTES, j > 0);
-            tc_commit(&pv_done[t]);
-          }
-          if (!ok) break;
-          tc_commit(&kv_empty[slot]);
-        }
+        if (!ok) break;
+        tc_commit(&kv_empty[v_slot]);
+        if (more) tc_commit(&kv_empty[k_slot]);
+        eph ^= 1;
       }
     }
   } else {
@@ -195,8 +191,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_addr + t * 128;
     const uint32_t o_addr = tmem_base + lane_addr + 256 + t * 128;
-    uint8_t* p_row = smem + SM_P + t * TILE_BYTES + r * 128;
-    const int sw = r & 7;
     float m_used = -1.0e30f, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
@@ -208,25 +202,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, s[c]);
       tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[t]);
       const int valid = kv_len - j * TILE;  // >= 1
-      float mx = -1.0e30f;
-      if (valid >= TILE) {
+      if (valid < TILE) {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < 32; ++i)
             if (c * 32 + i >= valid) s[c][i] = __float_as_uint(-1.0e30f);
-            mx = fmaxf(mx, __uint_as_float(s[c][i]));
-          }
       }
+      // row maximum as eight independent chains (one dependent chain of 128 costs about 500 clocks)
+      float mxa[8];
+#pragma unroll
+      for (int a = 0; a < 8; ++a) mxa[a] = __uint_as_float(s[a >> 1][(a & 1) * 16]);
+#pragma unroll
+      for (int i = 1; i < 16; ++i)
+#pragma unroll
+        for (int a = 0; a < 8; ++a) mxa[a] = fmaxf(mxa[a], __uint_as_float(s[a >> 1][(a & 1) * 16 + i]));
+      const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
+                             fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
       const float mx2 = mx * p.scale_log2;
       const bool need = mx2 > m_used + RESCALE_THRESHOLD;
       const float m_new = need ? mx2 : m_used;
@@ -234,43 +227,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // probabilities first (bf16, packed in registers): this is the long special-function phase
       // and it does not depend on the previous P*V, so it overlaps with it on the tensor pipe
       uint32_t pk[64];
-      float lsum = 0.f;
+      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const float e0 = fast_exp2(fmaf(__uint_as_float(s[c][i]), p.scale_log2, -m_new));
           const float e1 = fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), p.scale_log2, -m_new));
-          lsum += e0 + e1;
+          ls4[(i >> 1) & 3] += e0 + e1;
           pk[c * 16 + (i >> 1)] = pack_bf16(e0, e1);
         }
       }
-      if (j > 0) {
-        // P_t's shared buffer and O_t may only be touched once the previous P*V has finished
-        if (!mbar_wait(&pv_done[t], (j - 1) & 1, abort_flag, p.status, TT_ST_TIMEOUT_SOFTMAX + 2)) { ok = false; break; }
-        __syncwarp();
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, need)) {
+      const float lsum = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+      // S_t(j) was issued behind P_t V_{j-1}, so O_t is quiescent here and may be rescaled in place
+      if (j > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld32(o_addr + c * 32, o);
-            tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tmem_st32(o_addr + c * 32, o);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tmem_st32(o_addr + c * 32, o);
         }
       }
       l = l * f + lsum;
       m_used = m_new;
-#pragma unroll
-      for (int chunk = 0; chunk < 16; ++chunk) {  // 16-byte chunks along kv, 128-byte swizzle
-        uint4 v4 = make_uint4(pk[chunk * 4], pk[chunk * 4 + 1], pk[chunk * 4 + 2], pk[chunk * 4 + 3]);
-        *reinterpret_cast<uint4*>(p_row + (chunk >> 3) * HALF_BYTES + (((chunk & 7) ^ sw) << 4)) = v4;
+      // P_t over the first 64 columns of S_t: two bf16 per column, key order
+      {
+        uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[0]);
+        uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[32]);
+        tmem_st32(s_addr, lo);
+        tmem_st32(s_addr + 32, hi);
       }
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t]);
