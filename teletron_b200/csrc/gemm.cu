@@ -27,6 +27,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;
+constexpr int TP_MAX = 8;  // ranks of a tensor-parallel group
 
 enum Epi : int { EPI_NONE = 0, EPI_GELU = 1, EPI_GATE_RES = 2, EPI_ACCUM = 3, EPI_SILU = 4 };
 
@@ -45,7 +46,36 @@ struct GemmParams {
   bf16* aux_out;  // optional pre-activation copy (same ld as C)
   float alpha;
   unsigned* status;
+  // tensor-parallel variants: the M dimension is `world` segments of `seg_rows` rows (one per rank) and
+  // output tiles never straddle a segment.
+  //   tp_mode 1 (all-gather -> GEMM): segment s of A is read from rank s's buffer through its own tensor map
+  //   tp_mode 2 (GEMM -> reduce-scatter): the rows of segment s are stored into rank s's staging buffer
+  //             [world, seg_rows, ldc] at slot `rank`; tt_tp_reduce_rows then sums the slots
+  int tp_mode, seg_rows, world, rank;
+  bf16* peer_c[TP_MAX];
 };
+
+struct TmapSet {
+  CUtensorMap m[TP_MAX];
+};
+
+// first global row, owning segment, first row inside the segment and number of live rows of m-tile `tm`
+struct MTile {
+  int row0, seg, seg_row0, valid;
+};
+__device__ __forceinline__ MTile m_tile(const GemmParams& p, int tm) {
+  MTile t;
+  if (p.seg_rows == 0) {
+    t.row0 = tm * BM; t.seg = 0; t.seg_row0 = t.row0; t.valid = min(BM, p.M - t.row0);
+  } else {
+    const int tps = (p.seg_rows + BM - 1) / BM;
+    t.seg = tm / tps;
+    t.seg_row0 = (tm - t.seg * tps) * BM;
+    t.row0 = t.seg * p.seg_rows + t.seg_row0;
+    t.valid = min(BM, p.seg_rows - t.seg_row0);
+  }
+  return t;
+}
 
 template <int BN>
 struct Cfg {
@@ -56,10 +86,10 @@ struct Cfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
 };
 
-template <int BN, int A_MN, int B_MN>
+template <int BN, int A_MN, int B_MN, int TP>
 __global__ void __launch_bounds__(320, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const GemmParams p) {
+            const __grid_constant__ TmapSet tmAp, const GemmParams p) {
   using C_ = Cfg<BN>;
   constexpr int STAGES = C_::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -74,7 +104,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_m = p.seg_rows ? p.world * ((p.seg_rows + BM - 1) / BM) : (p.M + BM - 1) / BM;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
@@ -92,7 +122,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     mbar_fence_init();
   }
   if (warp == 0 && lane == 0) {
-    tma_prefetch_desc(&tmA);
+    if (TP == 1) {
+      for (int i = 0; i < p.world; ++i) tma_prefetch_desc(&tmAp.m[i]);
+    } else {
+      tma_prefetch_desc(&tmA);
+    }
     tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {
@@ -110,7 +144,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / tiles_n) * BM;
+        const MTile mt = m_tile(p, tile / tiles_n);
+        // all-gather variant: this tile's rows live in rank `seg`'s buffer (a plain TMA load from peer memory)
+        const CUtensorMap* mapA = (TP == 1) ? &tmAp.m[mt.seg] : &tmA;
+        const int m0 = (TP == 1) ? mt.seg_row0 : mt.row0;
         const int n0 = (tile % tiles_n) * BN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
@@ -125,9 +162,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int k0 = kb * BK;
           if (A_MN) {
 #pragma unroll
-            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, &tmA, &full[s], m0 + i * 64, k0);
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, mapA, &full[s], m0 + i * 64, k0);
           } else {
-            tma_load_2d(sa, &tmA, &full[s], k0, m0);
+            tma_load_2d(sa, mapA, &full[s], k0, m0);
           }
           if (B_MN) {
 #pragma unroll
@@ -182,10 +219,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const uint32_t aph = (tcount >> 1) & 1;
       if (!mbar_wait(&tfull[a], aph, abort_flag, p.status, TT_ST_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
-      const int m0 = (tile / tiles_n) * BM;
+      const MTile mt = m_tile(p, tile / tiles_n);
       const int n0 = (tile % tiles_n) * BN;
-      const int row = m0 + q * 32 + lane;
-      const bool row_ok = row < p.M;
+      const int row = mt.row0 + q * 32 + lane;
+      const bool row_ok = q * 32 + lane < mt.valid;
+      // reduce-scatter variant: the row goes to slot `rank` of the owner's staging buffer
+      bf16* c_row = (TP == 2) ? p.peer_c[mt.seg] + ((long long)p.rank * p.seg_rows + mt.seg_row0 + q * 32 + lane) * p.ldc
+                              : reinterpret_cast<bf16*>(p.C) + (long long)row * p.ldc;
       const float* gate_row = nullptr;
       if (p.epi == EPI_GATE_RES && row_ok)
         gate_row = p.gate + (long long)(row / p.rows_per_gate) * p.gate_ld;
@@ -277,7 +317,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             o.y = pack_bf16(v[2], v[3]);
             o.z = pack_bf16(v[4], v[5]);
             o.w = pack_bf16(v[6], v[7]);
-            *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.C) + (long long)row * p.ldc + col) = o;
+            *reinterpret_cast<uint4*>(c_row + col) = o;
           }
         }
         __syncwarp();  // tcgen05.ld is warp-collective: reconverge before the next chunk
@@ -299,19 +339,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (warp == 1) tmem_dealloc(tmem_base, C_::TMEM_COLS);
 }
 
-template <int BN, int A_MN, int B_MN>
+template <int BN, int A_MN, int B_MN, int TP = 0>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms,
-           cudaStream_t stream) {
+           cudaStream_t stream, const TmapSet* tmAp = nullptr) {
   using C_ = Cfg<BN>;
-  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, TP>;
+  static TmapSet no_maps;
+  if (!tmAp) tmAp = &no_maps;
   static bool attr_done = false;
   if (!attr_done) {
     TT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES));
     attr_done = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int tiles_m = p.seg_rows ? p.world * ((p.seg_rows + BM - 1) / BM) : (p.M + BM - 1) / BM;
+  const int tiles = tiles_m * ((p.N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, 320, C_::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  kern<<<grid, 320, C_::SMEM_BYTES, stream>>>(tmA, tmB, *tmAp, p);
   TT_LAUNCH_CHECK();
   return 0;
 }
@@ -368,6 +411,8 @@ TT_API int tt_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, l
   p.residual = (const bf16*)residual; p.ldr = ldr;
   p.gate = gate; p.gate_ld = gate_ld; p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1;
   p.aux_out = (bf16*)aux_out; p.alpha = alpha; p.status = status;
+  p.tp_mode = 0; p.seg_rows = 0; p.world = 1; p.rank = 0;
+  for (int i = 0; i < TP_MAX; ++i) p.peer_c[i] = nullptr;
   int dev = 0, sms = 0;
   TT_CUDA(cudaGetDevice(&dev));
   TT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -375,4 +420,154 @@ TT_API int tt_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, l
   if (BN == 256) return dispatch_major<256>(a_mn, b_mn, tmA, tmB, p, sms, stream);
   if (BN == 128) return dispatch_major<128>(a_mn, b_mn, tmA, tmB, p, sms, stream);
   return dispatch_major<64>(a_mn, b_mn, tmA, tmB, p, sms, stream);
+}
+
+namespace {
+
+__global__ void tp_reduce_rows_kernel(const bf16* __restrict__ staging, int world, long long rows, int N,
+                                      long long ld, const bf16* __restrict__ bias, bf16* __restrict__ out,
+                                      long long ldo) {
+  const long long vec_per_row = N / 8;
+  const long long total = rows * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int c = (int)(i - r * vec_per_row) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (bias) {
+      const uint4 bv = *reinterpret_cast<const uint4*>(bias + c);
+      const uint32_t* bu = reinterpret_cast<const uint32_t*>(&bv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16(bu[j]);
+        acc[2 * j] = f.x;
+        acc[2 * j + 1] = f.y;
+      }
+    }
+    for (int w = 0; w < world; ++w) {
+      const uint4 v = *reinterpret_cast<const uint4*>(staging + ((long long)w * rows + r) * ld + c);
+      const uint32_t* vu = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16(vu[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]);
+    o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]);
+    o.w = pack_bf16(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + r * ldo + c) = o;
+  }
+}
+
+int tp_common_checks(int seg_rows, int world, int N, int K, long long lda, long long ldb, long long ldc) {
+  TT_CHECK(world >= 1 && world <= TP_MAX, "gemm_tp: group size %d outside [1, %d]", world, TP_MAX);
+  TT_CHECK(seg_rows > 0 && N > 64 && K > 0, "gemm_tp: needs seg_rows > 0, N > 64, K > 0 (got %d, %d, %d)", seg_rows, N, K);
+  TT_CHECK(N % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0, "gemm_tp: N and leading dims must be multiples of 8");
+  return 0;
+}
+
+int make_b_map(CUtensorMap* tmB, const void* B, long long ldb, int b_mn, int N, int K, int BN) {
+  uint64_t dims[2], str[1];
+  uint32_t box[2];
+  if (b_mn) { dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 64; box[1] = 64; }
+  else      { dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = 64; box[1] = (uint32_t)BN; }
+  str[0] = (uint64_t)ldb * 2;
+  return tt_make_tmap(tmB, B, 2, 2, dims, str, box, 1);
+}
+
+int make_a_map(CUtensorMap* tmA, const void* A, long long lda, int rows, int K) {
+  uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows}, str[1] = {(uint64_t)lda * 2};
+  uint32_t box[2] = {64, BM};
+  return tt_make_tmap(tmA, A, 2, 2, dims, str, box, 1);
+}
+
+void tp_base_params(GemmParams& p, int seg_rows, int world, int rank, int N, int K, unsigned* status) {
+  memset(&p, 0, sizeof(p));
+  p.M = seg_rows * world; p.N = N; p.K = K;
+  p.rows_per_gate = 1; p.alpha = 1.f; p.status = status;
+  p.seg_rows = seg_rows; p.world = world; p.rank = rank;
+}
+
+int num_sms(int* sms) {
+  int dev = 0;
+  TT_CUDA(cudaGetDevice(&dev));
+  TT_CUDA(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev));
+  return 0;
+}
+
+}  // namespace
+
+// K-AG-GEMM.  C[world * seg_rows, N] = epilogue([A_0; A_1; ...] B^T) where A_s is rank s's [seg_rows, K] buffer
+// (a_peers[s] = its device address, mapped into this process): the all-gather of a column-parallel linear
+// happens inside the TMA loads of the GEMM, no gathered copy of the activations exists.  The caller orders the
+// launch behind a barrier that says every rank has written its A.
+TT_API int tt_gemm_bf16_ag(const long long* a_peers, long long lda, const void* B, long long ldb, int b_mn,
+                           void* C, long long ldc, int seg_rows, int world, int N, int K, const void* bias,
+                           int epi, void* aux_out, unsigned* status, cudaStream_t stream) {
+  if (tp_common_checks(seg_rows, world, N, K, lda, ldb, ldc)) return -1;
+  TT_CHECK(epi == EPI_NONE || epi == EPI_GELU || epi == EPI_SILU, "gemm_ag: epilogue %d not supported", epi);
+  TT_CHECK(((uintptr_t)C & 15) == 0 && (!bias || ((uintptr_t)bias & 15) == 0), "gemm_ag: misaligned C / bias");
+  const int BN = N > 128 ? 256 : 128;
+  TmapSet maps;
+  memset(&maps, 0, sizeof(maps));
+  for (int s = 0; s < world; ++s) {
+    TT_CHECK(a_peers[s] != 0 && (a_peers[s] & 15) == 0, "gemm_ag: bad peer pointer %d", s);
+    if (make_a_map(&maps.m[s], reinterpret_cast<const void*>(a_peers[s]), lda, seg_rows, K)) return -1;
+  }
+  CUtensorMap tmB;
+  if (make_b_map(&tmB, B, ldb, b_mn, N, K, BN)) return -1;
+  GemmParams p;
+  tp_base_params(p, seg_rows, world, 0, N, K, status);
+  p.tp_mode = 1; p.C = C; p.ldc = ldc; p.bias = (const bf16*)bias; p.epi = epi; p.aux_out = (bf16*)aux_out;
+  int sms = 0;
+  if (num_sms(&sms)) return -2;
+  if (BN == 256) return b_mn ? launch<256, 0, 1, 1>(maps.m[0], tmB, p, sms, stream, &maps)
+                             : launch<256, 0, 0, 1>(maps.m[0], tmB, p, sms, stream, &maps);
+  return b_mn ? launch<128, 0, 1, 1>(maps.m[0], tmB, p, sms, stream, &maps)
+              : launch<128, 0, 0, 1>(maps.m[0], tmB, p, sms, stream, &maps);
+}
+
+// K-GEMM-RS, first half.  The partial product A[world * seg_rows, K] B^T is stored tile by tile into the staging
+// buffers of the ranks that own the rows: c_peers[s] is rank s's buffer [world, seg_rows, ldc], this rank writes
+// slot `rank`.  After a barrier each rank sums its slots with tt_tp_reduce_rows.
+TT_API int tt_gemm_bf16_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn,
+                           const long long* c_peers, long long ldc, int seg_rows, int world, int rank, int N,
+                           int K, unsigned* status, cudaStream_t stream) {
+  if (tp_common_checks(seg_rows, world, N, K, lda, ldb, ldc)) return -1;
+  TT_CHECK(rank >= 0 && rank < world, "gemm_rs: bad rank");
+  const int BN = N > 128 ? 256 : 128;
+  CUtensorMap tmA, tmB;
+  if (make_a_map(&tmA, A, lda, seg_rows * world, K)) return -1;
+  if (make_b_map(&tmB, B, ldb, b_mn, N, K, BN)) return -1;
+  GemmParams p;
+  tp_base_params(p, seg_rows, world, rank, N, K, status);
+  p.tp_mode = 2; p.ldc = ldc;
+  for (int s = 0; s < world; ++s) {
+    TT_CHECK(c_peers[s] != 0 && (c_peers[s] & 15) == 0, "gemm_rs: bad peer pointer %d", s);
+    p.peer_c[s] = reinterpret_cast<bf16*>(c_peers[s]);
+  }
+  p.C = p.peer_c[rank];
+  int sms = 0;
+  if (num_sms(&sms)) return -2;
+  if (BN == 256) return b_mn ? launch<256, 0, 1, 2>(tmA, tmB, p, sms, stream) : launch<256, 0, 0, 2>(tmA, tmB, p, sms, stream);
+  return b_mn ? launch<128, 0, 1, 2>(tmA, tmB, p, sms, stream) : launch<128, 0, 0, 2>(tmA, tmB, p, sms, stream);
+}
+
+// K-GEMM-RS, second half: out[r, :] = bias + sum_w staging[w, r, :]   (fp32 accumulation, bf16 in / out)
+TT_API int tt_tp_reduce_rows(const void* staging, int world, long long rows, int N, long long ld, const void* bias,
+                             void* out, long long ldo, cudaStream_t stream) {
+  TT_CHECK(world >= 1 && rows > 0 && N > 0 && N % 8 == 0 && ld % 8 == 0 && ldo % 8 == 0, "tp_reduce_rows: bad shape");
+  TT_CHECK((((uintptr_t)staging | (uintptr_t)out | (uintptr_t)bias) & 15) == 0, "tp_reduce_rows: misaligned pointer");
+  const long long total = rows * (N / 8);
+  const int threads = 256;
+  long long blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  tp_reduce_rows_kernel<<<(unsigned)blocks, threads, 0, stream>>>((const bf16*)staging, world, rows, N, ld,
+                                                                 (const bf16*)bias, (bf16*)out, ldo);
+  TT_LAUNCH_CHECK();
+  return 0;
 }

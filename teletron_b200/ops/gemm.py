@@ -49,7 +49,7 @@ def gemm_ref(a, b, *, a_mn=False, b_mn=False, bias=None, epi=EPI_NONE, residual=
 
 
 def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, epi=EPI_NONE, residual=None, gate=None,
-         rows_per_gate=1, out=None, out_dtype=torch.bfloat16, alpha=1.0, want_aux=False, max_ctas=0):
+         rows_per_gate=1, out=None, out_dtype=torch.bfloat16, alpha=1.0, want_aux=False, max_ctas=0, aux=None):
     """C = epilogue(alpha * A @ B^T).
 
     a: [M,K] (or [K,M] when a_mn)   b: [N,K] (or [K,N] when b_mn); both bf16 with a
@@ -76,10 +76,12 @@ def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, epi=EPI_NONE, residual=None
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     else:
         assert out.shape == (M, N) and out.stride(1) == 1
-    aux = None
     if want_aux:
-        aux = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
-        assert out.stride(0) == aux.stride(0)
+        if aux is None:
+            aux = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+        assert aux.shape == (M, N) and out.stride(0) == aux.stride(0)
+    else:
+        aux = None
     if bias is not None:
         assert bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == N
     if epi == EPI_GATE_RES:
@@ -97,3 +99,48 @@ def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, epi=EPI_NONE, residual=None
         _lib.ptr(_lib.status_word(a.device)), _lib.c_int(max_ctas), _lib.stream())
     _lib.check(rc, "tt_gemm_bf16")
     return (out, aux) if want_aux else out
+
+
+# ------------------------------------------------------------------------------ tensor-parallel variants
+def gemm_ag(a_peer_ptrs, seg_rows: int, k: int, b, *, b_mn=False, bias=None, epi=EPI_NONE, want_aux=False,
+            device=None):
+    """all-gather -> GEMM in one kernel: ``C = epilogue([A_0; A_1; ...] @ B^T)`` where segment s of A
+    ([seg_rows, k], row stride k) is read from rank s's buffer at device address ``a_peer_ptrs[s]``
+    (csrc/gemm.cu, tt_gemm_bf16_ag).  The caller has put a barrier between the writes of A and this call."""
+    world = len(a_peer_ptrs)
+    n = b.shape[1] if b_mn else b.shape[0]
+    assert b.dtype == torch.bfloat16 and b.stride(1) == 1
+    out = torch.empty((world * seg_rows, n), dtype=torch.bfloat16, device=device or b.device)
+    aux = torch.empty_like(out) if want_aux else None
+    ptrs = (_lib.c_ll * world)(*[int(p) for p in a_peer_ptrs])
+    rc = _lib.lib().tt_gemm_bf16_ag(ptrs, _lib.c_ll(k), _lib.ptr(b), _lib.c_ll(b.stride(0)), _lib.c_int(int(b_mn)),
+                                    _lib.ptr(out), _lib.c_ll(out.stride(0)), _lib.c_int(seg_rows), _lib.c_int(world),
+                                    _lib.c_int(n), _lib.c_int(k), _lib.ptr(bias), _lib.c_int(epi), _lib.ptr(aux),
+                                    _lib.ptr(_lib.status_word(out.device)), _lib.stream())
+    _lib.check(rc, "tt_gemm_bf16_ag")
+    return (out, aux) if want_aux else out
+
+
+def gemm_rs_scatter(a, b, c_peer_ptrs, seg_rows: int, rank: int, *, b_mn=False):
+    """First half of GEMM -> reduce-scatter: the partial product ``a @ b^T`` ([world * seg_rows, n]) is stored,
+    tile by tile, into slot ``rank`` of the staging buffer ([world, seg_rows, n]) of the rank that owns the rows
+    (csrc/gemm.cu, tt_gemm_bf16_rs)."""
+    world = len(c_peer_ptrs)
+    n = b.shape[1] if b_mn else b.shape[0]
+    m, k = a.shape
+    assert m == world * seg_rows and a.stride(1) == 1 and b.stride(1) == 1
+    ptrs = (_lib.c_ll * world)(*[int(p) for p in c_peer_ptrs])
+    rc = _lib.lib().tt_gemm_bf16_rs(_lib.ptr(a), _lib.c_ll(a.stride(0)), _lib.ptr(b), _lib.c_ll(b.stride(0)),
+                                    _lib.c_int(int(b_mn)), ptrs, _lib.c_ll(n), _lib.c_int(seg_rows), _lib.c_int(world),
+                                    _lib.c_int(rank), _lib.c_int(n), _lib.c_int(k),
+                                    _lib.ptr(_lib.status_word(a.device)), _lib.stream())
+    _lib.check(rc, "tt_gemm_bf16_rs")
+
+
+def tp_reduce_rows(staging, world: int, rows: int, n: int, bias=None):
+    """Second half: ``out[r] = bias + sum_w staging[w, r]`` (fp32 accumulation)."""
+    out = torch.empty((rows, n), dtype=torch.bfloat16, device=staging.device)
+    rc = _lib.lib().tt_tp_reduce_rows(_lib.ptr(staging), _lib.c_int(world), _lib.c_ll(rows), _lib.c_int(n), _lib.c_ll(n),
+                                      _lib.ptr(bias), _lib.ptr(out), _lib.c_ll(n), _lib.stream())
+    _lib.check(rc, "tt_tp_reduce_rows")
+    return out

@@ -33,9 +33,52 @@ def _time(fn, iters=3):
     return e0.elapsed_time(e1) / iters
 
 
+def _tp_case(a):
+    """Column-parallel + row-parallel linear pair (an MLP), forward + backward, under torchrun on the ranks of one box:
+    ``--rows`` tokens per rank, hidden ``--c``, inner width ``--inner`` (sharded).  Max over ranks of the device time."""
+    import os
+
+    import torch.distributed as dist
+
+    from ..dist import SymmetricArena
+    from ..parallel.tp import ColumnParallelLinear, FusedTP, RowParallelLinear, TPContext
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dist.init_process_group("nccl")
+    tp = TPContext(dist.group.WORLD, world, rank)
+    if a.fused:
+        tp.fused = FusedTP(SymmetricArena(dist.group.WORLD))
+    torch.manual_seed(0)
+    col = ColumnParallelLinear(a.c, a.inner, tp).cuda().to(torch.bfloat16)
+    row = RowParallelLinear(a.inner, a.c, tp).cuda().to(torch.bfloat16)
+    x = torch.randn(a.rows, a.c, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn(a.rows, a.c, device="cuda", dtype=torch.bfloat16)
+
+    def step():
+        x.grad = None
+        row(col(x, act="gelu")).backward(dy)
+
+    for _ in range(3):
+        step()
+    dist.barrier()
+    ms = _time(step, a.iters)
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    _lib.check_status()
+    if rank == 0:
+        flops = 3 * 2 * 2.0 * a.rows * world * a.c * (a.inner / world)  # fwd + dgrad + wgrad of both linears, per rank
+        print(json.dumps(dict(case="tp", world=world, fused=bool(a.fused), rows_per_rank=a.rows, c=a.c, inner=a.inner,
+                              ms=float(t.item()), tflops_per_rank=flops / float(t.item()) / 1e9)), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "attn", "norm", "layers"])
+    ap.add_argument("case", choices=["gemm", "attn", "norm", "layers", "tp"])
+    ap.add_argument("--inner", type=int, default=12288, help="tp case: full inner width of the MLP")
+    ap.add_argument("--fused", action="store_true", help="tp case: peer-memory kernels instead of NCCL")
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--m", type=int, default=32760)
     ap.add_argument("--n", type=int, default=8960)
@@ -51,6 +94,8 @@ def main():
     ap.add_argument("--c", type=int, default=1536)
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
+    if a.case == "tp":
+        return _tp_case(a)
     dev = "cuda"
     torch.manual_seed(0)
     res = dict(case=a.case)

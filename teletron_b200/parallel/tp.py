@@ -10,7 +10,9 @@ Activations between TP regions are sharded along tokens (rows), so LayerNorm / A
 work on 1/T of the rows.  Backward of the all-gather is a reduce-scatter and vice versa.
 Weights are stored as shards; ``tp_shard_state_dict`` / ``tp_merge_state_dicts`` convert between a
 full state dict and per-rank shards (checkpoint files ``mp_rank_XX``).
-The collectives here are torch.distributed (NCCL / gloo); GEMMs are the tcgen05 kernels.
+The collectives are torch.distributed (NCCL / gloo) by default; when the TP group shares one NVLink box the trainer
+attaches a ``FusedTP`` and the linears run the all-gather inside the GEMM's TMA loads and the reduce-scatter
+inside its epilogue (csrc/gemm.cu).  GEMMs are the tcgen05 kernels either way.
 """
 from __future__ import annotations
 
@@ -84,9 +86,174 @@ class GatherRowsKeepLocalGrad(torch.autograd.Function):
         return g[rank * n:(rank + 1) * n].contiguous(), None, None, None
 
 
+class FusedTP:
+    """Peer-memory buffers and call order for the fused tensor-parallel kernels of one TP group on one box:
+
+      all-gather -> GEMM    each rank copies its rows into a symmetric buffer, a device barrier follows, and the
+                            remote segments are pulled over NVLink while the GEMM of the local segment runs
+                            (or, ``one_kernel``, the GEMM's TMA loads read the peers' buffers: ``ops.gemm_ag``)
+      GEMM -> reduce-scatter  the GEMM epilogue stores each tile of partial sums into the staging buffer of the rank
+                            that owns the rows (``ops.gemm_rs_scatter``); after a barrier every rank sums its
+                            ``world`` slots (``ops.tp_reduce_rows``)
+
+    Both buffers are double-buffered: the barrier of call n+1 is stream-ordered behind each rank's reads of call n,
+    so buffer n % 2 may be overwritten again in call n+2.  Every rank must issue the same calls in the same order.
+    """
+
+    def __init__(self, arena):
+        self.arena = arena
+        self.world, self.rank = arena.world, arena.rank
+        self._x = [None, None]
+        self._st = [None, None]
+        self._x_cap = 0
+        self._st_cap = 0
+        self._n_ag = 0
+        self._n_rs = 0
+        self._side = None
+
+    def _x_buf(self, numel):
+        if numel > self._x_cap:  # collective: every rank grows at the same call
+            self._x = [self.arena.alloc(numel, torch.bfloat16) for _ in range(2)]
+            self._x_cap = numel
+        self._n_ag += 1
+        return self._x[self._n_ag & 1]
+
+    def _st_buf(self, numel):
+        if numel > self._st_cap:
+            self._st = [self.arena.alloc(numel, torch.bfloat16) for _ in range(2)]
+            self._st_cap = numel
+        self._n_rs += 1
+        return self._st[self._n_rs & 1]
+
+    def ag_gemm(self, x_rows, w, *, b_mn=False, bias=None, epi=0, want_aux=False, one_kernel=False):
+        """epilogue(all_gather_rows(x_rows) @ W^T): x_rows [rows, k] bf16, W [n, k] (or [k, n] when b_mn).
+        Returns (y, pre-activation or None, gathered x or None).
+
+        Default: every remote segment is pulled once into a local gathered buffer by a copy on a side stream
+        while the GEMM of the local segment runs, and the GEMM of segment s starts when its copy has landed
+        (events, no kernel waits on another kernel).  ``one_kernel`` uses ``ops.gemm_ag`` instead, whose TMA
+        loads read the peers directly: one launch and no gathered copy, but every remote A tile crosses NVLink
+        once per column tile of the output (24 times for a 6,144-wide shard), which measured twice as slow as
+        NCCL on an MLP pair at 2 x 16,384 rows; it is kept for narrow outputs."""
+        rows, k = x_rows.shape
+        buf = self._x_buf(rows * k)
+        mine = buf.tensor[: rows * k].view(rows, k)
+        mine.copy_(x_rows)
+        self.arena.barrier(0)
+        if one_kernel:
+            res = ops.gemm_ag(buf.peer_ptrs, rows, k, w, b_mn=b_mn, bias=bias, epi=epi, want_aux=want_aux,
+                              device=x_rows.device)
+            return (res[0], res[1], None) if want_aux else (res, None, None)
+        n = w.shape[1] if b_mn else w.shape[0]
+        world, rank = self.world, self.rank
+        gathered = torch.empty((world * rows, k), dtype=torch.bfloat16, device=x_rows.device)
+        out = torch.empty((world * rows, n), dtype=torch.bfloat16, device=x_rows.device)
+        aux = torch.empty_like(out) if want_aux else None
+        cur = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = torch.cuda.Stream()
+        side = self._side
+        side.wait_stream(cur)  # behind the barrier: the peers' rows are complete
+        events = {}
+        with torch.cuda.stream(side):
+            for i in range(1, world):
+                s_ = (rank + i) % world
+                peer = buf.handle.get_buffer(s_, (rows, k), torch.bfloat16)
+                gathered[s_ * rows:(s_ + 1) * rows].copy_(peer, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(side)
+                events[s_] = ev
+        gathered.record_stream(side)
+        gathered[rank * rows:(rank + 1) * rows].copy_(mine)
+        for i in range(world):
+            s_ = (rank + i) % world
+            if i > 0:
+                cur.wait_event(events[s_])
+            sl = slice(s_ * rows, (s_ + 1) * rows)
+            ops.gemm(gathered[sl], w, b_mn=b_mn, bias=bias, epi=epi, out=out[sl], want_aux=want_aux,
+                     aux=aux[sl] if want_aux else None)
+        return out, aux, gathered
+
+    def gemm_rs(self, x, w, *, b_mn=False):
+        """reduce_scatter_rows(x @ W^T): x [world * rows, k]; returns this rank's [rows, n] of the sum."""
+        m = x.shape[0]
+        assert m % self.world == 0, "rows must divide by the tensor-parallel size"
+        rows = m // self.world
+        n = w.shape[1] if b_mn else w.shape[0]
+        st = self._st_buf(self.world * rows * n)
+        ops.gemm_rs_scatter(x, w, st.peer_ptrs, rows, self.rank, b_mn=b_mn)
+        self.arena.barrier(0)
+        return ops.tp_reduce_rows(st.tensor, self.world, rows, n)
+
+
+class _FusedColumnLinear(torch.autograd.Function):
+    """act(all_gather_rows(x) @ W^T + b) with the gather overlapped with (or inside) the GEMM; backward
+    reduce-scatters dX through the GEMM epilogue.  The weight gradient reuses the gathered activations."""
+
+    @staticmethod
+    def forward(ctx, x_rows, w, b, act, tp):
+        from ..ops.linear import _ACT
+
+        need_pre = act is not None
+        y, pre, gathered = tp.fused.ag_gemm(x_rows, w, bias=b, epi=_ACT[act], want_aux=need_pre)
+        # the gathered activations are kept for the weight gradient when the gather produced them
+        ctx.save_for_backward(x_rows if gathered is None else gathered, w, pre)
+        ctx.have_gathered = gathered is not None
+        ctx.act, ctx.tp, ctx.bias_ref = act, tp, b
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.linear import _bias_grad, _weight_grad, act_bwd
+
+        x_rows, w, pre = ctx.saved_tensors
+        tp = ctx.tp
+        if dy.stride(1) != 1:
+            dy = dy.contiguous()
+        if ctx.act is not None:
+            dy = act_bwd(dy, pre, ctx.act)
+        dx = tp.fused.gemm_rs(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            xg = x_rows if ctx.have_gathered else _ag_rows(x_rows, tp.group, tp.size)
+            dw = _weight_grad(dy, xg, w)
+        db = _bias_grad(dy, ctx.bias_ref) if (ctx.bias_ref is not None and ctx.needs_input_grad[2]) else None
+        return dx, dw, db, None, None
+
+
+class _FusedRowLinear(torch.autograd.Function):
+    """reduce_scatter_rows(x @ W^T) with the scatter inside the GEMM epilogue; backward gathers dY inside the
+    dgrad GEMM."""
+
+    @staticmethod
+    def forward(ctx, x_cols, w, tp):
+        ctx.save_for_backward(x_cols, w)
+        ctx.tp = tp
+        return tp.fused.gemm_rs(x_cols, w)
+
+    @staticmethod
+    def backward(ctx, dy_rows):
+        from ..ops.linear import _weight_grad
+
+        x_cols, w = ctx.saved_tensors
+        tp = ctx.tp
+        if dy_rows.stride(1) != 1:
+            dy_rows = dy_rows.contiguous()
+        dx, dyg = None, None
+        if ctx.needs_input_grad[0]:
+            dx, _, dyg = tp.fused.ag_gemm(dy_rows, w, b_mn=True)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            if dyg is None:
+                dyg = _ag_rows(dy_rows, tp.group, tp.size)
+            dw = _weight_grad(dyg, x_cols, w)
+        return dx, dw, None
+
+
 class TPContext:
     def __init__(self, group=None, size: int = 1, rank: int = 0):
         self.group, self.size, self.rank = group, size, rank
+        self.fused: Optional[FusedTP] = None  # set by the trainer when the group shares one NVLink box
 
     def gather_rows(self, x):
         return GatherRows.apply(x, self.group, self.size) if self.size > 1 else x
@@ -117,6 +284,9 @@ class ColumnParallelLinear(nn.Module):
         self.shard_dim = 0
 
     def forward(self, x_rows, act=None, gathered: bool = False):
+        if (not gathered and self.tp.size > 1 and self.tp.fused is not None and x_rows.is_cuda
+                and x_rows.dim() == 2 and self.weight.shape[0] > 64):
+            return _FusedColumnLinear.apply(x_rows, self.weight, self.bias, act, self.tp)
         x = x_rows if gathered else self.tp.gather_rows(x_rows)
         return ops.linear(x, self.weight, self.bias, act)
 
@@ -134,8 +304,12 @@ class RowParallelLinear(nn.Module):
         self.shard_dim = 1
 
     def forward(self, x_cols):
-        y = ops.linear(x_cols, self.weight, None)
-        y = self.tp.reduce_scatter_rows(y)
+        if (self.tp.size > 1 and self.tp.fused is not None and x_cols.is_cuda and x_cols.dim() == 2
+                and self.weight.shape[0] > 64):
+            y = _FusedRowLinear.apply(x_cols, self.weight, self.tp)
+        else:
+            y = ops.linear(x_cols, self.weight, None)
+            y = self.tp.reduce_scatter_rows(y)
         if self.bias is not None:
             y = y + self.bias
         return y

@@ -155,6 +155,19 @@ class Trainer:
                     if a.fused_comm == "on":
                         raise
                     print(f"WARNING: fused Ulysses unavailable ({e}); using NCCL all-to-all", flush=True)
+        tp_ctx = getattr(inner, "tp", None)
+        if (a.fused_comm != "off" and tp_ctx is not None and tp_ctx.size > 1 and self.device.type == "cuda"
+                and a.world_size <= torch.cuda.device_count()):
+            from ..dist import SymmetricArena, symmetric_memory_available
+            from ..parallel.tp import FusedTP
+
+            if symmetric_memory_available():
+                try:
+                    tp_ctx.fused = FusedTP(SymmetricArena(mpu.get_tensor_model_parallel_group()))
+                except Exception as e:
+                    if a.fused_comm == "on":
+                        raise
+                    print(f"WARNING: fused tensor-parallel kernels unavailable ({e}); using NCCL collectives", flush=True)
         self.buffer = ParamBuffer(inner, shard_world=world if a.use_distributed_optimizer else 1, arena=arena)
         self.optimizer = DistributedOptimizer(
             self.buffer, group if world > 1 else None, lr=a.lr, betas=(a.adam_beta1, a.adam_beta2),

@@ -111,3 +111,50 @@ def test_ulysses_cp2_matches_single_gpu(fused):
         assert rel(out, ref_out) < 1e-3          # same threshold as the reference's model test
         bad = [(n, rel(grads[n], ref_g[n])) for n in ref_g if ref_g[n].norm() > 2e-4 and rel(grads[n], ref_g[n]) > 2e-2]
         assert not bad, bad
+
+
+def _tp_worker(rank, world, fused):
+    import torch.distributed as dist
+
+    from teletron_b200.dist import SymmetricArena
+    from teletron_b200.ops import _lib
+    from teletron_b200.parallel.tp import ColumnParallelLinear, FusedTP, RowParallelLinear, TPContext
+
+    torch.manual_seed(0)
+    tp = TPContext(dist.group.WORLD, world, rank)
+    if fused:
+        tp.fused = FusedTP(SymmetricArena(dist.group.WORLD))
+    rows, C, inner = 200, 256, 768            # 200 rows per rank: not a multiple of the 128-row tile
+    col = ColumnParallelLinear(C, inner, tp).cuda().to(torch.bfloat16)
+    row = RowParallelLinear(inner, C, tp).cuda().to(torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    x_full = torch.randn(world * rows, C, device="cuda", generator=g).to(torch.bfloat16)
+    dy_full = torch.randn(world * rows, C, device="cuda", generator=g).to(torch.bfloat16)
+    x = x_full[rank * rows:(rank + 1) * rows].clone().requires_grad_(True)
+    outs = []
+    for _ in range(3):                        # three rounds: the peer buffers are double-buffered
+        x.grad = None
+        col.zero_grad()
+        row.zero_grad()
+        y = row(col(x, act="gelu"))
+        y.backward(dy_full[rank * rows:(rank + 1) * rows])
+        outs = [y.detach(), x.grad, col.weight.grad, col.bias.grad, row.weight.grad]
+    if fused:
+        # the one-kernel variant (TMA loads straight from the peers' buffers) against the pull-and-overlap default
+        xd = x.detach()
+        y1 = tp.fused.ag_gemm(xd, col.weight.detach(), bias=col.bias.detach(), one_kernel=True)[0]
+        y2 = tp.fused.ag_gemm(xd, col.weight.detach(), bias=col.bias.detach())[0]
+        torch.cuda.synchronize()
+        assert rel(y1, y2) < 1e-3, rel(y1, y2)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return [o.float().cpu() for o in outs]
+
+
+@needs2
+def test_fused_tp_linears_match_nccl():
+    ref = run_distributed(_tp_worker, 2, False, backend="nccl")
+    got = run_distributed(_tp_worker, 2, True, backend="nccl")
+    for r in range(2):
+        for a, b in zip(got[r], ref[r]):
+            assert rel(a, b) < 4e-3

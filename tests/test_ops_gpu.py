@@ -211,3 +211,44 @@ def test_flow_ops_and_adamw():
     assert torch.equal(p16, p32.to(torch.bfloat16))
     gn = ops.grad_norm(g, 1.0)
     assert abs(gn[0].item() - g.norm().item()) < 1e-3 * g.norm().item()
+
+
+@pytest.mark.parametrize("world,seg,K,N,b_mn", [(2, 200, 192, 320, False), (3, 128, 256, 136, True), (2, 70, 64, 512, False)])
+def test_gemm_ag_segments_on_one_device(world, seg, K, N, b_mn):
+    """all-gather -> GEMM kernel with every "rank" buffer on this GPU (the kernel only sees device addresses)."""
+    G = importlib.import_module("teletron_b200.ops.gemm")
+    torch.manual_seed(0)
+    segs = [torch.randn(seg, K, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    w = torch.randn(N, K, device="cuda").to(torch.bfloat16) * 0.1
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    b = w.t().contiguous() if b_mn else w
+    y, pre = G.gemm_ag([t.data_ptr() for t in segs], seg, K, b, b_mn=b_mn, bias=bias, epi=G.EPI_GELU, want_aux=True)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    ref_pre = torch.cat(segs).float() @ w.float().t() + bias.float()
+    ref = torch.nn.functional.gelu(ref_pre, approximate="tanh")
+    assert rel(pre, ref_pre) < 4e-3
+    assert rel(y, ref) < 4e-3
+
+
+@pytest.mark.parametrize("world,seg,K,N,b_mn", [(2, 200, 192, 320, False), (3, 128, 256, 136, True)])
+def test_gemm_rs_segments_on_one_device(world, seg, K, N, b_mn):
+    """GEMM -> reduce-scatter: every emulated rank scatters its partial product into the owners' staging buffers,
+    then each owner sums its slots."""
+    G = importlib.import_module("teletron_b200.ops.gemm")
+    torch.manual_seed(1)
+    xs = [torch.randn(world * seg, K, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    ws = [(torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(world)]
+    staging = [torch.full((world, seg, N), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    ptrs = [t.data_ptr() for t in staging]
+    for r in range(world):
+        b = ws[r].t().contiguous() if b_mn else ws[r]
+        G.gemm_rs_scatter(xs[r], b, ptrs, seg, r, b_mn=b_mn)
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    total = sum(x.float() @ w.float().t() for x, w in zip(xs, ws))
+    for s_ in range(world):
+        out = G.tp_reduce_rows(staging[s_], world, seg, N, bias=bias)
+        torch.cuda.synchronize()
+        ref = total[s_ * seg:(s_ + 1) * seg] + bias.float()
+        assert rel(out, ref) < 4e-3
+    _lib.check_status()
