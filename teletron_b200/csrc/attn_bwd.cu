@@ -20,6 +20,9 @@ constexpr int NTHREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 elementwise
 constexpr int BIG = 128 * 128 * 2;     // 128 x 128 bf16 tile (two 64-wide halves of 16 KB)
 constexpr int BIG_HALF = 128 * 128;    // 128 rows x 128 B
 constexpr float LOG2E = 1.4426950408889634f;
+#ifndef TT_BWD_POLY_EVERY
+#define TT_BWD_POLY_EVERY 0  // n > 0: every n-th exponential of phase 1 on the FMA pipe (exp2_fma); 2, 3 and 4 measured slower (22.4 / 21.2 / 20.8 ms against 19.6 at 32,760 tokens), as did 16 elementwise warps (20.1 ms)
+#endif
 constexpr uint32_t HI_K = umma_desc_hi(1024);  // both operand layouts here step 1024 bytes between 8-row groups
 
 struct BwdParams {
@@ -273,10 +276,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
         for (int e = 0; e < 32; e += 4) {
           const float4 a4 = *reinterpret_cast<const float4*>(ls + e);
-          pr[e] = fast_exp2(fmaf(__uint_as_float(s0[e]), p.scale_log2, -a4.x));
-          pr[e + 1] = fast_exp2(fmaf(__uint_as_float(s0[e + 1]), p.scale_log2, -a4.y));
-          pr[e + 2] = fast_exp2(fmaf(__uint_as_float(s0[e + 2]), p.scale_log2, -a4.z));
-          pr[e + 3] = fast_exp2(fmaf(__uint_as_float(s0[e + 3]), p.scale_log2, -a4.w));
+          pr[e] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s0[e]), p.scale_log2, -a4.x), e);
+          pr[e + 1] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s0[e + 1]), p.scale_log2, -a4.y), e + 1);
+          pr[e + 2] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s0[e + 2]), p.scale_log2, -a4.z), e + 2);
+          pr[e + 3] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s0[e + 3]), p.scale_log2, -a4.w), e + 3);
         }
 #pragma unroll
         for (int e = 0; e < 16; ++e) pk[e] = pack_bf16(pr[2 * e], pr[2 * e + 1]);
@@ -284,10 +287,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
         for (int e = 0; e < 32; e += 4) {
           const float4 a4 = *reinterpret_cast<const float4*>(ls + 32 + e);
-          pr[32 + e] = fast_exp2(fmaf(__uint_as_float(s1[e]), p.scale_log2, -a4.x));
-          pr[32 + e + 1] = fast_exp2(fmaf(__uint_as_float(s1[e + 1]), p.scale_log2, -a4.y));
-          pr[32 + e + 2] = fast_exp2(fmaf(__uint_as_float(s1[e + 2]), p.scale_log2, -a4.z));
-          pr[32 + e + 3] = fast_exp2(fmaf(__uint_as_float(s1[e + 3]), p.scale_log2, -a4.w));
+          pr[32 + e] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s1[e]), p.scale_log2, -a4.x), e);
+          pr[32 + e + 1] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s1[e + 1]), p.scale_log2, -a4.y), e + 1);
+          pr[32 + e + 2] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s1[e + 2]), p.scale_log2, -a4.z), e + 2);
+          pr[32 + e + 3] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s1[e + 3]), p.scale_log2, -a4.w), e + 3);
         }
 #pragma unroll
         for (int e = 0; e < 16; ++e) pk[e] = pack_bf16(pr[32 + 2 * e], pr[32 + 2 * e + 1]);
@@ -583,12 +586,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          const float pe = fast_exp2(fmaf(__uint_as_float(s0[e]), p.scale_log2, -lse2));
+          const float pe = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s0[e]), p.scale_log2, -lse2), e);
           pr[e] = (e < valid) ? pe : 0.f;
         }
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          const float pe = fast_exp2(fmaf(__uint_as_float(s1[e]), p.scale_log2, -lse2));
+          const float pe = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s1[e]), p.scale_log2, -lse2), e);
           pr[32 + e] = (32 + e < valid) ? pe : 0.f;
         }
       }
