@@ -158,3 +158,70 @@ def test_fused_tp_linears_match_nccl():
     for r in range(2):
         for a, b in zip(got[r], ref[r]):
             assert rel(a, b) < 4e-3
+
+
+def _hy_inputs():
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(1, 16, 4, 16, 16, generator=g)             # 4 * 8 * 8 = 256 video tokens
+    text = torch.randn(1, 24, 64, generator=g)
+    mask = torch.ones(1, 24, dtype=torch.long)
+    mask[:, 17:] = 0
+    return x, torch.tensor([700.0]), text, mask, torch.randn(1, 32, generator=g), torch.tensor([6000.0])
+
+
+def _hy_run(m):
+    x, t, text, mask, pooled, guid = _hy_inputs()
+    out = m(x.cuda().bfloat16(), t.cuda(), text.cuda().bfloat16(), mask.cuda(), pooled.cuda().bfloat16(), guid.cuda())
+    out.float().square().mean().backward()
+    torch.cuda.synchronize()
+    return out.detach().float().cpu(), {n: p.grad.detach().float().cpu() for n, p in m.named_parameters()
+                                        if p.grad is not None}
+
+
+def _hy_tp_worker(rank, world, full_sd, fused):
+    import torch.distributed as dist
+
+    from teletron_b200.dist import SymmetricArena
+    from teletron_b200.models.hunyuan import HunyuanVideoModel, hunyuan_config
+    from teletron_b200.ops import _lib
+    from teletron_b200.parallel.tp import FusedTP, TPContext, tp_shard_dims, tp_shard_state_dict
+
+    tp = TPContext(dist.group.WORLD, world, rank)
+    if fused:
+        tp.fused = FusedTP(SymmetricArena(dist.group.WORLD))
+    m = HunyuanVideoModel(hunyuan_config("hunyuan-tiny"), None, tp)
+    dims = tp_shard_dims(m)
+    m.load_state_dict(tp_shard_state_dict(full_sd, dims, rank, world))
+    m = m.cuda().to(torch.bfloat16)
+    out, grads = _hy_run(m)
+    for n, g in grads.items():
+        if n not in dims:                       # replicated parameters see only this rank's rows
+            gg = g.cuda()
+            dist.all_reduce(gg)
+            grads[n] = gg.cpu()
+    _lib.check_status()
+    return out, grads
+
+
+@needs2
+@pytest.mark.parametrize("fused", [False, True])
+def test_hunyuan_tp2_matches_single_gpu(fused):
+    import copy
+
+    from teletron_b200.models.hunyuan import HunyuanVideoModel, hunyuan_config
+    from teletron_b200.parallel.tp import TPContext, tp_merge_state_dicts, tp_shard_dims
+
+    torch.manual_seed(0)
+    ref = HunyuanVideoModel(hunyuan_config("hunyuan-tiny"))
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.copy_(p.to(torch.bfloat16).float())
+    full_sd = {k: v.clone() for k, v in ref.state_dict().items()}
+    ref_out, ref_g = _hy_run(copy.deepcopy(ref).cuda().to(torch.bfloat16))
+    outs = run_distributed(_hy_tp_worker, 2, full_sd, fused, backend="nccl")
+    dims = tp_shard_dims(HunyuanVideoModel(hunyuan_config("hunyuan-tiny"), None, TPContext(None, 2, 0)))
+    merged = tp_merge_state_dicts([o[1] for o in outs], dims)
+    for out, _ in outs:
+        assert rel(out, ref_out) < 1e-2
+    bad = [(n, rel(merged[n], g)) for n, g in ref_g.items() if g.norm() > 2e-4 and rel(merged[n], g) > 3e-2]
+    assert not bad, bad
