@@ -121,7 +121,18 @@ colsum_stage1_kernel(const bf16* __restrict__ x, long long ldx, float* __restric
   const int r0 = blockIdx.y * rows_per_chunk;
   const int r1 = min(r0 + rows_per_chunk, rows);
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int r = r0; r < r1; ++r) {
+  int r = r0;
+  for (; r + 3 < r1; r += 4) {  // four independent 16-byte loads in flight per thread
+    float v0[8], v1[8], v2[8], v3[8];
+    const bf16* px = x + (long long)r * ldx + vec * 8;
+    ld8(px, v0);
+    ld8(px + ldx, v1);
+    ld8(px + 2 * ldx, v2);
+    ld8(px + 3 * ldx, v3);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += (v0[j] + v1[j]) + (v2[j] + v3[j]);
+  }
+  for (; r < r1; ++r) {
     float v[8];
     ld8(x + (long long)r * ldx + vec * 8, v);
 #pragma unroll
@@ -131,12 +142,28 @@ colsum_stage1_kernel(const bf16* __restrict__ x, long long ldx, float* __restric
   *reinterpret_cast<float4*>(pp) = make_float4(acc[0], acc[1], acc[2], acc[3]);
   *reinterpret_cast<float4*>(pp + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
-__global__ void colsum_stage2_kernel(const float* __restrict__ partial, void* __restrict__ out, int n,
-                                     int C, int out_fp32, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+// stage 2: a CTA covers 32 columns, its 8 warps take every 8th chunk; slice sums are added in a fixed order
+__global__ void __launch_bounds__(256)
+colsum_stage2_kernel(const float* __restrict__ partial, void* __restrict__ out, int n, int C, int out_fp32,
+                     int accumulate) {
+  __shared__ float red[8][33];
+  const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  float s0 = 0.f, s1 = 0.f;
+  if (c < C) {
+    int i = slice;
+    for (; i + 8 < n; i += 16) {
+      s0 += partial[(long long)i * C + c];
+      s1 += partial[(long long)(i + 8) * C + c];
+    }
+    for (; i < n; i += 8) s0 += partial[(long long)i * C + c];
+  }
+  red[slice][lane] = s0 + s1;
+  __syncthreads();
+  if (slice != 0 || c >= C) return;
   float s = 0.f;
-  for (int i = 0; i < n; ++i) s += partial[(long long)i * C + c];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s += red[k][lane];
   if (out_fp32) {
     float* o = reinterpret_cast<float*>(out) + c;
     *o = accumulate ? *o + s : s;
@@ -351,7 +378,7 @@ TT_API int tt_colsum(const void* x, long long ldx, float* partial, int chunks, v
   dim3 g1((C / 8 + 255) / 256, chunks);
   colsum_stage1_kernel<<<g1, 256, 0, stream>>>((const bf16*)x, ldx, partial, rows, C, rpc);
   TT_LAUNCH_CHECK();
-  colsum_stage2_kernel<<<(C + 255) / 256, 256, 0, stream>>>(partial, out, chunks, C, out_fp32, accumulate);
+  colsum_stage2_kernel<<<(C + 31) / 32, 256, 0, stream>>>(partial, out, chunks, C, out_fp32, accumulate);
   TT_LAUNCH_CHECK();
   return 0;
 }
@@ -458,7 +485,7 @@ TT_API int tt_colsum_noalloc(const void* x, long long ldx, void* out, int out_fp
   // so stale contents from an earlier call are never observed.
   colsum_stage1_kernel<<<g1, 256, 0, stream>>>((const bf16*)x, ldx, partial, rows, C, rpc);
   TT_LAUNCH_CHECK();
-  colsum_stage2_kernel<<<(C + 255) / 256, 256, 0, stream>>>(partial, out, chunks, C, out_fp32, accumulate);
+  colsum_stage2_kernel<<<(C + 31) / 32, 256, 0, stream>>>(partial, out, chunks, C, out_fp32, accumulate);
   TT_LAUNCH_CHECK();
   return 0;
 }

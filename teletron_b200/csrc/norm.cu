@@ -144,6 +144,89 @@ adaln_fwd_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y
   }
 }
 
+// One row per warp (C = NV * 256, each lane holds NV 16-byte vectors): no block-wide barrier, eight rows per CTA in
+// flight.  The row-per-CTA kernel above reached a quarter of the copy bandwidth at C = 1536 (four barriers per 3 KB).
+template <int NV>
+__global__ void __launch_bounds__(NT, NV <= 6 ? 3 : 2)
+adaln_fwd_warp_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, long long ldy,
+                      const float* __restrict__ mul, const float* __restrict__ add, long long mod_ld,
+                      int plus_one, int rows, int rows_per_batch, float eps, float* __restrict__ mean_out,
+                      float* __restrict__ rstd_out) {
+  constexpr int C = NV * 256;
+  // the modulation rows of the first batch this CTA meets stay in shared memory: read from global for every row
+  // they are four times the bytes of the row itself
+  __shared__ __align__(16) float mod_s[2][C];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float invC = 1.f / (float)C;
+  const int first_row = blockIdx.x * (NT / 32);
+  const int cached_b = first_row < rows ? first_row / rows_per_batch : -1;
+  if (cached_b >= 0) {
+    for (int i = threadIdx.x; i < C; i += NT) {
+      const float mv = mul ? mul[(long long)cached_b * mod_ld + i] : (plus_one ? 0.f : 1.f);
+      mod_s[0][i] = plus_one ? 1.f + mv : mv;
+      mod_s[1][i] = add ? add[(long long)cached_b * mod_ld + i] : 0.f;
+    }
+  }
+  __syncthreads();
+  for (int row = first_row + warp; row < rows; row += gridDim.x * (NT / 32)) {
+    float v[NV][8];
+    float s = 0.f;
+    const bf16* xr = x + (long long)row * ldx;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) load8(xr + (lane + k * 32) * 8, v[k]);
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += v[k][j];
+    const float mean = warp_sum(s) * invC;
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float d = v[k][j] - mean;
+        s2 += d * d;
+      }
+    const float rstd = rsqrtf(warp_sum(s2) * invC + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    const int rb = row / rows_per_batch;
+    const long long mrow = (long long)rb * mod_ld;
+    bf16* yr = y + (long long)row * ldy;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c0 = (lane + k * 32) * 8;
+      float m[8], a[8], o[8];
+      if (rb == cached_b) {
+        loadf8(&mod_s[0][c0], m);
+        loadf8(&mod_s[1][c0], a);
+      } else {
+        if (mul) {
+          loadf8(mul + mrow + c0, m);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) m[j] = plus_one ? 0.f : 1.f;
+        }
+        if (plus_one) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) m[j] += 1.f;
+        }
+        if (add) {
+          loadf8(add + mrow + c0, a);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[j] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[k][j] - mean) * rstd * m[j] + a[j];
+      store8(yr + c0, o);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ AdaLN backward
 // grid = (chunks, batch). CTA (chunk, b) owns rows [b*rpb + chunk*rpc, min(.. + rpc, (b+1)*rpb)).
 template <int VPT>
@@ -235,17 +318,36 @@ adaln_bwd_kernel(const bf16* __restrict__ dy, long long lddy, const bf16* __rest
 }
 
 // out[g, c] (+)= sum_{i < n} partial[g*stride_g + i*stride_n + c]  (fixed order => deterministic)
-__global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
-                                       int groups, int n, int width, long long stride_g,
-                                       long long stride_n, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+// A CTA covers 32 columns; its 8 warps take every 8th partial row with four loads in flight each, then the 8 slice
+// sums are added in a fixed order (one thread walking all n rows took 47 us for n = 592).
+__global__ void __launch_bounds__(256)
+colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int groups, int n, int width,
+                       long long stride_g, long long stride_n, int accumulate) {
+  __shared__ float red[8][33];
+  const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   const int g = blockIdx.y;
-  if (c >= width || g >= groups) return;
-  const float* p = partial + (long long)g * stride_g + c;
-  float s = 0.f;
-  for (int i = 0; i < n; ++i) s += p[(long long)i * stride_n];
-  float* o = out + (long long)g * width + c;
-  *o = accumulate ? *o + s : s;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (c < width) {
+    const float* p = partial + (long long)g * stride_g + c;
+    int i = slice;
+    for (; i + 24 < n; i += 32) {
+      s0 += p[(long long)i * stride_n];
+      s1 += p[(long long)(i + 8) * stride_n];
+      s2 += p[(long long)(i + 16) * stride_n];
+      s3 += p[(long long)(i + 24) * stride_n];
+    }
+    for (; i < n; i += 8) s0 += p[(long long)i * stride_n];
+  }
+  red[slice][lane] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (slice == 0 && c < width) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][lane];
+    float* o = out + (long long)g * width + c;
+    *o = accumulate ? *o + t : t;
+  }
 }
 
 // ------------------------------------------------------------------ RMSNorm + RoPE
@@ -446,6 +548,30 @@ TT_API int tt_adaln_fwd(const void* x, long long ldx, void* y, long long ldy, co
   TT_CHECK(ldx % 8 == 0 && ldy % 8 == 0 && mod_ld % 4 == 0, "adaln_fwd: leading dims misaligned");
   TT_CHECK(aligned16(x) && aligned16(y) && aligned16(mul) && aligned16(add), "adaln_fwd: misaligned pointer");
   TT_CHECK(rows_per_batch > 0, "adaln_fwd: rows_per_batch must be positive");
+  if (C % 256 == 0 && C <= 3072) {  // one row per warp
+    const int want = (rows + NT / 32 - 1) / (NT / 32);
+    const int wgrid = want < 148 * 8 ? want : 148 * 8;
+#define TT_ADALN_WARP(NVV)                                                                                   \
+  adaln_fwd_warp_kernel<NVV><<<wgrid, NT, 0, stream>>>((const bf16*)x, ldx, (bf16*)y, ldy, mul, add, mod_ld, \
+                                                       plus_one, rows, rows_per_batch, eps, mean_out, rstd_out)
+    switch (C / 256) {
+      case 1: TT_ADALN_WARP(1); break;
+      case 2: TT_ADALN_WARP(2); break;
+      case 3: TT_ADALN_WARP(3); break;
+      case 4: TT_ADALN_WARP(4); break;
+      case 5: TT_ADALN_WARP(5); break;
+      case 6: TT_ADALN_WARP(6); break;
+      case 7: TT_ADALN_WARP(7); break;
+      case 8: TT_ADALN_WARP(8); break;
+      case 9: TT_ADALN_WARP(9); break;
+      case 10: TT_ADALN_WARP(10); break;
+      case 11: TT_ADALN_WARP(11); break;
+      default: TT_ADALN_WARP(12); break;
+    }
+#undef TT_ADALN_WARP
+    TT_LAUNCH_CHECK();
+    return 0;
+  }
   const int grid = rows < 148 * 16 ? rows : 148 * 16;
   TT_DISPATCH_VPT(vpt_for(C), adaln_fwd_kernel<VPT><<<grid, NT, 0, stream>>>(
       (const bf16*)x, ldx, (bf16*)y, ldy, mul, add, mod_ld, plus_one, rows, C, rows_per_batch, eps,
@@ -475,7 +601,7 @@ TT_API int tt_adaln_bwd(const void* dy, long long lddy, const void* x, long long
       (const bf16*)dx_add, ldadd, partial, C, rows_per_batch, rpc));
   TT_LAUNCH_CHECK();
   if (partial && (dmul || dadd)) {
-    dim3 g2((C + 255) / 256, batch);
+    dim3 g2((C + 31) / 32, batch);
     const long long sg = (long long)chunks * 2 * C, sn = 2ll * C;
     if (dmul) {
       colsum_partials_kernel<<<g2, 256, 0, stream>>>(partial, dmul, batch, chunks, C, sg, sn, accumulate);
@@ -492,7 +618,7 @@ TT_API int tt_adaln_bwd(const void* dy, long long lddy, const void* x, long long
 TT_API int tt_colsum_partials(const float* partial, float* out, int groups, int n, int width,
                               int accumulate, cudaStream_t stream) {
   TT_CHECK(groups > 0 && n > 0 && width > 0, "colsum_partials: bad shape");
-  dim3 grid((width + 255) / 256, groups);
+  dim3 grid((width + 31) / 32, groups);
   colsum_partials_kernel<<<grid, 256, 0, stream>>>(partial, out, groups, n, width, (long long)n * width, (long long)width, accumulate);
   TT_LAUNCH_CHECK();
   return 0;
