@@ -74,9 +74,57 @@ def _tp_case(a):
     dist.destroy_process_group()
 
 
+def _dpopt_case(a):
+    """Data-parallel gradient reduce-scatter + clip + AdamW + parameter all-gather of a flat buffer of ``--params``
+    million bf16 parameters with fp32 gradients, under torchrun on the ranks of one box.  ``--fused``: the peer-memory
+    kernels (pull-reduce of the owned shard from every peer, AdamW, parameter store into every peer); otherwise NCCL
+    reduce-scatter / all-gather around the AdamW kernel.  Device time, max over ranks."""
+    import os
+
+    import torch.distributed as dist
+
+    from ..dist import SymmetricArena
+    from ..parallel.ddp import DistributedOptimizer, ParamBuffer
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dist.init_process_group("nccl")
+    n = a.params * 1_000_000
+    holder = torch.nn.Module()
+    rows = n // 4096
+    holder.w = torch.nn.Parameter(torch.zeros(rows, 4096, device="cuda", dtype=torch.bfloat16))
+    arena = SymmetricArena(dist.group.WORLD) if a.fused else None
+    buf = ParamBuffer(holder, shard_world=world, arena=arena)
+    opt = DistributedOptimizer(buf, dist.group.WORLD, lr=1e-4, weight_decay=0.01, clip_grad=1.0, sharded=True,
+                               grad_scale=1.0 / world)
+    buf.grads.normal_()
+
+    def step():
+        opt.reduce_gradients()
+        opt.step()
+
+    for _ in range(3):
+        step()
+    dist.barrier()
+    ms = _time(step, a.iters)
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    _lib.check_status()
+    if rank == 0:
+        numel = buf.numel
+        link_bytes = (world - 1) / world * numel * (4 + 2)     # fp32 gradient shards in, bf16 parameter shards out
+        hbm_bytes = numel * 4 + numel / world * (30 + 4)         # zero-fill excluded: read grads, AdamW on the shard
+        print(json.dumps(dict(case="dpopt", world=world, fused=bool(a.fused), params=numel, ms=float(t.item()),
+                              nvlink_gbs_per_dir=link_bytes / float(t.item()) / 1e6,
+                              hbm_gbs=hbm_bytes / float(t.item()) / 1e6)), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "attn", "norm", "layers", "tp"])
+    ap.add_argument("case", choices=["gemm", "attn", "norm", "layers", "tp", "dpopt"])
+    ap.add_argument("--params", type=int, default=1400, help="dpopt case: millions of parameters")
     ap.add_argument("--inner", type=int, default=12288, help="tp case: full inner width of the MLP")
     ap.add_argument("--fused", action="store_true", help="tp case: peer-memory kernels instead of NCCL")
     ap.add_argument("--layers", type=int, default=2)
@@ -96,6 +144,8 @@ def main():
     a = ap.parse_args()
     if a.case == "tp":
         return _tp_case(a)
+    if a.case == "dpopt":
+        return _dpopt_case(a)
     dev = "cuda"
     torch.manual_seed(0)
     res = dict(case=a.case)
