@@ -192,17 +192,18 @@ class SelfAttention(nn.Module, _FusedStateMixin):
             a2d = fu.attention(qkv[:, 0:C], qkv[:, C:2 * C], qkv[:, 2 * C:3 * C], self.norm_q.weight,
                                self.norm_k.weight, freqs, batch, rows_per_batch, H, D, self.eps)
             return ops.linear_residual(a2d, self.o.weight, self.o.bias, residual, gate, rows_per_batch)
+        S = rows_per_batch
+        if cp is None or cp.size == 1:
+            # norm + rope + attention as one autograd node on the three column blocks of qkv
+            a2d = ops.self_attention_core(qkv, self.norm_q.weight, self.norm_k.weight, freqs, batch, S, H, D, self.eps)
+            return ops.linear_residual(a2d, self.o.weight, self.o.bias, residual, gate, rows_per_batch)
         q = ops.rmsnorm_rope(qkv[:, 0:C], self.norm_q.weight, freqs, D, False, self.eps)
         k = ops.rmsnorm_rope(qkv[:, C:2 * C], self.norm_k.weight, freqs, D, False, self.eps)
         v = qkv[:, 2 * C:3 * C]
-        S = rows_per_batch
         q4 = q.view(batch, S, H, D)
         k4 = k.view(batch, S, H, D)
         v4 = v.unflatten(1, (H, D)).unflatten(0, (batch, S))
-        if cp is not None and cp.size > 1:
-            a = cp.attention(q4, k4, v4)
-        else:
-            a = ops.attention(q4, k4, v4)
+        a = cp.attention(q4, k4, v4)
         a2d = a.reshape(batch * S, C)
         return ops.linear_residual(a2d, self.o.weight, self.o.bias, residual, gate, rows_per_batch)
 
@@ -266,13 +267,15 @@ class DiTBlock(nn.Module):
     def forward(self, x2d, context, t_mod, freqs, batch: int, cp: Optional[UlyssesContext]):
         rows_per_batch = x2d.shape[0] // batch
         e = self.modulation.float() + t_mod  # [B, 6, C] fp32
-        h = ops.adaln(x2d, e[:, 1], e[:, 0], rows_per_batch, self.eps)
-        x2d = self.self_attn(h, freqs, batch, cp, x2d, e[:, 2], rows_per_batch)
-        h = ops.layernorm_affine(x2d, self.norm3.weight, self.norm3.bias, self.eps)
-        x2d = self.cross_attn(h, context, batch, x2d, rows_per_batch)
-        h = ops.adaln(x2d, e[:, 4], e[:, 3], rows_per_batch, self.eps)
+        # each norm also hands back its input for the residual branch, so that the residual's gradient is added
+        # inside the norm's backward kernel
+        h, xr = ops.adaln_res(x2d, e[:, 1], e[:, 0], rows_per_batch, self.eps)
+        x2d = self.self_attn(h, freqs, batch, cp, xr, e[:, 2], rows_per_batch)
+        h, xr = ops.layernorm_affine(x2d, self.norm3.weight, self.norm3.bias, self.eps, with_res=True)
+        x2d = self.cross_attn(h, context, batch, xr, rows_per_batch)
+        h, xr = ops.adaln_res(x2d, e[:, 4], e[:, 3], rows_per_batch, self.eps)
         f = ops.linear(h, self.ffn[0].weight, self.ffn[0].bias, act="gelu")
-        return ops.linear_residual(f, self.ffn[2].weight, self.ffn[2].bias, x2d, e[:, 5], rows_per_batch)
+        return ops.linear_residual(f, self.ffn[2].weight, self.ffn[2].bias, xr, e[:, 5], rows_per_batch)
 
 
 class ImageEmbedMLP(nn.Module):

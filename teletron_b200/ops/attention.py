@@ -61,17 +61,25 @@ def attention_fwd(q, k, v, scale=None, kv_lens=None):
     return o, lse
 
 
-def attention_bwd(q, k, v, o, lse, dout, scale=None, kv_lens=None):
-    """Gradients (dq, dk, dv), each [B,S,H,D] bf16 contiguous."""
+def attention_bwd(q, k, v, o, lse, dout, scale=None, kv_lens=None, out=None):
+    """Gradients (dq, dk, dv), each [B,S,H,D] bf16 contiguous, or written into the three views of ``out``
+    (any token / batch strides, unit stride over H x D)."""
     B, Sq, H, D = q.shape
     Skv = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     for t, n in ((q, "q"), (k, "k"), (v, "v"), (o, "o"), (dout, "dout")):
         _check_layout(t, n)
         assert t.dtype == torch.bfloat16
-    dq = torch.empty((B, Sq, H, D), dtype=torch.bfloat16, device=q.device)
-    dk = torch.empty((B, Skv, H, D), dtype=torch.bfloat16, device=q.device)
-    dv = torch.empty((B, Skv, H, D), dtype=torch.bfloat16, device=q.device)
+    if out is not None:
+        dq, dk, dv = out
+        for t, n in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+            _check_layout(t, n)
+            assert t.dtype == torch.bfloat16
+        assert dq.shape == q.shape and dk.shape == k.shape and dv.shape == v.shape
+    else:
+        dq = torch.empty((B, Sq, H, D), dtype=torch.bfloat16, device=q.device)
+        dk = torch.empty((B, Skv, H, D), dtype=torch.bfloat16, device=q.device)
+        dv = torch.empty((B, Skv, H, D), dtype=torch.bfloat16, device=q.device)
     L = _lib.lib()
     L.tt_attn_bwd_scratch_floats.restype = _lib.c_ll
     n_scratch = L.tt_attn_bwd_scratch_floats(_lib.c_int(B), _lib.c_int(H), _lib.c_int(Sq))
@@ -118,3 +126,61 @@ def attention(q, k, v, scale=None, kv_lens=None):
     if not q.is_cuda:
         return attention_ref(q, k, v, scale, kv_lens)[0]
     return _Attention.apply(q, k, v, scale, kv_lens)
+
+
+class _SelfAttnCore(torch.autograd.Function):
+    """attention(rope(rmsnorm(q) w_q), rope(rmsnorm(k) w_k), v) on the three column blocks of one [rows, 3C]
+    projection output, as one autograd node: the backward kernels write dq / dk / dv straight into the three
+    column blocks of one gradient tensor, so the slice-gradient zero fills, strided copies and adds that autograd
+    would otherwise launch (about 1 ms per Wan2.1-1.3B block) do not exist."""
+
+    @staticmethod
+    def forward(ctx, qkv, wq, wk, freqs, batch, S, H, D, eps):
+        from .norm import rmsrope_fwd_raw
+
+        C = H * D
+        assert qkv.dim() == 2 and qkv.shape == (batch * S, 3 * C) and qkv.stride(1) == 1
+        wqf, wkf = wq.float().contiguous(), wk.float().contiguous()
+        q, rq = rmsrope_fwd_raw(qkv[:, 0:C], wqf, freqs, D, False, eps)
+        k, rk = rmsrope_fwd_raw(qkv[:, C:2 * C], wkf, freqs, D, False, eps)
+        v4 = qkv[:, 2 * C:3 * C].unflatten(1, (H, D)).unflatten(0, (batch, S))
+        q4, k4 = q.view(batch, S, H, D), k.view(batch, S, H, D)
+        o, lse = attention_fwd(q4, k4, v4)
+        ctx.save_for_backward(qkv, wqf, wkf, freqs, rq, rk, q, k, o, lse)
+        ctx.meta = (batch, S, H, D, wq.dtype)
+        return o.view(batch * S, C)
+
+    @staticmethod
+    def backward(ctx, do):
+        from .norm import rmsrope_bwd_raw
+
+        qkv, wqf, wkf, freqs, rq, rk, q, k, o, lse = ctx.saved_tensors
+        batch, S, H, D, wdtype = ctx.meta
+        C = H * D
+        if do.stride(1) != 1 or do.stride(0) != C:
+            do = do.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dqn = torch.empty((batch, S, H, D), dtype=torch.bfloat16, device=qkv.device)
+        dkn = torch.empty_like(dqn)
+        dv_view = dqkv[:, 2 * C:3 * C].unflatten(1, (H, D)).unflatten(0, (batch, S))
+        v4 = qkv[:, 2 * C:3 * C].unflatten(1, (H, D)).unflatten(0, (batch, S))
+        attention_bwd(q.view(batch, S, H, D), k.view(batch, S, H, D), v4, o, lse, do.view(batch, S, H, D),
+                      out=(dqn, dkn, dv_view))
+        _, dwq = rmsrope_bwd_raw(dqn.view(batch * S, C), qkv[:, 0:C], wqf, freqs, rq, D, False, out=dqkv[:, 0:C])
+        _, dwk = rmsrope_bwd_raw(dkn.view(batch * S, C), qkv[:, C:2 * C], wkf, freqs, rk, D, False,
+                                 out=dqkv[:, C:2 * C])
+        return dqkv, dwq.to(wdtype), dwk.to(wdtype), None, None, None, None, None, None
+
+
+def self_attention_core(qkv, wq, wk, freqs, batch, S, H, D, eps=1e-6):
+    """Self-attention of a Wan block from the fused projection output ``qkv`` [batch * S, 3 H D] (full-row RMSNorm
+    and rotary embedding on q and k): returns [batch * S, H D]."""
+    if not qkv.is_cuda:
+        from .norm import rmsnorm_rope
+
+        C = H * D
+        q = rmsnorm_rope(qkv[:, 0:C], wq, freqs, D, False, eps).view(batch, S, H, D)
+        k = rmsnorm_rope(qkv[:, C:2 * C], wk, freqs, D, False, eps).view(batch, S, H, D)
+        v = qkv[:, 2 * C:3 * C].unflatten(1, (H, D)).unflatten(0, (batch, S))
+        return attention(q, k, v).reshape(batch * S, C)
+    return _SelfAttnCore.apply(qkv, wq, wk, freqs, batch, S, H, D, eps)

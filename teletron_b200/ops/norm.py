@@ -39,8 +39,11 @@ def adaln_ref(x, scale, shift, rows_per_batch, eps=1e-6, plus_one=True):
 
 
 class _AdaLN(torch.autograd.Function):
+    """``with_res``: also return x itself as a second output (an alias) for the residual connection, so that
+    the residual's gradient arrives here and is added inside the backward kernel (no separate add kernel)."""
+
     @staticmethod
-    def forward(ctx, x, scale, shift, rows_per_batch, eps, plus_one):
+    def forward(ctx, x, scale, shift, rows_per_batch, eps, plus_one, with_res=False):
         rows, C = x.shape
         assert x.dtype == torch.bfloat16 and x.stride(1) == 1
         for m in (scale, shift):
@@ -61,16 +64,22 @@ class _AdaLN(torch.autograd.Function):
         _lib.check(rc, "tt_adaln_fwd")
         ctx.save_for_backward(x, mean, rstd, scale)
         ctx.meta = (rows_per_batch, plus_one, batch, mod_ld, shift is not None)
+        if with_res:
+            return y, x.view_as(x)
         return y
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dres=None):
         x, mean, rstd, scale = ctx.saved_tensors
         rows_per_batch, plus_one, batch, mod_ld, has_shift = ctx.meta
         rows, C = x.shape
         assert rows == batch * rows_per_batch, "adaln backward needs rows == batch * rows_per_batch"
+        if dy is None:  # only the residual alias was used
+            return dres, None, None, None, None, None, None
         if dy.stride(1) != 1:
             dy = dy.contiguous()
+        if dres is not None and (dres.dtype != torch.bfloat16 or dres.stride(1) != 1):
+            dres = dres.to(torch.bfloat16).contiguous()
         dx = torch.empty((rows, C), dtype=torch.bfloat16, device=x.device)
         want_mod = (scale is not None and ctx.needs_input_grad[1]) or (has_shift and ctx.needs_input_grad[2])
         chunks = _chunks(rows_per_batch, batch)
@@ -82,11 +91,12 @@ class _AdaLN(torch.autograd.Function):
         rc = _lib.lib().tt_adaln_bwd(
             _lib.ptr(dy), _lib.c_ll(dy.stride(0)), _lib.ptr(x), _lib.c_ll(x.stride(0)), _lib.ptr(mean),
             _lib.ptr(rstd), _lib.ptr(scale), _lib.c_ll(mod_ld), _lib.c_int(int(plus_one)), _lib.ptr(dx),
-            _lib.c_ll(C), _lib.ptr(None), _lib.c_ll(0), _lib.ptr(partial), _lib.c_int(chunks),
+            _lib.c_ll(C), _lib.ptr(dres), _lib.c_ll(dres.stride(0) if dres is not None else 0), _lib.ptr(partial),
+            _lib.c_int(chunks),
             _lib.ptr(dmul), _lib.ptr(dadd), _lib.c_int(0), _lib.c_int(batch), _lib.c_int(rows_per_batch),
             _lib.c_int(C), _lib.stream())
         _lib.check(rc, "tt_adaln_bwd")
-        return dx, dmul, dadd, None, None, None
+        return dx, dmul, dadd, None, None, None, None
 
 
 def adaln(x, scale, shift, rows_per_batch, eps=1e-6, plus_one=True):
@@ -96,11 +106,21 @@ def adaln(x, scale, shift, rows_per_batch, eps=1e-6, plus_one=True):
     return _AdaLN.apply(x, scale, shift, rows_per_batch, eps, plus_one)
 
 
-def layernorm_affine(x, weight, bias, eps=1e-6):
+def adaln_res(x, scale, shift, rows_per_batch, eps=1e-6, plus_one=True):
+    """(adaln(x), x): the second value is x for the residual branch; its gradient is added to the norm's input
+    gradient inside the backward kernel."""
+    if not x.is_cuda:
+        return adaln_ref(x, scale, shift, rows_per_batch, eps, plus_one), x
+    return _AdaLN.apply(x, scale, shift, rows_per_batch, eps, plus_one, True)
+
+
+def layernorm_affine(x, weight, bias, eps=1e-6, with_res=False):
     """nn.LayerNorm with affine parameters (Wan ``norm3``) through the AdaLN kernel."""
     rows = x.shape[0]
     w = weight.float().unsqueeze(0) if weight is not None else None
     b = bias.float().unsqueeze(0) if bias is not None else None
+    if with_res:
+        return adaln_res(x, w, b, rows, eps, plus_one=False)
     return adaln(x, w, b, rows, eps, plus_one=False)
 
 
@@ -134,23 +154,30 @@ def rmsnorm_rope_ref(x, weight, freqs, D, per_head=False, eps=1e-6):
     return xf.to(x.dtype)
 
 
+def rmsrope_fwd_raw(x, wf, freqs, D, per_head=False, eps=1e-6):
+    """rope(rmsnorm(x) * wf) without autograd: returns (y bf16 [rows, C], rstd fp32 or None). ``x`` may be a
+    column slice of a wider tensor (row stride > C)."""
+    rows, C = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1
+    if freqs is not None:
+        assert freqs.dtype == torch.float32 and freqs.is_contiguous() and freqs.shape[1:] == (D // 2, 2)
+    y = torch.empty((rows, C), dtype=torch.bfloat16, device=x.device)
+    rstd = None
+    if wf is not None:
+        rstd = torch.empty(rows * (C // D if per_head else 1), dtype=torch.float32, device=x.device)
+    rc = _lib.lib().tt_rmsrope_fwd(
+        _lib.ptr(x), _lib.c_ll(x.stride(0)), _lib.ptr(y), _lib.c_ll(C), _lib.ptr(wf), _lib.ptr(freqs),
+        _lib.c_int(freqs.shape[0] if freqs is not None else 1), _lib.ptr(rstd), _lib.c_int(rows),
+        _lib.c_int(C), _lib.c_int(D), _lib.c_int(int(per_head)), _lib.c_float(eps), _lib.stream())
+    _lib.check(rc, "tt_rmsrope_fwd")
+    return y, rstd
+
+
 class _RmsRope(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, freqs, D, per_head, eps):
-        rows, C = x.shape
-        assert x.dtype == torch.bfloat16 and x.stride(1) == 1
         wf = weight.float().contiguous() if weight is not None else None
-        if freqs is not None:
-            assert freqs.dtype == torch.float32 and freqs.is_contiguous() and freqs.shape[1:] == (D // 2, 2)
-        y = torch.empty((rows, C), dtype=torch.bfloat16, device=x.device)
-        rstd = None
-        if weight is not None:
-            rstd = torch.empty(rows * (C // D if per_head else 1), dtype=torch.float32, device=x.device)
-        rc = _lib.lib().tt_rmsrope_fwd(
-            _lib.ptr(x), _lib.c_ll(x.stride(0)), _lib.ptr(y), _lib.c_ll(C), _lib.ptr(wf), _lib.ptr(freqs),
-            _lib.c_int(freqs.shape[0] if freqs is not None else 1), _lib.ptr(rstd), _lib.c_int(rows),
-            _lib.c_int(C), _lib.c_int(D), _lib.c_int(int(per_head)), _lib.c_float(eps), _lib.stream())
-        _lib.check(rc, "tt_rmsrope_fwd")
+        y, rstd = rmsrope_fwd_raw(x, wf, freqs, D, per_head, eps)
         ctx.save_for_backward(x, wf, freqs, rstd)
         ctx.meta = (D, per_head, weight.dtype if weight is not None else None)
         return y
@@ -163,12 +190,14 @@ class _RmsRope(torch.autograd.Function):
         return dx, (dw.to(wdtype) if dw is not None else None), None, None, None, None
 
 
-def rmsrope_bwd_raw(dy, x, wf, freqs, rstd, D, per_head=False):
-    """Backward of rope(rmsnorm(x) * w) from the saved input and rstd: returns (dx bf16, dw fp32 or None)."""
+def rmsrope_bwd_raw(dy, x, wf, freqs, rstd, D, per_head=False, out=None):
+    """Backward of rope(rmsnorm(x) * w) from the saved input and rstd: returns (dx bf16, dw fp32 or None).
+    ``out``: optional [rows, C] view (any row stride) that receives dx."""
     rows, C = x.shape
     if dy.stride(1) != 1:
         dy = dy.contiguous()
-    dx = torch.empty((rows, C), dtype=torch.bfloat16, device=x.device)
+    dx = out if out is not None else torch.empty((rows, C), dtype=torch.bfloat16, device=x.device)
+    assert dx.shape == (rows, C) and dx.stride(1) == 1 and dx.dtype == torch.bfloat16
     L = _lib.lib()
     partial = None
     ctas = L.tt_rmsrope_bwd_ctas(_lib.c_int(rows))
@@ -176,7 +205,7 @@ def rmsrope_bwd_raw(dy, x, wf, freqs, rstd, D, per_head=False):
         partial = torch.empty((ctas, C), dtype=torch.float32, device=x.device)
     rc = L.tt_rmsrope_bwd(
         _lib.ptr(dy), _lib.c_ll(dy.stride(0)), _lib.ptr(x), _lib.c_ll(x.stride(0)), _lib.ptr(dx),
-        _lib.c_ll(C), _lib.ptr(wf), _lib.ptr(freqs), _lib.c_int(freqs.shape[0] if freqs is not None else 1),
+        _lib.c_ll(dx.stride(0)), _lib.ptr(wf), _lib.ptr(freqs), _lib.c_int(freqs.shape[0] if freqs is not None else 1),
         _lib.ptr(rstd), _lib.ptr(partial), _lib.c_int(rows), _lib.c_int(C), _lib.c_int(D),
         _lib.c_int(int(per_head)), _lib.stream())
     _lib.check(rc, "tt_rmsrope_bwd")
