@@ -337,15 +337,17 @@ class DualStreamBlock(nn.Module):
     def forward(self, xv, xt, temb, freqs, B, cp, text_lens):
         rv, rt = xv.shape[0] // B, xt.shape[0] // B
         ev, et = self.norm1(temb), self.norm1_context(temb)
-        hv = ops.adaln(xv, ev[:, 1], ev[:, 0], rv, self.eps)
-        ht = ops.adaln(xt, et[:, 1], et[:, 0], rt, self.eps)
+        # each norm hands its input back for the residual branch: the residual's gradient is then added inside
+        # the norm's backward kernel instead of by a separate add
+        hv, xv = ops.adaln_res(xv, ev[:, 1], ev[:, 0], rv, self.eps)
+        ht, xt = ops.adaln_res(xt, et[:, 1], et[:, 0], rt, self.eps)
         qv, kv, vv = self.attn.qkv(hv, freqs, False, B)
         qt, kt, vt = self.attn.qkv(ht, None, True, B)
         ov, ot = joint_attention(qv, kv, vv, qt, kt, vt, cp, text_lens)
         xv = _project_out(self.attn.to_out[0], ov.reshape(-1, ov.shape[2] * ov.shape[3]), xv, ev[:, 2], rv)
         xt = _project_out(self.attn.to_add_out, ot.reshape(-1, ot.shape[2] * ot.shape[3]), xt, et[:, 2], rt)
-        hv = ops.adaln(xv, ev[:, 4], ev[:, 3], rv, self.eps)
-        ht = ops.adaln(xt, et[:, 4], et[:, 3], rt, self.eps)
+        hv, xv = ops.adaln_res(xv, ev[:, 4], ev[:, 3], rv, self.eps)
+        ht, xt = ops.adaln_res(xt, et[:, 4], et[:, 3], rt, self.eps)
         xv = _gated_residual(self.ff(hv), xv, ev[:, 5], rv)
         xt = _gated_residual(self.ff_context(ht), xt, et[:, 5], rt)
         return xv, xt
@@ -374,8 +376,8 @@ class SingleStreamBlock(nn.Module):
     def forward(self, xv, xt, temb, freqs, B, cp, text_lens):
         rv, rt = xv.shape[0] // B, xt.shape[0] // B
         e = self.norm(temb)  # shift, scale, gate
-        hv = ops.adaln(xv, e[:, 1], e[:, 0], rv, self.eps)
-        ht = ops.adaln(xt, e[:, 1], e[:, 0], rt, self.eps)
+        hv, xv = ops.adaln_res(xv, e[:, 1], e[:, 0], rv, self.eps)
+        ht, xt = ops.adaln_res(xt, e[:, 1], e[:, 0], rt, self.eps)
         qv, kv, vv = self.attn.qkv(hv, freqs, False, B)
         qt, kt, vt = self.attn.qkv(ht, None, False, B)
         ov, ot = joint_attention(qv, kv, vv, qt, kt, vt, cp, text_lens)
