@@ -1,0 +1,320 @@
+// K-GEMM on CTA pairs: the same contract as gemm.cu (C = epilogue(alpha * A * B^T), either operand K-major or
+// MN-major) with tcgen05.mma.cta_group::2.  A cluster of two CTAs owns a 256 x 256 output tile: each CTA loads its
+// own 128 rows of A and one 128-row half of the B tile, the leader CTA's MMA thread issues 256 x 256 x 16
+// instructions that read A from each CTA's shared memory and the two B halves from both, and each CTA's tensor
+// memory receives its 128 rows of the accumulator.
+//
+// Why: with one CTA per 128 x 256 tile a 64-deep stage needs 48 KB of operand reads and 48 KB of TMA writes per 512
+// clocks of tensor work, 192 B/clock against the 128 B/clock of shared memory, which caps the one-CTA kernel at about
+// two thirds of the tensor peak (measured: 0.67 at K = 8960).  Here a stage is 32 KB per CTA: 128 B/clock.
+//
+// Roles per CTA (320 threads): warp 0 TMA producer (both CTAs; completions of both land on the leader's barrier),
+// warp 1 allocates tensor memory (both CTAs) and issues the MMAs (leader only), warps 2..9 epilogue.  Stage-free and
+// accumulator-ready signals reach both CTAs through tcgen05.commit with a CTA mask; the epilogue warps of both CTAs
+// arrive on the leader's accumulator-free barrier.  Every wait is bounded.
+#include "gemm_epilogue.cuh"
+
+using namespace tt;
+using namespace tt_gemm;
+
+namespace {
+
+constexpr int BN2 = 256;
+constexpr int STAGES2 = 6;
+constexpr int B_HALF_BYTES = 128 * BK * 2;
+constexpr int STAGE2_BYTES = A_BYTES + B_HALF_BYTES;  // 32 KB per CTA and stage
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 256 + 1024;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrives on the barrier at this shared-memory offset in every CTA of `mask` once all MMAs issued so far are done
+__device__ __forceinline__ void tc_commit2(uint64_t* bar, uint16_t mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(mask)
+      : "memory");
+}
+template <uint32_t HI_A, uint32_t HI_B>
+__device__ __forceinline__ void umma2_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 ad, bd;\n\t"
+      "mov.b64 ad, {%1, %5};\n\t"
+      "mov.b64 bd, {%2, %6};\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], ad, bd, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "n"(HI_A), "n"(HI_B)
+      : "memory");
+}
+// TMA load into this CTA's shared memory whose completion bytes are counted on a barrier given as a
+// shared::cluster address (the leader's)
+__device__ __forceinline__ void tma2_load_2d(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0,
+                                             int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+      "%4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+template <int A_MN, int B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE2_BYTES);  // used in the leader only
+  uint64_t* empty = full + STAGES2;   // both CTAs (tcgen05.commit with mask 0b11)
+  uint64_t* tfull = empty + STAGES2;  // both CTAs
+  uint64_t* tempty = tfull + 2;       // leader only: 8 local + 8 remote epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.N + BN2 - 1) / BN2;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 16);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, 512);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anybody signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int m0 = (tile / tiles_n) * 2 * BM + (int)cta * BM;
+        const int n0 = (tile % tiles_n) * BN2 + (int)cta * 128;  // this CTA's half of the B tile
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES2;
+          const uint32_t ph = (it / STAGES2) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, TT_ST_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * STAGE2_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          if (cta == 0) mbar_expect_tx(&full[s], 2 * STAGE2_BYTES);  // both CTAs' copies count on the leader's barrier
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma2_load_2d(sa + i * 8192, &tmA, bar, m0 + i * 64, k0);
+          } else {
+            tma2_load_2d(sa, &tmA, bar, k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) tma2_load_2d(sb + i * 8192, &tmB, bar, n0 + i * 64, k0);
+          } else {
+            tma2_load_2d(sb, &tmB, bar, k0, n0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && cta == 0) {
+      constexpr uint32_t idesc = umma_idesc(2 * BM, BN2, A_MN, B_MN);
+      constexpr uint32_t HI = umma_desc_hi(1024);
+      int it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tcount) {
+        const int a = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tempty[a], aph ^ 1, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 1)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + a * BN2;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES2;
+          const uint32_t ph = (it / STAGES2) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 2)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + s * STAGE2_BYTES);
+          const uint32_t a_lo = umma_desc_lo(a_base, A_MN ? 8192 : 16);
+          const uint32_t b_lo = umma_desc_lo(a_base + A_BYTES, B_MN ? 8192 : 16);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma2_ss_lo<HI, HI>(d_tmem, a_lo + k * ((A_MN ? 2048 : 32) >> 4), b_lo + k * ((B_MN ? 2048 : 32) >> 4),
+                                idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit2(&empty[s], 3);
+        }
+        if (ok) tc_commit2(&tfull[a], 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;
+    const int eg = (warp - 2) >> 2;
+    const uint32_t tempty_leader0 = map_to_cta(smem_u32(&tempty[0]), 0);
+    int tcount = 0;
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++tcount) {
+      const int a = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      if (!mbar_wait(&tfull[a], aph, abort_flag, p.status, TT_ST_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      const int m0 = (tile / tiles_n) * 2 * BM + (int)cta * BM;
+      const int n0 = (tile % tiles_n) * BN2;
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      bf16* c_row = reinterpret_cast<bf16*>(p.C) + (long long)row * p.ldc;
+      epilogue_tile<BN2>(p, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN2), eg, row, row_ok, c_row, n0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader0 + a * 8);
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the partner may still be reading this CTA's shared memory through the pair's MMAs
+  if (warp == 1) tmem_dealloc2(tmem_base, 512);
+}
+
+template <int A_MN, int B_MN>
+int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms, cudaStream_t stream) {
+  auto kern = gemm2_kernel<A_MN, B_MN>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    TT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES));
+    attr_done = true;
+  }
+  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN2 - 1) / BN2);
+  // persistent: as many CTA pairs as can be resident at once (GPCs with an odd SM count leave an SM unpaired)
+  static int max_clusters = 0;
+  if (max_clusters == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sms, 1, 1);
+    cfg.blockDim = dim3(320, 1, 1);
+    cfg.dynamicSmemBytes = SMEM2_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    TT_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+    max_clusters = n > 0 ? n : 1;
+  }
+  int clusters = max_clusters < sms / 2 ? max_clusters : sms / 2;
+  if (tiles < clusters) clusters = tiles;
+  kern<<<2 * clusters, 320, SMEM2_BYTES, stream>>>(tmA, tmB, p);
+  TT_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace
+
+// Same arguments as tt_gemm_bf16 (without the CTA cap); shapes outside the pair kernel's domain return -3 so that
+// the caller can fall back: N must be at least 256 and a multiple of 8, bf16 or fp32 output.
+TT_API int tt_gemm2_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* C,
+                         long long ldc, int c_fp32, int M, int N, int K, const void* bias, int epi,
+                         const void* residual, long long ldr, const float* gate, long long gate_ld,
+                         int rows_per_gate, void* aux_out, float alpha, unsigned* status, cudaStream_t stream) {
+  if (N < 256 || M < 256) return -3;
+  TT_CHECK(M > 0 && N > 0 && K > 0 && N % 8 == 0, "gemm2: bad shape %d x %d x %d", M, N, K);
+  TT_CHECK(lda % 8 == 0 && ldb % 8 == 0, "gemm2: lda/ldb must be multiples of 8 elements");
+  TT_CHECK(ldc % (c_fp32 ? 4 : 8) == 0 && ((uintptr_t)C & 15) == 0, "gemm2: C misaligned");
+  TT_CHECK(epi >= 0 && epi <= 4, "gemm2: unknown epilogue %d", epi);
+  if (epi == EPI_GATE_RES) {
+    TT_CHECK(residual && gate && rows_per_gate > 0, "gemm2: gate/residual epilogue needs both tensors");
+    TT_CHECK(ldr % 8 == 0 && gate_ld % 4 == 0 && (((uintptr_t)residual | (uintptr_t)gate) & 15) == 0,
+             "gemm2: residual/gate misaligned");
+  }
+  if (bias) TT_CHECK(((uintptr_t)bias & 15) == 0, "gemm2: bias is not 16-byte aligned");
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[2], str[1];
+    uint32_t box[2];
+    if (a_mn) { dims[0] = (uint64_t)M; dims[1] = (uint64_t)K; box[0] = 64; box[1] = 64; }
+    else      { dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = 64; box[1] = BM; }
+    str[0] = (uint64_t)lda * 2;
+    if (tt_make_tmap(&tmA, A, 2, 2, dims, str, box, 1)) return -1;
+    if (b_mn) { dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 64; box[1] = 64; }
+    else      { dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = 64; box[1] = 128; }
+    str[0] = (uint64_t)ldb * 2;
+    if (tt_make_tmap(&tmB, B, 2, 2, dims, str, box, 1)) return -1;
+  }
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32;
+  p.bias = (const bf16*)bias; p.epi = epi;
+  p.residual = (const bf16*)residual; p.ldr = ldr;
+  p.gate = gate; p.gate_ld = gate_ld; p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1;
+  p.aux_out = (bf16*)aux_out; p.alpha = alpha; p.status = status;
+  p.world = 1;
+  int dev = 0, sms = 0;
+  TT_CUDA(cudaGetDevice(&dev));
+  TT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (!a_mn && !b_mn) return launch2<0, 0>(tmA, tmB, p, sms, stream);
+  if (!a_mn && b_mn) return launch2<0, 1>(tmA, tmB, p, sms, stream);
+  if (a_mn && b_mn) return launch2<1, 1>(tmA, tmB, p, sms, stream);
+  return launch2<1, 0>(tmA, tmB, p, sms, stream);
+}

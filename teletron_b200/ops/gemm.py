@@ -14,6 +14,19 @@ from . import _lib
 
 EPI_NONE, EPI_GELU, EPI_GATE_RES, EPI_ACCUM, EPI_SILU = 0, 1, 2, 3, 4
 
+# CTA-pair kernel (csrc/gemm2.cu, tcgen05.mma.cta_group::2) for outputs of at least 256 x 256; the one-CTA kernel
+# (csrc/gemm.cu) takes everything else.  TT_GEMM_PAIR=0 switches the pair kernel off.
+import os as _os
+
+_PAIR = _os.environ.get("TT_GEMM_PAIR", "1") != "0"
+
+
+def set_pair_gemm(on: bool) -> bool:
+    """Enable / disable the CTA-pair GEMM kernel; returns the previous setting."""
+    global _PAIR
+    old, _PAIR = _PAIR, bool(on)
+    return old
+
 
 def _logical(a: torch.Tensor, mn_major: bool) -> torch.Tensor:
     return a.t() if mn_major else a
@@ -88,6 +101,19 @@ def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, epi=EPI_NONE, residual=None
         assert residual.dtype == torch.bfloat16 and gate.dtype == torch.float32
         assert residual.shape == (M, N) and residual.stride(1) == 1 and gate.stride(-1) == 1
     L = _lib.lib()
+    if _PAIR and max_ctas == 0 and M >= 256 and N >= 256:
+        rc = L.tt_gemm2_bf16(
+            _lib.ptr(a), _lib.c_ll(a.stride(0)), _lib.c_int(int(a_mn)),
+            _lib.ptr(b), _lib.c_ll(b.stride(0)), _lib.c_int(int(b_mn)),
+            _lib.ptr(out), _lib.c_ll(out.stride(0)), _lib.c_int(int(out.dtype == torch.float32)),
+            _lib.c_int(M), _lib.c_int(N), _lib.c_int(K), _lib.ptr(bias), _lib.c_int(epi),
+            _lib.ptr(residual), _lib.c_ll(residual.stride(0) if residual is not None else 0),
+            _lib.ptr(gate), _lib.c_ll(gate.stride(0) if gate is not None else 0),
+            _lib.c_int(rows_per_gate), _lib.ptr(aux), _lib.c_float(alpha),
+            _lib.ptr(_lib.status_word(a.device)), _lib.stream())
+        if rc != -3:
+            _lib.check(rc, "tt_gemm2_bf16")
+            return (out, aux) if want_aux else out
     rc = L.tt_gemm_bf16(
         _lib.ptr(a), _lib.c_ll(a.stride(0)), _lib.c_int(int(a_mn)),
         _lib.ptr(b), _lib.c_ll(b.stride(0)), _lib.c_int(int(b_mn)),

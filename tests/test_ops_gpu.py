@@ -252,3 +252,62 @@ def test_gemm_rs_segments_on_one_device(world, seg, K, N, b_mn):
         ref = total[s_ * seg:(s_ + 1) * seg] + bias.float()
         assert rel(out, ref) < 4e-3
     _lib.check_status()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N_,K", [(520, 512, 192), (256, 776, 136), (1100, 264, 64)])
+def test_gemm_pair_kernel_layouts(a_mn, b_mn, M, N_, K):
+    """CTA-pair kernel (tcgen05.mma.cta_group::2) against the fp32 reference and the one-CTA kernel."""
+    G = importlib.import_module("teletron_b200.ops.gemm")
+    if a_mn:
+        M = (M + 7) // 8 * 8
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda").to(torch.bfloat16)
+    b = torch.randn((K, N_) if b_mn else (N_, K), device="cuda").to(torch.bfloat16)
+    old = G.set_pair_gemm(True)
+    try:
+        y2 = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+        G.set_pair_gemm(False)
+        y1 = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    finally:
+        G.set_pair_gemm(old)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    ref = G.gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    assert rel(y2, ref) < 4e-3
+    assert rel(y2, y1) < 1e-3
+
+
+@pytest.mark.parametrize("epi", ["gelu", "gate_res", "accum_fp32", "bias"])
+def test_gemm_pair_kernel_epilogues(epi):
+    G = importlib.import_module("teletron_b200.ops.gemm")
+    torch.manual_seed(1)
+    M, N_, K = 700, 512, 256
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(N_, K, device="cuda") * 0.1).to(torch.bfloat16)
+    bias = torch.randn(N_, device="cuda").to(torch.bfloat16)
+    kw = dict(bias=bias)
+    if epi == "gelu":
+        kw.update(epi=G.EPI_GELU, want_aux=True)
+    elif epi == "gate_res":
+        kw.update(epi=G.EPI_GATE_RES, residual=torch.randn(M, N_, device="cuda").to(torch.bfloat16),
+                  gate=torch.randn(2, N_, device="cuda"), rows_per_gate=350, want_aux=True)
+    elif epi == "accum_fp32":
+        kw = dict(epi=G.EPI_ACCUM)
+    outs = []
+    for pair in (True, False):
+        old = G.set_pair_gemm(pair)
+        try:
+            if epi == "accum_fp32":
+                o = torch.full((M, N_), 0.5, device="cuda", dtype=torch.float32)
+                G.gemm(a, b, out=o, **kw)
+                outs.append((o,))
+            else:
+                r = G.gemm(a, b, **kw)
+                outs.append(r if isinstance(r, tuple) else (r,))
+        finally:
+            G.set_pair_gemm(old)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    for x, y in zip(outs[0], outs[1]):
+        assert rel(x, y) < 1e-3
