@@ -658,37 +658,64 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
 // ===================================================================== preprocess
 // delta[b,h,q] = sum_d dO*O and lse2 = lse * log2(e), both written to [B,H,Sq_pad] buffers whose
-// padding rows hold 0 / 1e30 (so padded queries get probability 0). One warp per (b, q, h).
-__global__ void attn_preprocess_kernel(const bf16* __restrict__ o, long long ldo, long long o_bs,
-                                       const bf16* __restrict__ dout, long long lddo, long long do_bs,
-                                       const float* __restrict__ lse, float* __restrict__ lse2,
-                                       float* __restrict__ delta, int B, int H, int Sq, int Sq_pad) {
+// padding rows hold 0 / 1e30 (so padded queries get probability 0).  Sixteen lanes per (b, q, h) row with 16-byte
+// loads; a warp takes eight consecutive rows (2 KB of each tensor when the rows are dense) with all of its loads
+// in flight before the first is used.
+__global__ void __launch_bounds__(256)
+attn_preprocess_kernel(const bf16* __restrict__ o, long long ldo, long long o_bs, const bf16* __restrict__ dout,
+                       long long lddo, long long do_bs, const float* __restrict__ lse, float* __restrict__ lse2,
+                       float* __restrict__ delta, int B, int H, int Sq, int Sq_pad) {
   const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
+  const int sub = lane >> 4, l16 = lane & 15;
   const long long total = (long long)B * Sq_pad * H;
-  if (gw >= total) return;
-  const int hh = (int)(gw % H);
-  const long long t = gw / H;
-  const int qi = (int)(t % Sq_pad);
-  const int bb = (int)(t / Sq_pad);
-  const long long oidx = ((long long)bb * H + hh) * Sq_pad + qi;
-  if (qi >= Sq) {
-    if (lane == 0) {
-      delta[oidx] = 0.f;
-      lse2[oidx] = 1.0e30f;
+  uint4 av[4], dv[4];
+  long long oidx[4];
+  int state[4];  // 0: beyond the end, 1: padding row, 2: live row
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const long long R = gw * 8 + it * 2 + sub;
+    state[it] = 0;
+    av[it] = make_uint4(0, 0, 0, 0);
+    dv[it] = make_uint4(0, 0, 0, 0);
+    oidx[it] = 0;
+    if (R < total) {
+      const int hh = (int)(R % H);
+      const long long t = R / H;
+      const int qi = (int)(t % Sq_pad);
+      const int bb = (int)(t / Sq_pad);
+      oidx[it] = ((long long)bb * H + hh) * Sq_pad + qi;
+      state[it] = qi < Sq ? 2 : 1;
+      if (qi < Sq) {
+        av[it] = *reinterpret_cast<const uint4*>(o + bb * o_bs + (long long)qi * ldo + hh * 128 + l16 * 8);
+        dv[it] = *reinterpret_cast<const uint4*>(dout + bb * do_bs + (long long)qi * lddo + hh * 128 + l16 * 8);
+      }
     }
-    return;
   }
-  const bf16* op = o + bb * o_bs + (long long)qi * ldo + hh * 128 + lane * 4;
-  const bf16* dp = dout + bb * do_bs + (long long)qi * lddo + hh * 128 + lane * 4;
-  uint2 a = *reinterpret_cast<const uint2*>(op);
-  uint2 d = *reinterpret_cast<const uint2*>(dp);
-  float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), d0 = unpack_bf16(d.x), d1 = unpack_bf16(d.y);
-  float s = a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y;
-  s = warp_sum(s);
-  if (lane == 0) {
-    delta[oidx] = s;
-    lse2[oidx] = lse[((long long)bb * H + hh) * Sq + qi] * LOG2E;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const uint32_t* au = reinterpret_cast<const uint32_t*>(&av[it]);
+    const uint32_t* du = reinterpret_cast<const uint32_t*>(&dv[it]);
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = unpack_bf16(au[j]), d = unpack_bf16(du[j]);
+      s += a.x * d.x + a.y * d.y;
+    }
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (l16 == 0 && state[it] != 0) {
+      if (state[it] == 1) {
+        delta[oidx[it]] = 0.f;
+        lse2[oidx[it]] = 1.0e30f;
+      } else {
+        const long long per = (long long)Sq_pad;
+        const long long bh = oidx[it] / per;
+        const int qi = (int)(oidx[it] - bh * per);
+        delta[oidx[it]] = s;
+        lse2[oidx[it]] = lse[bh * Sq + qi] * LOG2E;
+      }
+    }
   }
 }
 
@@ -728,7 +755,7 @@ static int attn_bwd_impl(const void* q, long long ldq, long long q_bs, const voi
   float* lse2 = scratch;
   float* delta = scratch + (long long)B * H * Sq_pad;
   {
-    const long long warps = (long long)B * Sq_pad * H;
+    const long long warps = ((long long)B * Sq_pad * H + 7) / 8;  // eight rows per warp
     const int threads = 256;
     const long long blocks = (warps * 32 + threads - 1) / threads;
     attn_preprocess_kernel<<<(unsigned)blocks, threads, 0, stream>>>(

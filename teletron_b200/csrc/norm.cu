@@ -624,6 +624,150 @@ TT_API int tt_colsum_partials(const float* partial, float* out, int groups, int 
   return 0;
 }
 
+// ------------------------------------------------------------------ RMSNorm + RoPE, one row per warp
+// Full-row statistics only (Wan q / k norm), C = NV * 256: each lane holds NV 16-byte vectors of the row, the
+// reductions are warp shuffles, eight rows per CTA are in flight.  The row-per-CTA kernel above reached a third of the
+// copy bandwidth at C = 1536 (two block barriers per 3 KB row).  The weight row lives in shared memory.
+template <int NV>
+__global__ void __launch_bounds__(NT, 2)
+rmsrope_fwd_warp_kernel(const bf16* __restrict__ in, long long ldi, bf16* __restrict__ out, long long ldo,
+                        const float* __restrict__ w, const float2* __restrict__ freqs, int freq_rows,
+                        float* __restrict__ rstd_io, int rows, int D, float eps, const TTScatter sc) {
+  constexpr int C = NV * 256;
+  __shared__ __align__(16) float w_s[C];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int vec_per_head = D >> 3;
+  for (int i = threadIdx.x; i < C; i += NT) w_s[i] = w ? w[i] : 1.f;
+  __syncthreads();
+  for (int row = blockIdx.x * (NT / 32) + warp; row < rows; row += gridDim.x * (NT / 32)) {
+    float v[NV][8];
+    const float2* frow = freqs ? freqs + (long long)(row % freq_rows) * (D >> 1) : nullptr;
+    const bf16* xr = in + (long long)row * ldi;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) load8(xr + (lane + k * 32) * 8, v[k]);
+    float r = 1.f;
+    if (w) {
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < NV; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[k][j] * v[k][j];
+      r = rsqrtf(warp_sum(ss) / (float)C + eps);
+      if (lane == 0 && rstd_io) rstd_io[row] = r;
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int vec = lane + k * 32;
+      float o[8], wk[8];
+      loadf8(&w_s[vec * 8], wk);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[k][j] * r * wk[j];
+      if (frow) {
+        float cs[8];
+        loadf8(reinterpret_cast<const float*>(frow + (vec % vec_per_head) * 4), cs);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float c = cs[2 * j], sn = cs[2 * j + 1];
+          const float a = o[2 * j], b = o[2 * j + 1];
+          o[2 * j] = a * c - b * sn;
+          o[2 * j + 1] = a * sn + b * c;
+        }
+      }
+      if (sc.mode == 0) {
+        store8(out + (long long)row * ldo + vec * 8, o);
+      } else {  // all-to-all fused into the store: write straight into the owning peer's buffer
+        const int col = vec * 8;
+        const int hd = col / D;
+        store8(scatter_dst(sc, row / sc.S_l, row % sc.S_l, hd) + (col - hd * D), o);
+      }
+    }
+  }
+}
+
+// backward of the above.  Each warp keeps its weight-gradient sums in its own shared-memory slab (48 registers per
+// lane otherwise); at the end the CTA's eight slabs are added in a fixed order into one partial row.
+template <int NV>
+__global__ void __launch_bounds__(NT, 2)
+rmsrope_bwd_warp_kernel(const bf16* __restrict__ dy, long long lddy, const bf16* __restrict__ xsave, long long ldx,
+                        bf16* __restrict__ dx, long long lddx, const float* __restrict__ w,
+                        const float2* __restrict__ freqs, int freq_rows, const float* __restrict__ rstd_io,
+                        float* __restrict__ partial, int rows, int D) {
+  constexpr int C = NV * 256;
+  extern __shared__ __align__(16) float dyn_s[];   // [1 + 8 warps][C]: weight row, then one slab per warp
+  float* w_s = dyn_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* acc_s = dyn_s + (1 + warp) * C;
+  const int vec_per_head = D >> 3;
+  for (int i = threadIdx.x; i < C; i += NT) w_s[i] = w ? w[i] : 1.f;
+  for (int i = threadIdx.x; i < (NT / 32) * C; i += NT) dyn_s[C + i] = 0.f;
+  __syncthreads();
+  for (int row = blockIdx.x * (NT / 32) + warp; row < rows; row += gridDim.x * (NT / 32)) {
+    float v[NV][8], xh[NV][8];
+    const float2* frow = freqs ? freqs + (long long)(row % freq_rows) * (D >> 1) : nullptr;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int vec = lane + k * 32;
+      load8(dy + (long long)row * lddy + vec * 8, v[k]);
+      if (w) load8(xsave + (long long)row * ldx + vec * 8, xh[k]);
+    }
+    if (frow) {
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        float cs[8];
+        loadf8(reinterpret_cast<const float*>(frow + ((lane + k * 32) % vec_per_head) * 4), cs);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float c = cs[2 * j], sn = cs[2 * j + 1];
+          const float a = v[k][2 * j], b = v[k][2 * j + 1];
+          v[k][2 * j] = a * c + b * sn;
+          v[k][2 * j + 1] = -a * sn + b * c;
+        }
+      }
+    }
+    if (w) {
+      const float r = rstd_io[row];
+      float dot = 0.f;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int c0 = (lane + k * 32) * 8;
+        float wk[8], ak[8];
+        loadf8(&w_s[c0], wk);
+        loadf8(&acc_s[c0], ak);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[k][j] *= r;
+          ak[j] += v[k][j] * xh[k][j];
+          v[k][j] *= wk[j];
+          dot += v[k][j] * xh[k][j];
+        }
+        *reinterpret_cast<float4*>(&acc_s[c0]) = make_float4(ak[0], ak[1], ak[2], ak[3]);
+        *reinterpret_cast<float4*>(&acc_s[c0 + 4]) = make_float4(ak[4], ak[5], ak[6], ak[7]);
+      }
+      const float sdot = warp_sum(dot) / (float)C;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = r * (v[k][j] - xh[k][j] * sdot);
+        store8(dx + (long long)row * lddx + (lane + k * 32) * 8, o);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < NV; ++k) store8(dx + (long long)row * lddx + (lane + k * 32) * 8, v[k]);
+    }
+  }
+  if (partial && w) {
+    __syncthreads();
+    float* pw = partial + (long long)blockIdx.x * C;
+    for (int c = threadIdx.x; c < C; c += NT) {
+      float t = 0.f;
+#pragma unroll
+      for (int ww = 0; ww < NT / 32; ++ww) t += dyn_s[(1 + ww) * C + c];
+      pw[c] = t;
+    }
+  }
+}
+
 // Forward: in = x. Saves rstd ([rows] or [rows, H]) when w != null.
 static int rmsrope_fwd_impl(const void* x, long long ldx, void* y, long long ldy, const float* w,
                             const void* freqs, int freq_rows, float* rstd, int rows, int C, int D,
@@ -633,6 +777,26 @@ static int rmsrope_fwd_impl(const void* x, long long ldx, void* y, long long ldy
   TT_CHECK(freqs == nullptr || (D % 8 == 0 && freq_rows > 0), "rmsrope_fwd: bad rotary table");
   TT_CHECK(ldx % 8 == 0 && ldy % 8 == 0, "rmsrope_fwd: leading dims misaligned");
   TT_CHECK(aligned16(x) && aligned16(y) && aligned16(w) && aligned16(freqs), "rmsrope_fwd: misaligned pointer");
+  if (!per_head && C % 256 == 0 && C <= 2048) {  // one row per warp
+    const int want = (rows + NT / 32 - 1) / (NT / 32);
+    const int wgrid = want < 148 * 8 ? want : 148 * 8;
+#define TT_RMS_FWD_WARP(NVV)                                                                                        \
+  rmsrope_fwd_warp_kernel<NVV><<<wgrid, NT, 0, stream>>>((const bf16*)x, ldx, (bf16*)y, ldy, w, (const float2*)freqs, \
+                                                         freq_rows, rstd, rows, D, eps, sc)
+    switch (C / 256) {
+      case 1: TT_RMS_FWD_WARP(1); break;
+      case 2: TT_RMS_FWD_WARP(2); break;
+      case 3: TT_RMS_FWD_WARP(3); break;
+      case 4: TT_RMS_FWD_WARP(4); break;
+      case 5: TT_RMS_FWD_WARP(5); break;
+      case 6: TT_RMS_FWD_WARP(6); break;
+      case 7: TT_RMS_FWD_WARP(7); break;
+      default: TT_RMS_FWD_WARP(8); break;
+    }
+#undef TT_RMS_FWD_WARP
+    TT_LAUNCH_CHECK();
+    return 0;
+  }
   const int rpc = rows > 148 * 32 ? (rows + 148 * 16 - 1) / (148 * 16) : 1;
   const int grid = (rows + rpc - 1) / rpc;
   TT_DISPATCH_VPT(vpt_for(C), rmsrope_kernel<VPT, false><<<grid, NT, 0, stream>>>(
@@ -689,7 +853,33 @@ TT_API int tt_rmsrope_bwd(const void* dy, long long lddy, const void* x, long lo
            "rmsrope_bwd: misaligned pointer");
   TT_CHECK(w == nullptr || (x != nullptr && rstd != nullptr), "rmsrope_bwd: norm backward needs x and rstd");
   const int rpc = (rows + 592 - 1) / 592;
-  const int grid = (rows + rpc - 1) / rpc;
+  const int grid = (rows + rpc - 1) / rpc;  // = tt_rmsrope_bwd_ctas(rows): the number of partial rows the caller folds
+  if (!per_head && C % 256 == 0 && C <= 2048) {  // one row per warp; every CTA writes its partial row (zeros if idle)
+    const int dyn = 9 * C * 4;  // weight row + eight per-warp gradient slabs
+#define TT_RMS_BWD_WARP(NVV)                                                                                            \
+  do {                                                                                                                  \
+    static bool attr_##NVV = false;                                                                                      \
+    if (!attr_##NVV) {                                                                                                   \
+      TT_CUDA(cudaFuncSetAttribute(rmsrope_bwd_warp_kernel<NVV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 9 * NVV * 256 * 4)); \
+      attr_##NVV = true;                                                                                                 \
+    }                                                                                                                   \
+    rmsrope_bwd_warp_kernel<NVV><<<grid, NT, dyn, stream>>>((const bf16*)dy, lddy, (const bf16*)x, ldx, (bf16*)dx, lddx, \
+                                                            w, (const float2*)freqs, freq_rows, rstd, partial, rows, D); \
+  } while (0)
+    switch (C / 256) {
+      case 1: TT_RMS_BWD_WARP(1); break;
+      case 2: TT_RMS_BWD_WARP(2); break;
+      case 3: TT_RMS_BWD_WARP(3); break;
+      case 4: TT_RMS_BWD_WARP(4); break;
+      case 5: TT_RMS_BWD_WARP(5); break;
+      case 6: TT_RMS_BWD_WARP(6); break;
+      case 7: TT_RMS_BWD_WARP(7); break;
+      default: TT_RMS_BWD_WARP(8); break;
+    }
+#undef TT_RMS_BWD_WARP
+    TT_LAUNCH_CHECK();
+    return 0;
+  }
   TT_DISPATCH_VPT(vpt_for(C), rmsrope_kernel<VPT, true><<<grid, NT, 0, stream>>>(
       (const bf16*)dy, lddy, (const bf16*)x, ldx, (bf16*)dx, lddx, w, (const float2*)freqs, freq_rows,
       rstd, partial, rows, C, D, per_head, 0.f, rpc, TTScatter{}));
