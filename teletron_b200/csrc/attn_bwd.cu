@@ -665,30 +665,32 @@ __global__ void __launch_bounds__(256)
 attn_preprocess_kernel(const bf16* __restrict__ o, long long ldo, long long o_bs, const bf16* __restrict__ dout,
                        long long lddo, long long do_bs, const float* __restrict__ lse, float* __restrict__ lse2,
                        float* __restrict__ delta, int B, int H, int Sq, int Sq_pad) {
-  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  // row counts stay below 2^31 (checked on the host), so the index arithmetic is 32-bit
+  const unsigned gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int sub = lane >> 4, l16 = lane & 15;
-  const long long total = (long long)B * Sq_pad * H;
+  const unsigned total = (unsigned)B * (unsigned)Sq_pad * (unsigned)H;
   uint4 av[4], dv[4];
-  long long oidx[4];
+  unsigned bh[4], qv[4];
   int state[4];  // 0: beyond the end, 1: padding row, 2: live row
 #pragma unroll
   for (int it = 0; it < 4; ++it) {
-    const long long R = gw * 8 + it * 2 + sub;
+    const unsigned R = gw * 8 + it * 2 + sub;
     state[it] = 0;
     av[it] = make_uint4(0, 0, 0, 0);
     dv[it] = make_uint4(0, 0, 0, 0);
-    oidx[it] = 0;
+    bh[it] = qv[it] = 0;
     if (R < total) {
-      const int hh = (int)(R % H);
-      const long long t = R / H;
-      const int qi = (int)(t % Sq_pad);
-      const int bb = (int)(t / Sq_pad);
-      oidx[it] = ((long long)bb * H + hh) * Sq_pad + qi;
-      state[it] = qi < Sq ? 2 : 1;
-      if (qi < Sq) {
-        av[it] = *reinterpret_cast<const uint4*>(o + bb * o_bs + (long long)qi * ldo + hh * 128 + l16 * 8);
-        dv[it] = *reinterpret_cast<const uint4*>(dout + bb * do_bs + (long long)qi * lddo + hh * 128 + l16 * 8);
+      const unsigned t = R / (unsigned)H;
+      const unsigned hh = R - t * (unsigned)H;
+      const unsigned bb = t / (unsigned)Sq_pad;
+      const unsigned qi = t - bb * (unsigned)Sq_pad;
+      bh[it] = bb * (unsigned)H + hh;
+      qv[it] = qi;
+      state[it] = qi < (unsigned)Sq ? 2 : 1;
+      if (qi < (unsigned)Sq) {
+        av[it] = *reinterpret_cast<const uint4*>(o + (long long)bb * o_bs + (long long)qi * ldo + hh * 128 + l16 * 8);
+        dv[it] = *reinterpret_cast<const uint4*>(dout + (long long)bb * do_bs + (long long)qi * lddo + hh * 128 + l16 * 8);
       }
     }
   }
@@ -705,15 +707,13 @@ attn_preprocess_kernel(const bf16* __restrict__ o, long long ldo, long long o_bs
 #pragma unroll
     for (int off = 8; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
     if (l16 == 0 && state[it] != 0) {
+      const long long oi = (long long)bh[it] * Sq_pad + qv[it];
       if (state[it] == 1) {
-        delta[oidx[it]] = 0.f;
-        lse2[oidx[it]] = 1.0e30f;
+        delta[oi] = 0.f;
+        lse2[oi] = 1.0e30f;
       } else {
-        const long long per = (long long)Sq_pad;
-        const long long bh = oidx[it] / per;
-        const int qi = (int)(oidx[it] - bh * per);
-        delta[oidx[it]] = s;
-        lse2[oidx[it]] = lse[bh * Sq + qi] * LOG2E;
+        delta[oi] = s;
+        lse2[oi] = lse[(long long)bh[it] * Sq + qv[it]] * LOG2E;
       }
     }
   }
@@ -755,6 +755,7 @@ static int attn_bwd_impl(const void* q, long long ldq, long long q_bs, const voi
   float* lse2 = scratch;
   float* delta = scratch + (long long)B * H * Sq_pad;
   {
+    TT_CHECK((long long)B * Sq_pad * H < (1ll << 31), "attn_bwd: too many (batch, token, head) rows");
     const long long warps = ((long long)B * Sq_pad * H + 7) / 8;  // eight rows per warp
     const int threads = 256;
     const long long blocks = (warps * 32 + threads - 1) / threads;
