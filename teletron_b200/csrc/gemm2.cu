@@ -21,6 +21,10 @@ namespace {
 
 constexpr int BN2 = 256;
 constexpr int STAGES2 = 6;
+#ifndef TT_GEMM2_ROUND
+#define TT_GEMM2_ROUND 3
+#endif
+constexpr int ROUND2 = TT_GEMM2_ROUND;  // stages consumed per wait / commit round of the MMA thread
 constexpr int B_HALF_BYTES = 128 * BK * 2;
 constexpr int STAGE2_BYTES = A_BYTES + B_HALF_BYTES;  // 32 KB per CTA and stage
 constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 256 + 1024;
@@ -181,22 +185,28 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         if (!mbar_wait(&tempty[a], aph ^ 1, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 1)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * BN2;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES2;
-          const uint32_t ph = (it / STAGES2) & 1;
-          if (!mbar_wait(&full[s], ph, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 2)) {
-            ok = false;
-            break;
+        // several stages per round: the waits and commits between groups of MMAs are what lets the tensor pipe run
+        // dry, so they are taken for 4 * ROUND2 MMAs at a time
+        for (int kb = 0; kb < num_kb; kb += ROUND2) {
+          const int n_st = (kb + ROUND2 <= num_kb) ? ROUND2 : num_kb - kb;
+          int st[ROUND2];
+          for (int u = 0; u < n_st; ++u, ++it) {
+            st[u] = it % STAGES2;
+            const uint32_t ph = (it / STAGES2) & 1;
+            if (!mbar_wait(&full[st[u]], ph, abort_flag, p.status, TT_ST_TIMEOUT_MMA + 2)) ok = false;
           }
+          if (!ok) break;
           tc_fence_after();
-          const uint32_t a_base = smem_u32(smem + s * STAGE2_BYTES);
-          const uint32_t a_lo = umma_desc_lo(a_base, A_MN ? 8192 : 16);
-          const uint32_t b_lo = umma_desc_lo(a_base + A_BYTES, B_MN ? 8192 : 16);
+          for (int u = 0; u < n_st; ++u) {
+            const uint32_t a_base = smem_u32(smem + st[u] * STAGE2_BYTES);
+            const uint32_t a_lo = umma_desc_lo(a_base, A_MN ? 8192 : 16);
+            const uint32_t b_lo = umma_desc_lo(a_base + A_BYTES, B_MN ? 8192 : 16);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma2_ss_lo<HI, HI>(d_tmem, a_lo + k * ((A_MN ? 2048 : 32) >> 4), b_lo + k * ((B_MN ? 2048 : 32) >> 4),
-                                idesc, (kb | k) != 0 ? 1u : 0u);
-          tc_commit2(&empty[s], 3);
+            for (int k = 0; k < BK / 16; ++k)
+              umma2_ss_lo<HI, HI>(d_tmem, a_lo + k * ((A_MN ? 2048 : 32) >> 4), b_lo + k * ((B_MN ? 2048 : 32) >> 4),
+                                  idesc, ((kb + u) | k) != 0 ? 1u : 0u);
+          }
+          for (int u = 0; u < n_st; ++u) tc_commit2(&empty[st[u]], 3);
         }
         if (ok) tc_commit2(&tfull[a], 3);
       }
