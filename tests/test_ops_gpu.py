@@ -311,3 +311,24 @@ def test_gemm_pair_kernel_epilogues(epi):
     _lib.check_status()
     for x, y in zip(outs[0], outs[1]):
         assert rel(x, y) < 1e-3
+
+
+def test_attention_bwd_pair_dq_kernel_matches():
+    """The CTA-pair dQ kernel (cta_group::2, off by default) against the one-CTA kernel, ragged sizes included."""
+    L = _lib.lib()
+    torch.manual_seed(0)
+    for (B, Sq, Skv, H) in [(1, 520, 700, 2), (2, 384, 512, 1)]:
+        q, k, v = (torch.randn(B, S_, H, 128, device=DEV).to(torch.bfloat16) for S_ in (Sq, Skv, Skv))
+        o, lse = attention_fwd(q, k, v)
+        do = torch.randn_like(o)
+        outs = []
+        for pair in (0, 1):
+            old = L.tt_attn_bwd_set_pair(pair)
+            try:
+                outs.append(attention_bwd(q, k, v, o, lse, do))
+            finally:
+                L.tt_attn_bwd_set_pair(0 if old < 0 else old)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        for a, b_ in zip(outs[0], outs[1]):
+            assert rel(a, b_) < 2e-3
