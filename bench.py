@@ -32,6 +32,12 @@ FRAMES, HEIGHT, WIDTH = 81, 480, 832
 TOKENS_PER_SAMPLE = 21 * 30 * 52  # 32,760
 GLOBAL_BATCH = 8
 PUBLISHED_TOKENS_PER_S_PER_GPU = 1090.0  # 21.6 FPS/node on 16 x H800, read off ComparativeGraph.jpg
+PUBLISHED_720P_TOKENS_PER_S_PER_GPU = 567.0  # 4.8 FPS/node at 720P x 81, same chart
+
+
+def tokens_per_sample(frames: int, height: int, width: int) -> int:
+    """Latent frames x (H/16) x (W/16): 8x VAE, 4x temporal compression, patch (1, 2, 2)."""
+    return ((frames - 1) // 4 + 1) * (height // 16) * (width // 16)
 
 
 def clock_sampler_start(path: str):
@@ -98,17 +104,25 @@ def run_ours(a):
     assert world == a.gpus, f"WORLD_SIZE {world} != --gpus {a.gpus} (launch N > 1 under torchrun)"
     cp = a.cp
     dp = world // cp
+    frames, height, width, gbs = a.frames, a.height, a.width, a.global_batch
+    headline = (a.model == "wan2.1-1.3b-t2v" and (frames, height, width, gbs) == (FRAMES, HEIGHT, WIDTH, GLOBAL_BATCH))
+    tok_sample = tokens_per_sample(frames, height, width)
+    i2v = "i2v" in a.model
     argv = ["--model", "ParallelWanModel", "--model-preset", a.model, "--bf16", "--micro-batch-size", "1",
-            "--global-batch-size", str(GLOBAL_BATCH), "--train-iters", "1000000", "--lr", "1e-5",
+            "--global-batch-size", str(gbs), "--train-iters", "1000000", "--lr", "1e-5",
             "--weight-decay", "1e-2", "--clip-grad", "1.0", "--context-parallel-size", str(cp),
-            "--num-frames", str(FRAMES), "--video-resolution", str(HEIGHT), str(WIDTH), "--synthetic-latents",
+            "--num-frames", str(frames), "--video-resolution", str(height), str(width), "--synthetic-latents",
             "--log-interval", "1000000", "--seed", "1234"]
+    if i2v:
+        argv += ["--task-type", "i2v"]
+    if a.init_on_device or "14b" in a.model:
+        argv.append("--init-on-device")
     if world > 1:
         argv.append("--use-distributed-optimizer")
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     argv += ["--fused-comm", a.fused_comm]
     if a.recompute:
-        argv += ["--recompute-granularity", "full", "--recompute-method", "block", "--recompute-num-layers", "30"]
+        argv += ["--recompute-granularity", "full", "--recompute-method", "block", "--recompute-num-layers", "1000"]
     if a.layers:
         argv += ["--num-layers", str(a.layers)]
     targs = parse_args(argv=argv)
@@ -118,7 +132,7 @@ def run_ours(a):
     n_mb = targs.num_micro_batches
 
     # a small pool of distinct samples, kept both in pinned host memory and on the device
-    ds = SyntheticLatentDataset(FRAMES, HEIGHT, WIDTH, seed=1234 + rank)
+    ds = SyntheticLatentDataset(frames, height, width, i2v=i2v, seed=1234 + rank)
     pool_host = []
     for i in range(max(n_mb, 2)):
         it = ds[i]
@@ -167,18 +181,29 @@ def run_ours(a):
     clocks = clock_sampler_stop(proc, fh, clk_path, local) if rank == 0 else {}
     ms_e2e, _, last_loss = timed(pool_host, a.steps, read_loss=True)
     _lib.check_status()
-    tokens = GLOBAL_BATCH * TOKENS_PER_SAMPLE * a.steps
+    tokens = gbs * tok_sample * a.steps
     value = tokens / (ms_dev * 1e-3)
     e2e = tokens / (ms_e2e * 1e-3)
     if rank == 0:
+        cfg = getattr(trainer.model, "module", trainer.model).cfg
+        desc = (f"{a.model} ({cfg.num_layers} layers, dim {cfg.dim}, {cfg.num_heads}x{cfg.dim // cfg.num_heads} heads, "
+                f"ffn {cfg.ffn_dim})")
+        if headline:
+            metric, published = METRIC, PUBLISHED_TOKENS_PER_S_PER_GPU
+            desc = "Wan2.1-1.3B t2v (30 layers, dim 1536, 12x128 heads, ffn 8960)"
+        else:
+            metric = f"{a.model.replace('-', '_')}_{height}p{frames}f_train_tokens_per_s"
+            published = {(480, 832, 81): PUBLISHED_TOKENS_PER_S_PER_GPU,
+                         (720, 1280, 81): PUBLISHED_720P_TOKENS_PER_S_PER_GPU}.get((height, width, frames))
+        if a.layers:
+            desc = f"{a.model} truncated to {a.layers} layers (NOT the named config)"
         res = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+            "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": ms_dev / a.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": value / (PUBLISHED_TOKENS_PER_S_PER_GPU * world), "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": value / (published * world) if published else None, "dtype": "bf16", "data": "synthetic",
             "impl": "teletron_b200",
-            "config": {"model": "Wan2.1-1.3B t2v (30 layers, dim 1536, 12x128 heads, ffn 8960)" if not a.layers
-                       else f"Wan2.1-1.3B t2v truncated to {a.layers} layers (NOT the named config)",
-                       "global_batch": GLOBAL_BATCH, "seq_len": TOKENS_PER_SAMPLE,
+            "config": {"model": desc,
+                       "global_batch": gbs, "seq_len": tok_sample,
                        "parallelism": f"dp{dp}" + (f"xcp{cp}" if cp > 1 else ""), "micro_batches_per_step": n_mb,
                        "optimizer": "AdamW fp32 master" + (" (sharded)" if world > 1 else ""),
                        "recompute": "full" if a.recompute else "none",
@@ -186,10 +211,11 @@ def run_ours(a):
                                 getattr(getattr(getattr(trainer.model, "module", trainer.model), "cp", None), "fused", None))
                                 else ("nccl" if world > 1 else "none")),
                        "l2": "inputs and working set far larger than L2 (each step touches > 50 GB)",
-                       "baseline_note": "vs_baseline divides by 1.09k tokens/s/GPU read off the reference's H800 chart"},
+                       "baseline_note": "vs_baseline divides by the tokens/s/GPU read off the reference's H800 chart "
+                                        "(1.09k at 480P x 81, 0.57k at 720P x 81; model size not stated there)"},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps,
-                    "h2d_bytes_per_step": bytes_h2d_per_mb * GLOBAL_BATCH, "d2h_bytes_per_step": 4 * world,
+                    "h2d_bytes_per_step": bytes_h2d_per_mb * gbs, "d2h_bytes_per_step": 4 * world,
                     "last_loss": last_loss},
             "gpu_launches": launches,
         }
@@ -277,7 +303,7 @@ def run_reference(a):
     torch.cuda.synchronize()
     clocks = clock_sampler_stop(proc, fh, clk_path, local)
     ms = e0.elapsed_time(e1)
-    tokens = GLOBAL_BATCH * TOKENS_PER_SAMPLE * a.steps
+    tokens = gbs * tok_sample * a.steps
     value = tokens / (ms * 1e-3)
     print(json.dumps({
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
@@ -304,6 +330,11 @@ def main():
     ap.add_argument("--cp", type=int, default=1, help="Ulysses context-parallel size (rest is DP)")
     ap.add_argument("--recompute", action="store_true", help="full activation recompute (not needed at 1.3B)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (invalid as a result)")
+    ap.add_argument("--frames", type=int, default=FRAMES)
+    ap.add_argument("--height", type=int, default=HEIGHT)
+    ap.add_argument("--width", type=int, default=WIDTH)
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
+    ap.add_argument("--init-on-device", action="store_true", help="create parameters on the GPU (default for 14B)")
     ap.add_argument("--ref-no-recompute", action="store_true")
     ap.add_argument("--fused-comm", type=str, default="auto", choices=["auto", "on", "off"],
                     help="peer-memory fused collectives (off = NCCL baseline path)")

@@ -11,8 +11,10 @@ dQ / dK / dV into the token owners' staging buffers, and the RMSNorm+RoPE backwa
 This replaces four NCCL all-to-alls per direction with no separate communication kernels and no
 pack / unpack copies (reference: teletron/core/context_parallel/context_parallel_mixin.py:87-125).
 Activations that must live until backward (q/k/v in head layout, O in sequence layout) are
-bump-allocated from one symmetric slab that is reset every micro-batch; gradient staging
-buffers are reused across layers.  Ordering across ranks relies on every rank executing the
+taken from one symmetric slab used as a stack: a layer's region is released by its backward
+(layers run backward in reverse order), at once when the forward pass is one whose activations
+are dropped (the first pass of a checkpointed range, or no-grad evaluation), and the whole slab is
+reset every micro-batch; gradient staging buffers are reused across layers.  Ordering across ranks relies on every rank executing the
 same kernel sequence; each exchange is fenced by the bounded flag barrier of csrc/comm.cu.
 Requirements: heads divisible by the group size, head_dim 128, bf16, one NVLink box.
 """
@@ -24,6 +26,7 @@ import torch
 
 from ..ops import _lib
 from ..ops.norm import rmsrope_bwd_raw
+from .recompute import forward_is_discarded
 
 _ALIGN = 128  # elements (256 bytes)
 
@@ -37,10 +40,15 @@ class SymmSlab:
         self.buf = arena.alloc(numel, torch.bfloat16)
         self.numel = numel
         self.off = 0
+        self.live = []
         self.high_water = 0
 
     def reset(self):
         self.off = 0
+        self.live = []  # (start, end) of the regions that wait for their backward, in forward order
+
+    def release_to(self, mark: int):
+        self.off = mark
 
     def take(self, numel: int):
         n = (numel + _ALIGN - 1) // _ALIGN * _ALIGN
@@ -94,6 +102,8 @@ class FusedUlysses:
 
     def attention(self, q_pre, k_pre, v, wq, wk, freqs, B, S_l, H, D, eps, scale=None):
         """q_pre/k_pre/v: [B*S_l, H*D] bf16 views (row stride free). Returns [B*S_l, H*D]."""
+        # decided here: inside an autograd function's forward the grad mode is always off
+        self._keep_for_backward = torch.is_grad_enabled() and not forward_is_discarded()
         return _FusedUlyssesFn.apply(self, q_pre, k_pre, v, wq, wk, freqs, B, S_l, H, D, eps, scale)
 
 
@@ -120,6 +130,7 @@ class _FusedUlyssesFn(torch.autograd.Function):
         dev = q_pre.device
         scale = scale if scale is not None else 1.0 / math.sqrt(D)
         n_h = B * S_pad * Hl * D
+        slab_mark = fu.slab.off
         qh, qh_p = fu.slab.take(n_h)
         kh, kh_p = fu.slab.take(n_h)
         vh, vh_p = fu.slab.take(n_h)
@@ -147,6 +158,12 @@ class _FusedUlyssesFn(torch.autograd.Function):
             _lib.stream())
         _lib.check(rc, "tt_attn_fwd_scatter")
         fu.arena.barrier(fu.slot)
+        if not fu._keep_for_backward:
+            # nothing of this layer is read after its own consumers (already enqueued): the next layer may
+            # take the same region; its writers run behind this layer's last barrier on every rank
+            fu.slab.release_to(slab_mark)
+        else:
+            fu.slab.live.append((slab_mark, fu.slab.off))
         ctx.fu = fu
         ctx.meta = (B, S_l, H, D, scale, kv_lens)
         ctx.save_for_backward(q_pre, k_pre, wq_f, wk_f, freqs, rstd_q, rstd_k, qh, kh, vh, o_h, lse)
@@ -184,5 +201,8 @@ class _FusedUlyssesFn(torch.autograd.Function):
         dq_pre, dwq = rmsrope_bwd_raw(dq_s.tensor[:rows * C].view(rows, C), q_pre, wq_f, freqs, rstd_q, D, False)
         dk_pre, dwk = rmsrope_bwd_raw(dk_s.tensor[:rows * C].view(rows, C), k_pre, wk_f, freqs, rstd_k, D, False)
         dv = dv_s.tensor[:rows * C].view(rows, C).clone()
+        # layers run backward in reverse order, so this layer's region is the top of the stack
+        if fu.slab.live and fu.slab.live[-1][1] == fu.slab.off:
+            fu.slab.release_to(fu.slab.live.pop()[0])
         wdq, wdk = ctx.w_dtypes
         return (None, dq_pre, dk_pre, dv, dwq.to(wdq), dwk.to(wdk), None, None, None, None, None, None, None)

@@ -18,6 +18,17 @@ import torch
 from torch.utils.checkpoint import checkpoint
 
 
+_DISCARDED_FORWARD = False
+
+
+def forward_is_discarded() -> bool:
+    """True inside the first forward pass of a checkpointed range, whose saved activations are dropped
+    (they are produced again by the recompute pass right before the range's backward).  Allocators that
+    keep per-layer activations outside autograd (the symmetric slab of the fused Ulysses path) use it to
+    recycle their space at once."""
+    return _DISCARDED_FORWARD
+
+
 def _run_range(blocks: Sequence, start: int, end: int, extra):
     def fn(x):
         for i in range(start, end):
@@ -25,6 +36,24 @@ def _run_range(blocks: Sequence, start: int, end: int, extra):
         return x
 
     return fn
+
+
+def _checkpointed(blocks: Sequence, start: int, end: int, extra, x):
+    inner = _run_range(blocks, start, end, extra)
+    calls = [0]
+
+    def fn(x):
+        global _DISCARDED_FORWARD
+        first = calls[0] == 0
+        calls[0] += 1
+        prev = _DISCARDED_FORWARD
+        _DISCARDED_FORWARD = first
+        try:
+            return inner(x)
+        finally:
+            _DISCARDED_FORWARD = prev
+
+    return checkpoint(fn, x, use_reentrant=False)
 
 
 def run_blocks(blocks: Sequence, x, extra: tuple, cfg, training: bool):
@@ -42,13 +71,13 @@ def run_blocks(blocks: Sequence, x, extra: tuple, cfg, training: bool):
             k = max(k, 1)
             i = 0
             while i < n:
-                x = checkpoint(_run_range(blocks, i, min(i + k, n), extra), x, use_reentrant=False)
+                x = _checkpointed(blocks, i, min(i + k, n), extra, x)
                 i += k
             return x
         if method == "block":
             for i in range(n):
                 if i < k:
-                    x = checkpoint(_run_range(blocks, i, i + 1, extra), x, use_reentrant=False)
+                    x = _checkpointed(blocks, i, i + 1, extra, x)
                 else:
                     x = blocks[i](x, *extra)
             return x

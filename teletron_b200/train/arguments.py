@@ -67,6 +67,9 @@ _FLAGS = [
     ("--recompute-method", dict(type=str, default=None, choices=["uniform", "block"])),
     ("--recompute-num-layers", dict(type=int, default=None)),
     ("--activation-offload", dict(action="store_true")),
+    ("--init-on-device", dict(action="store_true",
+                              help="create the parameters on the GPU instead of the host (models too large or too slow "
+                                   "to initialise in host memory); the random stream then differs from a host-side init")),
     ("--use-distributed-optimizer", dict(action="store_true")),
     ("--use-zero2", dict(action="store_true", help="accepted; maps to the sharded optimizer")),
     ("--overlap-grad-reduce", dict(action="store_true")),

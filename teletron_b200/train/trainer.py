@@ -121,7 +121,11 @@ class Trainer:
     # ------------------------------------------------------------------ model / optimizer
     def setup_model_and_optimizer(self):
         a = self.args
-        model = build_model(a.model, a).to(self.device)
+        if getattr(a, "init_on_device", False) and self.device.type == "cuda":
+            with torch.device(self.device):
+                model = build_model(a.model, a)
+        else:
+            model = build_model(a.model, a).to(self.device)
         if a.bf16:
             model = Float16Module(model)
         self.model = model

@@ -54,7 +54,7 @@ def test_fused_dp_optimizer_matches_nccl(clip):
         assert all(abs(a - b) < 1e-3 * abs(b) for a, b in zip(got[r][2], ref[r][2]))
 
 
-def _cp_worker(rank, world, fused=False):
+def _cp_worker(rank, world, fused=False, layers=2, recompute_layers=0):
     from teletron_b200 import ops
     from teletron_b200.models import WanModel, wan_config
     from teletron_b200.ops import _lib
@@ -69,7 +69,10 @@ def _cp_worker(rank, world, fused=False):
 
         cp.fused = FusedUlysses(SymmetricArena(mpu.get_context_parallel_group()))
     torch.manual_seed(0)
-    cfg = wan_config("wan-tiny", dim=256, num_heads=2, ffn_dim=512, text_dim=64, freq_dim=64, num_layers=2)
+    extra = dict(recompute_granularity="full", recompute_method="block",
+                 recompute_num_layers=recompute_layers) if recompute_layers else {}
+    cfg = wan_config("wan-tiny", dim=256, num_heads=2, ffn_dim=512, text_dim=64, freq_dim=64, num_layers=layers,
+                     **extra)
     model = WanModel(cfg, cp).cuda().to(torch.bfloat16)
     g = torch.Generator().manual_seed(5)
     x = torch.randn(1, 16, 3, 16, 20, generator=g).cuda().bfloat16()   # 3*8*10 = 240 tokens
@@ -87,11 +90,11 @@ def _cp_worker(rank, world, fused=False):
     return out.float().cpu(), {k: v.cpu() for k, v in grads.items()}
 
 
-def _single_gpu_reference():
+def _single_gpu_reference(layers=2):
     from teletron_b200.models import WanModel, wan_config
 
     torch.manual_seed(0)
-    cfg = wan_config("wan-tiny", dim=256, num_heads=2, ffn_dim=512, text_dim=64, freq_dim=64, num_layers=2)
+    cfg = wan_config("wan-tiny", dim=256, num_heads=2, ffn_dim=512, text_dim=64, freq_dim=64, num_layers=layers)
     model = WanModel(cfg).cuda().to(torch.bfloat16)
     g = torch.Generator().manual_seed(5)
     x = torch.randn(1, 16, 3, 16, 20, generator=g).cuda().bfloat16()
@@ -109,6 +112,18 @@ def test_ulysses_cp2_matches_single_gpu(fused):
     outs = run_distributed(_cp_worker, 2, fused, backend="nccl")
     for out, grads in outs:
         assert rel(out, ref_out) < 1e-3          # same threshold as the reference's model test
+        bad = [(n, rel(grads[n], ref_g[n])) for n in ref_g if ref_g[n].norm() > 2e-4 and rel(grads[n], ref_g[n]) > 2e-2]
+        assert not bad, bad
+
+
+@needs2
+def test_ulysses_cp2_fused_with_recompute_recycles_the_slab():
+    """Four layers, the first three checkpointed: the symmetric slab is sized for three layers, so the run
+    only fits (and only matches) when discarded forward passes hand their regions back."""
+    ref_out, ref_g = _single_gpu_reference(layers=4)
+    outs = run_distributed(_cp_worker, 2, True, 4, 3, backend="nccl")
+    for out, grads in outs:
+        assert rel(out, ref_out) < 1e-3
         bad = [(n, rel(grads[n], ref_g[n])) for n in ref_g if ref_g[n].norm() > 2e-4 and rel(grads[n], ref_g[n]) > 2e-2]
         assert not bad, bad
 

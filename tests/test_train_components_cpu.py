@@ -125,6 +125,31 @@ def test_recompute_policy_counts_and_grads(method, k, expect_extra):
     assert _CountingLinear.calls == 4
 
 
+class _PhaseRecorder(torch.nn.Module):
+    seen = []
+
+    def __init__(self):
+        super().__init__()
+        self.lin = torch.nn.Linear(8, 8)
+
+    def forward(self, x):
+        _PhaseRecorder.seen.append(rc.forward_is_discarded())
+        return self.lin(x)
+
+
+def test_recompute_marks_the_forward_pass_whose_activations_are_dropped():
+    blocks = torch.nn.ModuleList([_PhaseRecorder() for _ in range(3)])
+    x = torch.randn(2, 8, requires_grad=True)
+    cfg = Namespace(recompute_granularity="full", recompute_method="block", recompute_num_layers=2,
+                    activation_offload=False)
+    _PhaseRecorder.seen = []
+    y = rc.run_blocks(blocks, x, (), cfg, True)
+    assert _PhaseRecorder.seen == [True, True, False]       # two checkpointed blocks, one plain
+    y.sum().backward()
+    assert _PhaseRecorder.seen[3:] == [False, False]         # their recompute passes keep what they save
+    assert not rc.forward_is_discarded()
+
+
 def _trainer_args(tmp, extra=""):
     argv = (f"--model ParallelWanModel --model-preset wan-tiny --train-iters 4 --micro-batch-size 1 --global-batch-size 2 "
             f"--lr 1e-3 --synthetic-latents --num-frames 5 --video-resolution 64 64 --log-interval 100 --clip-grad 1.0 "
