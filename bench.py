@@ -21,6 +21,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import time
 from pathlib import Path
 
@@ -38,6 +39,13 @@ PUBLISHED_720P_TOKENS_PER_S_PER_GPU = 567.0  # 4.8 FPS/node at 720P x 81, same c
 def tokens_per_sample(frames: int, height: int, width: int) -> int:
     """Latent frames x (H/16) x (W/16): 8x VAE, 4x temporal compression, patch (1, 2, 2)."""
     return ((frames - 1) // 4 + 1) * (height // 16) * (width // 16)
+
+
+def clock_log_dir() -> str:
+    """Folder for the raw nvidia-smi samples (the JSON line carries their summary)."""
+    d = os.environ.get("TT_BENCH_LOG_DIR") or os.path.join(tempfile.gettempdir(), "teletron_b200_bench")
+    os.makedirs(d, exist_ok=True)
+    return d
 
 
 def clock_sampler_start(path: str):
@@ -174,8 +182,7 @@ def run_ours(a):
         trainer.train_step(fwd, cycle(pool_dev))
     sync_all()
     _lib.check_status()
-    clk_path = str(ROOT / "gpurun_out" / f"bench_clocks_rank{rank}.csv")
-    os.makedirs(os.path.dirname(clk_path), exist_ok=True)
+    clk_path = os.path.join(clock_log_dir(), f"bench_clocks_rank{rank}.csv")
     proc, fh = clock_sampler_start(clk_path) if rank == 0 else (None, None)
     ms_dev, launches, _ = timed(pool_dev, a.steps, read_loss=False)
     clocks = clock_sampler_stop(proc, fh, clk_path, local) if rank == 0 else {}
@@ -292,8 +299,7 @@ def run_reference(a):
     except torch.cuda.OutOfMemoryError:
         return unavailable("reference model ran out of memory in warm-up")
     torch.cuda.synchronize()
-    clk_path = str(ROOT / "gpurun_out" / "bench_clocks_reference.csv")
-    os.makedirs(os.path.dirname(clk_path), exist_ok=True)
+    clk_path = os.path.join(clock_log_dir(), "bench_clocks_reference.csv")
     proc, fh = clock_sampler_start(clk_path)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()

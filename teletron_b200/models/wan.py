@@ -274,8 +274,8 @@ class DiTBlock(nn.Module):
         h, xr = ops.layernorm_affine(x2d, self.norm3.weight, self.norm3.bias, self.eps, with_res=True)
         x2d = self.cross_attn(h, context, batch, xr, rows_per_batch)
         h, xr = ops.adaln_res(x2d, e[:, 4], e[:, 3], rows_per_batch, self.eps)
-        f = ops.linear(h, self.ffn[0].weight, self.ffn[0].bias, act="gelu")
-        return ops.linear_residual(f, self.ffn[2].weight, self.ffn[2].bias, xr, e[:, 5], rows_per_batch)
+        return ops.ffn(h, self.ffn[0].weight, self.ffn[0].bias, self.ffn[2].weight, self.ffn[2].bias, xr, e[:, 5],
+                       rows_per_batch, act="gelu")
 
 
 class ImageEmbedMLP(nn.Module):

@@ -27,8 +27,10 @@ def pytest_collection_modifyitems(config, items):
 
 
 def reference_file(rel: str):
-    """Path of a file of the reference tree (offline install first, then the read-only mount)."""
-    for base in (ROOT / "baseline" / "_ref", Path("/root/reference")):
+    """Path of a file of the reference tree: the offline install under ``baseline/_ref`` first, then the
+    checkout named by ``TELETRON_REFERENCE`` (default: a ``reference`` folder beside this repository)."""
+    mount = Path(os.environ.get("TELETRON_REFERENCE", str(ROOT.parent / "reference")))
+    for base in (ROOT / "baseline" / "_ref", mount):
         p = base / rel
         if p.exists():
             return p
