@@ -189,7 +189,9 @@ def validate_args(args):
     per_step = args.micro_batch_size * args.data_parallel_size
     if args.global_batch_size % per_step:
         raise ValueError(f"global batch {args.global_batch_size} not divisible by micro batch x dp = {per_step}")
-    args.num_micro_batches = args.global_batch_size // per_step
+    from .microbatches import build_num_microbatches_calculator
+
+    build_num_microbatches_calculator(args)  # sets args.num_micro_batches / args.current_global_batch_size
     if args.task_type is not None:
         args.task_type = "i2v" if "i2v" in args.task_type else "t2v"
     if args.fp16:
@@ -232,4 +234,6 @@ def get_args():
 
 
 def get_num_microbatches() -> int:
-    return get_args().num_micro_batches
+    from .microbatches import get_num_microbatches as _get
+
+    return _get()

@@ -57,7 +57,7 @@ class TrainLogger:
             samples = a.consumed_train_samples
             w.add_scalar("learning-rate", lr, iteration)
             w.add_scalar("learning-rate vs samples", lr, samples)
-            w.add_scalar("batch-size", a.global_batch_size, iteration)
+            w.add_scalar("batch-size", getattr(a, "current_global_batch_size", a.global_batch_size), iteration)
             for k, v in loss_dict.items():
                 w.add_scalar(k, float(v), iteration)
                 w.add_scalar(k + " vs samples", float(v), samples)
@@ -78,7 +78,7 @@ class TrainLogger:
         parts = [f"iteration {iteration:8d}/{a.train_iters or 0:8d}",
                  f"consumed samples: {a.consumed_train_samples:12d}",
                  f"elapsed time per iteration (ms): {elapsed * 1000.0 / max(self.counts[self.ADV] + self.counts[self.SKIP], 1):.1f}",
-                 f"learning rate: {lr:.3E}", f"global batch size: {a.global_batch_size:5d}"]
+                 f"learning rate: {lr:.3E}", f"global batch size: {getattr(a, 'current_global_batch_size', a.global_batch_size):5d}"]
         for k, tot in self.totals.items():
             parts.append(f"{k}: {tot / n_adv:.6E}")
         parts.append(f"loss scale: {float(loss_scale):.1f}")

@@ -28,6 +28,7 @@ from ..parallel.ddp import DistributedOptimizer, ParamBuffer
 from ..parallel.tp import tp_shard_dims
 from . import checkpoint as ckpt
 from .arguments import set_args
+from .microbatches import BatchSchedule
 from .schedule import scheduler_from_args
 from .telelog import TrainLogger
 
@@ -215,6 +216,17 @@ class Trainer:
                                     "single", 0, a.seed + 1)
             self.valid_data_iterator = iter(vdl)
 
+    def _set_batch_level(self, strict: bool):
+        """Global batch and micro-batch count for the samples consumed so far (constant unless
+        ``--rampup-batch-size`` is given), mirrored into the arguments the rest of the loop reads."""
+        a = self.args
+        if getattr(self, "batch_schedule", None) is None:
+            self.batch_schedule = BatchSchedule(a.global_batch_size, a.micro_batch_size, a.data_parallel_size,
+                                                getattr(a, "rampup_batch_size", None))
+        self.batch_schedule.update(a.consumed_train_samples, strict=strict)
+        a.num_micro_batches = self.batch_schedule.num_micro_batches
+        a.current_global_batch_size = self.batch_schedule.current_global_batch_size
+
     # ------------------------------------------------------------------ one step
     def train_step(self, forward_step_func: Callable, data_iterator=None):
         """Forward/backward over the micro-batches, gradient reduction, optimizer and schedule step.
@@ -233,7 +245,7 @@ class Trainer:
         self.optimizer.reduce_gradients()
         ok, grad_norm, num_zeros = self.optimizer.step()
         if ok and self.opt_param_scheduler is not None:
-            self.opt_param_scheduler.step(increment=a.global_batch_size)
+            self.opt_param_scheduler.step(increment=getattr(a, "current_global_batch_size", a.global_batch_size))
         loss_dict = {}
         for k in (reduced_all[0] or {}):
             vals = [r[k] for r in reduced_all]
@@ -292,7 +304,18 @@ class Trainer:
             gc.disable()
             gc.collect()
         use_events = torch.cuda.is_available()
+        n_mb_prev = a.num_micro_batches
         while iteration < a.train_iters:
+            # batch-size ramp-up: a new level starts from a checkpoint, then has to split into micro-batches
+            self._set_batch_level(strict=False)
+            if a.num_micro_batches != n_mb_prev and iteration != 0:
+                if a.num_micro_batches < n_mb_prev:
+                    raise RuntimeError("the number of micro-batches shrank during batch-size ramp-up")
+                if a.save:
+                    self.save(iteration)
+            n_mb_prev = a.num_micro_batches
+            self._set_batch_level(strict=True)
+            tokens_per_step = getattr(a, "tokens_per_sample", 0) * a.current_global_batch_size
             if a.profile and iteration == a.profile_step_start and a.rank in a.profile_ranks and use_events:
                 torch.cuda.cudart().cudaProfilerStart()
             if use_events:
@@ -310,7 +333,7 @@ class Trainer:
                     _lib.check_status()
             iteration += 1
             a.iteration = iteration
-            a.consumed_train_samples += a.global_batch_size
+            a.consumed_train_samples += a.current_global_batch_size
             lr = self.optimizer.param_groups[0]["lr"]
             params_norm = self.buffer.params.float().norm() if a.log_params_norm else None
             self.logger.log(loss_dict, iteration, lr, 1.0, grad_norm, skipped, params_norm,

@@ -150,6 +150,47 @@ def test_recompute_marks_the_forward_pass_whose_activations_are_dropped():
     assert not rc.forward_is_discarded()
 
 
+def test_batch_size_rampup_schedule():
+    from teletron_b200.train.microbatches import BatchSchedule
+
+    const = BatchSchedule(16, 2, 4)
+    assert (const.num_micro_batches, const.current_global_batch_size) == (2, 16)
+    assert const.update(10 ** 9) == 2
+    # 8 -> 32 in steps of 8 over 240 samples: three increments, 80 samples per level
+    ramp = BatchSchedule(32, 2, 4, rampup=["8", "8", "240"])
+    seen = [(c, ramp.global_batch_at(c)) for c in (0, 79, 80, 159, 160, 239, 240, 241, 10_000)]
+    assert seen == [(0, 8), (79, 8), (80, 16), (159, 16), (160, 24), (239, 24), (240, 32), (241, 32), (10_000, 32)]
+    assert ramp.update(160) == 3 and ramp.current_global_batch_size == 24
+    odd = BatchSchedule(32, 2, 4, rampup=[4, 4, 70])         # level 4 does not split into passes of 8 samples
+    assert odd.update(0, strict=False) == 0
+    with pytest.raises(ValueError):
+        odd.update(0, strict=True)
+    for bad in ([8, 8], [8, 5, 100], [64, 8, 100], [0, 8, 100]):
+        with pytest.raises(ValueError):
+            BatchSchedule(32, 2, 4, rampup=bad)
+
+
+def test_trainer_ramps_the_global_batch_and_checkpoints_at_each_level(tmp_path):
+    from teletron_b200.train import Trainer
+    from teletron_b200.train.checkpoint import read_tracker
+
+    a = _trainer_args(tmp_path, "--rampup-batch-size 1 1 3")   # global batch 1 for the first 3 samples, then 2
+    a.train_iters, a.save_interval = 5, 1000
+    t = Trainer(a)
+    levels = []
+    orig = t.train_step
+
+    def spy(fwd, it=None):
+        levels.append((a.num_micro_batches, a.current_global_batch_size))
+        return orig(fwd, it)
+
+    t.train_step = spy
+    t.train(make_forward_step())
+    assert levels == [(1, 1), (1, 1), (1, 1), (2, 2), (2, 2)]
+    assert a.consumed_train_samples == 1 + 1 + 1 + 2 + 2
+    assert read_tracker(str(tmp_path)) == (3, False)            # saved when the level changed, before step 4
+
+
 def _trainer_args(tmp, extra=""):
     argv = (f"--model ParallelWanModel --model-preset wan-tiny --train-iters 4 --micro-batch-size 1 --global-batch-size 2 "
             f"--lr 1e-3 --synthetic-latents --num-frames 5 --video-resolution 64 64 --log-interval 100 --clip-grad 1.0 "
