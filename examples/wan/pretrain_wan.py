@@ -16,8 +16,8 @@ sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
 
 from teletron_b200.models import FlowMatchScheduler  # noqa: E402
 from teletron_b200.parallel import state as mpu  # noqa: E402
-from teletron_b200.train import (Trainer, average_losses_across_data_parallel_group, make_forward_step,  # noqa: E402
-                                 parse_args)
+from teletron_b200.train import (Trainer, average_losses_across_data_parallel_group, get_args,  # noqa: E402
+                                 make_forward_step, parse_args)
 
 
 def loss_func(output_tensor):
@@ -40,8 +40,9 @@ def extra_args(parser):
 
 
 def forward_step(data_iterator, model):
-    flow = FlowMatchScheduler(shift=5, sigma_min=0.0, extra_one_step=True)
-    flow.set_timesteps(1000, training=True)
+    a = get_args()
+    flow = FlowMatchScheduler(shift=a.flow_shift, sigma_min=0.0, extra_one_step=True)
+    flow.set_timesteps(a.flow_train_timesteps, training=True)
     batch = next(data_iterator)
     device = next(model.parameters()).device
     latents = batch["latents"].to(device)
@@ -64,4 +65,4 @@ def forward_step(data_iterator, model):
 if __name__ == "__main__":
     args = parse_args(extra_args=extra_args)
     trainer = Trainer(args)
-    trainer.pretrain(forward_step_func=make_forward_step() if args.fused_step else forward_step)
+    trainer.pretrain(forward_step_func=make_forward_step(shift=args.flow_shift, train_timesteps=args.flow_train_timesteps) if args.fused_step else forward_step)

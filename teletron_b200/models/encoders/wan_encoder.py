@@ -68,7 +68,17 @@ class HFTokenizer:
 class WanVideoEncoder(BaseEncoder):
     def __init__(self, device=None, args=None, dtype=torch.bfloat16, text_len=512, small: bool = False, **kw):
         super().__init__(device, **kw)
+        named = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "fp16": torch.float16, "float16": torch.float16,
+                 "fp32": torch.float32, "float32": torch.float32}
+        enc_dtype = getattr(args, "encoder_dtype", None)     # --encoder-dtype (teletron/core/distributed/base_encoder.py:25)
+        if enc_dtype is not None:
+            if enc_dtype not in named:
+                raise ValueError(f"unknown --encoder-dtype {enc_dtype!r}")
+            dtype = named[enc_dtype]
         self.args, self.dtype, self.text_len, self.small = args, dtype, text_len, small
+        self.vae_kw = dict(tiled=bool(getattr(args, "vae_tiled", False)),
+                           tile_size=tuple(getattr(args, "vae_tile_size", (34, 34))),
+                           tile_stride=tuple(getattr(args, "vae_tile_stride", (18, 16))))
         self.i2v = getattr(args, "task_type", None) == "i2v"
         self.with_noise = getattr(args, "consumer_models_num", 1) > 1
         self.model_path = getattr(args, "encoder_model_path", None)
@@ -123,13 +133,13 @@ class WanVideoEncoder(BaseEncoder):
         if video.dim() == 4:
             video = video.unsqueeze(0)
         video = video.to(dev, dt).clamp(-1, 1).permute(0, 2, 1, 3, 4)                     # [B, 3, T, H, W]
-        latents = self.vae.encode(list(video), device=dev)                                  # [B, 16, f, h, w]
+        latents = self.vae.encode(list(video), device=dev, **self.vae_kw)                 # [B, 16, f, h, w]
         B, _, f, h, w = latents.shape
         if self.i2v:
             first = video[:, :, 0]
             clip = self.clip.encode_image(first)
             cond = torch.cat([video[:, :, :1], torch.zeros_like(video[:, :, 1:])], dim=2)
-            y = self.vae.encode(list(cond), device=dev)
+            y = self.vae.encode(list(cond), device=dev, **self.vae_kw)
             msk = torch.zeros(B, 4, f, h, w, device=dev, dtype=dt)
             msk[:, :, 0] = 1
             y = torch.cat([msk, y], dim=1)

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import datetime
 import gc
+import math
 import os
 import random
 import sys
@@ -86,6 +87,14 @@ class Trainer:
         self.logger = TrainLogger(args, TrainLogger.make_writer(args))
         if build_data:
             self.build_data_iterators()
+        self._signal_seen = False
+        if getattr(args, "exit_signal_handler", False):
+            import signal
+
+            def _on_sigterm(signum, frame):   # acted on between steps, so no kernel or collective is cut short
+                self._signal_seen = True
+
+            self._prev_sigterm = signal.signal(signal.SIGTERM, _on_sigterm)
         if getattr(args, "deferred_rng_state", None) is not None:
             ckpt.set_rng_state(args.deferred_rng_state, 0)   # after everything that consumes start-up randomness
             args.deferred_rng_state = None
@@ -242,14 +251,25 @@ class Trainer:
             loss, reduced = loss_func(output)
             (loss / n_mb).backward()
             reduced_all.append(reduced)
+        if a.empty_unused_memory_level >= 2 and self.device.type == "cuda":
+            torch.cuda.empty_cache()
         self.optimizer.reduce_gradients()
         ok, grad_norm, num_zeros = self.optimizer.step()
+        if a.empty_unused_memory_level >= 1 and self.device.type == "cuda":
+            torch.cuda.empty_cache()
         if ok and self.opt_param_scheduler is not None:
             self.opt_param_scheduler.step(increment=getattr(a, "current_global_batch_size", a.global_batch_size))
         loss_dict = {}
         for k in (reduced_all[0] or {}):
             vals = [r[k] for r in reduced_all]
             loss_dict[k] = sum(v if torch.is_tensor(v) else torch.tensor(v) for v in vals) / len(vals)
+        if a.check_for_nan_in_loss_and_grad:
+            bad = [k for k, v in loss_dict.items() if not math.isfinite(float(v))]
+            if grad_norm is not None and not math.isfinite(float(grad_norm)):
+                bad.append("grad_norm")
+            if bad:
+                raise RuntimeError(f"non-finite {', '.join(bad)} at iteration {a.iteration + 1} on rank {a.rank} "
+                                   "(--check-for-nan-in-loss-and-grad)")
         return loss_dict, (0 if ok else 1), grad_norm, num_zeros
 
     # ------------------------------------------------------------------ evaluation
@@ -345,10 +365,25 @@ class Trainer:
             if a.manual_gc and a.manual_gc_interval and iteration % a.manual_gc_interval == 0:
                 gc.collect()
             if a.eval_interval and a.eval_iters > 0 and iteration % a.eval_interval == 0:
+                if a.manual_gc and a.manual_gc_eval:
+                    gc.collect()          # evaluation allocates differently: start and leave it with a clean heap
                 res = self.evaluate(forward_step_func)
+                if a.manual_gc and a.manual_gc_eval:
+                    gc.collect(generation=0)
+                if a.empty_unused_memory_level >= 1 and self.device.type == "cuda":
+                    torch.cuda.empty_cache()
                 self.logger.log_validation(res, iteration)
             if a.save and a.save_interval and iteration % a.save_interval == 0:
                 self.save(iteration)
+            if a.exit_signal_handler:
+                flag = torch.tensor([int(self._signal_seen)], device=self.device)
+                if dist.is_initialized():
+                    dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=mpu.get_transformer_model_group())
+                if int(flag.item()):        # any rank got SIGTERM: everybody saves and leaves together
+                    if a.save:
+                        self.save(iteration)
+                    print(f"exiting at iteration {iteration}: termination signal received", flush=True)
+                    break
             if a.exit_duration_in_mins:
                 mins = (time.time() - self.start_time) / 60.0
                 flag = torch.tensor([int(mins > a.exit_duration_in_mins)], device=self.device)

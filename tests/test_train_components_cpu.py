@@ -191,6 +191,47 @@ def test_trainer_ramps_the_global_batch_and_checkpoints_at_each_level(tmp_path):
     assert read_tracker(str(tmp_path)) == (3, False)            # saved when the level changed, before step 4
 
 
+def test_trainer_exits_on_sigterm_between_steps_and_saves(tmp_path):
+    import signal
+
+    from teletron_b200.train import Trainer
+    from teletron_b200.train.checkpoint import read_tracker
+
+    a = _trainer_args(tmp_path, "--exit-signal-handler")
+    a.train_iters, a.save_interval = 50, 1000
+    t = Trainer(a)
+    try:
+        orig, calls = t.train_step, []
+
+        def step(fwd, it=None):
+            calls.append(1)
+            if len(calls) == 2:
+                os.kill(os.getpid(), signal.SIGTERM)     # arrives in the middle of step 2
+            return orig(fwd, it)
+
+        t.train_step = step
+        assert t.train(make_forward_step()) == 2           # step 2 completes, then the loop leaves
+        assert read_tracker(str(tmp_path)) == (2, False)
+    finally:
+        signal.signal(signal.SIGTERM, t._prev_sigterm)
+
+
+def test_trainer_nan_check_raises(tmp_path):
+    from teletron_b200.train import Trainer
+
+    a = _trainer_args(tmp_path, "--check-for-nan-in-loss-and-grad")
+    t = Trainer(a)
+    fwd = make_forward_step()
+
+    def poisoned(it, model):
+        loss, loss_func = fwd(it, model)
+        return loss * float("nan"), loss_func
+
+    t.train_step(fwd)                                      # a healthy step passes
+    with pytest.raises(RuntimeError, match="non-finite"):
+        t.train_step(poisoned)
+
+
 def _trainer_args(tmp, extra=""):
     argv = (f"--model ParallelWanModel --model-preset wan-tiny --train-iters 4 --micro-batch-size 1 --global-batch-size 2 "
             f"--lr 1e-3 --synthetic-latents --num-frames 5 --video-resolution 64 64 --log-interval 100 --clip-grad 1.0 "
