@@ -25,6 +25,7 @@ from typing import List
 import torch
 
 from ...data.base_encoder import BaseEncoder
+from ...utils.prompt import apply_clean_mode
 from ..registry import ENCODERS
 from .clip_vit import WanImageEncoder
 from .umt5 import UMT5Encoder, encode_prompt
@@ -45,20 +46,24 @@ class HashTokenizer:
         ids = torch.zeros(len(texts), self.seq_len, dtype=torch.long)
         mask = torch.zeros(len(texts), self.seq_len, dtype=torch.long)
         for i, t in enumerate(texts):
-            toks = [2 + zlib.crc32(w.encode()) % (self.vocab - 2) for w in t.split()][: self.seq_len - 1] + [1]
+            toks = [2 + zlib.crc32(w.encode()) % (self.vocab - 2) for w in apply_clean_mode(t, "whitespace").split()][: self.seq_len - 1] + [1]
             ids[i, :len(toks)] = torch.tensor(toks)
             mask[i, :len(toks)] = 1
         return ids, mask
 
 
 class HFTokenizer:
-    def __init__(self, path: str, seq_len: int):
+    """Hugging Face tokenizer with the prompter's text cleaning in front (``clean``: None, "whitespace", "lower"
+    or "canonicalize"; the Wan prompter uses "whitespace", teletron/models/wan/encoder/wan_prompter.py:38-97)."""
+
+    def __init__(self, path: str, seq_len: int, clean: str = "whitespace"):
         from transformers import AutoTokenizer
 
         self.tok = AutoTokenizer.from_pretrained(path)
-        self.seq_len = seq_len
+        self.seq_len, self.clean = seq_len, clean
 
     def __call__(self, texts):
+        texts = [apply_clean_mode(t, self.clean) for t in ([texts] if isinstance(texts, str) else texts)]
         out = self.tok(texts, return_tensors="pt", padding="max_length", truncation=True, max_length=self.seq_len,
                        add_special_tokens=True)
         return out.input_ids, out.attention_mask

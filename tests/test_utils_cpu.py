@@ -1,0 +1,134 @@
+"""Utility modules on CPU: video reading / writing round trip through whichever backend is installed,
+frame sampling, time windows."""
+import numpy as np
+import pytest
+import torch
+
+from teletron_b200.utils import video_io
+
+
+def _have_writer():
+    try:
+        import imageio  # noqa: F401
+        return True
+    except ImportError:
+        pass
+    try:
+        import cv2  # noqa: F401
+        return True
+    except ImportError:
+        return False
+
+
+def _clip(T=12, H=48, W=64):
+    t = np.arange(T, dtype=np.float32)[:, None, None]
+    y = np.arange(H, dtype=np.float32)[None, :, None]
+    x = np.arange(W, dtype=np.float32)[None, None, :]
+    r = (x * 3 + t * 10) % 256
+    g = (y * 4 + t * 5) % 256
+    b = np.full((T, H, W), 128.0, dtype=np.float32)
+    return np.stack([np.broadcast_to(c, (T, H, W)) for c in (r, g, b)], axis=-1).astype(np.uint8)
+
+
+@pytest.mark.skipif(not _have_writer(), reason="no video writer backend installed")
+def test_video_round_trip_sampling_and_time_window(tmp_path):
+    clip = _clip()
+    path = str(tmp_path / "clip.avi")
+    video_io.save_video(list(clip), path, fps=8)
+    fr = video_io.read_video_frames(path)
+    assert fr.shape == (12, 48, 64, 3) and fr.dtype == torch.uint8
+    # lossy codec: compare smooth statistics, frame by frame
+    err = (fr.float() - torch.from_numpy(clip).float()).abs().mean().item()
+    assert err < 12.0, err
+    assert abs(video_io.get_fps(path) - 8.0) < 1e-3
+    sub = video_io.read_video_frames(path, num_frames=3, stride=4, start=1)      # frames 1, 5, 9
+    assert sub.shape[0] == 3 and torch.equal(sub[1], fr[5])
+    picked = video_io.sample_video(path, [0, 7, 3])
+    assert picked.shape == (3, 48, 64, 3) and np.array_equal(picked[1], fr[7].numpy())
+    assert np.array_equal(video_io.sample_video(fr, [2, 2]), fr[[2, 2]].numpy())
+    frames, info = video_io.read_video(path, backend=None, start_sec=0.5, end_sec=1.0)   # frames 4..8 at 8 fps
+    assert frames.shape == (5, 3, 48, 64) and abs(info["video_fps"] - 8.0) < 1e-3
+    assert torch.equal(frames[0], fr[4].permute(2, 0, 1))
+    thwc, _ = video_io.read_video(path, backend=None, output_format="thwc")
+    assert thwc.shape == (12, 48, 64, 3)
+    pil = video_io.load_video(path)
+    assert len(pil) == 12
+    x = video_io.frames_to_tensor(fr)
+    assert x.shape == (12, 3, 48, 64) and -1.0 <= float(x.min()) and float(x.max()) <= 1.0
+
+
+def test_video_io_argument_errors(tmp_path):
+    with pytest.raises(FileNotFoundError):
+        video_io.open_frames(str(tmp_path / "missing.mp4"))
+    p = tmp_path / "x.avi"
+    p.write_bytes(b"")
+    with pytest.raises(ValueError):
+        video_io.open_frames(str(p), backend="vlc")
+    with pytest.raises(ValueError):
+        video_io.read_video(str(p), output_format="CTHW")
+    with pytest.raises(ValueError):
+        video_io.read_video(str(p), start_sec=2.0, end_sec=1.0)
+
+
+CAPTIONS = [
+    "Visit https://example.com/cat.png NOW!!! @bob  a <person> walks -- “quoted” 192.168.1.1 #12 #123456 1920x1080",
+    "this-is-my-cute-cat_video_file.mp4 page 12 click for details... jc6640 6640vc231 free shipping worldwide",
+    "一只猫 a cat   sitting &amp; &quot;smiling&quot; ‘single’ — dash",
+    "'quoted whole'", "Hello_World, it's (fine) [ok] {yes} | no * star", "  A%20url+encoded caption\\nnext line ",
+    "download free wallpaper 1024×768 j2d1a2a3 : spaced ,comma", ".hidden", "-leading dash and trailing:",
+]
+
+
+def test_clean_prompt_matches_the_reference_rules():
+    """Same output as the reference's function on a spread of captions (its ``ftfy`` import is stubbed with
+    an identity repair, which is also what this package does when ftfy is missing)."""
+    import importlib.util
+    import sys
+    import types
+
+    from conftest import reference_file
+    from teletron_b200.utils import prompt as P
+
+    ref_path = reference_file("teletron/utils/prompt.py")
+    if ref_path is None:
+        pytest.skip("reference tree not available")
+    had = "ftfy" in sys.modules
+    try:
+        import ftfy  # noqa: F401
+    except ImportError:
+        sys.modules["ftfy"] = types.SimpleNamespace(fix_text=lambda t: t)
+    try:
+        spec = importlib.util.spec_from_file_location("ref_prompt", ref_path)
+        ref = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref)
+        for c in CAPTIONS:
+            assert P.clean_prompt(c) == ref.clean_prompt(c), c
+    finally:
+        if not had:
+            sys.modules.pop("ftfy", None)
+    assert P.clean_prompt("一只猫 cat", keep_cjk=True) == "一只猫 cat" and P.clean_prompt("一只猫 cat") == "cat"
+
+
+def test_prompt_clean_modes_and_long_prompt_chunks():
+    from teletron_b200.utils import prompt as P
+
+    assert P.canonicalize("Hello_World!! It's <|x|> ok", "<|x|>") == "hello world its <|x|> ok"
+    assert P.apply_clean_mode("  A  &amp;amp; B ", "lower") == "a & b"
+    assert P.apply_clean_mode("  A   B ", "whitespace") == "A B" and P.apply_clean_mode(" x ", None) == " x "
+    with pytest.raises(ValueError):
+        P.apply_clean_mode("x", "shout")
+
+    class Tok:                                              # the slice of the HF tokenizer API that is used
+        model_max_length = 4
+
+        def __call__(self, text, return_tensors="pt", padding=None, max_length=None, truncation=False):
+            ids = [3 + len(w) for w in text.split()]
+            if padding == "max_length":
+                ids = (ids + [0] * max_length)[:max_length]
+            return types.SimpleNamespace(input_ids=torch.tensor([ids]))
+
+    import types
+
+    ids = P.tokenize_long_prompt(Tok(), "a bb ccc dddd eeeee ffffff")
+    assert ids.shape == (2, 4) and ids.tolist() == [[4, 5, 6, 7], [8, 9, 0, 0]]
+    assert Tok.model_max_length == 4
