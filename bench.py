@@ -188,6 +188,9 @@ def run_ours(a):
     clocks = clock_sampler_stop(proc, fh, clk_path, local) if rank == 0 else {}
     ms_e2e, _, last_loss = timed(pool_host, a.steps, read_loss=True)
     _lib.check_status()
+    peak = torch.tensor([torch.cuda.max_memory_allocated(dev) / 2 ** 30], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(peak, op=dist.ReduceOp.MAX)
     tokens = gbs * tok_sample * a.steps
     value = tokens / (ms_dev * 1e-3)
     e2e = tokens / (ms_e2e * 1e-3)
@@ -225,6 +228,7 @@ def run_ours(a):
                     "h2d_bytes_per_step": bytes_h2d_per_mb * gbs, "d2h_bytes_per_step": 4 * world,
                     "last_loss": last_loss},
             "gpu_launches": launches,
+            "peak_mem_gib": round(float(peak.item()), 2),   # torch allocator high-water mark, max over ranks
         }
         print(json.dumps(res), flush=True)
     if world > 1:

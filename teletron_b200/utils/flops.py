@@ -29,3 +29,33 @@ def memory_report(prefix: str = "") -> str:
     return (f"{prefix} memory (MB) | allocated: {torch.cuda.memory_allocated() / mb:.0f} | max allocated: "
             f"{torch.cuda.max_memory_allocated() / mb:.0f} | reserved: {torch.cuda.memory_reserved() / mb:.0f} | "
             f"max reserved: {torch.cuda.max_memory_reserved() / mb:.0f}")
+
+
+def fit_activation_memory(points):
+    """Least-squares line through measured ``(tokens_per_gpu, peak_GiB)`` points: returns
+    ``(static_GiB, GiB_per_token)``.  With full activation recompute the peak is linear in the sequence
+    length (one checkpoint per block plus one block's working set), so two runs pin it down."""
+    n = len(points)
+    if n < 2:
+        raise ValueError("need at least two (tokens, GiB) measurements")
+    mx = sum(p[0] for p in points) / n
+    my = sum(p[1] for p in points) / n
+    sxx = sum((p[0] - mx) ** 2 for p in points)
+    if sxx == 0:
+        raise ValueError("measurements must differ in sequence length")
+    slope = sum((p[0] - mx) * (p[1] - my) for p in points) / sxx
+    return my - slope * mx, slope
+
+
+def max_trainable_frames(capacity_gib: float, static_gib: float, gib_per_token: float, height: int, width: int,
+                         cp: int = 1, reserve_gib: float = 8.0) -> int:
+    """Largest frame count 4k+1 whose activations fit: ``static + tokens / cp * gib_per_token`` must stay
+    below ``capacity - reserve``.  ``gib_per_token`` is per token held on one GPU (Ulysses keeps 1/cp of
+    the tokens, or of the heads, of every activation), ``static_gib`` the weights / gradients / optimizer
+    share of that GPU.  This bounds memory only; step time grows with the square of the frame count."""
+    room = capacity_gib - reserve_gib - static_gib
+    if room <= 0 or gib_per_token <= 0:
+        return 0
+    per_latent_frame = (height // 16) * (width // 16)
+    latent_frames = int(room / gib_per_token * cp) // per_latent_frame
+    return 0 if latent_frames < 1 else (latent_frames - 1) * 4 + 1

@@ -132,3 +132,18 @@ def test_prompt_clean_modes_and_long_prompt_chunks():
     ids = P.tokenize_long_prompt(Tok(), "a bb ccc dddd eeeee ffffff")
     assert ids.shape == (2, 4) and ids.tolist() == [[4, 5, 6, 7], [8, 9, 0, 0]]
     assert Tok.model_max_length == 4
+
+
+def test_activation_memory_fit_and_max_frames():
+    from teletron_b200.utils.flops import fit_activation_memory, max_trainable_frames
+
+    static, per_tok = fit_activation_memory([(1000, 12.0), (3000, 16.0), (2000, 14.0)])
+    assert abs(static - 10.0) < 1e-9 and abs(per_tok - 0.002) < 1e-12
+    with pytest.raises(ValueError):
+        fit_activation_memory([(1000, 12.0)])
+    with pytest.raises(ValueError):
+        fit_activation_memory([(1000, 12.0), (1000, 13.0)])
+    # 64 x 64 video: 16 tokens per latent frame; room = 100 - 8 - 10 = 82 GiB -> 41,000 tokens -> 2,562 latent frames
+    assert max_trainable_frames(100.0, 10.0, 0.002, 64, 64) == (2562 - 1) * 4 + 1
+    assert max_trainable_frames(100.0, 10.0, 0.002, 64, 64, cp=2) == (5125 - 1) * 4 + 1
+    assert max_trainable_frames(15.0, 10.0, 0.002, 64, 64) == 0
