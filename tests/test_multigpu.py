@@ -240,3 +240,43 @@ def test_hunyuan_tp2_matches_single_gpu(fused):
         assert rel(out, ref_out) < 1e-2
     bad = [(n, rel(merged[n], g)) for n, g in ref_g.items() if g.norm() > 2e-4 and rel(merged[n], g) > 3e-2]
     assert not bad, bad
+
+
+def _encoder_fed_nccl_worker(rank, world):
+    """Rank 0 trains a two-layer DiT, rank 1 is its encoder rank; samples cross over NCCL send / recv."""
+    import os
+
+    from teletron_b200.ops import _lib
+    from teletron_b200.train import Trainer, make_forward_step, parse_args
+
+    os.environ["WORLD_SIZE"], os.environ["RANK"] = str(world), str(rank)
+    argv = ("--model ParallelWanModel --model-preset wan-tiny --hidden-size 256 --num-attention-heads 2 "
+            "--ffn-hidden-size 512 --num-layers 2 --bf16 --train-iters 3 --micro-batch-size 1 --lr 1e-3 "
+            "--num-frames 5 --video-resolution 64 64 --log-interval 100 --clip-grad 1.0 --seed 5 "
+            "--distributed-backend nccl --distributed-vae --distributed-vae-world-size 1 "
+            "--encoder-name synthetic_wan_encoder --dataset-type FakeDataset").split()
+
+    def extra_args(p):
+        p.add_argument("--encoder-name", type=str, default=None)
+        p.add_argument("--text-dim", type=int, default=64)
+        p.add_argument("--text-len", type=int, default=16)
+        return p
+
+    a = parse_args(extra_args, argv)
+    try:
+        t = Trainer(a)
+    except SystemExit:
+        return "encoder-rank-done"
+    before = t.buffer.params.float().clone()
+    t.pretrain(make_forward_step())
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return a.iteration, float((t.buffer.params.float() - before).abs().sum())
+
+
+@needs2
+def test_training_fed_by_an_encoder_rank_over_nccl():
+    outs = run_distributed(_encoder_fed_nccl_worker, 2, backend="nccl", timeout=150)
+    assert outs[1] == "encoder-rank-done"
+    iters, moved = outs[0]
+    assert iters == 3 and moved > 0
