@@ -30,6 +30,11 @@ _FLAGS = [
     ("--max-position-embeddings", dict(type=int, default=4096)),
     ("--tokenizer-type", dict(type=str, default="NullTokenizer")),
     ("--vocab-size", dict(type=int, default=0)),
+    ("--vocab-file", dict(type=str, default=None)),
+    ("--merge-file", dict(type=str, default=None)),
+    ("--tokenizer-model", dict(type=str, default=None)),
+    ("--vocab-extra-ids", dict(type=int, default=0)),
+    ("--make-vocab-size-divisible-by", dict(type=int, default=128)),
     ("--model", dict(type=str, default="ParallelWanModel")),
     ("--model-preset", dict(type=str, default=None, help="e.g. wan2.1-1.3b-t2v, wan2.1-14b-i2v")),
     ("--task-type", dict(type=str, default=None, help="t2v | i2v (reference spelling wan_i2v_prone accepted)")),

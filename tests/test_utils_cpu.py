@@ -147,3 +147,44 @@ def test_activation_memory_fit_and_max_frames():
     assert max_trainable_frames(100.0, 10.0, 0.002, 64, 64) == (2562 - 1) * 4 + 1
     assert max_trainable_frames(100.0, 10.0, 0.002, 64, 64, cp=2) == (5125 - 1) * 4 + 1
     assert max_trainable_frames(15.0, 10.0, 0.002, 64, 64) == 0
+
+
+def test_megatron_tokenizer_types(tmp_path):
+    from argparse import Namespace
+
+    import sentencepiece as spm
+
+    from teletron_b200.utils.tokenizer import build_tokenizer
+
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text("\n".join(["a cat sits on the mat", "the dog runs in the park", "video of a sunny beach",
+                                 "a person walks the dog on the beach"] * 20))
+    spm.SentencePieceTrainer.train(input=str(corpus), model_prefix=str(tmp_path / "sp"), vocab_size=60,
+                                   model_type="bpe", pad_id=3)
+    model = str(tmp_path / "sp.model")
+    a = Namespace(tokenizer_type="SentencePieceTokenizer", tokenizer_model=model, vocab_extra_ids=2,
+                  make_vocab_size_divisible_by=16, tensor_model_parallel_size=2)
+    tok = build_tokenizer(a)
+    assert tok.vocab_size == 60 + 4 + 2                        # <CLS> <SEP> <EOD> <MASK> + two sentinels; pad/bos/eos exist
+    assert a.padded_vocab_size == 96 and a.padded_vocab_size % 32 == 0
+    ids = tok.tokenize("a cat <SEP> the dog <extra_id_1>")
+    assert tok.sep in ids and ids[-1] == tok.vocab["<extra_id_1>"]
+    assert tok.detokenize(ids) == "a cat <SEP> the dog <extra_id_1>"
+    assert len({tok.cls, tok.sep, tok.eod, tok.mask, tok.pad, tok.bos, tok.eos}) == 7
+    gpt = build_tokenizer(Namespace(tokenizer_type="GPTSentencePieceTokenizer", tokenizer_model=model))
+    assert gpt.vocab_size == 60 and gpt.eod == gpt.eos and gpt.detokenize(gpt.tokenize("the park")) == "the park"
+    ll = build_tokenizer(Namespace(tokenizer_type="Llama2Tokenizer", tokenizer_model=model))
+    plain = ll.tokenize("a cat", bos=False)
+    assert ll.tokenize("a cat") == [ll.bos] + plain and ll.tokenize("a cat", bos=False, eos=True) == plain + [ll.eos]
+
+    vocab = tmp_path / "vocab.txt"
+    vocab.write_text("\n".join(["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]", "the", "cat", "sat", "##s", "dog"]))
+    bert = build_tokenizer(Namespace(tokenizer_type="BertWordPieceLowerCase", vocab_file=str(vocab),
+                                     make_vocab_size_divisible_by=8))
+    assert bert.tokenize("The cats sat") == [5, 6, 8, 7] and (bert.cls, bert.sep, bert.pad, bert.mask) == (2, 3, 0, 4)
+    assert bert.eod == 3 and bert.vocab_size == 10
+
+    null = build_tokenizer(Namespace(tokenizer_type="NullTokenizer", vocab_size=100))
+    assert null.tokenize("3 14 15") == [3, 14, 15] and null.eod == 100
+    with pytest.raises(NotImplementedError):
+        build_tokenizer(Namespace(tokenizer_type="Klingon"))
