@@ -4,6 +4,10 @@ sharded lists), model-type detection and meta-device instantiation with ``assign
 Counterpart of the reference ModelManager and its helpers (teletron/models/wan/encoder/
 model_manager.py:13-415, wan_encoder_utils.py:232-368).  Detection is by characteristic keys /
 shapes instead of key-hash tables; the Wan DiT accepts native, diffusers and prefixed layouts.
+``load_lora`` folds low-rank adapter files (PEFT ``lora_A`` / ``lora_B`` or kohya ``lora_down`` /
+``lora_up`` naming, optional per-module ``alpha``) into the weights of a loaded model, so inference
+and further training run on the fused kernels unchanged (the reference's ``load_lora``, model_manager.py:
+333-353, depends on loaders that are not in its tree).
 """
 from __future__ import annotations
 
@@ -46,6 +50,52 @@ def init_weights_on_device(device=torch.device("meta")):
         yield
 
 
+_LORA_PAIRS = ((".lora_A.weight", ".lora_B.weight"), (".lora_A.default.weight", ".lora_B.default.weight"),
+               (".lora_down.weight", ".lora_up.weight"))
+_LORA_PREFIXES = ("base_model.model.", "diffusion_model.", "transformer.", "model.", "lora_unet_")
+
+
+def is_lora_state_dict(sd: Dict[str, torch.Tensor]) -> bool:
+    return any(k.endswith(down) for k in sd for down, _ in _LORA_PAIRS)
+
+
+def merge_lora(model: torch.nn.Module, lora_sd: Dict[str, torch.Tensor], alpha: float = 1.0) -> List[str]:
+    """``W += alpha * scale * up @ down`` for every adapter pair whose module exists in ``model``; ``scale`` is
+    ``<module>.alpha / rank`` when the file carries it, else 1.  Returns the names of the updated parameters
+    and raises when the file matches nothing (a wrong base model)."""
+    # checkpoint-layout names: a fused projection (q, k, v stored as one matrix) appears under its separate
+    # names as views of the fused storage, so the in-place update below reaches the parameter
+    params = {k: v for k, v in model.state_dict().items() if torch.is_tensor(v)}
+    updated = []
+    for key, down in lora_sd.items():
+        for d_suffix, u_suffix in _LORA_PAIRS:
+            if not key.endswith(d_suffix):
+                continue
+            stem = key[: -len(d_suffix)]
+            up = lora_sd.get(stem + u_suffix)
+            if up is None:
+                raise KeyError(f"{key} has no matching {stem + u_suffix}")
+            name = stem
+            for pre in _LORA_PREFIXES:
+                if name.startswith(pre) and (name[len(pre):] + ".weight") in params:
+                    name = name[len(pre):]
+                    break
+            target = params.get(name + ".weight")
+            if target is None:
+                continue
+            rank = down.shape[0]
+            scale = float(lora_sd[stem + ".alpha"]) / rank if (stem + ".alpha") in lora_sd else 1.0
+            delta = (up.float().flatten(1) @ down.float().flatten(1)) * (alpha * scale)
+            if delta.numel() != target.numel():
+                raise ValueError(f"adapter for {name} has shape {tuple(delta.shape)}, weight is {tuple(target.shape)}")
+            with torch.no_grad():
+                target.add_(delta.view_as(target).to(device=target.device, dtype=target.dtype))
+            updated.append(name + ".weight")
+    if not updated:
+        raise ValueError("no adapter in the file matches a module of this model")
+    return updated
+
+
 def detect_model_type(sd: Dict[str, torch.Tensor]) -> Optional[str]:
     keys = sd.keys()
     if any(k.endswith("patch_embedding.weight") for k in keys) and any("self_attn" in k or ".attn1." in k for k in keys):
@@ -69,6 +119,12 @@ class ModelManager:
 
     def load_model(self, path, device=None, torch_dtype=None):
         device, dt = device or self.device, torch_dtype or self.torch_dtype
+        if isinstance(path, str) and os.path.isdir(path):     # a folder of shards counts as one checkpoint
+            shards = sorted(os.path.join(path, f) for f in os.listdir(path)
+                            if f.endswith((".safetensors", ".pth", ".pt", ".bin", ".ckpt")))
+            if not shards:
+                raise FileNotFoundError(f"no weight files in {path}")
+            path = shards
         sd = load_state_dict(path, "cpu", dt)
         kind = detect_model_type(sd)
         if kind is None:
@@ -85,6 +141,25 @@ class ModelManager:
     def load_models(self, paths, device=None, torch_dtype=None):
         for p in paths:
             self.load_model(p, device, torch_dtype)
+
+    def load_lora(self, path=None, state_dict=None, lora_alpha: float = 1.0, kind: Optional[str] = None):
+        """Fold an adapter file into a loaded model: ``kind`` if given, else the first loaded model it matches."""
+        sd = state_dict if state_dict is not None else load_state_dict(path, "cpu")
+        if not is_lora_state_dict(sd):
+            raise ValueError(f"{path or 'state dict'} holds no low-rank adapter weights")
+        for k in ([kind] if kind else list(self.models)):
+            try:
+                return k, merge_lora(self.models[k], sd, lora_alpha)
+            except ValueError:
+                if kind:
+                    raise
+        raise ValueError("the adapter matches none of the loaded models")
+
+    def to(self, device):
+        for k, m in self.models.items():
+            self.models[k] = m.to(device)
+        self.device = device
+        return self
 
     def _instantiate(self, kind, sd):
         with init_weights_on_device():

@@ -2,6 +2,7 @@
 converter and model-shape detection, and the sampling pipeline end to end on tiny models."""
 from argparse import Namespace
 
+import pytest
 import torch
 
 from teletron_b200.infer import HunyuanVideoPipeline, WanVideoPipeline
@@ -125,3 +126,48 @@ def test_pipelines_run_end_to_end():
     lat = hp(torch.randn(1, 8, 64), torch.ones(1, 8, dtype=torch.long), torch.randn(1, 32), height=32, width=32,
              num_frames=5, num_inference_steps=2, seed=1)
     assert lat.shape == (1, 16, 2, 4, 4) and torch.isfinite(lat).all()
+
+
+def test_model_manager_loads_shards_detects_type_and_merges_lora(tmp_path):
+    from teletron_b200.models import WanModel, wan_config
+    from teletron_b200.models.model_manager import ModelManager, is_lora_state_dict, merge_lora
+
+    torch.manual_seed(0)
+    cfg = wan_config("wan-tiny", dim=256, num_heads=2, ffn_dim=512, text_dim=64, freq_dim=64, num_layers=2)
+    src = WanModel(cfg)
+    sd = {k: v.detach().clone() for k, v in src.state_dict().items()}
+    keys = sorted(sd)
+    folder = tmp_path / "dit"
+    folder.mkdir()
+    torch.save({k: sd[k] for k in keys[: len(keys) // 2]}, folder / "part-00001.pth")       # two shards
+    torch.save({"state_dict": {k: sd[k] for k in keys[len(keys) // 2:]}}, folder / "part-00002.pth")
+    mm = ModelManager(torch_dtype=torch.float32, device="cpu")
+    model = mm.load_model(str(folder))
+    assert mm.fetch_model("wan_video_dit") is model and mm.fetch_model("wan_video_vae") is None
+    with pytest.raises(KeyError):
+        mm.fetch_model("wan_video_vae", require=True)
+    got = model.state_dict()
+    assert all(torch.equal(got[k], sd[k]) for k in sd)
+    assert (model.cfg.dim, model.cfg.num_layers, model.cfg.ffn_dim) == (256, 2, 512)
+
+    # a rank-4 adapter on two projections, PEFT naming with a prefix and kohya naming with alpha
+    down1, up1 = torch.randn(4, 256) * 0.1, torch.randn(256, 4) * 0.1
+    down2, up2 = torch.randn(4, 256) * 0.1, torch.randn(512, 4) * 0.1
+    lora = {"base_model.model.blocks.0.self_attn.q.lora_A.weight": down1,
+            "base_model.model.blocks.0.self_attn.q.lora_B.weight": up1,
+            "blocks.1.ffn.0.lora_down.weight": down2, "blocks.1.ffn.0.lora_up.weight": up2,
+            "blocks.1.ffn.0.alpha": torch.tensor(2.0)}
+    assert is_lora_state_dict(lora) and not is_lora_state_dict(sd)
+    kind, names = mm.load_lora(state_dict=lora, lora_alpha=0.5)
+    assert kind == "wan_video_dit" and sorted(names) == ["blocks.0.self_attn.q.weight", "blocks.1.ffn.0.weight"]
+    got = model.state_dict()
+    assert torch.allclose(got["blocks.0.self_attn.q.weight"], sd["blocks.0.self_attn.q.weight"] + 0.5 * up1 @ down1,
+                          atol=1e-6)
+    assert torch.allclose(got["blocks.1.ffn.0.weight"], sd["blocks.1.ffn.0.weight"] + 0.5 * (2.0 / 4) * up2 @ down2,
+                          atol=1e-6)
+    assert torch.equal(got["blocks.1.self_attn.q.weight"], sd["blocks.1.self_attn.q.weight"])
+    with pytest.raises(ValueError):
+        merge_lora(model, {"nowhere.lora_A.weight": down1, "nowhere.lora_B.weight": up1})
+    with pytest.raises(ValueError):
+        mm.load_lora(state_dict=sd)
+    assert mm.to("cpu") is mm
