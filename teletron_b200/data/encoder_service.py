@@ -88,10 +88,23 @@ def merge_comm_pairs(pairs: List[CommPair]) -> List[Dict]:
     return list(groups.values())
 
 
-def items_needed(args, iteration: int) -> int:
-    """Samples one consumer will request from `iteration` to the end of training."""
+def items_needed(args, iteration: int, consumed_train_samples: int = 0) -> int:
+    """Samples one consumer will request from `iteration` to the end of training.  With
+    ``--rampup-batch-size`` the global batch grows with the samples consumed, so the count follows the
+    same schedule the trainer steps through."""
     remaining = max((args.train_iters or 0) - iteration, 0)
-    return remaining * args.num_micro_batches * args.micro_batch_size
+    if not getattr(args, "rampup_batch_size", None):
+        return remaining * args.num_micro_batches * args.micro_batch_size
+    from ..train.microbatches import BatchSchedule
+
+    sched = BatchSchedule(args.global_batch_size, args.micro_batch_size, args.data_parallel_size,
+                          args.rampup_batch_size)
+    consumed, total = int(consumed_train_samples), 0
+    for _ in range(remaining):
+        n_mb = sched.update(consumed, strict=True)
+        total += n_mb * args.micro_batch_size
+        consumed += sched.current_global_batch_size
+    return total
 
 
 def _comm_device(backend: str):
@@ -117,7 +130,7 @@ def producer_process(args, encoder=None, dataset=None):
         for req in [dist.irecv(info[i], src=p.consumer) for i, p in enumerate(pairs)]:
             req.wait()
         iteration, consumed_train = int(info[0, 0]), int(info[0, 1])
-        total = items_needed(args, iteration)
+        total = items_needed(args, iteration, consumed_train)
         # 2. one data iterator per group of consumers that share data
         groups = merge_comm_pairs(pairs)
         if dataset is None:

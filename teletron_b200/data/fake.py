@@ -63,3 +63,34 @@ class SyntheticLatentDataset(Dataset):
             out["image_emb_y"] = torch.cat([mask, cond], dim=0).to(self.dtype)
             out["clip_feature"] = torch.randn(self.clip_tokens, self.clip_dim, generator=g).to(self.dtype)
         return out
+
+
+@DATASETS.register("SyntheticHunyuanDataset")
+class SyntheticHunyuanDataset(Dataset):
+    """Already-encoded HunyuanVideo samples in the order the encoder ranks deliver them (prompt_embeds,
+    clip_text_embed, first_ref_image, latents): LLM text states ``[text_len, text_dim]`` with a ragged
+    ``prompt_mask`` (the model masks the padded tail), the pooled CLIP text vector, the VAE latent of the first
+    frame (image-to-video only) and the video latent."""
+
+    def __init__(self, num_frames=129, height=720, width=1280, length=10_000_000, text_len=256, text_dim=4096,
+                 pooled_dim=768, i2v=False, dtype=torch.bfloat16, seed=0, **_):
+        self.grid = latent_grid(num_frames, height, width)
+        self.length, self.text_len, self.text_dim, self.pooled_dim = length, text_len, text_dim, pooled_dim
+        self.i2v, self.dtype, self.seed = i2v, dtype, seed
+
+    def __len__(self):
+        return self.length
+
+    def __getitem__(self, idx):
+        g = torch.Generator().manual_seed(self.seed * 1_000_003 + int(idx))
+        f, h, w = self.grid
+        n_text = int(torch.randint(max(self.text_len // 4, 1), self.text_len + 1, (1,), generator=g))
+        mask = torch.zeros(self.text_len, dtype=torch.long)
+        mask[:n_text] = 1
+        out = dict(latents=torch.randn(16, f, h, w, generator=g).to(self.dtype),
+                   prompt_embeds=torch.randn(self.text_len, self.text_dim, generator=g).to(self.dtype),
+                   prompt_mask=mask,
+                   clip_text_embed=torch.randn(self.pooled_dim, generator=g).to(self.dtype))
+        if self.i2v:
+            out["first_ref_image"] = torch.randn(16, 1, h, w, generator=g).to(self.dtype)
+        return out

@@ -39,8 +39,11 @@ class Registry:
 
 MODELS = Registry("model")
 ENCODERS = Registry("encoder")
+# HunyuanVideo: the reference ships no encoder bundle for it; the weight-free stand-in serves the schema until a
+# user-supplied BaseEncoder subclass is named with --encoder-name
 MODEL_TO_ENCODER = {"ParallelWanModel": "wan_encoder", "WanModel": "wan_encoder",
-                    "ParallelHunyuanVideoModel": "hunyuan_encoder"}
+                    "ParallelHunyuanVideoModel": "synthetic_hunyuan_encoder",
+                    "HunyuanVideoModel": "synthetic_hunyuan_encoder"}
 
 
 def build_model(name: str, config, **kw):

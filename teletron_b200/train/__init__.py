@@ -2,4 +2,5 @@ from .arguments import build_parser, get_args, get_num_microbatches, parse_args,
 from .microbatches import (BatchSchedule, get_current_global_batch_size,  # noqa: F401
                            update_num_microbatches)
 from .trainer import Float16Module, Trainer  # noqa: F401
+from .hunyuan_step import make_hunyuan_forward_step  # noqa: F401
 from .wan_step import average_losses_across_data_parallel_group, make_forward_step  # noqa: F401

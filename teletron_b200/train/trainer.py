@@ -211,6 +211,10 @@ class Trainer:
         i2v = (a.task_type == "i2v")
         name = "SyntheticLatentDataset" if (a.synthetic_latents or a.dataset_type == "SyntheticLatentDataset") else a.dataset_type
         kw = dict(num_frames=a.num_frames, height=h, width=w, i2v=i2v, seed=a.seed)
+        if name == "SyntheticLatentDataset" and "Hunyuan" in a.model:
+            name = "SyntheticHunyuanDataset"                  # same role, the HunyuanVideo batch schema
+            cfg = (self.model.module if hasattr(self.model, "module") else self.model).cfg
+            kw.update(text_dim=cfg.text_embed_dim, pooled_dim=cfg.pooled_projection_dim, i2v=cfg.in_channels > 16)
         if getattr(a, "text_dim", None):
             kw["text_dim"] = a.text_dim
         if getattr(a, "text_len", None):

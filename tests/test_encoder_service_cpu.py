@@ -101,3 +101,17 @@ def test_encoder_service_streams_identical_batches_to_cp_group():
 def test_encoder_failure_reaches_the_consumer():
     out = run_distributed(_service_worker, 3, True)
     assert out[2] == "failed-as-planned" and out[0] == "consumer-saw-failure"
+
+
+def test_items_needed_follows_the_batch_size_ramp():
+    from argparse import Namespace
+
+    from teletron_b200.data.encoder_service import items_needed
+
+    const = Namespace(train_iters=10, num_micro_batches=3, micro_batch_size=2, rampup_batch_size=None)
+    assert items_needed(const, 4) == 6 * 3 * 2
+    # dp 2, micro batch 1: global batch 2 for the first 8 samples, then 4 -> per consumer 1, 1, 1, 1, 2, 2
+    ramp = Namespace(train_iters=6, num_micro_batches=1, micro_batch_size=1, data_parallel_size=2,
+                     global_batch_size=4, rampup_batch_size=["2", "2", "8"])
+    assert items_needed(ramp, 0, 0) == 1 + 1 + 1 + 1 + 2 + 2
+    assert items_needed(ramp, 4, 8) == 2 + 2                  # resumed after the ramp

@@ -97,3 +97,97 @@ def test_tensor_parallel_matches_single_rank_and_shards_round_trip():
         assert (merged_g[n] - g).norm() <= 1e-4 * (g.norm() + 1e-6), n
     for k, v in full_sd.items():
         assert torch.equal(merged_sd[k], v), k
+
+
+def _hy_train_args(world, extra=""):
+    import os
+
+    from teletron_b200.train import parse_args
+
+    os.environ["WORLD_SIZE"], os.environ["RANK"] = str(world), os.environ.get("RANK", "0")
+    argv = (f"--model ParallelHunyuanVideoModel --model-preset hunyuan-tiny --train-iters 2 --micro-batch-size 1 "
+            f"--global-batch-size 2 --lr 1e-3 --synthetic-latents --num-frames 5 --video-resolution 64 64 "
+            f"--log-interval 100 --clip-grad 1.0 --seed 11 --distributed-backend gloo {extra}").split()
+
+    def extra_args(p):
+        p.add_argument("--text-len", type=int, default=12)
+        return p
+
+    return parse_args(extra_args, argv)
+
+
+def _hy_train_worker(rank, world, extra):
+    from teletron_b200.train import Trainer, make_hunyuan_forward_step
+
+    t = Trainer(_hy_train_args(world, extra))
+    gen = torch.Generator().manual_seed(4)
+    fwd = make_hunyuan_forward_step(timestep_generator=gen)
+    losses = []
+    for _ in range(2):
+        ld, skipped, gnorm, _ = t.train_step(fwd)
+        assert skipped == 0 and torch.isfinite(gnorm)
+        losses.append(float(ld["loss"]))
+    return losses, t.buffer.params.float().clone()
+
+
+def test_hunyuan_trains_through_the_trainer_alone_and_with_cp2_tp2():
+    """Same seed, data and timesteps: one rank and Ulysses CP = 2 give the same loss (the noise is drawn on the
+    source rank of the TP x CP group and broadcast; its generator state equals the one-rank state).  Under TP = 2
+    the sharded layers draw their initial weights per shard, so only agreement between the ranks is checked."""
+    (single, p1), = run_distributed(_hy_train_worker, 1, "")
+    assert all(l == l and l > 0 for l in single)
+    cp = run_distributed(_hy_train_worker, 2, "--context-parallel-size 2 --use-distributed-optimizer")
+    assert cp[0][0] == cp[1][0] and torch.equal(cp[0][1], cp[1][1])
+    assert abs(cp[0][0][0] - single[0]) < 2e-3 * abs(single[0])
+    tp = run_distributed(_hy_train_worker, 2, "--tensor-model-parallel-size 2")
+    assert tp[0][0] == tp[1][0] and all(l == l and l > 0 for l in tp[0][0])
+
+
+def test_hunyuan_i2v_step_builds_the_33_channel_input():
+    from teletron_b200.data import SyntheticHunyuanDataset
+    from teletron_b200.models.hunyuan import ParallelHunyuanVideoModel
+    from teletron_b200.train import make_hunyuan_forward_step
+
+    cfg = hunyuan_config("hunyuan-tiny", in_channels=33)
+    model = ParallelHunyuanVideoModel(cfg)
+    ds = SyntheticHunyuanDataset(5, 64, 64, text_len=12, text_dim=cfg.text_embed_dim,
+                                 pooled_dim=cfg.pooled_projection_dim, i2v=True, dtype=torch.float32)
+    item = ds[3]
+    assert item["first_ref_image"].shape == (16, 1, 8, 8) and 3 <= int(item["prompt_mask"].sum()) <= 12
+    batch = {k: v.unsqueeze(0) for k, v in item.items()}
+    seen = {}
+    hook = model.x_embedder.register_forward_pre_hook(lambda m, a: seen.setdefault("x", a[0]))
+    orig = model.patchify
+
+    def spy(x):
+        seen["in"] = x
+        return orig(x)
+
+    model.patchify = spy
+    loss, loss_func = make_hunyuan_forward_step()(iter([batch]), model)
+    hook.remove()
+    assert seen["in"].shape[1] == 33
+    x = seen["in"]
+    assert torch.equal(x[:, 16:32, :1], batch["first_ref_image"]) and float(x[:, 16:32, 1:].abs().sum()) == 0
+    assert float(x[:, 32, 0].min()) == 1.0 and float(x[:, 32, 1:].abs().sum()) == 0
+    loss.backward()
+    _, reduced = loss_func(loss)
+    assert torch.isfinite(reduced["loss"])
+
+
+def _hy_encoder_fed_worker(rank, world):
+    from teletron_b200.train import Trainer, make_hunyuan_forward_step
+
+    a = _hy_train_args(world, "--distributed-vae --distributed-vae-world-size 1 --dataset-type FakeDataset")
+    try:
+        t = Trainer(a)
+    except SystemExit:
+        return "encoder-rank-done"
+    before = t.buffer.params.float().clone()
+    t.pretrain(make_hunyuan_forward_step())
+    return float((t.buffer.params.float() - before).abs().sum())
+
+
+def test_hunyuan_training_fed_by_an_encoder_rank():
+    outs = run_distributed(_hy_encoder_fed_worker, 2, timeout=240)
+    assert outs[1] == "encoder-rank-done" and outs[0] > 0
