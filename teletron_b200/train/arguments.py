@@ -138,6 +138,10 @@ _FLAGS = [
     ("--tensorboard-log-interval", dict(type=int, default=1)),
     ("--log-params-norm", dict(action="store_true")),
     ("--log-timers-to-tensorboard", dict(action="store_true")),
+    ("--timing-log-level", dict(type=int, default=0, choices=[0, 1, 2],
+                                help="1: time forward-backward / gradient reduction / optimizer per step (device "
+                                     "events, max over ranks) and print them at every log interval; 2: also each "
+                                     "micro-batch's forward and backward")),
     ("--log-memory-to-tensorboard", dict(action="store_true")),
     ("--log-throughput", dict(action="store_true")),
     ("--eval-interval", dict(type=int, default=1000)),

@@ -50,28 +50,37 @@ class MemorySnapshot:
 
 
 class DeviceTimers:
-    """Named CUDA-event timers; ``summary()`` gives per-name milliseconds, max over ranks."""
+    """Named phase timers: CUDA events on the current stream when a GPU is present (no host synchronisation
+    until ``summary``), the wall clock otherwise.  ``summary()`` gives per-name milliseconds summed over the
+    recorded intervals, as the maximum over the ranks of ``group``."""
 
-    def __init__(self):
+    def __init__(self, use_cuda=None):
+        self.cuda = torch.cuda.is_available() if use_cuda is None else use_cuda
         self._open = {}
         self._pairs = defaultdict(list)
 
+    def _mark(self):
+        if self.cuda:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            return e
+        return time.perf_counter()
+
     def start(self, name: str):
-        e = torch.cuda.Event(enable_timing=True)
-        e.record()
-        self._open[name] = e
+        self._open[name] = self._mark()
 
     def stop(self, name: str):
-        e = torch.cuda.Event(enable_timing=True)
-        e.record()
-        self._pairs[name].append((self._open.pop(name), e))
+        self._pairs[name].append((self._open.pop(name), self._mark()))
 
     def summary(self, group=None, reset: bool = True):
-        torch.cuda.synchronize()
+        if self.cuda:
+            torch.cuda.synchronize()
         names = sorted(self._pairs)
-        vals = torch.tensor([sum(a.elapsed_time(b) for a, b in self._pairs[n]) for n in names],
-                            dtype=torch.float64, device="cuda")
-        if dist.is_initialized() and dist.get_world_size(group) > 1:
+        span = (lambda a, b: a.elapsed_time(b)) if self.cuda else (lambda a, b: (b - a) * 1e3)
+        vals = torch.tensor([sum(span(a, b) for a, b in self._pairs[n]) for n in names], dtype=torch.float64,
+                            device="cuda" if (self.cuda and (not dist.is_initialized() or dist.get_backend(group) == "nccl"))
+                            else "cpu")
+        if dist.is_initialized() and dist.get_world_size(group) > 1 and len(names):
             dist.all_reduce(vals, op=dist.ReduceOp.MAX, group=group)
         if reset:
             self._pairs.clear()

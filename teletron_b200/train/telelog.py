@@ -40,7 +40,10 @@ class TrainLogger:
             return None
 
     def log(self, loss_dict, iteration, lr, loss_scale, grad_norm, skipped_iter, params_norm=None,
-            tokens: int = 0, device_ms: float = 0.0) -> bool:
+            tokens: int = 0, device_ms: float = 0.0, timers=None) -> bool:
+        """``timers``: a ``DeviceTimers`` whose intervals since the last report are summarised (collectively: every
+        rank must pass it) at the log interval, printed as ``name: ms per iteration`` and, with
+        ``--log-timers-to-tensorboard``, written as ``<name>-time`` scalars."""
         a = self.args
         self.counts[self.SKIP if skipped_iter else self.ADV] += 1
         got_nan = False
@@ -95,6 +98,18 @@ class TrainLogger:
         parts.append(f"number of nan iterations: {self.counts[self.NAN]:3d}")
         if a.rank == a.world_size - 1:
             print(" | ".join(parts), flush=True)
+        if timers is not None:
+            n_it = max(self.counts[self.ADV] + self.counts[self.SKIP], 1)
+            from ..parallel import state as mpu
+
+            grp = mpu.get_transformer_model_group() if mpu.model_parallel_is_initialized() else None
+            per_it = {k: v / n_it for k, v in timers.summary(group=grp).items()}   # encoder ranks take no part
+            self.last_timings = per_it
+            if a.rank == a.world_size - 1 and per_it:
+                print("    time (ms) | " + " | ".join(f"{k}: {v:.2f}" for k, v in per_it.items()), flush=True)
+            if w is not None and a.log_timers_to_tensorboard:
+                for k, v in per_it.items():
+                    w.add_scalar(f"{k}-time", v, iteration)
         report_mem = not self.reported_memory and torch.cuda.is_available()
         if report_mem:
             self.reported_memory = True

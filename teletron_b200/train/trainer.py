@@ -85,6 +85,11 @@ class Trainer:
         _set_random_seed(args.seed, mpu.get_data_parallel_rank(), args.data_parallel_random_init)
         self.setup_model_and_optimizer()
         self.logger = TrainLogger(args, TrainLogger.make_writer(args))
+        self.timers = None
+        if getattr(args, "timing_log_level", 0) > 0 or getattr(args, "log_timers_to_tensorboard", False):
+            from .profiling import DeviceTimers
+
+            self.timers = DeviceTimers()
         if build_data:
             self.build_data_iterators()
         self._signal_seen = False
@@ -250,15 +255,34 @@ class Trainer:
         self.optimizer.zero_grad()
         n_mb = a.num_micro_batches
         reduced_all = []
+        tm = getattr(self, "timers", None)
+        fine = tm is not None and a.timing_log_level >= 2
+        if tm is not None:
+            tm.start("forward-backward")
         for _ in range(n_mb):
+            if fine:
+                tm.start("forward-compute")
             output, loss_func = forward_step_func(it, self.model)
             loss, reduced = loss_func(output)
+            if fine:
+                tm.stop("forward-compute")
+                tm.start("backward-compute")
             (loss / n_mb).backward()
+            if fine:
+                tm.stop("backward-compute")
             reduced_all.append(reduced)
+        if tm is not None:
+            tm.stop("forward-backward")
+            tm.start("grads-reduce")
         if a.empty_unused_memory_level >= 2 and self.device.type == "cuda":
             torch.cuda.empty_cache()
         self.optimizer.reduce_gradients()
+        if tm is not None:
+            tm.stop("grads-reduce")
+            tm.start("optimizer")
         ok, grad_norm, num_zeros = self.optimizer.step()
+        if tm is not None:
+            tm.stop("optimizer")
         if a.empty_unused_memory_level >= 1 and self.device.type == "cuda":
             torch.cuda.empty_cache()
         if ok and self.opt_param_scheduler is not None:
@@ -361,7 +385,7 @@ class Trainer:
             lr = self.optimizer.param_groups[0]["lr"]
             params_norm = self.buffer.params.float().norm() if a.log_params_norm else None
             self.logger.log(loss_dict, iteration, lr, 1.0, grad_norm, skipped, params_norm,
-                            tokens=tokens_per_step, device_ms=dev_ms)
+                            tokens=tokens_per_step, device_ms=dev_ms, timers=self.timers)
             if prof is not None:
                 prof.step()
             if a.profile and iteration == a.profile_step_end and a.rank in a.profile_ranks and use_events:

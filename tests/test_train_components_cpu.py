@@ -271,3 +271,17 @@ def test_trainer_checkpoint_layout_and_exact_resume(tmp_path):
         fh.write(b"truncated")
     with pytest.raises(RuntimeError):
         Trainer(_trainer_args(tmp_path / "third", f"--load {root} --ckpt-step 2"))
+
+
+def test_phase_timers_are_reported_per_iteration(tmp_path, capsys):
+    from teletron_b200.train import Trainer
+
+    a = _trainer_args(tmp_path, "--timing-log-level 2")
+    a.train_iters, a.log_interval, a.save_interval = 2, 2, 1000
+    t = Trainer(a)
+    t.train(make_forward_step())
+    got = t.logger.last_timings
+    assert set(got) == {"forward-backward", "forward-compute", "backward-compute", "grads-reduce", "optimizer"}
+    assert all(v > 0 for v in got.values())
+    assert got["forward-backward"] >= 0.9 * (got["forward-compute"] + got["backward-compute"])
+    assert "time (ms) | backward-compute:" in capsys.readouterr().out
