@@ -163,6 +163,9 @@ _FLAGS = [
     ("--vae-tiled", dict(action="store_true")),
     ("--vae-tile-size", dict(type=int, nargs=2, default=[34, 34])),
     ("--vae-tile-stride", dict(type=int, nargs=2, default=[18, 16])),
+    ("--yaml-cfg", dict(type=str, default=None,
+                        help="YAML (or JSON) file of flag values, flat or grouped one level deep, keys spelled like "
+                             "the flags with - or _; values given on the command line win")),
 ]
 
 
@@ -222,8 +225,51 @@ def validate_args(args):
     return args
 
 
+def _defaults_from_file(parser: argparse.ArgumentParser, path: str) -> dict:
+    """Flag values from a YAML / JSON file as ``dest -> value``; unknown keys are an error (a typo in a config
+    file must not silently train with a default)."""
+    import json
+
+    with open(path) as f:
+        if path.endswith(".json"):
+            data = json.load(f)
+        else:
+            import yaml
+
+            data = yaml.safe_load(f)
+    if not isinstance(data, dict):
+        raise ValueError(f"{path}: expected a mapping of flag names to values")
+    flat = {}
+    for k, v in data.items():
+        if isinstance(v, dict):          # one level of grouping (model:, training:, ...) is only for the reader
+            flat.update(v)
+        else:
+            flat[k] = v
+    actions = {a.dest: a for a in parser._actions}
+    out = {}
+    for k, v in flat.items():
+        dest = str(k).lstrip("-").replace("-", "_")
+        if dest.startswith("no_") and dest not in actions:     # store_false flags are spelled --no-x
+            for a in parser._actions:
+                if f"--{str(k).lstrip('-').replace('_', '-')}" in a.option_strings:
+                    dest, v = a.dest, (not bool(v)) if isinstance(a, argparse._StoreFalseAction) else v
+                    break
+        if dest not in actions:
+            raise ValueError(f"{path}: unknown option {k!r}")
+        act = actions[dest]
+        if act.choices is not None and v not in act.choices and v is not None:
+            raise ValueError(f"{path}: {k} = {v!r} is not one of {list(act.choices)}")
+        if act.type is not None and v is not None and not isinstance(v, (list, tuple, bool)):
+            v = act.type(v)
+        out[dest] = v
+    return out
+
+
 def parse_args(extra_args: Optional[Callable] = None, argv=None):
     parser = build_parser(extra_args)
+    pre, _ = parser.parse_known_args(argv)
+    if pre.yaml_cfg:
+        parser.set_defaults(**_defaults_from_file(parser, pre.yaml_cfg))
     args = parser.parse_args(argv)
     args = validate_args(args)
     if args.show_args and args.rank == 0:

@@ -285,3 +285,30 @@ def test_phase_timers_are_reported_per_iteration(tmp_path, capsys):
     assert all(v > 0 for v in got.values())
     assert got["forward-backward"] >= 0.9 * (got["forward-compute"] + got["backward-compute"])
     assert "time (ms) | backward-compute:" in capsys.readouterr().out
+
+
+def test_flags_from_a_yaml_file_with_command_line_override(tmp_path):
+    cfg = tmp_path / "run.yaml"
+    cfg.write_text("""
+model:
+  model-preset: wan-tiny
+  num_layers: 3
+training:
+  lr: 3.0e-4
+  bf16: true
+  train-iters: 7
+  no-manual-gc-eval: true
+  recompute-granularity: full
+seed: 99
+""")
+    a = parse_args(argv=["--yaml-cfg", str(cfg), "--lr", "1e-5"])
+    assert (a.model_preset, a.num_layers, a.train_iters, a.seed, a.bf16) == ("wan-tiny", 3, 7, 99, True)
+    assert a.lr == 1e-5                                   # the command line wins over the file
+    assert a.manual_gc_eval is False and a.recompute_granularity == "full" and a.recompute_method == "block"
+    bad = tmp_path / "bad.yaml"
+    bad.write_text("learning-rate: 1.0\n")
+    with pytest.raises(ValueError, match="unknown option"):
+        parse_args(argv=["--yaml-cfg", str(bad)])
+    bad.write_text("recompute-granularity: sometimes\n")
+    with pytest.raises(ValueError, match="not one of"):
+        parse_args(argv=["--yaml-cfg", str(bad)])
