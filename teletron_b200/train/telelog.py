@@ -124,9 +124,19 @@ class TrainLogger:
         self.t_last = time.time()
         return report_mem
 
-    def log_validation(self, loss_dict, iteration):
+    def log_validation(self, loss_dict, iteration, prefix: str = None):
+        """Framed console line on the last rank (each value with its perplexity ``exp(min(20, value))``, as the
+        reference prints, teletron/train/trainer.py:776-795) and the validation scalars (telelogger.py:256-262)."""
+        a = self.args
+        if a.rank == a.world_size - 1 and loss_dict:
+            line = f" validation loss at {prefix or f'iteration {iteration}'} | "
+            for k, v in loss_dict.items():
+                line += f"{k} value: {float(v):.6E} | {k} PPL: {math.exp(min(20.0, float(v))):.6E} | "
+            bar = "-" * (len(line) + 1)
+            print(f"{bar}\n{line}\n{bar}", flush=True)
         if self.writer is None:
             return
         for k, v in loss_dict.items():
             self.writer.add_scalar(f"{k} validation", float(v), iteration)
-            self.writer.add_scalar(f"{k} validation vs samples", float(v), self.args.consumed_train_samples)
+            self.writer.add_scalar(f"{k} validation vs samples", float(v), a.consumed_train_samples)
+            self.writer.add_scalar(f"{k} validation ppl", math.exp(min(20.0, float(v))), iteration)

@@ -326,9 +326,7 @@ class Trainer:
             self.train(forward_step_func)
         if a.eval_iters > 0 and self.valid_data_iterator is not None:
             res = self.evaluate(forward_step_func)
-            if a.rank == a.world_size - 1:
-                print(f"validation at iteration {a.iteration}: " +
-                      " | ".join(f"{k}: {v:.6E}" for k, v in res.items()), flush=True)
+            self.logger.log_validation(res, a.iteration, prefix=f"the end of training (iteration {a.iteration})")
         if a.save and a.iteration != 0 and not getattr(self, "_saved_at", None) == a.iteration:
             self.save(a.iteration)
         self._shutdown()

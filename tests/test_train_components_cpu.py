@@ -312,3 +312,23 @@ seed: 99
     bad.write_text("recompute-granularity: sometimes\n")
     with pytest.raises(ValueError, match="not one of"):
         parse_args(argv=["--yaml-cfg", str(bad)])
+
+
+def test_validation_runs_at_the_interval_and_reports_perplexity(tmp_path, capsys):
+    import math
+
+    from teletron_b200.train import Trainer
+
+    a = _trainer_args(tmp_path, "--eval-iters 2 --eval-interval 1")
+    a.train_iters, a.save_interval = 2, 1000
+    t = Trainer(a)
+    assert t.valid_data_iterator is not None
+    t.pretrain(make_forward_step())
+    out = capsys.readouterr().out
+    assert "validation loss at iteration 1 |" in out and "validation loss at iteration 2 |" in out
+    assert "validation loss at the end of training (iteration 2)" in out
+    line = [l for l in out.splitlines() if "validation loss at iteration 1" in l][0]
+    val = float(line.split("loss value: ")[1].split(" |")[0])
+    ppl = float(line.split("loss PPL: ")[1].split(" |")[0])
+    assert abs(ppl - math.exp(min(20.0, val))) < 1e-3 * ppl
+    assert a.consumed_valid_samples == 3 * 2 * a.global_batch_size
