@@ -152,6 +152,7 @@ class DistributedOptimizer:
         self._shard_grads: List[Optional[torch.Tensor]] = [None] * len(self.shards)
         # fused path: peer-memory reduce-scatter + AdamW + parameter scatter (csrc/comm.cu)
         self.fused = bool(self.sharded and buf.arena is not None and buf.grads.dtype == torch.float32)
+        self.log_num_zeros = False
         self._reduced = None
         self.last_path = "nccl"
 
@@ -221,6 +222,9 @@ class DistributedOptimizer:
         ss = partials.sum()
         dist.all_reduce(ss, op=dist.ReduceOp.SUM, group=self.group)
         norm = ss.sqrt() * self.grad_scale
+        zeros = None
+        if self.log_num_zeros and need_clip:      # the reduced shards exist only on the two-pass (clipping) path
+            zeros = self._count_zeros(self._reduced)
         if need_clip:
             coef = torch.clamp(self.clip_grad / (norm + 1e-6), max=1.0).reshape(1).float()
             for i in range(len(self.shards)):
@@ -228,7 +232,7 @@ class DistributedOptimizer:
         arena.barrier(1)  # every rank has written its parameter shard into every peer
         self._shard_grads = [None] * len(self.shards)
         self.last_path = "fused"
-        return True, norm, None
+        return True, norm, zeros
 
     @torch.no_grad()
     def step(self):
@@ -240,6 +244,7 @@ class DistributedOptimizer:
         lr = self.param_groups[0]["lr"]
         wd_base = self.param_groups[0]["weight_decay"]
         norm = self._global_grad_norm()
+        zeros = self._count_zeros(self._shard_grads) if self.log_num_zeros else None
         coef = None
         if self.clip_grad and self.clip_grad > 0:
             coef = torch.clamp(self.clip_grad / (norm + 1e-6), max=1.0).reshape(1).float()
@@ -256,7 +261,15 @@ class DistributedOptimizer:
             for (s, e, _), (rs, re, _) in zip(self.shards, self.buf.regions()):
                 dist.all_gather_into_tensor(self.buf.params[rs:re], self.buf.params[s:e].clone(), group=self.group)
         self._shard_grads = [None] * len(self.shards)
-        return True, norm, None
+        return True, norm, zeros
+
+    def _count_zeros(self, shard_grads) -> torch.Tensor:
+        """Number of exactly-zero elements of the reduced gradient (``--log-num-zeros-in-grad``); every element
+        belongs to one shard, so the shard counts add up over the group."""
+        n = sum((g == 0).sum() for g in shard_grads).to(torch.float32)
+        if self.sharded and self.world > 1:
+            dist.all_reduce(n, op=dist.ReduceOp.SUM, group=self.group)
+        return n
 
     def zero_grad(self, set_to_none: bool = True):
         self.buf.zero_grads()

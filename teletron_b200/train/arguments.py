@@ -144,6 +144,16 @@ _FLAGS = [
                                      "micro-batch's forward and backward")),
     ("--log-memory-to-tensorboard", dict(action="store_true")),
     ("--log-throughput", dict(action="store_true")),
+    ("--log-num-zeros-in-grad", dict(action="store_true")),
+    # the scalars these gate in the reference are always written here; the flags are accepted so its command lines run
+    ("--log-batch-size-to-tensorboard", dict(action="store_true")),
+    ("--log-world-size-to-tensorboard", dict(action="store_true")),
+    ("--log-validation-ppl-to-tensorboard", dict(action="store_true")),
+    ("--no-log-learnig-rate-to-tensorboard", dict(action="store_false", dest="log_learning_rate_to_tensorboard")),
+    ("--no-log-loss-scale-to-tensorboard", dict(action="store_false", dest="log_loss_scale_to_tensorboard")),
+    ("--wandb-project", dict(type=str, default="")),
+    ("--wandb-exp-name", dict(type=str, default="")),
+    ("--wandb-save-dir", dict(type=str, default="")),
     ("--eval-interval", dict(type=int, default=1000)),
     ("--eval-iters", dict(type=int, default=0)),
     ("--skip-train", dict(action="store_true")),

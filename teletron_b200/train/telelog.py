@@ -40,7 +40,7 @@ class TrainLogger:
             return None
 
     def log(self, loss_dict, iteration, lr, loss_scale, grad_norm, skipped_iter, params_norm=None,
-            tokens: int = 0, device_ms: float = 0.0, timers=None) -> bool:
+            tokens: int = 0, device_ms: float = 0.0, timers=None, num_zeros_in_grad=None) -> bool:
         """``timers``: a ``DeviceTimers`` whose intervals since the last report are summarised (collectively: every
         rank must pass it) at the log interval, printed as ``name: ms per iteration`` and, with
         ``--log-timers-to-tensorboard``, written as ``<name>-time`` scalars."""
@@ -68,6 +68,9 @@ class TrainLogger:
             w.add_scalar("world-size", a.world_size, iteration)
             if grad_norm is not None:
                 w.add_scalar("grad-norm", float(grad_norm), iteration)
+            if num_zeros_in_grad is not None:
+                w.add_scalar("num-zeros", float(num_zeros_in_grad), iteration)
+                w.add_scalar("num-zeros vs samples", float(num_zeros_in_grad), samples)
             if params_norm is not None:
                 w.add_scalar("params-norm", float(params_norm), iteration)
             if a.log_memory_to_tensorboard and torch.cuda.is_available():
@@ -87,6 +90,8 @@ class TrainLogger:
         parts.append(f"loss scale: {float(loss_scale):.1f}")
         if grad_norm is not None:
             parts.append(f"grad norm: {float(grad_norm):.3f}")
+        if num_zeros_in_grad is not None:
+            parts.append(f"num zeros: {float(num_zeros_in_grad):.1f}")
         if params_norm is not None:
             parts.append(f"params norm: {float(params_norm):.3f}")
         if self.device_ms_since > 0:

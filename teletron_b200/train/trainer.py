@@ -194,6 +194,7 @@ class Trainer:
             sharded=a.use_distributed_optimizer, grad_scale=1.0 / max(a.data_parallel_size, 1),
             tp_group=mpu.get_tensor_model_parallel_group() if a.tensor_model_parallel_size > 1 else None,
             tp_sharded_names=tuple(tp_shard_dims(inner)) if a.tensor_model_parallel_size > 1 else ())
+        self.optimizer.log_num_zeros = bool(getattr(a, "log_num_zeros_in_grad", False))
         self.opt_param_scheduler = scheduler_from_args(a, self.optimizer) if (a.train_iters or a.train_samples) else None
         if a.load or a.pretrained_checkpoint:
             a.iteration, self.num_floating_point_operations_so_far = ckpt.load_checkpoint(
@@ -367,7 +368,7 @@ class Trainer:
             if use_events:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-            loss_dict, skipped, grad_norm, _ = self.train_step(forward_step_func)
+            loss_dict, skipped, grad_norm, num_zeros = self.train_step(forward_step_func)
             dev_ms = 0.0
             if use_events:
                 e1.record()
@@ -383,7 +384,7 @@ class Trainer:
             lr = self.optimizer.param_groups[0]["lr"]
             params_norm = self.buffer.params.float().norm() if a.log_params_norm else None
             self.logger.log(loss_dict, iteration, lr, 1.0, grad_norm, skipped, params_norm,
-                            tokens=tokens_per_step, device_ms=dev_ms, timers=self.timers)
+                            tokens=tokens_per_step, device_ms=dev_ms, timers=self.timers, num_zeros_in_grad=num_zeros)
             if prof is not None:
                 prof.step()
             if a.profile and iteration == a.profile_step_end and a.rank in a.profile_ranks and use_events:

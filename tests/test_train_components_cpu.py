@@ -332,3 +332,20 @@ def test_validation_runs_at_the_interval_and_reports_perplexity(tmp_path, capsys
     ppl = float(line.split("loss PPL: ")[1].split(" |")[0])
     assert abs(ppl - math.exp(min(20.0, val))) < 1e-3 * ppl
     assert a.consumed_valid_samples == 3 * 2 * a.global_batch_size
+
+
+def test_num_zeros_in_grad_is_counted_on_the_reduced_gradient(tmp_path, capsys):
+    from teletron_b200.train import Trainer
+
+    a = _trainer_args(tmp_path, "--log-num-zeros-in-grad --log-interval 1 --log-batch-size-to-tensorboard "
+                                "--no-log-loss-scale-to-tensorboard --wandb-project x")
+    t = Trainer(a)
+    _, _, _, nz = t.train_step(make_forward_step())
+    assert nz is not None and 0 <= float(nz) < t.buffer.grads.numel()
+    t.optimizer.zero_grad()
+    t.buffer.grads.zero_()
+    t.optimizer._shard_grads = [t.buffer.grads[s:e] for s, e, _ in t.optimizer.shards]
+    assert float(t.optimizer._count_zeros(t.optimizer._shard_grads)) == t.buffer.grads.numel()
+    a.train_iters = 1
+    t.train(make_forward_step())
+    assert "num zeros:" in capsys.readouterr().out
