@@ -93,3 +93,53 @@ def detect_wan_config(state_dict: Dict[str, torch.Tensor], head_dim: int = 128) 
 def convert_wan_state_dict(state_dict) -> Tuple[Dict[str, torch.Tensor], WanConfig]:
     sd = from_diffusers(state_dict) if is_diffusers_layout(state_dict) else from_civitai(state_dict)
     return sd, detect_wan_config(sd)
+
+
+# ------------------------------------------------------------------------------------- command line
+def write_release_checkpoint(state_dict: Dict[str, torch.Tensor], out_dir: str, dtype=torch.bfloat16) -> str:
+    """Write ``state_dict`` (native names) as a Megatron-layout checkpoint the trainer loads with ``--load`` or
+    ``--pretrained-checkpoint``: ``<out>/release/mp_rank_00/model_optim_rng.pt`` plus a tracker file that says
+    ``release`` (weights only: iteration 0, no optimizer state)."""
+    import os
+
+    path = os.path.join(out_dir, "release", "mp_rank_00", "model_optim_rng.pt")
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    sd = {k: (v.to(dtype) if torch.is_tensor(v) and v.is_floating_point() else v) for k, v in state_dict.items()}
+    tmp = path + ".tmp"
+    torch.save(dict(model=sd, checkpoint_version=3.0, iteration=0), tmp)
+    os.replace(tmp, path)
+    with open(os.path.join(out_dir, "latest_checkpointed_iteration.txt"), "w") as f:
+        f.write("release")
+    return path
+
+
+def main(argv=None) -> int:
+    """``python -m teletron_b200.models.convert --input <file | shard ... | folder> --output <dir>``: read a Wan DiT
+    checkpoint in diffusers, community single-file or native naming, report the detected shape and write it in the
+    trainer's checkpoint layout."""
+    import argparse
+
+    from .model_manager import load_state_dict
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--input", nargs="+", required=True)
+    ap.add_argument("--output", required=True)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
+    a = ap.parse_args(argv)
+    import os
+
+    paths = a.input
+    if len(paths) == 1 and os.path.isdir(paths[0]):
+        paths = sorted(os.path.join(paths[0], f) for f in os.listdir(paths[0])
+                       if f.endswith((".safetensors", ".pth", ".pt", ".bin", ".ckpt")))
+    sd, cfg = convert_wan_state_dict(load_state_dict(paths if len(paths) > 1 else paths[0]))
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[a.dtype]
+    out = write_release_checkpoint(sd, a.output, dtype)
+    n = sum(v.numel() for v in sd.values() if torch.is_tensor(v))
+    print(f"Wan DiT: dim {cfg.dim}, {cfg.num_layers} layers, {cfg.num_heads} heads, ffn {cfg.ffn_dim}, in {cfg.in_dim}, "
+          f"image branch {cfg.has_image_input}; {n / 1e9:.3f} B parameters ({hash_state_dict_keys(sd)}) -> {out}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

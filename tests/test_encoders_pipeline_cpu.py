@@ -171,3 +171,24 @@ def test_model_manager_loads_shards_detects_type_and_merges_lora(tmp_path):
     with pytest.raises(ValueError):
         mm.load_lora(state_dict=sd)
     assert mm.to("cpu") is mm
+
+
+def test_convert_cli_writes_a_checkpoint_the_trainer_loads(tmp_path, capsys):
+    from teletron_b200.models.convert import main as convert_main
+    from teletron_b200.train import Trainer, parse_args
+
+    torch.manual_seed(3)
+    cfg = wan_config("wan-tiny")
+    src = WanModel(cfg)
+    sd = {k: v.detach().clone() for k, v in src.state_dict().items()}
+    torch.save({"model.diffusion_model." + k: v for k, v in sd.items()}, tmp_path / "community.pth")
+    out = tmp_path / "ckpt"
+    assert convert_main(["--input", str(tmp_path / "community.pth"), "--output", str(out), "--dtype", "fp32"]) == 0
+    assert f"dim {cfg.dim}, {cfg.num_layers} layers" in capsys.readouterr().out
+    assert (out / "latest_checkpointed_iteration.txt").read_text() == "release"
+    a = parse_args(argv=("--model ParallelWanModel --model-preset wan-tiny --train-iters 1 --micro-batch-size 1 "
+                         f"--synthetic-latents --num-frames 5 --video-resolution 64 64 --pretrained-checkpoint {out}").split())
+    a.text_dim, a.text_len = 64, 16
+    t = Trainer(a, build_data=False)
+    got = t.model.state_dict()
+    assert a.iteration == 0 and all(torch.equal(got[k].float(), sd[k]) for k in sd)
