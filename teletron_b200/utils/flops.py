@@ -59,3 +59,37 @@ def max_trainable_frames(capacity_gib: float, static_gib: float, gib_per_token: 
     per_latent_frame = (height // 16) * (width // 16)
     latent_frames = int(room / gib_per_token * cp) // per_latent_frame
     return 0 if latent_frames < 1 else (latent_frames - 1) * 4 + 1
+
+
+# Activation memory per token held on a GPU, calibrated on Wan2.1-1.3B runs on B200 (bf16 activations):
+#   full recompute: one [C] checkpoint per block plus one block's live working set, 197 KiB per token at
+#                   L = 30, C = 1536  ->  2*L*C + 36*C*2 bytes
+#   no recompute:   76 GiB for 32,760 tokens at L = 30, C = 1536 (FFN 8960)  ->  about 53*C bytes per block
+_WORKING_SET_WIDTHS = 36.0
+_SAVED_BYTES_PER_BLOCK_WIDTH = 53.0
+
+
+def activation_gib_per_token(dim: int, num_layers: int, recompute: bool = True) -> float:
+    """Estimated activation memory per token on one GPU (see the calibration above); linear in the hidden size, so
+    wider feed-forward ratios than Wan's 5.8x are under-counted without recompute."""
+    if recompute:
+        b = 2.0 * num_layers * dim + _WORKING_SET_WIDTHS * dim * 2.0
+    else:
+        b = _SAVED_BYTES_PER_BLOCK_WIDTH * dim * num_layers + _WORKING_SET_WIDTHS * dim * 2.0
+    return b / 2 ** 30
+
+
+def plan(cfg, num_params: float, height: int, width: int, frames: int, gpus: int = 1, cp: int = 1,
+         recompute: bool = True, capacity_gib: float = 179.0, tflops_per_gpu: float = 850.0) -> dict:
+    """Back-of-envelope plan for one configuration: tokens, FLOPs per sample, static and activation memory per GPU,
+    whether it fits, the largest frame count that would, and the step time at ``tflops_per_gpu`` of executed work
+    (850 is what the 14B / CP 8 step measured; the 1.3B step reaches about 1,000)."""
+    tokens = ((frames - 1) // 4 + 1) * (height // 16) * (width // 16)
+    static = theoretical_memory_gb(int(num_params), gpus, sharded_optimizer=gpus > 1)
+    per_tok = activation_gib_per_token(cfg.dim, cfg.num_layers, recompute)
+    act = tokens / cp * per_tok
+    flops = wan_flops_per_sample(cfg, tokens, recompute=recompute)
+    return dict(tokens=tokens, flops_per_sample=flops, static_gib=static, activation_gib=act,
+                fits=static + act + 8.0 <= capacity_gib,
+                max_frames=max_trainable_frames(capacity_gib, static, per_tok, height, width, cp=cp),
+                seconds_per_sample=flops / (tflops_per_gpu * 1e12 * cp))

@@ -188,3 +188,20 @@ def test_megatron_tokenizer_types(tmp_path):
     assert null.tokenize("3 14 15") == [3, 14, 15] and null.eod == 100
     with pytest.raises(NotImplementedError):
         build_tokenizer(Namespace(tokenizer_type="Klingon"))
+
+
+def test_planner_reproduces_the_measured_configurations(capsys):
+    from teletron_b200.models import wan_config
+    from teletron_b200.utils.flops import activation_gib_per_token, plan
+    from teletron_b200.utils.plan import main as plan_main
+
+    # the calibration point: Wan2.1-1.3B, full recompute, 197 KiB per token
+    assert abs(activation_gib_per_token(1536, 30, True) * 2 ** 20 - 197.5) < 3.0
+    r = plan(wan_config("wan2.1-1.3b-t2v"), 1.42e9, 720, 1280, 161, tflops_per_gpu=1000.0)
+    assert r["tokens"] == 147_600 and abs(r["static_gib"] + r["activation_gib"] - 51.7) < 2.0   # measured 51.73 GiB
+    assert r["fits"] and 800 < r["max_frames"] < 900 and 17.0 < r["seconds_per_sample"] < 23.0  # measured 21.9 s
+    big = plan(wan_config("wan2.1-14b-i2v"), 16.4e9, 720, 1280, 81, gpus=8, cp=8)
+    assert big["fits"] and 3.5 < big["seconds_per_sample"] < 5.0                                 # measured 4.36 s
+    assert not plan(wan_config("wan2.1-14b-i2v"), 16.4e9, 720, 1280, 81, gpus=1)["fits"]
+    assert plan_main(["--model", "wan-tiny", "--height", "64", "--width", "64", "--frames", "5"]) == 0
+    assert "tokens per sample" in capsys.readouterr().out
