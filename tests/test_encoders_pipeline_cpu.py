@@ -192,3 +192,24 @@ def test_convert_cli_writes_a_checkpoint_the_trainer_loads(tmp_path, capsys):
     t = Trainer(a, build_data=False)
     got = t.model.state_dict()
     assert a.iteration == 0 and all(torch.equal(got[k].float(), sd[k]) for k in sd)
+
+
+def test_generation_example_runs_on_tiny_models(tmp_path):
+    import importlib.util
+    from pathlib import Path
+
+    from teletron_b200.utils.video_io import read_video_frames
+
+    path = Path(__file__).resolve().parents[1] / "examples" / "wan" / "generate_wan.py"
+    spec = importlib.util.spec_from_file_location("generate_wan", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    out = tmp_path / "smoke.avi"
+    assert mod.main(["--tiny", "--device", "cpu", "--height", "64", "--width", "64", "--frames", "9", "--steps", "2",
+                     "--out", str(out)]) == 0
+    assert read_video_frames(str(out)).shape == (9, 64, 64, 3)
+    # image-to-video: the first frame comes from the clip just written
+    out2 = tmp_path / "smoke_i2v.avi"
+    assert mod.main(["--tiny", "--device", "cpu", "--height", "64", "--width", "64", "--frames", "5", "--steps", "1",
+                     "--image", str(out), "--out", str(out2)]) == 0
+    assert read_video_frames(str(out2)).shape[0] == 5
