@@ -9,6 +9,10 @@ synthetic latents / text embeddings, random-init weights, AdamW.  The same globa
 used at every N (strong scaling): DP over the ranks that are not used for Ulysses CP, gradient
 accumulation when fewer than 8 replicas exist.  Rank 0 prints one JSON line.
 
+Other rows of the same benchmark: ``--model wan2.1-14b-i2v --cp 8 --height 720 --width 1280 --global-batch 1
+--recompute`` (any Wan preset, resolution, frame count, global batch, Ulysses size); the metric name then carries the
+preset and resolution.  ``peak_mem_gib`` is the allocator's high-water mark, max over ranks.
+
 `value` is timed on the device with CUDA events with inputs already resident; `e2e` repeats
 the measurement through ``Trainer.train_step`` with every step's inputs copied from pinned host
 memory and the loss read back to the host.
