@@ -63,3 +63,48 @@ def test_training_fed_by_an_encoder_rank():
     outs = run_distributed(_encoder_fed_worker, 3, timeout=240)
     assert outs[2] == "encoder-rank-done"
     assert outs[0] == outs[1] and outs[0] > 0
+
+
+def _resilience_worker(rank, world, root, mode):
+    """mode "full": 3 uninterrupted iterations.  "fail": rank 1 leaves after iteration 1 (between steps, nothing
+    of its own in flight); rank 0 finds out at its next collective.  "resume": continue from the last checkpoint."""
+    from teletron_b200.train import Trainer, make_forward_step
+
+    extra = ("--use-distributed-optimizer --synthetic-latents --global-batch-size 2 --save-interval 1 "
+             f"--save {root}/{'full' if mode == 'full' else 'run'}")
+    if mode == "resume":
+        extra += f" --load {root}/run"
+    a = _args(world, extra)
+    a.train_iters = 3
+    t = Trainer(a)
+    # the timestep stream is a function of the iteration, so a resumed run draws what the first run would have
+    def fwd_for(it):
+        g = torch.Generator().manual_seed(100 + it)
+        return make_forward_step(timestep_generator=g)
+
+    start = a.iteration
+    try:
+        for it in range(start, a.train_iters):
+            if mode == "fail" and rank == 1 and it == 1:
+                return "left-after-1"
+            a.train_iters = it + 1                 # one iteration per call: train() saves at --save-interval 1
+            t.train(fwd_for(it))
+    except Exception as e:  # the survivor: its collective fails once the peer is gone
+        return f"peer-lost at iteration {a.iteration}: {type(e).__name__}"
+    return start, a.iteration, t.buffer.params.float().clone()
+
+
+def test_a_rank_leaving_is_detected_and_training_resumes_from_the_checkpoint(tmp_path):
+    root = str(tmp_path)
+    full = run_distributed(_resilience_worker, 2, root, "full", timeout=240)
+    assert full[0][:2] == (0, 3) and torch.equal(full[0][2], full[1][2])
+    failed = run_distributed(_resilience_worker, 2, root, "fail", timeout=240)
+    assert failed[1] == "left-after-1"
+    assert isinstance(failed[0], str) and failed[0].startswith("peer-lost at iteration 1"), failed[0]
+    from teletron_b200.train.checkpoint import read_tracker
+
+    assert read_tracker(f"{root}/run") == (1, False)              # the last complete checkpoint
+    resumed = run_distributed(_resilience_worker, 2, root, "resume", timeout=240)
+    assert resumed[0][:2] == (1, 3) and resumed[1][:2] == (1, 3)
+    assert torch.equal(resumed[0][2], resumed[1][2])
+    assert torch.allclose(resumed[0][2], full[0][2], atol=1e-6)    # same end state as the uninterrupted run
