@@ -137,7 +137,8 @@ def producer_process(args, encoder=None, dataset=None):
             from . import build_dataset
 
             h, w = args.video_resolution
-            dataset = build_dataset(args.dataset_type, num_frames=args.num_frames, height=h, width=w, seed=args.seed)
+            dataset = build_dataset(args.dataset_type, num_frames=args.num_frames, height=h, width=w, seed=args.seed,
+                                    data_path=getattr(args, "data_path", None))
         from .samplers import build_data_loader
 
         iters = []

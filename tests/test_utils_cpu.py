@@ -205,3 +205,42 @@ def test_planner_reproduces_the_measured_configurations(capsys):
     assert not plan(wan_config("wan2.1-14b-i2v"), 16.4e9, 720, 1280, 81, gpus=1)["fits"]
     assert plan_main(["--model", "wan-tiny", "--height", "64", "--width", "64", "--frames", "5"]) == 0
     assert "tokens per sample" in capsys.readouterr().out
+
+
+@pytest.mark.skipif(not _have_writer(), reason="no video writer backend installed")
+def test_video_folder_dataset_feeds_the_encoders(tmp_path):
+    import json
+
+    from teletron_b200.data import build_dataset
+    from teletron_b200.data.synthetic_encoder import SyntheticWanEncoder
+    from teletron_b200.data.video_folder import resize_center_crop
+
+    root = tmp_path / "data"
+    (root / "clips").mkdir(parents=True)
+    video_io.save_video(list(_clip(T=12, H=48, W=64)), str(root / "clips" / "a.avi"), fps=8)
+    video_io.save_video(list(_clip(T=3, H=40, W=40)), str(root / "clips" / "b.avi"), fps=8)        # shorter than asked
+    with open(root / "metadata.jsonl", "w") as f:
+        f.write(json.dumps({"video": "clips/a.avi", "caption": "A CAT  @bob on   a mat"}) + "\n")
+        f.write(json.dumps({"video": "clips/b.avi", "caption": "dog"}) + "\n")
+    ds = build_dataset("VideoFolderDataset", data_path=[str(root)], num_frames=5, height=32, width=32, frame_stride=2)
+    assert len(ds) == 2
+    it = ds[0]
+    assert it["images"].shape == (5, 3, 32, 32) and it["raw_first_image"].shape == (3, 32, 32) and it["index"] == 0
+    assert -1.0 <= float(it["images"].min()) and float(it["images"].max()) <= 1.0
+    assert it["prompts"] == "a cat on a mat"
+    short = ds[1]
+    assert short["images"].shape == (5, 3, 32, 32) and torch.equal(short["images"][3], short["images"][4])
+    x = resize_center_crop(torch.zeros(2, 3, 48, 64), 32, 32)
+    assert x.shape == (2, 3, 32, 32)
+    enc = SyntheticWanEncoder(device="cpu", text_len=8, text_dim=16)
+    tensors, _ = enc.encode(it)
+    assert tensors[3].shape == (1, 16, 2, 4, 4)                                    # latents of a 5 x 32 x 32 clip
+    # captions from sidecar files when there is no metadata file
+    side = tmp_path / "side"
+    side.mkdir()
+    video_io.save_video(list(_clip(T=5, H=32, W=32)), str(side / "c.avi"), fps=8)
+    (side / "c.txt").write_text("a red car\n")
+    ds2 = build_dataset("VideoFolderDataset", data_path=str(side), num_frames=5, height=32, width=32)
+    assert ds2[0]["prompts"] == "a red car"
+    with pytest.raises(ValueError):
+        build_dataset("VideoFolderDataset", data_path=None)
