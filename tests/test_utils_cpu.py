@@ -110,6 +110,8 @@ def test_clean_prompt_matches_the_reference_rules():
 
 
 def test_prompt_clean_modes_and_long_prompt_chunks():
+    import types
+
     from teletron_b200.utils import prompt as P
 
     assert P.canonicalize("Hello_World!! It's <|x|> ok", "<|x|>") == "hello world its <|x|> ok"
@@ -126,8 +128,6 @@ def test_prompt_clean_modes_and_long_prompt_chunks():
             if padding == "max_length":
                 ids = (ids + [0] * max_length)[:max_length]
             return types.SimpleNamespace(input_ids=torch.tensor([ids]))
-
-    import types
 
     ids = P.tokenize_long_prompt(Tok(), "a bb ccc dddd eeeee ffffff")
     assert ids.shape == (2, 4) and ids.tolist() == [[4, 5, 6, 7], [8, 9, 0, 0]]
