@@ -13,6 +13,27 @@ import torch
 import torch.distributed as dist
 
 
+class _TeeWriter:
+    """``add_scalar`` to TensorBoard (when present) and to a Weights & Biases run."""
+
+    def __init__(self, tb, wb_run):
+        self.tb, self.wb = tb, wb_run
+
+    def add_scalar(self, tag, value, step):
+        if self.tb is not None:
+            self.tb.add_scalar(tag, value, step)
+        self.wb.log({tag: value}, step=int(step))
+
+    def flush(self):
+        if self.tb is not None:
+            self.tb.flush()
+
+    def close(self):
+        if self.tb is not None:
+            self.tb.close()
+        self.wb.finish()
+
+
 class TrainLogger:
     ADV, SKIP, NAN = "advanced iterations", "skipped iterations", "nan iterations"
 
@@ -28,16 +49,32 @@ class TrainLogger:
 
     @staticmethod
     def make_writer(args):
-        """SummaryWriter on the last rank only (teletron/utils/config.py:59-70)."""
-        if not args.tensorboard_dir or args.rank != args.world_size - 1:
+        """Scalar writer on the last rank only (teletron/utils/config.py:59-70): a TensorBoard ``SummaryWriter``
+        when ``--tensorboard-dir`` is given, mirrored to Weights & Biases when ``--wandb-project`` is given and the
+        package is installed (the reference declares that mirror but never creates it, utils/config.py:42-45)."""
+        if args.rank != args.world_size - 1:
             return None
-        try:
-            from torch.utils.tensorboard import SummaryWriter
+        tb = wb = None
+        if args.tensorboard_dir:
+            try:
+                from torch.utils.tensorboard import SummaryWriter
 
-            return SummaryWriter(log_dir=args.tensorboard_dir, max_queue=args.tensorboard_queue_size)
-        except Exception as e:  # tensorboard missing: keep training
-            print(f"WARNING: TensorBoard unavailable ({e})", flush=True)
-            return None
+                tb = SummaryWriter(log_dir=args.tensorboard_dir, max_queue=args.tensorboard_queue_size)
+            except Exception as e:  # tensorboard missing: keep training
+                print(f"WARNING: TensorBoard unavailable ({e})", flush=True)
+        if getattr(args, "wandb_project", ""):
+            try:
+                import wandb
+
+                wb = wandb.init(project=args.wandb_project, name=getattr(args, "wandb_exp_name", "") or None,
+                                dir=getattr(args, "wandb_save_dir", "") or None,
+                                config={k: v for k, v in vars(args).items()
+                                        if isinstance(v, (int, float, str, bool, type(None)))})
+            except Exception as e:
+                print(f"WARNING: Weights & Biases unavailable ({e})", flush=True)
+        if wb is None:
+            return tb
+        return _TeeWriter(tb, wb)
 
     def log(self, loss_dict, iteration, lr, loss_scale, grad_norm, skipped_iter, params_norm=None,
             tokens: int = 0, device_ms: float = 0.0, timers=None, num_zeros_in_grad=None) -> bool:

@@ -349,3 +349,31 @@ def test_num_zeros_in_grad_is_counted_on_the_reduced_gradient(tmp_path, capsys):
     a.train_iters = 1
     t.train(make_forward_step())
     assert "num zeros:" in capsys.readouterr().out
+
+
+def test_scalar_writer_mirrors_to_a_wandb_run(tmp_path, monkeypatch):
+    import sys
+    import types
+
+    from teletron_b200.train.telelog import TrainLogger
+
+    logged, inits = [], []
+
+    class Run:
+        def log(self, d, step):
+            logged.append((d, step))
+
+        def finish(self):
+            logged.append("finished")
+
+    fake = types.SimpleNamespace(init=lambda **kw: (inits.append(kw), Run())[1])
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    a = _trainer_args(tmp_path, "--wandb-project proj --wandb-exp-name run7")
+    w = TrainLogger.make_writer(a)
+    assert inits and inits[0]["project"] == "proj" and inits[0]["name"] == "run7" and "lr" in inits[0]["config"]
+    w.add_scalar("loss", 0.5, 3)
+    w.close()
+    assert logged == [({"loss": 0.5}, 3), "finished"]
+    a.rank = 0
+    a.world_size = 2
+    assert TrainLogger.make_writer(a) is None                  # only the last rank writes
