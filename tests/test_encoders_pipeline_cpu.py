@@ -213,3 +213,27 @@ def test_generation_example_runs_on_tiny_models(tmp_path):
     assert mod.main(["--tiny", "--device", "cpu", "--height", "64", "--width", "64", "--frames", "5", "--steps", "1",
                      "--image", str(out), "--out", str(out2)]) == 0
     assert read_video_frames(str(out2)).shape[0] == 5
+
+
+def test_hunyuan_pipeline_cfg_and_image_to_video():
+    torch.manual_seed(0)
+    kw = dict(hidden_size=64, num_attention_heads=4, attention_head_dim=16, rope_axes_dim=(4, 6, 6))
+    text, mask, pooled = torch.randn(1, 8, 64), torch.ones(1, 8, dtype=torch.long), torch.randn(1, 32)
+    ntext, npooled = torch.randn(1, 8, 64), torch.randn(1, 32)
+    hp = HunyuanVideoPipeline(HunyuanVideoModel(hunyuan_config("hunyuan-tiny", **kw)).eval(), None, device="cpu",
+                              torch_dtype=torch.float32)
+    common = dict(height=32, width=32, num_frames=5, num_inference_steps=2, seed=1)
+    base = hp(text, mask, pooled, **common)
+    same = hp(text, mask, pooled, negative_prompt_embeds=ntext, negative_prompt_mask=mask,
+              negative_pooled_embeds=npooled, cfg_scale=1.0, **common)
+    cfg = hp(text, mask, pooled, negative_prompt_embeds=ntext, negative_prompt_mask=mask,
+             negative_pooled_embeds=npooled, cfg_scale=4.0, **common)
+    assert torch.equal(base, same) and not torch.allclose(base, cfg) and torch.isfinite(cfg).all()
+    with pytest.raises(ValueError):
+        hp(text, mask, pooled, negative_prompt_embeds=ntext, cfg_scale=2.0, **common)
+    # image-to-video: 33 input channels, the first-frame latent changes the sample
+    i2v = HunyuanVideoPipeline(HunyuanVideoModel(hunyuan_config("hunyuan-tiny", in_channels=33, **kw)).eval(), None,
+                               device="cpu", torch_dtype=torch.float32)
+    free = i2v(text, mask, pooled, **common)
+    cond = i2v(text, mask, pooled, first_frame_latent=torch.randn(1, 16, 1, 4, 4), **common)
+    assert free.shape == cond.shape == (1, 16, 2, 4, 4) and not torch.allclose(free, cond)
