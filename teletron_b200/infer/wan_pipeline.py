@@ -6,8 +6,10 @@ set the flow-matching timesteps, draw noise ``(1, 16, (F-1)/4+1, H/8, W/8)``, en
 (and negative prompt) with umT5, encode image conditions with CLIP + VAE, run the DiT with
 classifier-free guidance ``neg + s * (pos - neg)``, take Euler steps, decode with the (optionally
 tiled) VAE and return frames.  Differences: the DiT runs on this repo's sm_100a kernels; models
-stay resident on the GPU (180 GB) unless ``enable_cpu_offload()`` is called; TeaCache, which the
-reference ships but force-disables (wan_video.py:337), is left out.
+stay resident on the GPU (180 GB) unless ``enable_cpu_offload()`` is called.  The reference ships a TeaCache
+class but force-disables it (wan_video.py:272-337); ``StepCache`` here is the same idea applied to the model output
+(skip the DiT call and reuse the last velocity while the accumulated relative change of the timestep modulation
+stays under a threshold), off unless ``tea_cache_l1_thresh`` is given.
 """
 from __future__ import annotations
 
@@ -17,6 +19,42 @@ import torch
 
 from ..models.encoders.umt5 import encode_prompt
 from ..models.flow_match import FlowMatchScheduler
+
+
+class StepCache:
+    """Decides, per sampling step, whether the DiT has to run.  The indicator is the relative L1 change of the
+    timestep modulation ``[6, C]`` between consecutive steps, optionally rescaled by a polynomial fitted for the
+    checkpoint (``coefficients``, highest power first; identity when omitted), accumulated since the last computed
+    step; the first and last steps always compute.  One cache per guidance branch keeps that branch's last output."""
+
+    def __init__(self, num_inference_steps: int, rel_l1_thresh: float, coefficients=None):
+        self.n, self.thresh = int(num_inference_steps), float(rel_l1_thresh)
+        self.coefficients = list(coefficients) if coefficients is not None else None
+        self.step, self.acc, self.prev_mod, self.last_out = 0, 0.0, None, None
+        self.skipped = 0
+
+    def _rescale(self, d: float) -> float:
+        if self.coefficients is None:
+            return d
+        y = 0.0
+        for c in self.coefficients:           # Horner
+            y = y * d + c
+        return y
+
+    def should_skip(self, modulation: torch.Tensor) -> bool:
+        first_or_last = self.step == 0 or self.step == self.n - 1
+        if first_or_last or self.prev_mod is None or self.last_out is None:
+            compute, self.acc = True, 0.0
+        else:
+            d = float((modulation - self.prev_mod).abs().mean() / self.prev_mod.abs().mean().clamp_min(1e-12))
+            self.acc += self._rescale(d)
+            compute = self.acc >= self.thresh
+            if compute:
+                self.acc = 0.0
+        self.prev_mod = modulation.detach().clone()
+        self.step = (self.step + 1) % self.n
+        self.skipped += int(not compute)
+        return not compute
 
 
 class WanVideoPipeline:
@@ -117,7 +155,8 @@ class WanVideoPipeline:
     def __call__(self, prompt, negative_prompt="", input_image=None, end_image=None, input_video=None,
                  denoising_strength=1.0, seed=None, rand_device="cpu", height=480, width=832, num_frames=81,
                  cfg_scale=5.0, num_inference_steps=50, sigma_shift=5.0, tiled=True, tile_size=(30, 52),
-                 tile_stride=(15, 26), progress_bar_cmd=lambda x: x, output_type="pil"):
+                 tile_stride=(15, 26), progress_bar_cmd=lambda x: x, output_type="pil", tea_cache_l1_thresh=None,
+                 tea_cache_coefficients=None):
         height, width = self.check_resize_height_width(height, width)
         if num_frames % 4 != 1:
             num_frames = (num_frames + 2) // 4 * 4 + 1
@@ -142,11 +181,30 @@ class WanVideoPipeline:
             extra = self.encode_image(input_image, num_frames, height, width, end_image)
         self._use("dit")
         self.dit.eval()
+        caches = None
+        if tea_cache_l1_thresh is not None:
+            n_steps = len(self.scheduler.timesteps)
+            caches = [StepCache(n_steps, tea_cache_l1_thresh, tea_cache_coefficients) for _ in range(2)]
+        self.last_step_caches = caches
+
+        def run(branch, ts, ctx):
+            if caches is not None:
+                from ..models.wan import sinusoidal_embedding_1d
+
+                emb = self.dit._small_mlp(self.dit.time_embedding,
+                                          sinusoidal_embedding_1d(self.dit.cfg.freq_dim, ts.to(self.device)))
+                if caches[branch].should_skip(self.dit._small_mlp(self.dit.time_projection, emb)):
+                    return caches[branch].last_out
+            out = self.dit(latents, ts, ctx, extra.get("clip_feature"), extra.get("y"))
+            if caches is not None:
+                caches[branch].last_out = out
+            return out
+
         for t in progress_bar_cmd(self.scheduler.timesteps):
             ts = t.reshape(1).to(self.device, torch.float32)
-            v_pos = self.dit(latents, ts, pos["context"], extra.get("clip_feature"), extra.get("y"))
+            v_pos = run(0, ts, pos["context"])
             if neg is not None:
-                v_neg = self.dit(latents, ts, neg["context"], extra.get("clip_feature"), extra.get("y"))
+                v_neg = run(1, ts, neg["context"])
                 v = v_neg + cfg_scale * (v_pos - v_neg)
             else:
                 v = v_pos

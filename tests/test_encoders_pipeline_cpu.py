@@ -237,3 +237,33 @@ def test_hunyuan_pipeline_cfg_and_image_to_video():
     free = i2v(text, mask, pooled, **common)
     cond = i2v(text, mask, pooled, first_frame_latent=torch.randn(1, 16, 1, 4, 4), **common)
     assert free.shape == cond.shape == (1, 16, 2, 4, 4) and not torch.allclose(free, cond)
+
+
+def test_step_cache_skips_dit_calls_only_above_zero_threshold():
+    from teletron_b200.infer.wan_pipeline import StepCache
+
+    torch.manual_seed(0)
+    dit = WanModel(wan_config("wan-tiny", text_dim=64)).eval()
+    t5 = UMT5Encoder(vocab=512, dim=64, dim_attn=64, dim_ffn=128, num_heads=4, num_layers=1)
+    pipe = WanVideoPipeline.from_modules(dit, WanVideoVAE(dim=16), t5, None, HashTokenizer(512, 512), device="cpu",
+                                         torch_dtype=torch.float32)
+    calls = []
+    dit.register_forward_hook(lambda m, a, o: calls.append(1))
+    kw = dict(negative_prompt="blurry", height=64, width=64, num_frames=5, num_inference_steps=6, seed=0,
+              tiled=False, output_type="latent")
+    plain = pipe("a cat", **kw)
+    n_plain = len(calls)
+    assert n_plain == 12                                            # 6 steps x 2 guidance branches
+    calls.clear()
+    exact = pipe("a cat", tea_cache_l1_thresh=0.0, **kw)            # threshold 0: every step computes
+    assert len(calls) == 12 and torch.equal(exact, plain)
+    calls.clear()
+    fast = pipe("a cat", tea_cache_l1_thresh=1e9, **kw)             # huge threshold: only first and last steps compute
+    assert len(calls) == 4 and [c.skipped for c in pipe.last_step_caches] == [4, 4]
+    assert fast.shape == plain.shape and torch.isfinite(fast).all() and not torch.equal(fast, plain)
+    c = StepCache(4, 0.5, coefficients=[2.0, 0.0])                  # rescale d -> 2 d
+    m = torch.ones(1, 6, 8)
+    assert c.should_skip(m) is False
+    c.last_out = torch.zeros(1)
+    assert c.should_skip(m * 1.1) is True                           # 2 * 0.1 = 0.2 < 0.5
+    assert c.should_skip(m * 1.1 * 1.2) is False                    # + 2 * 0.2 = 0.6 >= 0.5
