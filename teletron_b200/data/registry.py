@@ -6,5 +6,6 @@ from ..models.registry import Registry
 DATASETS = Registry("dataset")
 
 
-def build_dataset(name: str, **kwargs):
-    return DATASETS.get(name)(**kwargs)
+def build_dataset(name_or_spec, **kwargs):
+    """``build_dataset("FakeDataset", num_frames=...)`` or ``build_dataset({"type": "FakeDataset", ...})``."""
+    return DATASETS.build(name_or_spec, **kwargs)

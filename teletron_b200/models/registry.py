@@ -11,27 +11,62 @@ from typing import Callable, Dict
 
 
 class Registry:
+    """Name -> class table.  ``@REG.register("name")``, ``@REG.register`` (class name) and
+    ``REG.register_module(cls, name)`` add entries; ``REG.build("name", config, **kw)`` or
+    ``REG.build({"type": "name", ...})`` instantiate one (the two spellings of the reference's model and dataset
+    registries, teletron/models/registry.py:70-190, teletron/datasets/registry.py:24-63)."""
+
     def __init__(self, kind: str):
         self.kind = kind
         self._items: Dict[str, Callable] = {}
 
-    def register(self, name: str = None):
-        def deco(obj):
-            key = name or obj.__name__
-            if key in self._items and self._items[key] is not obj:
-                raise KeyError(f"{self.kind} {key!r} is already registered")
-            self._items[key] = obj
-            return obj
+    def register_module(self, obj, name: str = None):
+        key = name or obj.__name__
+        if key in self._items and self._items[key] is not obj:
+            raise KeyError(f"{self.kind} {key!r} is already registered")
+        self._items[key] = obj
+        return obj
 
-        return deco
+    def register(self, name=None):
+        if isinstance(name, str) or name is None:
+            return lambda obj: self.register_module(obj, name)
+        return self.register_module(name)                     # used as a bare decorator
+
+    def unregister(self, name: str) -> None:
+        if name not in self._items:
+            raise KeyError(f"unknown {self.kind} {name!r}")
+        del self._items[name]
 
     def get(self, name: str):
         if name not in self._items:
             raise KeyError(f"unknown {self.kind} {name!r}; known: {sorted(self._items)}")
         return self._items[name]
 
+    get_module = get
+
+    def build(self, spec, *args, **kwargs):
+        """``spec``: a registered name, or a mapping with a ``type`` key whose other items become keyword arguments
+        (explicit keyword arguments win)."""
+        if isinstance(spec, dict):
+            params = dict(spec)
+            if "type" not in params:
+                raise KeyError(f"a {self.kind} spec needs a 'type' entry, got keys {sorted(params)}")
+            name = params.pop("type")
+            params.update(kwargs)
+            return self.get(name)(*args, **params)
+        return self.get(spec)(*args, **kwargs)
+
+    def list_modules(self) -> Dict[str, Callable]:
+        return dict(self._items)
+
     def __contains__(self, name):
         return name in self._items
+
+    def __len__(self):
+        return len(self._items)
+
+    def __repr__(self):
+        return f"Registry({self.kind}: {', '.join(sorted(self._items))})"
 
     def names(self):
         return sorted(self._items)

@@ -244,3 +244,36 @@ def test_video_folder_dataset_feeds_the_encoders(tmp_path):
     assert ds2[0]["prompts"] == "a red car"
     with pytest.raises(ValueError):
         build_dataset("VideoFolderDataset", data_path=None)
+
+
+def test_registry_surface():
+    from teletron_b200.data import build_dataset
+    from teletron_b200.models.registry import MODELS, Registry
+
+    reg = Registry("thing")
+
+    @reg.register("named")
+    class A:
+        def __init__(self, x=1, y=2):
+            self.x, self.y = x, y
+
+    @reg.register
+    class B(A):
+        pass
+
+    reg.register_module(A, "alias")
+    assert len(reg) == 3 and "B" in reg and reg.get_module("alias") is A and set(reg.list_modules()) == {"named", "B", "alias"}
+    assert reg.build("named", 5).x == 5
+    obj = reg.build({"type": "B", "x": 7, "y": 8}, y=9)
+    assert isinstance(obj, B) and (obj.x, obj.y) == (7, 9)
+    with pytest.raises(KeyError):
+        reg.register_module(B, "named")                       # a different class under a taken name
+    with pytest.raises(KeyError):
+        reg.build({"x": 1})
+    reg.unregister("alias")
+    assert "alias" not in reg and "thing" in repr(reg)
+    with pytest.raises(KeyError):
+        reg.unregister("alias")
+    assert "ParallelWanModel" in MODELS and "ParallelHunyuanVideoModel" in MODELS
+    ds = build_dataset({"type": "FakeDataset", "num_frames": 5, "height": 16, "width": 16, "length": 3})
+    assert len(ds) == 3 and ds[0]["images"].shape == (5, 3, 16, 16)
