@@ -277,3 +277,38 @@ def test_registry_surface():
     assert "ParallelWanModel" in MODELS and "ParallelHunyuanVideoModel" in MODELS
     ds = build_dataset({"type": "FakeDataset", "num_frames": 5, "height": 16, "width": 16, "length": 3})
     assert len(ds) == 3 and ds[0]["images"].shape == (5, 3, 16, 16)
+
+
+def test_config_dictionary(tmp_path):
+    from teletron_b200.utils.config import Config, load_config
+
+    c = Config(model=dict(dim=128, patch=(1, 2, 2), blocks=[dict(kind="dual"), dict(kind="single")]), lr=1e-4)
+    assert c.model.dim == 128 and c.model.blocks[1].kind == "single" and c.model.patch == (1, 2, 2)
+    c.update(model=dict(dim=256), seed=3)
+    assert c.model.dim == 256 and c.model.patch == (1, 2, 2) and c.seed == 3        # nested merge keeps siblings
+    c.update(model={"__force__": True, "dim": 64})
+    assert c.model.to_dict() == {"dim": 64}                                             # forced replacement
+    assert c.setdefault("lr", 5.0) == 1e-4 and c.setdefault("wd", 0.1) == 0.1 and c.wd == 0.1
+    d = c.copy()
+    d.model.dim = 1
+    assert c.model.dim == 64
+    with pytest.raises(AttributeError):
+        c.missing
+    del c.wd
+    assert "wd" not in c and "Config:" in str(c)
+    c.sizes = (3, (4, 5))
+    for name in ("cfg.json", "cfg.yaml", "cfg.pkl"):
+        path = tmp_path / "sub" / name
+        c.save(str(path))
+        back = Config.load(str(path))
+        assert back.to_dict() == c.to_dict() and back.sizes == (3, (4, 5)), name
+    (tmp_path / "folder").mkdir()
+    c.save(str(tmp_path / "folder" / "config.json"))
+    assert load_config(str(tmp_path / "folder")).lr == 1e-4 and load_config({"a": {"b": 1}}).a.b == 1
+    assert load_config(c) is c
+    extra = tmp_path / "extra.yaml"
+    extra.write_text("model:\n  dim: 512\nnew: yes\n")
+    c.merge_from_file(str(extra))
+    assert c.model.dim == 512 and c.new is True
+    with pytest.raises(ValueError):
+        Config.load(str(tmp_path / "conf.py"))
