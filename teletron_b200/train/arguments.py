@@ -231,7 +231,9 @@ def validate_args(args):
     args.consumed_valid_samples = 0
     args.iteration = 0
     if args.train_iters is None and args.train_samples is not None:
-        args.train_iters = args.train_samples // args.global_batch_size
+        from .helpers import update_train_iters
+
+        update_train_iters(args)      # follows the batch-size ramp when there is one
     return args
 
 

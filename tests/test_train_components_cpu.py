@@ -377,3 +377,40 @@ def test_scalar_writer_mirrors_to_a_wandb_run(tmp_path, monkeypatch):
     a.rank = 0
     a.world_size = 2
     assert TrainLogger.make_writer(a) is None                  # only the last rank writes
+
+
+def test_training_helpers(capsys):
+    from teletron_b200 import train as T
+    from teletron_b200.models import wan_config
+
+    lin = torch.nn.Linear(3, 2)
+    with torch.no_grad():
+        lin.weight.fill_(2.0)
+        lin.bias.fill_(1.0)
+    wrapped = Namespace(module=Namespace(module=lin))
+    assert T.get_attr_wrapped_model(wrapped, "in_features") == 3 and T.get_attr_wrapped_model(wrapped, "nope") is None
+    with pytest.raises(AttributeError):
+        T.get_attr_wrapped_model(wrapped, "nope", allow_none=False)
+    assert abs(T.calc_params_l2_norm(lin) - (6 * 4 + 2) ** 0.5) < 1e-9
+    lin(torch.ones(1, 3)).sum().backward()
+    assert abs(T.get_grad_norm(lin) - (6 + 2) ** 0.5) < 1e-9
+    a = Namespace(train_samples=None, train_iters=10, global_batch_size=4, eval_interval=5, eval_iters=2)
+    assert T.get_train_valid_test_num_samples(a) == (40, 3 * 2 * 4, 2 * 4)
+    # sample-based training with a ramp 2 -> 6 in steps of 2 over 12 samples (6 per level): batches 2,2,2,4,4,6 reach
+    # 20 > 12, then (50 - 20) // 6 = 5 full batches
+    r = Namespace(train_iters=None, train_samples=50, global_batch_size=6, micro_batch_size=1, data_parallel_size=2,
+                  rampup_batch_size=[2, 2, 12])
+    assert T.update_train_iters(r) == 6 + 5 and r.train_iters == 11
+    c = Namespace(train_iters=None, train_samples=50, global_batch_size=6, rampup_batch_size=None)
+    assert T.update_train_iters(c) == 8
+    assert T.is_last_rank()
+    T.print_rank_0("zero")
+    T.print_rank_last("last")
+    T.print_datetime("after setup")
+    out = capsys.readouterr().out
+    assert "zero" in out and "last" in out and "[after setup] datetime:" in out
+    gb = T.report_theoretical_memory(Namespace(data_parallel_size=4, context_parallel_size=2,
+                                               use_distributed_optimizer=True), int(1e9))
+    assert abs(gb - 1e9 * (2 + 4 + 12 / 8) / 2 ** 30) < 1e-6
+    cfg = wan_config("wan2.1-1.3b-t2v")
+    assert T.num_floating_point_operations(cfg, 32760, 8) == 8 * T.num_floating_point_operations(cfg, 32760, 1)
