@@ -114,6 +114,8 @@ def run_ours(a):
 
     rank, world, local = dist_env()
     assert world == a.gpus, f"WORLD_SIZE {world} != --gpus {a.gpus} (launch N > 1 under torchrun)"
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py measures on a GPU: no CUDA device on this machine")
     cp = a.cp
     dp = world // cp
     frames, height, width, gbs = a.frames, a.height, a.width, a.global_batch
@@ -262,6 +264,8 @@ def run_reference(a):
 
     import torch
 
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device on this machine")
     spec = importlib.util.spec_from_file_location("ref_wan_model", ref_file)
     ref = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(ref)
