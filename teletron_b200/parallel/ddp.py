@@ -21,6 +21,7 @@ is one object here:
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from typing import Dict, Iterable, List, Optional, Tuple
 
@@ -324,3 +325,79 @@ class DistributedOptimizer:
             for key, lst in (("master", self.master), ("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
                 lst[i].copy_(full[key][pos + (s - rs): pos + (e - rs)])
             pos += re - rs
+
+
+class DistributedDataParallel(torch.nn.Module):
+    """The reference's DDP wrapper surface (teletron/core/distributed/distributed_data_parallel.py:40-298) over
+    ``ParamBuffer``: ``forward``, ``no_sync()``, ``start_grad_sync()`` / ``finish_grad_sync()``,
+    ``zero_grad_buffer()``, ``broadcast_params()``, ``scale_gradients()`` and the state-dict passthroughs, for code
+    written against those names.  The trainer itself drives ``ParamBuffer`` + ``DistributedOptimizer`` directly.
+
+    Gradients accumulate in the flat fp32 buffer over micro-batches; ``finish_grad_sync`` sums them over
+    ``group`` and scales by ``1 / data_parallel_world_size``-style ``grad_scale`` (default ``1 / group size``).
+    Inside ``no_sync()`` the sync calls do nothing, as in the reference."""
+
+    def __init__(self, module: torch.nn.Module, group=None, grad_dtype=torch.float32, grad_scale: float = None,
+                 broadcast: bool = True):
+        super().__init__()
+        self.module = module
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.buffer = ParamBuffer(module, shard_world=1, grad_dtype=grad_dtype)
+        self.grad_scale = (1.0 / self.world) if grad_scale is None else float(grad_scale)
+        self._sync_enabled = True
+        self._pending = None
+        if broadcast and self.world > 1:
+            self.broadcast_params()
+
+    def forward(self, *inputs, **kwargs):
+        return self.module(*inputs, **kwargs)
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        prev, self._sync_enabled = self._sync_enabled, False
+        try:
+            yield
+        finally:
+            self._sync_enabled = prev
+
+    def start_grad_sync(self, *unused):
+        """Fold autograd gradients into the flat buffer, scale, and launch the all-reduce asynchronously."""
+        if not self._sync_enabled:
+            return
+        self.buffer.collect_grads()
+        if self.grad_scale != 1.0:
+            self.buffer.grads.mul_(self.grad_scale)
+        if self.world > 1:
+            self._pending = dist.all_reduce(self.buffer.grads, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+
+    def finish_grad_sync(self):
+        if not self._sync_enabled:
+            return
+        if self._pending is None:
+            self.start_grad_sync()
+        if self._pending is not None:
+            self._pending.wait()
+            self._pending = None
+
+    def scale_gradients(self, factor: float):
+        self.buffer.grads.mul_(factor)
+
+    def zero_grad_buffer(self):
+        self.buffer.zero_grads()
+
+    def broadcast_params(self):
+        """Every rank takes the parameters of the first rank of the group."""
+        if self.world > 1:
+            src = dist.get_global_rank(self.group, 0) if self.group is not None else 0
+            dist.broadcast(self.buffer.params, src=src, group=self.group)
+
+    def state_dict(self, prefix="", keep_vars=False):
+        return self.module.state_dict(prefix=prefix, keep_vars=keep_vars)
+
+    def state_dict_for_save_checkpoint(self, prefix="", keep_vars=False):
+        fn = getattr(self.module, "state_dict_for_save_checkpoint", None)
+        return fn(prefix=prefix, keep_vars=keep_vars) if fn else self.state_dict(prefix, keep_vars)
+
+    def load_state_dict(self, state_dict, strict=True):
+        return self.module.load_state_dict(state_dict, strict=strict)

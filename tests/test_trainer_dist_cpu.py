@@ -108,3 +108,45 @@ def test_a_rank_leaving_is_detected_and_training_resumes_from_the_checkpoint(tmp
     assert resumed[0][:2] == (1, 3) and resumed[1][:2] == (1, 3)
     assert torch.equal(resumed[0][2], resumed[1][2])
     assert torch.allclose(resumed[0][2], full[0][2], atol=1e-6)    # same end state as the uninterrupted run
+
+
+def _ddp_wrapper_worker(rank, world):
+    from teletron_b200.parallel.ddp import DistributedDataParallel
+
+    torch.manual_seed(100 + rank)                          # different initial weights: broadcast must equalise them
+    net = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 2))
+    ddp = DistributedDataParallel(net)
+    start = ddp.buffer.params.clone()
+    g = torch.Generator().manual_seed(7)
+    data = torch.randn(world, 2, 4, 6, generator=g)        # [rank, micro-batch, rows, features]
+    ddp.zero_grad_buffer()
+    with ddp.no_sync():
+        ddp(data[rank, 0]).square().mean().backward()
+        ddp.start_grad_sync()                              # ignored inside no_sync
+        ddp.finish_grad_sync()
+        assert all(p.grad is not None for p in net.parameters())
+    ddp(data[rank, 1]).square().mean().backward()
+    ddp.start_grad_sync()
+    ddp.finish_grad_sync()
+    assert all(p.grad is None for p in net.parameters())   # folded into the flat buffer
+    sd = ddp.state_dict_for_save_checkpoint()
+    assert set(sd) == set(net.state_dict())
+    return start, ddp.buffer.grads.clone(), data
+
+
+def test_ddp_wrapper_accumulates_and_averages_like_one_process():
+    outs = run_distributed(_ddp_wrapper_worker, 2)
+    assert torch.equal(outs[0][0], outs[1][0])              # broadcast_params at construction
+    assert torch.equal(outs[0][1], outs[1][1])              # same reduced gradient everywhere
+    # one process: same weights, sum over micro-batches, mean over the two ranks' data
+    torch.manual_seed(100)
+    net = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 2))
+    data = outs[0][2]
+    for r in range(2):
+        for mb in range(2):
+            (net(data[r, mb]).square().mean() / 2).backward()
+    from teletron_b200.parallel.ddp import ParamBuffer
+
+    ref = ParamBuffer(net)
+    ref.collect_grads()
+    assert torch.allclose(outs[0][1], ref.grads, atol=1e-6)
