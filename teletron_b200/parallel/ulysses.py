@@ -139,3 +139,23 @@ class UlyssesContext:
         oh = ops.attention(qh, kh, vh, scale, kv_lens)
         o = _HeadToSeq.apply(oh.contiguous(), self.group, P)
         return o[:, :, :H] if Hp != H else o
+
+    # ---- the reference mixin's spellings (teletron/core/context_parallel/context_parallel_mixin.py:39-125) -------
+    def split_input(self, x, dim: int = 1):
+        """Pad ``x`` along ``dim`` to a multiple of the group size and keep this rank's chunk (backward gathers)."""
+        if dim == 1:
+            return self.split_tokens(x)
+        return self.split_tokens(x.movedim(dim, 1)).movedim(1, dim)
+
+    def gather_output(self, output, dim: int = 1):
+        """Inverse of ``split_input``: all ranks' chunks concatenated along ``dim``, padding removed."""
+        if dim == 1:
+            return self.gather_tokens(output)
+        return self.gather_tokens(output.movedim(dim, 1)).movedim(1, dim)
+
+    def forward_attn(self, q, k, v, num_heads: int):
+        """q, k, v: local ``[B, S_l, H*D]``; returns ``[B, S_l, H*D]`` of attention over the whole sequence."""
+        B, Sl, C = q.shape
+        D = C // num_heads
+        o = self.attention(q.view(B, Sl, num_heads, D), k.view(B, Sl, num_heads, D), v.view(B, Sl, num_heads, D))
+        return o.reshape(B, Sl, C)

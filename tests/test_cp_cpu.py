@@ -113,3 +113,29 @@ def _heads_not_divisible_worker(rank, world):
 
 def test_ulysses_pads_heads():
     assert all(run_distributed(_heads_not_divisible_worker, 2))
+
+
+def _mixin_names_worker(rank, world):
+    import torch
+
+    from teletron_b200.parallel import state as mpu
+    from teletron_b200.parallel.ulysses import UlyssesContext
+
+    mpu.initialize_model_parallel(context_parallel_size=world)
+    cp = UlyssesContext(mpu.get_context_parallel_group(), world, rank)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2, 3, 7, 4, generator=g)                 # sequence on dim 2, length 7: padded to 8
+    part = cp.split_input(x, dim=2)
+    assert part.shape == (2, 3, 4, 4)
+    back = cp.gather_output(part, dim=2)
+    assert torch.equal(back, x)
+    q, k, v = (torch.randn(1, 7, 2 * 8, generator=g) for _ in range(3))
+    ql, kl, vl = (cp.split_input(t, dim=1) for t in (q, k, v))
+    o = cp.gather_output(cp.forward_attn(ql, kl, vl, num_heads=2), dim=1)
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        *(t.view(1, 7, 2, 8).transpose(1, 2) for t in (q, k, v))).transpose(1, 2).reshape(1, 7, 16)
+    return float((o - ref).abs().max())
+
+
+def test_reference_mixin_method_names():
+    assert max(run_distributed(_mixin_names_worker, 2)) < 1e-5
