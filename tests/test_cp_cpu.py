@@ -139,3 +139,41 @@ def _mixin_names_worker(rank, world):
 
 def test_reference_mixin_method_names():
     assert max(run_distributed(_mixin_names_worker, 2)) < 1e-5
+
+
+def _mappings_worker(rank, world):
+    import torch
+    import torch.distributed as dist
+
+    from teletron_b200.parallel.mappings import (even_sizes, gather_forward_split_backward,
+                                                 split_forward_gather_backward)
+
+    assert even_sizes(7, 3) == [3, 2, 2]
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(2, 7, 3, generator=g, requires_grad=True)
+    # default: 7 over 2 ranks -> 4 + 3; explicit: 2 + 5
+    for sizes in (None, [2, 5]):
+        part = split_forward_gather_backward(x, None, dim=1, split_sizes=sizes, grad_scale="down")
+        want = sizes or [4, 3]
+        assert part.shape[1] == want[rank]
+        full = gather_forward_split_backward(part, None, dim=1, gather_sizes=want, grad_scale="up")
+        assert torch.equal(full, x)
+        w = torch.arange(7.0).view(1, 7, 1)
+        x.grad = None
+        (full * w).sum().backward()
+        # gather backward: split, x world ("up"); split backward: gather, / world ("down") -> the plain gradient
+        assert torch.allclose(x.grad, w.expand_as(x))
+    y = torch.full((3,), float(rank + 1), requires_grad=True)
+    z = gather_forward_split_backward(y, None, dim=0)                   # equal sizes, no scaling
+    assert z.tolist() == [1.0] * 3 + [2.0] * 3
+    z.sum().backward()
+    assert y.grad.tolist() == [1.0] * 3
+    try:
+        split_forward_gather_backward(x, None, dim=1, split_sizes=[1, 1])
+    except ValueError:
+        return "ok"
+    return "no error"
+
+
+def test_split_gather_mappings_with_uneven_sizes_and_grad_scale():
+    assert run_distributed(_mappings_worker, 2) == ["ok", "ok"]
