@@ -72,6 +72,12 @@ class WanImageEncoder(nn.Module):
         self.register_buffer("mean", torch.tensor(CLIP_MEAN).view(1, 3, 1, 1), persistent=False)
         self.register_buffer("std", torch.tensor(CLIP_STD).view(1, 3, 1, 1), persistent=False)
 
+    def reset_constants(self, device=None):
+        """(Re)create the pixel normalisation constants (not part of any checkpoint)."""
+        dev = device if device is not None else self.model.visual.patch_embedding.weight.device
+        self.mean = torch.tensor(CLIP_MEAN, device=dev).view(1, 3, 1, 1)
+        self.std = torch.tensor(CLIP_STD, device=dev).view(1, 3, 1, 1)
+
     @torch.no_grad()
     def encode_image(self, frames):
         """frames: [B, 3, H, W] in [-1, 1] -> CLIP tokens [B, 257, dim]."""

@@ -95,8 +95,16 @@ class WanVideoEncoder(BaseEncoder):
 
     def _load(self, module, filename):
         if self.model_path and os.path.exists(os.path.join(self.model_path, filename)):
-            sd = torch.load(os.path.join(self.model_path, filename), map_location="cpu", weights_only=True)
-            module.load_state_dict(sd.get("model_state", sd), strict=False)
+            from ..model_manager import align_checkpoint_keys
+
+            path = os.path.join(self.model_path, filename)
+            sd = torch.load(path, map_location="cpu", weights_only=True)
+            sd = align_checkpoint_keys(module, sd.get("model_state", sd))
+            missing, _ = module.load_state_dict(sd, strict=False)
+            missing = [k for k in missing if k.split(".")[-1] not in ("mean", "std", "inv_std")]
+            if missing:        # a half-loaded encoder would train the DiT on noise features without any other sign
+                raise RuntimeError(f"{path}: {len(missing)} tensors of {type(module).__name__} are not in the file, "
+                                   f"e.g. {missing[:3]}")
             return True
         return False
 
@@ -113,10 +121,8 @@ class WanVideoEncoder(BaseEncoder):
             for m in (self.t5, self.clip, self.vae):
                 for p in m.parameters():
                     torch.nn.init.normal_(p, std=0.02)
-            self.vae.mean = self.vae.mean.new_tensor(__import__("teletron_b200.models.encoders.wan_vae", fromlist=["x"]).LATENT_MEAN)
-            self.vae.inv_std = 1.0 / self.vae.mean.new_tensor(__import__("teletron_b200.models.encoders.wan_vae", fromlist=["x"]).LATENT_STD)
-            self.clip.mean = self.clip.mean.new_tensor((0.48145466, 0.4578275, 0.40821073)).view(1, 3, 1, 1)
-            self.clip.std = self.clip.std.new_tensor((0.26862954, 0.26130258, 0.27577711)).view(1, 3, 1, 1)
+            self.vae.reset_constants(dev)        # buffers built on the meta device hold no values
+            self.clip.reset_constants(dev)
         self._load(self.t5, T5_FILE)
         self._load(self.clip, CLIP_FILE)
         self._load(self.vae, VAE_FILE)

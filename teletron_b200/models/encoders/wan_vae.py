@@ -209,6 +209,13 @@ class WanVideoVAE(nn.Module):
         self.model = VideoVAE_(dim=dim, z_dim=z_dim).eval().requires_grad_(False)
         self.z_dim = z_dim
 
+    def reset_constants(self, device=None):
+        """(Re)create the latent normalisation constants, e.g. after building the module on the meta device:
+        they are not part of any checkpoint."""
+        dev = device if device is not None else next(self.model.parameters()).device
+        self.mean = torch.tensor(LATENT_MEAN[:self.z_dim], device=dev)
+        self.inv_std = 1.0 / torch.tensor(LATENT_STD[:self.z_dim], device=dev)
+
     def _scale(self, ref):
         return self.mean.to(ref), self.inv_std.to(ref)
 

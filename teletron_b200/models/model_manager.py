@@ -43,6 +43,22 @@ def load_state_dict(path: Union[str, List[str]], device="cpu", torch_dtype=None)
     return sd
 
 
+_CONSTANT_BUFFERS = ("mean", "std", "inv_std")   # normalisation constants set by the module itself, never in a file
+
+
+def align_checkpoint_keys(module: torch.nn.Module, sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """Checkpoint files of the encoders come without the wrapper prefix the module classes use (the CLIP and VAE
+    files store ``visual.*`` / ``encoder.*`` while the modules hold them under ``model.``; the CLIP file also carries
+    the unused text tower and ``log_scale``).  Returns the entries of ``sd`` renamed to the spelling (as is,
+    ``model.`` added, ``model.`` removed) that matches most of ``module``'s keys, dropping entries the module does not
+    have (the reference does this per model in its ``from_civitai`` converters, wan_video_image_encoder.py:889-904)."""
+    want = set(module.state_dict().keys())
+    spellings = (sd, {"model." + k: v for k, v in sd.items()},
+                 {k[len("model."):]: v for k, v in sd.items() if k.startswith("model.")})
+    best = max(spellings, key=lambda d: len(want.intersection(d)))
+    return {k: v for k, v in best.items() if k in want}
+
+
 @contextmanager
 def init_weights_on_device(device=torch.device("meta")):
     """Construct modules without allocating / initialising real storage."""
@@ -130,10 +146,17 @@ class ModelManager:
         if kind is None:
             raise ValueError(f"cannot tell what model {path} holds ({len(sd)} tensors)")
         model = self._instantiate(kind, sd)
-        missing, unexpected = model.load_state_dict(sd if kind != "wan_video_dit" else self._wan_sd, assign=True,
-                                                    strict=False)
+        use = self._wan_sd if kind == "wan_video_dit" else align_checkpoint_keys(model, sd)
+        missing, unexpected = model.load_state_dict(use, assign=True, strict=False)
+        missing = [k for k in missing if k.split(".")[-1] not in _CONSTANT_BUFFERS]
         if missing:
             raise RuntimeError(f"{path}: {len(missing)} parameters missing, e.g. {missing[:3]}")
+        if hasattr(model, "reset_constants"):        # constants built on the meta device hold no values
+            model.reset_constants("cpu")
+        stale = [n for n, b in model.named_buffers() if b.is_meta]
+        if stale:
+            raise RuntimeError(f"{path}: buffers {stale[:3]} of {type(model).__name__} were built on the meta device "
+                               "and are set by neither the file nor reset_constants()")
         self.models[kind] = model.to(device=device).eval()
         self.paths[kind] = path
         return self.models[kind]

@@ -267,3 +267,51 @@ def test_step_cache_skips_dit_calls_only_above_zero_threshold():
     c.last_out = torch.zeros(1)
     assert c.should_skip(m * 1.1) is True                           # 2 * 0.1 = 0.2 < 0.5
     assert c.should_skip(m * 1.1 * 1.2) is False                    # + 2 * 0.2 = 0.6 >= 0.5
+
+
+def test_encoder_checkpoints_load_from_their_published_key_spelling(tmp_path):
+    """The CLIP and VAE files store ``visual.*`` / ``encoder.*`` (plus an unused text tower); the modules keep them
+    under ``model.``.  Both loaders must rename, and must refuse a file that leaves tensors unset."""
+    from teletron_b200.models.model_manager import ModelManager, align_checkpoint_keys
+
+    torch.manual_seed(0)
+    clip = WanImageEncoder(dim=64, layers=2, heads=4)
+    published = {k[len("model."):]: v.clone() for k, v in clip.state_dict().items()}
+    published["textual.embedding.weight"] = torch.zeros(3, 3)
+    published["log_scale"] = torch.zeros(())
+    fresh = WanImageEncoder(dim=64, layers=2, heads=4)
+    aligned = align_checkpoint_keys(fresh, published)
+    assert set(aligned) == set(fresh.state_dict()) and not any(k.startswith("model.textual") for k in aligned)
+    fresh.load_state_dict(aligned)
+    assert all(torch.equal(a, b) for a, b in zip(fresh.state_dict().values(), clip.state_dict().values()))
+    # the encoder bundle's loader: same renaming, and a loud error for an incomplete file
+    enc = get_encoder("wan_encoder", device="cpu", args=Namespace(task_type="i2v", consumer_models_num=1,
+                                                                 encoder_model_path=str(tmp_path),
+                                                                 encoder_tokenizer_path=None), small=True)
+    vae = WanVideoVAE(dim=16)
+    torch.save({k[len("model."):]: v for k, v in vae.state_dict().items() if k.startswith("model.")},
+               tmp_path / "Wan2.1_VAE.pth")
+    target = WanVideoVAE(dim=16)
+    assert enc._load(target, "Wan2.1_VAE.pth")
+    assert torch.equal(target.state_dict()["model.encoder.conv1.weight"], vae.state_dict()["model.encoder.conv1.weight"])
+    broken = {k: v for k, v in list(published.items())[:5]}
+    torch.save(broken, tmp_path / "models_clip_open-clip-xlm-roberta-large-vit-huge-14.pth")
+    with pytest.raises(RuntimeError, match="are not in the file"):
+        enc._load(WanImageEncoder(dim=64, layers=2, heads=4), "models_clip_open-clip-xlm-roberta-large-vit-huge-14.pth")
+    assert not enc._load(target, "absent.pth")
+
+
+def test_model_manager_loads_a_published_style_vae_file(tmp_path):
+    """Full-size VAE built on the meta device, weights from a file with the published key spelling, constants
+    re-created: the loaded model encodes exactly like the source."""
+    from teletron_b200.models.model_manager import ModelManager
+
+    torch.manual_seed(0)
+    vae = WanVideoVAE()
+    path = tmp_path / "Wan2.1_VAE.pth"
+    torch.save({k[len("model."):]: v for k, v in vae.state_dict().items()}, path)
+    mm = ModelManager(torch_dtype=torch.float32, device="cpu")
+    loaded = mm.load_model(str(path))
+    assert mm.fetch_model("wan_video_vae") is loaded and not any(b.is_meta for b in loaded.buffers())
+    x = torch.randn(3, 5, 32, 32)
+    assert torch.equal(loaded.encode([x], device="cpu"), vae.encode([x], device="cpu"))
