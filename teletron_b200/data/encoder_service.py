@@ -138,7 +138,8 @@ def producer_process(args, encoder=None, dataset=None):
 
             h, w = args.video_resolution
             dataset = build_dataset(args.dataset_type, num_frames=args.num_frames, height=h, width=w, seed=args.seed,
-                                    data_path=getattr(args, "data_path", None))
+                                    data_path=getattr(args, "data_path", None),
+                                    min_length=consumed_train + total * max(g["dp_size"] for g in groups))
         from .samplers import build_data_loader
 
         iters = []

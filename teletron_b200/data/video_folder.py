@@ -67,7 +67,9 @@ def resize_center_crop(frames: torch.Tensor, height: int, width: int) -> torch.T
 @DATASETS.register("VideoFolderDataset")
 class VideoFolderDataset(Dataset):
     def __init__(self, data_path, num_frames=81, height=480, width=832, frame_stride=1, clean_captions=True,
-                 backend=None, seed=0, **_):
+                 backend=None, seed=0, min_length=0, **_):
+        """``min_length``: the sample count the run will ask for; the clip list is repeated (whole epochs) until it
+        covers it, because the resumable samplers walk ``range(len(dataset))`` once."""
         roots: Sequence[str] = [data_path] if isinstance(data_path, str) else list(data_path or [])
         if not roots:
             raise ValueError("VideoFolderDataset needs --data-path <folder> [<folder> ...]")
@@ -80,9 +82,11 @@ class VideoFolderDataset(Dataset):
             raise ValueError(f"no videos found under {roots}")
         self.num_frames, self.height, self.width = num_frames, height, width
         self.stride, self.clean, self.backend = max(int(frame_stride), 1), clean_captions, backend
+        self.min_length = min_length
 
     def __len__(self):
-        return len(self.items)
+        n = len(self.items)
+        return n * max(1, -(-int(self.min_length) // n))
 
     def __getitem__(self, idx):
         path, caption = self.items[int(idx) % len(self.items)]

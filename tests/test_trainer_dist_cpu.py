@@ -150,3 +150,42 @@ def test_ddp_wrapper_accumulates_and_averages_like_one_process():
     ref = ParamBuffer(net)
     ref.collect_grads()
     assert torch.allclose(outs[0][1], ref.grads, atol=1e-6)
+
+
+def _real_clips_worker(rank, world, data_root):
+    from teletron_b200.train import Trainer, make_forward_step
+
+    a = _args(world, "--distributed-vae --distributed-vae-world-size 1 --encoder-name synthetic_wan_encoder "
+                     f"--dataset-type VideoFolderDataset --data-path {data_root}")
+    a.train_iters = 3                                       # three samples from two clips: the list repeats
+    try:
+        t = Trainer(a)
+    except SystemExit:
+        return "encoder-rank-done"
+    before = t.buffer.params.float().clone()
+    t.pretrain(make_forward_step())
+    return a.iteration, float((t.buffer.params.float() - before).abs().sum())
+
+
+def test_training_on_a_folder_of_clips_through_an_encoder_rank(tmp_path):
+    import json
+
+    import numpy as np
+    import pytest
+
+    from teletron_b200.utils import video_io
+
+    try:
+        import cv2  # noqa: F401
+    except ImportError:
+        pytest.skip("no video writer backend installed")
+    root = tmp_path / "clips"
+    root.mkdir()
+    rng = np.random.default_rng(0)
+    with open(root / "metadata.jsonl", "w") as f:
+        for name in ("a.avi", "b.avi"):
+            video_io.save_video(list(rng.integers(0, 255, (6, 72, 80, 3), dtype=np.uint8)), str(root / name), fps=8)
+            f.write(json.dumps({"video": name, "caption": f"clip {name}"}) + "\n")
+    outs = run_distributed(_real_clips_worker, 2, str(root), timeout=240)
+    assert outs[1] == "encoder-rank-done"
+    assert outs[0][0] == 3 and outs[0][1] > 0
