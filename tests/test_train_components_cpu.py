@@ -414,3 +414,19 @@ def test_training_helpers(capsys):
     assert abs(gb - 1e9 * (2 + 4 + 12 / 8) / 2 ** 30) < 1e-6
     cfg = wan_config("wan2.1-1.3b-t2v")
     assert T.num_floating_point_operations(cfg, 32760, 8) == 8 * T.num_floating_point_operations(cfg, 32760, 1)
+
+
+def test_exit_interval_and_exit_duration_save_and_leave(tmp_path):
+    from teletron_b200.train import Trainer
+    from teletron_b200.train.checkpoint import read_tracker
+
+    a = _trainer_args(tmp_path / "a", "--exit-interval 2")
+    a.train_iters, a.save_interval = 10, 1000
+    assert Trainer(a).train(make_forward_step()) == 2
+    assert read_tracker(str(tmp_path / "a")) == (2, False)
+    b = _trainer_args(tmp_path / "b", "--exit-duration-in-mins 1")
+    b.train_iters, b.save_interval = 10, 1000
+    t = Trainer(b)
+    t.start_time -= 120.0                                   # the run "started" two minutes ago
+    assert t.train(make_forward_step()) == 1
+    assert read_tracker(str(tmp_path / "b")) == (1, False)
