@@ -230,7 +230,9 @@ def validate_args(args):
     args.consumed_train_samples = 0
     args.consumed_valid_samples = 0
     args.iteration = 0
-    if args.train_iters is None and args.train_samples is not None:
+    # sample-based runs keep their sample-denominated schedule horizons even after train_iters is derived
+    args.sample_based_training = args.train_iters is None and args.train_samples is not None
+    if args.sample_based_training:
         from .helpers import update_train_iters
 
         update_train_iters(args)      # follows the batch-size ramp when there is one

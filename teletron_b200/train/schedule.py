@@ -105,7 +105,7 @@ class OptimizerParamScheduler:
 
 def scheduler_from_args(args, optimizer) -> OptimizerParamScheduler:
     """Sample-based horizon arithmetic of teletron/train/lr_scheduler.py:255-302."""
-    if args.train_iters:
+    if args.train_iters and not getattr(args, "sample_based_training", False):
         decay_iters = args.lr_decay_iters if args.lr_decay_iters is not None else args.train_iters
         decay_steps = decay_iters * args.global_batch_size
         wd_steps = args.train_iters * args.global_batch_size

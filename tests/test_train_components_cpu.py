@@ -430,3 +430,34 @@ def test_exit_interval_and_exit_duration_save_and_leave(tmp_path):
     t.start_time -= 120.0                                   # the run "started" two minutes ago
     assert t.train(make_forward_step()) == 1
     assert read_tracker(str(tmp_path / "b")) == (1, False)
+
+
+def test_sample_based_training_uses_sample_denominated_schedules(tmp_path):
+    """--train-samples with --lr-warmup-samples / --lr-decay-samples: warm-up ends after 2 samples (= 1 step of 2),
+    the cosine reaches --min-lr at 8 samples, weight decay ramps linearly over the run."""
+    import math
+
+    from teletron_b200.train import Trainer
+
+    argv = ("--model ParallelWanModel --model-preset wan-tiny --train-samples 8 --micro-batch-size 1 --global-batch-size 2 "
+            "--lr 1e-3 --min-lr 1e-4 --lr-decay-style cosine --lr-warmup-samples 2 --lr-decay-samples 8 "
+            "--synthetic-latents --num-frames 5 --video-resolution 64 64 --log-interval 100 --seed 11 "
+            "--start-weight-decay 0.0 --end-weight-decay 0.1 --weight-decay-incr-style linear").split()
+    a = parse_args(argv=argv)
+    a.text_dim, a.text_len = 64, 16
+    assert a.train_iters == 4 and a.sample_based_training
+    t = Trainer(a)
+    seen = []
+    orig = t.train_step
+
+    def spy(f, it=None):
+        r = orig(f, it)
+        g = t.optimizer.param_groups[0]
+        seen.append((g["lr"], g["weight_decay"]))
+        return r
+
+    t.train_step = spy
+    t.train(make_forward_step())
+    want_lr = [1e-3] + [1e-4 + 0.9e-3 * 0.5 * (1 + math.cos(math.pi * (c - 2) / 6)) for c in (4, 6, 8)]
+    assert all(abs(l - w) < 1e-9 for (l, _), w in zip(seen, want_lr)), (seen, want_lr)
+    assert all(abs(wd - w) < 1e-9 for (_, wd), w in zip(seen, (0.025, 0.05, 0.075, 0.1)))
