@@ -191,3 +191,35 @@ def _hy_encoder_fed_worker(rank, world):
 def test_hunyuan_training_fed_by_an_encoder_rank():
     outs = run_distributed(_hy_encoder_fed_worker, 2, timeout=240)
     assert outs[1] == "encoder-rank-done" and outs[0] > 0
+
+
+def _hy_tp_resume_worker(rank, world, root, mode):
+    import os
+
+    from teletron_b200.train import Trainer, make_hunyuan_forward_step
+
+    extra = f"--tensor-model-parallel-size 2 --save {root}/ck --save-interval 1"
+    if mode == "resume":
+        extra += f" --load {root}/ck"
+    a = _hy_train_args(world, extra)
+    a.global_batch_size = a.current_global_batch_size = 1
+    a.num_micro_batches = 1
+    t = Trainer(a)
+    start = a.iteration
+    for it in range(start, 3):
+        if mode == "first" and it == 1:
+            break
+        a.train_iters = it + 1
+        t.train(make_hunyuan_forward_step(timestep_generator=torch.Generator().manual_seed(50 + it)))
+    shards = sorted(os.listdir(f"{root}/ck/iter_0000001")) if os.path.isdir(f"{root}/ck/iter_0000001") else []
+    return start, a.iteration, t.buffer.params.float().clone(), shards
+
+
+def test_hunyuan_tp2_checkpoint_resumes_exactly(tmp_path):
+    full = run_distributed(_hy_tp_resume_worker, 2, str(tmp_path / "full"), "full", timeout=240)
+    first = run_distributed(_hy_tp_resume_worker, 2, str(tmp_path / "run"), "first", timeout=240)
+    assert [o[:2] for o in first] == [(0, 1), (0, 1)] and first[0][3] == ["mp_rank_00", "mp_rank_01"]
+    resumed = run_distributed(_hy_tp_resume_worker, 2, str(tmp_path / "run"), "resume", timeout=240)
+    assert [o[:2] for o in resumed] == [(1, 3), (1, 3)]
+    for r in range(2):
+        assert torch.allclose(resumed[r][2], full[r][2], atol=1e-6)       # each TP rank's shard
