@@ -461,3 +461,29 @@ def test_sample_based_training_uses_sample_denominated_schedules(tmp_path):
     want_lr = [1e-3] + [1e-4 + 0.9e-3 * 0.5 * (1 + math.cos(math.pi * (c - 2) / 6)) for c in (4, 6, 8)]
     assert all(abs(l - w) < 1e-9 for (l, _), w in zip(seen, want_lr)), (seen, want_lr)
     assert all(abs(wd - w) < 1e-9 for (_, wd), w in zip(seen, (0.025, 0.05, 0.075, 0.1)))
+
+
+def test_load_options_finetune_no_optim_no_rng(tmp_path):
+    from teletron_b200.train import Trainer
+
+    first = Trainer(_trainer_args(tmp_path))
+    first.pretrain(make_forward_step())                                  # 4 iterations, checkpoints at 2 and 4
+    root = str(tmp_path)
+    trained = first.buffer.params.clone()
+    m_state = first.optimizer.exp_avg[0].clone()
+    assert float(m_state.abs().sum()) > 0
+
+    a = _trainer_args(tmp_path / "ft", f"--load {root} --finetune")
+    t = Trainer(a)
+    assert a.iteration == 0 and a.consumed_train_samples == 0            # weights only: counters start over
+    assert torch.equal(t.buffer.params, trained) and float(t.optimizer.exp_avg[0].abs().sum()) == 0
+    assert torch.equal(t.optimizer.master[0][:16], trained[:16].float())  # master weights follow the loaded ones
+
+    b = _trainer_args(tmp_path / "noopt", f"--load {root} --no-load-optim --no-load-rng")
+    t2 = Trainer(b)
+    assert b.iteration == 4 and torch.equal(t2.buffer.params, trained)
+    assert float(t2.optimizer.exp_avg[0].abs().sum()) == 0               # optimizer state not restored
+
+    c = _trainer_args(tmp_path / "full", f"--load {root}")
+    t3 = Trainer(c)
+    assert c.iteration == 4 and torch.equal(t3.optimizer.exp_avg[0], m_state)
