@@ -177,3 +177,32 @@ def _mappings_worker(rank, world):
 
 def test_split_gather_mappings_with_uneven_sizes_and_grad_scale():
     assert run_distributed(_mappings_worker, 2) == ["ok", "ok"]
+
+
+def _cp_sampling_worker(rank, world):
+    import torch
+
+    from teletron_b200.infer import WanVideoPipeline
+    from teletron_b200.models import WanModel, wan_config
+    from teletron_b200.models.encoders import UMT5Encoder, WanVideoVAE
+    from teletron_b200.models.encoders.wan_encoder import HashTokenizer
+    from teletron_b200.parallel import state as mpu
+    from teletron_b200.parallel.ulysses import UlyssesContext
+
+    cp = None
+    if world > 1:
+        mpu.initialize_model_parallel(context_parallel_size=world)
+        cp = UlyssesContext(mpu.get_context_parallel_group(), world, rank)
+    torch.manual_seed(0)
+    dit = WanModel(wan_config("wan-tiny", text_dim=64), cp).eval()
+    t5 = UMT5Encoder(vocab=512, dim=64, dim_attn=64, dim_ffn=128, num_heads=4, num_layers=1)
+    pipe = WanVideoPipeline.from_modules(dit, WanVideoVAE(dim=16), t5, None, HashTokenizer(512, 512), device="cpu",
+                                         torch_dtype=torch.float32)
+    return pipe("a cat", negative_prompt="blurry", height=64, width=48, num_frames=5, num_inference_steps=2, seed=0,
+                tiled=False, output_type="latent")
+
+
+def test_sampling_with_a_context_parallel_dit_matches_one_rank():
+    one = run_distributed(_cp_sampling_worker, 1)[0]
+    for out in run_distributed(_cp_sampling_worker, 2):
+        assert (out - one).abs().max() < 1e-4
