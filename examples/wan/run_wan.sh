@@ -34,7 +34,8 @@ TRAINING_ARGS=(--model ParallelWanModel --task-type wan_i2v_prone --micro-batch-
                --global-batch-size $GBS --train-iters 10000 --weight-decay 1e-2 --init-method-std 0.006
                --clip-grad 0.0 --bf16 --lr 1e-5 --lr-decay-style constant --lr-warmup-fraction 0
                --recompute-granularity full --recompute-method block --recompute-num-layers $N_LAYERS
-               --use-distributed-optimizer --no-rope-fusion --distributed-timeout-minutes 60)
+               --use-distributed-optimizer --no-rope-fusion --distributed-timeout-minutes 60
+               --init-on-device)   # 7 B parameters at 20 layers: create them on the GPU, not in host memory
 MODEL_PARALLEL_ARGS=(--tensor-model-parallel-size $TP --context-parallel-size $CP --distributed-vae
                      --distributed-vae-world-size $N_GPU_FOR_DATA --consumer-models-num $N_MOE)
 DATA_ARGS=(--dataset-type FakeDataset --split 949,50,1 --dataloader-type single --num-workers 1 --num-frames 81)
