@@ -86,13 +86,36 @@ def status_word(device: torch.device | None = None) -> torch.Tensor:
     return t
 
 
+# status codes written by the kernels (csrc/tt_common.cuh): high byte = who gave up, low byte = which wait / peer
+_STATUS_ROLES = {0x100: "a TMA producer warp waiting for a free stage", 0x200: "the MMA-issuing warp",
+                 0x300: "an epilogue warp waiting for an accumulator",
+                 0x400: "a softmax / elementwise warp waiting for a tensor-memory tile",
+                 0x500: "a peer barrier waiting for rank", 0x600: "a kernel whose dynamic shared memory is misaligned"}
+
+
+def describe_status(code: int) -> str:
+    """Readable form of a status word value, e.g. 0x503 -> the peer barrier gave up waiting for rank 3."""
+    if code == 0:
+        return "ok"
+    role, detail = code & ~0xFF, code & 0xFF
+    what = _STATUS_ROLES.get(role)
+    if what is None:
+        return f"unknown status 0x{code:x}"
+    if role == 0x500:
+        return f"{what} {detail} ran out of its time budget"
+    if role == 0x600:
+        return what
+    return f"{what} ran out of its time budget (wait #{detail})"
+
+
 def check_status(device: torch.device | None = None) -> None:
     """Raise if any kernel recorded a timed-out wait since the last check (one D2H read)."""
     t = status_word(device)
     code = int(t[0].item())
     if code != 0:
         t.zero_()
-        raise RuntimeError(f"a device-side wait timed out (status 0x{code:x}); results are invalid")
+        raise RuntimeError(f"a device-side wait gave up (status 0x{code:x}: {describe_status(code)}); "
+                           "results of this step are invalid")
 
 
 def launch_count() -> int:

@@ -312,3 +312,12 @@ def test_config_dictionary(tmp_path):
     assert c.model.dim == 512 and c.new is True
     with pytest.raises(ValueError):
         Config.load(str(tmp_path / "conf.py"))
+
+
+def test_status_word_values_are_described():
+    from teletron_b200.ops._lib import describe_status
+
+    assert describe_status(0) == "ok"
+    assert describe_status(0x503) == "a peer barrier waiting for rank 3 ran out of its time budget"
+    assert "MMA-issuing warp" in describe_status(0x202) and "wait #2" in describe_status(0x202)
+    assert "misaligned" in describe_status(0x600) and describe_status(0x7ff).startswith("unknown status")
