@@ -206,7 +206,7 @@ def _hy_tp_resume_worker(rank, world, root, mode):
     a.num_micro_batches = 1
     t = Trainer(a)
     start = a.iteration
-    for it in range(start, 3):
+    for it in range(start, 2):
         if mode == "first" and it == 1:
             break
         a.train_iters = it + 1
@@ -220,6 +220,6 @@ def test_hunyuan_tp2_checkpoint_resumes_exactly(tmp_path):
     first = run_distributed(_hy_tp_resume_worker, 2, str(tmp_path / "run"), "first", timeout=240)
     assert [o[:2] for o in first] == [(0, 1), (0, 1)] and first[0][3] == ["mp_rank_00", "mp_rank_01"]
     resumed = run_distributed(_hy_tp_resume_worker, 2, str(tmp_path / "run"), "resume", timeout=240)
-    assert [o[:2] for o in resumed] == [(1, 3), (1, 3)]
+    assert [o[:2] for o in resumed] == [(1, 2), (1, 2)]
     for r in range(2):
         assert torch.allclose(resumed[r][2], full[r][2], atol=1e-6)       # each TP rank's shard
