@@ -6,8 +6,8 @@ cudaMalloc's device-wide synchronisation is unacceptable) passes only its own in
 buffers; the partial sums live in a fixed array inside the library.  The test checks the result
 against the ordinary entry point (``tt_colsum``, caller-provided scratch) on two calls in a row —
 the second with a smaller problem, so the array still holds the first call's partial sums — and
-checks that an oversized request is refused with a readable message.  It is collected last so a
-run that stops at the first failure has already exercised everything else.
+checks that an oversized request is refused with a readable message.  It is collected near the end
+so a run that stops at the first failure has already exercised the rest.
 """
 import ctypes
 
