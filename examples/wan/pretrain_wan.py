@@ -65,4 +65,5 @@ def forward_step(data_iterator, model):
 if __name__ == "__main__":
     args = parse_args(extra_args=extra_args)
     trainer = Trainer(args)
-    trainer.pretrain(forward_step_func=make_forward_step(shift=args.flow_shift, train_timesteps=args.flow_train_timesteps) if args.fused_step else forward_step)
+    fused = make_forward_step(shift=args.flow_shift, train_timesteps=args.flow_train_timesteps)
+    trainer.pretrain(forward_step_func=fused if args.fused_step else forward_step)

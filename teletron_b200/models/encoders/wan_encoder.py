@@ -46,7 +46,8 @@ class HashTokenizer:
         ids = torch.zeros(len(texts), self.seq_len, dtype=torch.long)
         mask = torch.zeros(len(texts), self.seq_len, dtype=torch.long)
         for i, t in enumerate(texts):
-            toks = [2 + zlib.crc32(w.encode()) % (self.vocab - 2) for w in apply_clean_mode(t, "whitespace").split()][: self.seq_len - 1] + [1]
+            words = apply_clean_mode(t, "whitespace").split()[: self.seq_len - 1]
+            toks = [2 + zlib.crc32(w.encode()) % (self.vocab - 2) for w in words] + [1]
             ids[i, :len(toks)] = torch.tensor(toks)
             mask[i, :len(toks)] = 1
         return ids, mask

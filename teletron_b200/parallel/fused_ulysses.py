@@ -14,8 +14,9 @@ Activations that must live until backward (q/k/v in head layout, O in sequence l
 taken from one symmetric slab used as a stack: a layer's region is released by its backward
 (layers run backward in reverse order), at once when the forward pass is one whose activations
 are dropped (the first pass of a checkpointed range, or no-grad evaluation), and the whole slab is
-reset every micro-batch; gradient staging buffers are reused across layers.  Ordering across ranks relies on every rank executing the
-same kernel sequence; each exchange is fenced by the bounded flag barrier of csrc/comm.cu.
+reset every micro-batch; gradient staging buffers are reused across layers.  Ordering across ranks
+relies on every rank executing the same kernel sequence; each exchange is fenced by the bounded flag
+barrier of csrc/comm.cu.
 Requirements: heads divisible by the group size, head_dim 128, bf16, one NVLink box.
 """
 from __future__ import annotations

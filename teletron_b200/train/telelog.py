@@ -118,10 +118,12 @@ class TrainLogger:
             return False
         n_adv = max(self.counts[self.ADV], 1)
         elapsed = time.time() - self.t_last
+        n_iters = max(self.counts[self.ADV] + self.counts[self.SKIP], 1)
+        batch = getattr(a, "current_global_batch_size", a.global_batch_size)
         parts = [f"iteration {iteration:8d}/{a.train_iters or 0:8d}",
                  f"consumed samples: {a.consumed_train_samples:12d}",
-                 f"elapsed time per iteration (ms): {elapsed * 1000.0 / max(self.counts[self.ADV] + self.counts[self.SKIP], 1):.1f}",
-                 f"learning rate: {lr:.3E}", f"global batch size: {getattr(a, 'current_global_batch_size', a.global_batch_size):5d}"]
+                 f"elapsed time per iteration (ms): {elapsed * 1000.0 / n_iters:.1f}",
+                 f"learning rate: {lr:.3E}", f"global batch size: {batch:5d}"]
         for k, tot in self.totals.items():
             parts.append(f"{k}: {tot / n_adv:.6E}")
         parts.append(f"loss scale: {float(loss_scale):.1f}")

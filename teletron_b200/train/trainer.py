@@ -215,7 +215,8 @@ class Trainer:
             return
         h, w = a.video_resolution
         i2v = (a.task_type == "i2v")
-        name = "SyntheticLatentDataset" if (a.synthetic_latents or a.dataset_type == "SyntheticLatentDataset") else a.dataset_type
+        synthetic = a.synthetic_latents or a.dataset_type == "SyntheticLatentDataset"
+        name = "SyntheticLatentDataset" if synthetic else a.dataset_type
         kw = dict(num_frames=a.num_frames, height=h, width=w, i2v=i2v, seed=a.seed, data_path=getattr(a, "data_path", None),
                   min_length=(a.train_iters or 0) * a.global_batch_size)    # finite datasets repeat up to this
         if name == "SyntheticLatentDataset" and "Hunyuan" in a.model:
