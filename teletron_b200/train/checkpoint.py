@@ -70,11 +70,20 @@ def read_tracker(root: str) -> Tuple[int, bool]:
 
 
 # ----------------------------------------------------------------------------- rng
-def get_rng_state():
+def get_rng_state(per_dp_rank: bool = False):
+    """``[state]`` of this rank, or, with ``per_dp_rank`` (``--data-parallel-random-init``: every data-parallel rank
+    runs its own random stream), the states of all data-parallel ranks in rank order.  Collective in that case:
+    every rank of the DP x CP group calls it."""
     st = dict(random_rng_state=random.getstate(), np_rng_state=np.random.get_state(),
               torch_rng_state=torch.get_rng_state(),
               cuda_rng_state=torch.cuda.get_rng_state() if torch.cuda.is_available() else None,
               rng_tracker_states={})
+    if per_dp_rank and dist.is_initialized() and mpu.model_parallel_is_initialized() \
+            and mpu.get_data_parallel_world_size(with_context_parallel=True) > 1:
+        grp = mpu.get_data_parallel_group(with_context_parallel=True)
+        states = [None] * dist.get_world_size(grp)
+        dist.all_gather_object(states, st, group=grp)
+        return states
     return [st]
 
 
@@ -85,6 +94,13 @@ def set_rng_state(states, dp_rank: int = 0):
     torch.set_rng_state(st["torch_rng_state"])
     if st.get("cuda_rng_state") is not None and torch.cuda.is_available():
         torch.cuda.set_rng_state(st["cuda_rng_state"])
+
+
+def _rng_index(args) -> int:
+    """Which saved state this rank takes: its own when the run keeps one stream per data-parallel rank."""
+    if getattr(args, "data_parallel_random_init", False) and mpu.model_parallel_is_initialized():
+        return mpu.get_data_parallel_rank(with_context_parallel=True)
+    return 0
 
 
 def _atomic_save(obj, path: str):
@@ -115,6 +131,8 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
     dp_rank = mpu.get_data_parallel_rank(with_context_parallel=True)
     sharded_opt = optimizer is not None and getattr(optimizer, "sharded", False) and not args.no_save_optim
     full_opt = optimizer.gather_full_state() if sharded_opt else None  # collective: every rank calls it
+    per_rank_rng = bool(getattr(args, "data_parallel_random_init", False)) and not args.no_save_rng
+    rng_states = get_rng_state(per_dp_rank=True) if per_rank_rng else None  # collective too
     path = None
     if dp_rank == 0:
         sd = dict(args=_plain_namespace(args), checkpoint_version=3.0, iteration=iteration,
@@ -130,7 +148,7 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
             if opt_param_scheduler is not None:
                 sd["opt_param_scheduler"] = opt_param_scheduler.state_dict()
         if not args.no_save_rng:
-            sd["rng_state"] = get_rng_state()
+            sd["rng_state"] = rng_states if rng_states is not None else get_rng_state()
         path = checkpoint_name(root, iteration)
         _atomic_save(sd, path)
         if sharded_opt and full_opt is not None:
@@ -211,6 +229,6 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, strict: bool = 
             if defer_rng:
                 args.deferred_rng_state = sd["rng_state"]
             else:
-                set_rng_state(sd["rng_state"], 0)
+                set_rng_state(sd["rng_state"], _rng_index(args))
     _barrier()
     return iteration, flops

@@ -101,7 +101,8 @@ class Trainer:
 
             self._prev_sigterm = signal.signal(signal.SIGTERM, _on_sigterm)
         if getattr(args, "deferred_rng_state", None) is not None:
-            ckpt.set_rng_state(args.deferred_rng_state, 0)   # after everything that consumes start-up randomness
+            # after everything that consumes start-up randomness
+            ckpt.set_rng_state(args.deferred_rng_state, ckpt._rng_index(args))
             args.deferred_rng_state = None
 
     # ------------------------------------------------------------------ distributed

@@ -189,3 +189,37 @@ def test_training_on_a_folder_of_clips_through_an_encoder_rank(tmp_path):
     outs = run_distributed(_real_clips_worker, 2, str(root), timeout=240)
     assert outs[1] == "encoder-rank-done"
     assert outs[0][0] == 3 and outs[0][1] > 0
+
+
+def _per_rank_rng_worker(rank, world, root, mode):
+    """Every data-parallel rank draws its own timesteps and noise from its global generators
+    (--data-parallel-random-init); a resumed run must continue each rank's stream."""
+    from teletron_b200.train import Trainer, make_forward_step
+
+    extra = ("--use-distributed-optimizer --synthetic-latents --global-batch-size 2 --save-interval 1 "
+             f"--data-parallel-random-init --num-workers 0 --save {root}/{'full' if mode == 'full' else 'run'}")
+    if mode == "resume":
+        extra += f" --load {root}/run"
+    a = _args(world, extra)
+    a.train_iters = 3
+    t = Trainer(a)                        # schedules are built for the whole run
+    if mode == "first":
+        a.train_iters = 1                 # ... of which the first launch only gets through one iteration
+    start = a.iteration
+    # different on the two ranks, and part of the stream a resume continues (so a resumed run must not draw it again)
+    drawn = float(torch.rand(1)) if mode != "resume" else None
+    t.train(make_forward_step())
+    return start, a.iteration, drawn, t.buffer.params.float().clone()
+
+
+def test_per_rank_random_streams_survive_a_resume(tmp_path):
+    root = str(tmp_path)
+    full = run_distributed(_per_rank_rng_worker, 2, root, "full", timeout=240)
+    assert full[0][2] != full[1][2]                                       # the ranks really use different streams
+    first = run_distributed(_per_rank_rng_worker, 2, root, "first", timeout=240)
+    assert [o[:2] for o in first] == [(0, 1), (0, 1)] and first[0][2] == full[0][2] and first[1][2] == full[1][2]
+    sd = torch.load(f"{root}/run/iter_0000001/mp_rank_00/model_optim_rng.pt", weights_only=False)
+    assert len(sd["rng_state"]) == 2                                      # one state per data-parallel rank
+    resumed = run_distributed(_per_rank_rng_worker, 2, root, "resume", timeout=240)
+    assert [o[:2] for o in resumed] == [(1, 3), (1, 3)]
+    assert torch.allclose(resumed[0][3], full[0][3], atol=1e-6) and torch.equal(resumed[0][3], resumed[1][3])
