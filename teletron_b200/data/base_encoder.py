@@ -7,6 +7,8 @@ names the tensors, ``_pack_tensors`` flattens them into one bf16 blob.
 Wire format (one message pair per sample, NCCL/gloo p2p):
   header  int32[HEADER_INTS] = [MAGIC, VERSION, seq_no, n_tensors, flags, then per tensor (ndim, d0..d4)]
   payload flat bf16 = the tensors flattened in schema order
+After an early stop request the producer closes each stream with one header that carries ``FLAG_STOP`` and no payload,
+which completes the header receive the consumer keeps in flight.
 A fixed, versioned header replaces the reference's bare int32[16] of concatenated shapes
 (teletron/train/consumer_dataloader.py:106-122), whose length silently disagreed between
 producer and consumer once a fifth tensor (shared noise) was added.
@@ -24,6 +26,7 @@ HEADER_INTS = 64
 MAX_TENSORS = 9
 MAX_DIMS = 5
 FLAG_LAST = 1
+FLAG_STOP = 2   # header without a payload: the producer was asked to stop and will send nothing more
 
 
 def encode_header(shapes: Sequence[Sequence[int]], seq_no: int, flags: int = 0) -> torch.Tensor:

@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist
 
 from ..parallel import state as mpu
-from .base_encoder import FLAG_LAST, HEADER_INTS, decode_header, numel_of, unpack_tensors
+from .base_encoder import FLAG_LAST, FLAG_STOP, HEADER_INTS, decode_header, numel_of, unpack_tensors
 from .encoder_service import PolledWork, store, store_has
 
 WAN_SCHEMA = ["context", "clip_feature", "image_emb_y", "latents", "noise"]
@@ -87,6 +87,9 @@ class DistBatchLoader:
         work, hdr = self._pending
         self._wait(work, "a sample header")
         shapes, seq, flags = decode_header(hdr.cpu())
+        if flags & FLAG_STOP:                      # the producer closed the stream after a stop request
+            self.finished, self._pending = True, None
+            return None
         if seq != (self.received & 0x7FFFFFFF):
             raise ValueError(f"encoder stream out of order: got sample {seq}, expected {self.received}")
         blob = torch.empty(numel_of(shapes), dtype=torch.bfloat16, device=self.dev)
@@ -107,7 +110,10 @@ class DistBatchLoader:
         if self.is_leader:
             if self.finished and self._pending is None and self.received > 0 and self._exhausted():
                 raise StopIteration
-            hdr, blob, shapes = self._receive()
+            got = self._receive()
+            if got is None:
+                raise StopIteration
+            hdr, blob, shapes = got
         else:
             hdr = torch.zeros(HEADER_INTS, dtype=torch.int32, device=self.dev)
             blob, shapes = None, None
@@ -141,10 +147,13 @@ class DistBatchLoader:
             if time.time() - t0 > self.timeout_s:
                 raise EncoderTimeout("producer did not acknowledge the stop request")
             if self._pending is not None and self._pending[0].done():
-                self._receive()
+                if self._receive() is None:
+                    break
             time.sleep(0.005)
         issued = int(st.get(key).decode())
         while self.received < issued:
+            self._receive()
+        if self._pending is not None:              # the prefetched header receive: completed by the stop header
             self._receive()
         self.finished = True
 

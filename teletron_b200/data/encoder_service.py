@@ -27,7 +27,7 @@ import torch.distributed as dist
 from ..models.registry import encoder_for_model, get_encoder
 from ..parallel import state as mpu
 from ..parallel.state import CommPair
-from .base_encoder import FLAG_LAST, pack_tensors
+from .base_encoder import FLAG_LAST, FLAG_STOP, pack_tensors
 
 QUEUE_DEPTH = 2
 MAX_OUTSTANDING_SENDS = 1
@@ -189,8 +189,24 @@ def producer_process(args, encoder=None, dataset=None):
             if prof is not None:
                 prof.step()
             time.sleep(POLL_SECONDS)
-        for c, n in issued.items():
-            st.set(f"tt_issued_{rank}_{c}", str(n))
+        if stopping:
+            # close every unfinished stream with a payload-less header: the consumer's prefetched header receive
+            # completes instead of staying in flight until the process group is torn down
+            from .base_encoder import encode_header
+
+            closing = []
+            for c, n in issued.items():
+                if n < total:
+                    hdr = encode_header([], n, FLAG_STOP).to(dev)
+                    closing.append((PolledWork(dist.isend(hdr, dst=c), backend), hdr))
+            for c, n in issued.items():
+                st.set(f"tt_issued_{rank}_{c}", str(n))
+            t_end = time.time() + 60.0
+            while any(not w.done() for w, _ in closing) and time.time() < t_end:
+                time.sleep(POLL_SECONDS)
+        else:
+            for c, n in issued.items():
+                st.set(f"tt_issued_{rank}_{c}", str(n))
         if prof is not None:
             prof.__exit__(None, None, None)
         return sum(issued.values())

@@ -128,6 +128,11 @@ class Trainer:
             self.start_time = float(t.item())
 
     def _shutdown(self):
+        # an early exit (--exit-interval, --exit-duration-in-mins, SIGTERM) leaves encoder ranks mid-stream: ask them to
+        # stop and drain what they already sent, or they would never reach the barrier below
+        it = getattr(self, "train_data_iterator", None)
+        if hasattr(it, "close") and self.args.iteration < (self.args.train_iters or 0):
+            it.close()
         if dist.is_initialized():
             try:
                 dist.barrier()

@@ -223,3 +223,27 @@ def test_per_rank_random_streams_survive_a_resume(tmp_path):
     resumed = run_distributed(_per_rank_rng_worker, 2, root, "resume", timeout=240)
     assert [o[:2] for o in resumed] == [(1, 3), (1, 3)]
     assert torch.allclose(resumed[0][3], full[0][3], atol=1e-6) and torch.equal(resumed[0][3], resumed[1][3])
+
+
+def _early_exit_worker(rank, world):
+    from teletron_b200.train import Trainer, make_forward_step
+
+    a = _args(world, "--distributed-vae --distributed-vae-world-size 1 --encoder-name synthetic_wan_encoder "
+                     "--dataset-type FakeDataset --exit-interval 2")
+    a.train_iters = 10                                       # the encoder rank plans for ten samples
+    try:
+        t = Trainer(a)
+    except SystemExit:
+        return "encoder-rank-done"
+    t.pretrain(make_forward_step())
+    it = t.train_data_iterator
+    return a.iteration, it.finished, it._pending is None
+
+
+def test_an_early_exit_stops_the_encoder_rank_and_closes_the_stream():
+    """--exit-interval ends training after 2 of 10 iterations: the encoder rank is told to stop, sends what it had in
+    flight plus a stop header (which completes the consumer's prefetched receive), and both ranks reach the final
+    barrier instead of hanging."""
+    outs = run_distributed(_early_exit_worker, 2, timeout=120)
+    assert outs[1] == "encoder-rank-done"
+    assert outs[0] == (2, True, True)
