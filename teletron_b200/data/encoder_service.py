@@ -17,6 +17,7 @@ store so consumers raise instead of waiting forever (the reference aborts the wo
 from __future__ import annotations
 
 import collections
+import os
 import time
 import traceback
 from typing import Dict, List
@@ -116,7 +117,15 @@ def producer_process(args, encoder=None, dataset=None):
     backend = dist.get_backend()
     dev = _comm_device(backend)
     st = store()
+    if getattr(args, "exit_signal_handler", False):
+        # a scheduler's SIGTERM reaches every process of the job: the DiT ranks save and then ask this rank to stop,
+        # so it has to outlive the signal and keep serving until that request arrives
+        import signal
+
+        signal.signal(signal.SIGTERM, lambda signum, frame: print(
+            f"[encoder rank {rank}] SIGTERM received: serving until the consumers close their streams", flush=True))
     try:
+        st.set(f"tt_pid_{rank}", str(os.getpid()))
         pairs = [p for p in mpu.get_comm_pair() if p.producer == rank]
         if not pairs:
             dist.barrier()

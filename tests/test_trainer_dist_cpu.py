@@ -247,3 +247,41 @@ def test_an_early_exit_stops_the_encoder_rank_and_closes_the_stream():
     outs = run_distributed(_early_exit_worker, 2, timeout=120)
     assert outs[1] == "encoder-rank-done"
     assert outs[0] == (2, True, True)
+
+
+def _sigterm_job_worker(rank, world, root):
+    import signal
+
+    from teletron_b200.data.encoder_service import store
+    from teletron_b200.train import Trainer, make_forward_step
+
+    a = _args(world, "--distributed-vae --distributed-vae-world-size 1 --encoder-name synthetic_wan_encoder "
+                     f"--dataset-type FakeDataset --exit-signal-handler --save {root} --save-interval 1000")
+    a.train_iters = 10
+    try:
+        t = Trainer(a)
+    except SystemExit:
+        return "encoder-rank-done"
+    orig, calls = t.train_step, []
+
+    def step(fwd, it=None):
+        calls.append(1)
+        if len(calls) == 2:                                 # the scheduler's SIGTERM reaches every process of the job
+            os.kill(int(store().get("tt_pid_1").decode()), signal.SIGTERM)
+            os.kill(os.getpid(), signal.SIGTERM)
+        return orig(fwd, it)
+
+    t.train_step = step
+    try:
+        t.pretrain(make_forward_step())
+    finally:
+        signal.signal(signal.SIGTERM, t._prev_sigterm)
+    return a.iteration
+
+
+def test_sigterm_to_the_whole_job_saves_and_leaves_with_the_encoder_rank(tmp_path):
+    from teletron_b200.train.checkpoint import read_tracker
+
+    outs = run_distributed(_sigterm_job_worker, 2, str(tmp_path), timeout=120)
+    assert outs == [2, "encoder-rank-done"]
+    assert read_tracker(str(tmp_path)) == (2, False)
