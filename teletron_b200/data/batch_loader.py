@@ -182,6 +182,8 @@ class OriginBatchLoader:
 def create_batch_loader(model_name: str, args, iterator=None):
     if iterator is not None and not args.distributed_vae:
         return OriginBatchLoader(iterator)
+    kw = dict(timeout_s=float(getattr(args, "encoder_timeout_seconds", 600.0)),
+              heartbeat_stale_s=float(getattr(args, "encoder_heartbeat_stale_seconds", 120.0)))
     if "Hunyuan" in model_name:
-        return HunyuanDistBatchLoader(args)
-    return WanDistBatchLoader(args)
+        return HunyuanDistBatchLoader(args, **kw)
+    return WanDistBatchLoader(args, **kw)

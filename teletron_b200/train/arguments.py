@@ -173,6 +173,10 @@ _FLAGS = [
     ("--vae-tiled", dict(action="store_true")),
     ("--vae-tile-size", dict(type=int, nargs=2, default=[34, 34])),
     ("--vae-tile-stride", dict(type=int, nargs=2, default=[18, 16])),
+    ("--encoder-timeout-seconds", dict(type=float, default=600.0,
+                                       help="how long a DiT rank waits for one sample from its encoder rank")),
+    ("--encoder-heartbeat-stale-seconds", dict(type=float, default=120.0,
+                                               help="an encoder rank whose heartbeat is older than this counts as dead")),
     ("--yaml-cfg", dict(type=str, default=None,
                         help="YAML (or JSON) file of flag values, flat or grouped one level deep, keys spelled like "
                              "the flags with - or _; values given on the command line win")),
