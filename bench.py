@@ -243,28 +243,96 @@ def run_ours(a):
 
 
 # ------------------------------------------------------------------------------ reference
-def run_reference(a):
+REF_SHAPES = {  # hidden, heads, layers, ffn (the public Wan2.1 checkpoints' shapes)
+    "wan2.1-1.3b": (1536, 12, 30, 8960),
+    "wan2.1-14b": (5120, 40, 40, 13824),
+}
+
+
+class _Stopwatch:
+    """CUDA events on a GPU; the host clock when the arm is driven on CPU by the tests."""
+
+    def __init__(self, torch, dev):
+        self.torch, self.cuda = torch, dev.type == "cuda"
+
+    def start(self):
+        if self.cuda:
+            self.torch.cuda.synchronize()
+            self.e0 = self.torch.cuda.Event(enable_timing=True)
+            self.e1 = self.torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        else:
+            self.t0 = time.perf_counter()
+
+    def stop_ms(self):
+        if self.cuda:
+            self.e1.record()
+            self.torch.cuda.synchronize()
+            return self.e0.elapsed_time(self.e1)
+        return (time.perf_counter() - self.t0) * 1e3
+
+
+def reference_result(a, *, tok_sample, gbs, desc, ms_dev, ms_e2e, e2e_steps, h2d_bytes_per_step, clocks, last_loss,
+                     recompute, settings_tried):
+    """The reference arm's JSON line, built from plain numbers (unit-tested without a GPU)."""
+    headline = (a.model == "wan2.1-1.3b-t2v" and (a.frames, a.height, a.width, gbs) == (FRAMES, HEIGHT, WIDTH, GLOBAL_BATCH)
+                and not a.layers)
+    published = {(480, 832, 81): PUBLISHED_TOKENS_PER_S_PER_GPU,
+                 (720, 1280, 81): PUBLISHED_720P_TOKENS_PER_S_PER_GPU}.get((a.height, a.width, a.frames))
+    metric = METRIC if headline else f"{a.model.replace('-', '_')}_{a.height}p{a.frames}f_train_tokens_per_s"
+    value = gbs * tok_sample * a.steps / (ms_dev * 1e-3)
+    e2e = gbs * tok_sample * e2e_steps / (ms_e2e * 1e-3)
+    return {
+        "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": ms_dev / a.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": value / published if published else None, "dtype": "bf16", "data": "synthetic",
+        "impl": "reference",
+        "config": {"model": desc, "global_batch": gbs, "seq_len": tok_sample, "parallelism": "dp1",
+                   "micro_batches_per_step": gbs, "optimizer": "torch fused AdamW on bf16 parameters",
+                   "recompute": recompute, "recompute_settings_tried": settings_tried,
+                   "l2": "inputs and working set far larger than L2",
+                   "note": "unmodified teletron/models/wan/wan_model.py + flow_match.py from baseline/_ref, flash_attn 2 "
+                           "attention; the reference Trainer itself cannot be imported offline (megatron-core, apex, "
+                           "yunchang missing)"},
+        "clocks": clocks,
+        "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
+                "h2d_bytes_per_step": h2d_bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last_loss},
+    }
+
+
+def run_reference(a, device=None, shape=None, ref_root=None, time_budget_s=1500.0):
     """The reference's own DiT code from baseline/_ref, driven directly: its Trainer needs
-    megatron-core / apex / yunchang, none of which can be installed offline."""
+    megatron-core / apex / yunchang, none of which can be installed offline.
+
+    One step = `--global-batch` micro-batches of one sample through the reference's `WanModel.forward`
+    (`teletron/models/wan/wan_model.py:339-396`) with the flow-matching loss of its example
+    (`examples/wan/pretrain_wan.py:26-62`), gradient clipping and one AdamW step.  Both of its activation settings are
+    tried for two steps (per-block checkpointing as shipped, and none); the faster one that fits is measured and
+    named in `config.recompute`.  `device` / `shape` / `ref_root` exist for the CPU test of this function."""
     rank, world, local = dist_env()
+    t_wall0 = time.time()
 
     def unavailable(why):
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
         return 0
 
-    ref_file = ROOT / "baseline" / "_ref" / "teletron" / "models" / "wan" / "wan_model.py"
+    ref_root = Path(ref_root) if ref_root else ROOT / "baseline" / "_ref"
+    ref_file = ref_root / "teletron" / "models" / "wan" / "wan_model.py"
     if not ref_file.exists():
         return unavailable("reference not installed under baseline/_ref (pip --no-deps install missing)")
     if world > 1 or a.gpus > 1:
         return unavailable("multi-GPU reference path needs megatron-core 0.6.0 + yunchang (parallel_state, DDP, "
                            "Ulysses all-to-all); neither is in the offline wheelhouse, so only N=1 runs")
+    key = a.model.rsplit("-", 1)[0]
+    if key not in REF_SHAPES and shape is None:
+        return unavailable(f"the reference has no model named {a.model}")
     import importlib.util
     from types import SimpleNamespace
 
     import torch
 
-    if not torch.cuda.is_available():
+    if device is None and not torch.cuda.is_available():
         return unavailable("no CUDA device on this machine")
     spec = importlib.util.spec_from_file_location("ref_wan_model", ref_file)
     ref = importlib.util.module_from_spec(spec)
@@ -272,73 +340,116 @@ def run_reference(a):
     fm_spec = importlib.util.spec_from_file_location("ref_flow_match", ref_file.parent.parent / "flow_match.py")
     fm = importlib.util.module_from_spec(fm_spec)
     fm_spec.loader.exec_module(fm)
+    dev = torch.device(device) if device is not None else torch.device("cuda", local)
+    on_gpu = dev.type == "cuda"
+    if on_gpu:
+        torch.cuda.set_device(dev)
+    else:  # CPU test: the flash-attention wheels cannot take CPU tensors
+        ref.FLASH_ATTN_3_AVAILABLE = ref.FLASH_ATTN_2_AVAILABLE = ref.SAGE_ATTN_AVAILABLE = False
+    hidden, heads, layers, ffn = shape["dims"] if shape else REF_SHAPES[key]
+    text_dim, text_len = (shape["text_dim"], shape["text_len"]) if shape else (4096, 512)
+    i2v = "i2v" in a.model
     P = ref.WanParams  # model shape is class-level configuration in the reference
-    P.in_channels, P.ffn_dim, P.has_image_input = 16, 8960, False
-    dev = torch.device("cuda", local)
-    torch.cuda.set_device(dev)
+    P.in_channels, P.ffn_dim, P.has_image_input, P.text_dim = (36 if i2v else 16), ffn, i2v, text_dim
+    if shape:
+        P.freq_dim = shape.get("freq_dim", P.freq_dim)
+    n_layers = a.layers or layers
+    gbs = a.global_batch
+    tok_sample = tokens_per_sample(a.frames, a.height, a.width)
+    dtype = torch.bfloat16 if on_gpu else torch.float32
     torch.manual_seed(1234)
-    n_layers = a.layers or 30
-    model = ref.WanModel(SimpleNamespace(hidden_size=1536, num_attention_heads=12, num_layers=n_layers))
-    model = model.to(dev).to(torch.bfloat16).train()
-    opt = torch.optim.AdamW(model.parameters(), lr=1e-5, weight_decay=1e-2, fused=True)
+    model = ref.WanModel(SimpleNamespace(hidden_size=hidden, num_attention_heads=heads, num_layers=n_layers))
+    model = model.to(dev).to(dtype).train()
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-5, weight_decay=1e-2, fused=on_gpu)
     sched = fm.FlowMatchScheduler(shift=5, sigma_min=0.0, extra_one_step=True)
     sched.set_timesteps(1000, training=True)
-    f, h, w = 21, 60, 104
-    pool = [dict(latents=torch.randn(1, 16, f, h, w, device=dev, dtype=torch.bfloat16),
-                 context=torch.randn(1, 512, 4096, device=dev, dtype=torch.bfloat16)) for _ in range(GLOBAL_BATCH)]
-    use_ckpt = not a.ref_no_recompute
+    f, h, w = (a.frames - 1) // 4 + 1, a.height // 8, a.width // 8
 
-    def step():
+    def sample(g):
+        b = dict(latents=torch.randn(1, 16, f, h, w, generator=g).to(dtype),
+                 context=torch.randn(1, text_len, text_dim, generator=g).to(dtype))
+        if i2v:
+            b["clip_feature"] = torch.randn(1, 257, 1280, generator=g).to(dtype)
+            b["y"] = torch.randn(1, 20, f, h, w, generator=g).to(dtype)
+        return {k: (v.pin_memory() if on_gpu else v) for k, v in b.items()}
+
+    g = torch.Generator().manual_seed(1234)
+    pool_host = [sample(g) for _ in range(min(gbs, 8))]
+    pool_dev = [{k: v.to(dev) for k, v in b.items()} for b in pool_host]
+    h2d_per_mb = sum(v.numel() * v.element_size() for v in pool_host[0].values())
+
+    def step(pool, use_ckpt, copy_in):
         opt.zero_grad(set_to_none=True)
-        for mb in range(GLOBAL_BATCH):
-            b = pool[mb]
+        for mb in range(gbs):
+            b = pool[mb % len(pool)]
+            if copy_in:  # this micro-batch's inputs come from pinned host memory
+                b = {k: v.to(dev, non_blocking=True) for k, v in b.items()}
             latents = b["latents"]
             noise = torch.randn_like(latents)
             tid = torch.randint(0, sched.num_train_timesteps, (1,))
-            timestep = sched.timesteps[tid].to(dtype=torch.bfloat16, device=dev)
+            timestep = sched.timesteps[tid].to(dtype=dtype, device=dev)
             target = sched.training_target(latents, noise, timestep)
             noisy = sched.add_noise(latents, noise, timestep)
-            out = model(x=noisy, timestep=timestep, context=b["context"], use_gradient_checkpointing=use_ckpt)
+            out = model(x=noisy, timestep=timestep, context=b["context"], clip_feature=b.get("clip_feature"),
+                        y=b.get("y"), use_gradient_checkpointing=use_ckpt)
             loss = torch.nn.functional.mse_loss(out.float(), target.float()) * sched.training_weight(timestep)
-            (loss / GLOBAL_BATCH).backward()
+            (loss / gbs).backward()
         torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
         opt.step()
         return loss
 
-    try:
-        for _ in range(a.warmup):
-            step()
-    except torch.cuda.OutOfMemoryError:
-        return unavailable("reference model ran out of memory in warm-up")
-    torch.cuda.synchronize()
+    oom = torch.cuda.OutOfMemoryError if on_gpu else MemoryError
+    watch = _Stopwatch(torch, dev)
+    # two steps of each activation setting; the second one is timed
+    candidates = [False] if a.ref_no_recompute else ([True] if a.ref_recompute_only else [True, False])
+    tried, probe_ms = {}, {}
+    for use_ckpt in candidates:
+        name = "per-block checkpointing (the reference's shipped setting)" if use_ckpt else "none"
+        try:
+            step(pool_dev, use_ckpt, False)
+            watch.start()
+            step(pool_dev, use_ckpt, False)
+            probe_ms[use_ckpt] = watch.stop_ms()
+            tried[name] = f"{probe_ms[use_ckpt]:.0f} ms/step"
+        except oom:
+            tried[name] = "out of memory"
+            opt.zero_grad(set_to_none=True)
+            if on_gpu:
+                torch.cuda.empty_cache()
+    if not probe_ms:
+        return unavailable("reference model ran out of memory in warm-up with every activation setting")
+    use_ckpt = min(probe_ms, key=probe_ms.get)
+    recompute = "per-block checkpointing (the reference's shipped setting)" if use_ckpt else "none"
+    for _ in range(max(0, a.warmup - 2)):
+        step(pool_dev, use_ckpt, False)
     clk_path = os.path.join(clock_log_dir(), "bench_clocks_reference.csv")
-    proc, fh = clock_sampler_start(clk_path)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
+    proc, fh = clock_sampler_start(clk_path) if on_gpu else (None, None)
+    watch.start()
     for _ in range(a.steps):
-        loss = step()
-    e1.record()
-    torch.cuda.synchronize()
+        step(pool_dev, use_ckpt, False)
+    ms_dev = watch.stop_ms()
     clocks = clock_sampler_stop(proc, fh, clk_path, local)
-    ms = e0.elapsed_time(e1)
-    tokens = gbs * tok_sample * a.steps
-    value = tokens / (ms * 1e-3)
-    print(json.dumps({
-        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
-        "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": value / PUBLISHED_TOKENS_PER_S_PER_GPU, "dtype": "bf16", "data": "synthetic",
-        "impl": "reference",
-        "config": {"model": "Wan2.1-1.3B t2v" if not a.layers else f"truncated to {a.layers} layers",
-                   "global_batch": GLOBAL_BATCH, "seq_len": TOKENS_PER_SAMPLE, "parallelism": "dp1",
-                   "recompute": "per-block checkpointing (the reference's shipped setting)" if use_ckpt else "none",
-                   "note": "unmodified teletron/models/wan/wan_model.py + flow_match.py from baseline/_ref, flash_attn 2 "
-                           "attention, torch fused AdamW on bf16 parameters; the reference Trainer itself cannot be "
-                           "imported offline (megatron-core, apex, yunchang missing)"},
-        "clocks": clocks, "last_loss": float(loss)}), flush=True)
+    # end to end: inputs from pinned host memory every micro-batch, the loss read back every step; fewer steps
+    # only if the whole arm would otherwise outrun its time budget (said in e2e.steps)
+    per_step_s = ms_dev * 1e-3 / a.steps
+    left = time_budget_s - (time.time() - t_wall0)
+    e2e_steps = max(1, min(a.steps, int(left / max(per_step_s, 1e-9))))
+    last_loss = None
+    watch.start()
+    for _ in range(e2e_steps):
+        last_loss = float(step(pool_host, use_ckpt, True).detach())
+    ms_e2e = watch.stop_ms()
+    desc = f"{a.model} ({n_layers} layers, dim {hidden}, {heads}x{hidden // heads} heads, ffn {ffn})"
+    if a.layers:
+        desc += " truncated (NOT the named config)"
+    print(json.dumps(reference_result(
+        a, tok_sample=tok_sample, gbs=gbs, desc=desc, ms_dev=ms_dev, ms_e2e=ms_e2e, e2e_steps=e2e_steps,
+        h2d_bytes_per_step=h2d_per_mb * gbs, clocks=clocks, last_loss=last_loss, recompute=recompute,
+        settings_tried=tried)), flush=True)
     return 0
 
 
-def main():
+def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
@@ -353,10 +464,11 @@ def main():
     ap.add_argument("--width", type=int, default=WIDTH)
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
     ap.add_argument("--init-on-device", action="store_true", help="create parameters on the GPU (default for 14B)")
-    ap.add_argument("--ref-no-recompute", action="store_true")
+    ap.add_argument("--ref-no-recompute", action="store_true", help="reference arm: only the no-checkpointing setting")
+    ap.add_argument("--ref-recompute-only", action="store_true", help="reference arm: only per-block checkpointing")
     ap.add_argument("--fused-comm", type=str, default="auto", choices=["auto", "on", "off"],
                     help="peer-memory fused collectives (off = NCCL baseline path)")
-    a = ap.parse_args()
+    a = ap.parse_args(argv)
     if a.impl == "reference":
         sys.exit(run_reference(a) or 0)
     run_ours(a)

@@ -59,3 +59,53 @@ def test_reference_arm_answers_on_a_box_without_a_gpu():
     line = [l for l in r.stdout.splitlines() if l.startswith("{")][-1]
     msg = json.loads(line)
     assert msg["impl"] == "reference" and "unavailable" in msg and isinstance(msg["unavailable"], str)
+
+
+def _ref_args(b, extra=()):
+    import argparse
+
+    ns = argparse.Namespace(gpus=1, steps=2, warmup=3, impl="reference", model="wan2.1-1.3b-t2v", cp=1, recompute=False,
+                            layers=0, frames=9, height=64, width=64, global_batch=2, init_on_device=False,
+                            ref_no_recompute=False, ref_recompute_only=False, fused_comm="auto")
+    for k, v in extra:
+        setattr(ns, k, v)
+    return ns
+
+
+def test_reference_arm_prints_a_full_line_when_driven_on_cpu(capsys):
+    """The whole reference arm (both activation settings probed, device-timed pass, end-to-end pass, result line)
+    runs on CPU with a tiny shape of the reference's own model file, so that a broken result line cannot ship."""
+    from conftest import reference_file
+
+    b = _bench()
+    wan = reference_file("teletron/models/wan/wan_model.py")
+    if wan is None:
+        import pytest
+        pytest.skip("reference tree not available")
+    shape = {"dims": (128, 4, 2, 512), "text_dim": 64, "text_len": 32, "freq_dim": 64}
+    rc = b.run_reference(_ref_args(b), device="cpu", shape=shape, ref_root=wan.parents[3])
+    assert rc == 0
+    line = [l for l in capsys.readouterr().out.splitlines() if l.startswith("{")][-1]
+    msg = json.loads(line)
+    assert msg["impl"] == "reference" and "unavailable" not in msg
+    tok = b.tokens_per_sample(9, 64, 64)
+    assert msg["config"]["seq_len"] == tok == 48 and msg["config"]["global_batch"] == 2
+    assert msg["steps"] == 2 and msg["warmup"] == 3 and msg["value"] > 0 and msg["ms_per_step"] > 0
+    assert abs(msg["value"] - 2 * tok / (msg["ms_per_step"] * 1e-3)) < 1e-6 * msg["value"]
+    e = msg["e2e"]
+    assert e["value"] > 0 and e["steps"] == 2 and e["d2h_bytes_per_step"] == 4
+    assert e["h2d_bytes_per_step"] == 2 * 4 * (16 * 3 * 8 * 8 + 32 * 64)      # fp32 on CPU: latents + context, 2 samples
+    assert set(msg["config"]["recompute_settings_tried"]) == {"none", "per-block checkpointing (the reference's shipped setting)"}
+    assert msg["config"]["recompute"] in msg["config"]["recompute_settings_tried"]
+    assert msg["metric"].endswith("_64p9f_train_tokens_per_s") and msg["vs_baseline"] is None
+    assert isinstance(e["last_loss"], float)
+
+
+def test_reference_result_line_names_the_headline_metric():
+    b = _bench()
+    a = _ref_args(b, (("frames", 81), ("height", 480), ("width", 832), ("global_batch", 8), ("steps", 20), ("warmup", 5)))
+    r = b.reference_result(a, tok_sample=32760, gbs=8, desc="d", ms_dev=20 * 24_000.0, ms_e2e=10 * 24_100.0, e2e_steps=10,
+                           h2d_bytes_per_step=1, clocks={}, last_loss=1.0, recompute="none", settings_tried={})
+    assert r["metric"] == b.METRIC and abs(r["value"] - 8 * 32760 / 24.0) < 1e-6
+    assert abs(r["e2e"]["value"] - 8 * 32760 / 24.1) < 1e-6 and r["e2e"]["steps"] == 10
+    assert abs(r["vs_baseline"] - r["value"] / 1090.0) < 1e-9
