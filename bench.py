@@ -7,7 +7,9 @@
 One step = one optimizer step over a global batch of 8 samples (32,760 tokens each), bf16,
 synthetic latents / text embeddings, random-init weights, AdamW.  The same global batch is
 used at every N (strong scaling): DP over the ranks that are not used for Ulysses CP, gradient
-accumulation when fewer than 8 replicas exist.  Rank 0 prints one JSON line.
+accumulation when fewer than 8 replicas exist.  At N > 1 every Ulysses size that divides N is
+tried for a few steps (`layouts` in the JSON line) and the fastest layout is measured in full.
+Rank 0 prints one JSON line.
 
 Other rows of the same benchmark: ``--model wan2.1-14b-i2v --cp 8 --height 720 --width 1280 --global-batch 1
 --recompute`` (any Wan preset, resolution, frame count, global batch, Ulysses size); the metric name then carries the
@@ -104,55 +106,84 @@ def dist_env():
 
 
 # ------------------------------------------------------------------------------ ours
+def candidate_layouts(world: int, gbs: int, cp_flag: int):
+    """Ulysses sizes to measure at `world` GPUs: the one asked for, or every power of two that divides the world and
+    leaves a data-parallel size that divides the global batch; data parallelism only (cp = 1) comes last."""
+    if cp_flag > 0:
+        return [cp_flag]
+    out = [cp for cp in (8, 4, 2, 1) if cp <= world and world % cp == 0 and gbs % (world // cp) == 0]
+    return out or [world]
+
+
+def layout_name(world: int, cp: int) -> str:
+    dp = world // cp
+    return f"dp{dp}" + (f"xcp{cp}" if cp > 1 else "")
+
+
 def run_ours(a):
+    import gc
+
     import torch
     import torch.distributed as dist
 
     from teletron_b200.data import SyntheticLatentDataset
     from teletron_b200.ops import _lib
+    from teletron_b200.parallel import state as mpu
     from teletron_b200.train import Trainer, make_forward_step, parse_args
 
     rank, world, local = dist_env()
     assert world == a.gpus, f"WORLD_SIZE {world} != --gpus {a.gpus} (launch N > 1 under torchrun)"
     if not torch.cuda.is_available():
         raise SystemExit("bench.py measures on a GPU: no CUDA device on this machine")
-    cp = a.cp
-    dp = world // cp
     frames, height, width, gbs = a.frames, a.height, a.width, a.global_batch
     headline = (a.model == "wan2.1-1.3b-t2v" and (frames, height, width, gbs) == (FRAMES, HEIGHT, WIDTH, GLOBAL_BATCH))
     tok_sample = tokens_per_sample(frames, height, width)
     i2v = "i2v" in a.model
-    argv = ["--model", "ParallelWanModel", "--model-preset", a.model, "--bf16", "--micro-batch-size", "1",
-            "--global-batch-size", str(gbs), "--train-iters", "1000000", "--lr", "1e-5",
-            "--weight-decay", "1e-2", "--clip-grad", "1.0", "--context-parallel-size", str(cp),
-            "--num-frames", str(frames), "--video-resolution", str(height), str(width), "--synthetic-latents",
-            "--log-interval", "1000000", "--seed", "1234"]
-    if i2v:
-        argv += ["--task-type", "i2v"]
-    if a.init_on_device or "14b" in a.model:
-        argv.append("--init-on-device")
     if world > 1:
-        argv.append("--use-distributed-optimizer")
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    argv += ["--fused-comm", a.fused_comm]
-    if a.recompute:
-        argv += ["--recompute-granularity", "full", "--recompute-method", "block", "--recompute-num-layers", "1000"]
-    if a.layers:
-        argv += ["--num-layers", str(a.layers)]
-    targs = parse_args(argv=argv)
-    trainer = Trainer(targs, build_data=False)
-    dev = trainer.device
     fwd = make_forward_step()
-    n_mb = targs.num_micro_batches
+    # the same global batch at every N and in every layout: sample i (latents, text, noise, timestep) is a function
+    # of i alone, and data-parallel rank d takes samples [d * n_mb, (d + 1) * n_mb)
+    ds = SyntheticLatentDataset(frames, height, width, i2v=i2v, seed=1234, fixed_noise=True)
 
-    # a small pool of distinct samples, kept both in pinned host memory and on the device
-    ds = SyntheticLatentDataset(frames, height, width, i2v=i2v, seed=1234 + rank)
-    pool_host = []
-    for i in range(max(n_mb, 2)):
-        it = ds[i]
-        pool_host.append({k: v.unsqueeze(0).pin_memory() for k, v in it.items()})
-    pool_dev = [{k: v.to(dev) for k, v in b.items()} for b in pool_host]
-    bytes_h2d_per_mb = sum(v.numel() * v.element_size() for v in pool_host[0].values())
+    def build(cp):
+        argv = ["--model", "ParallelWanModel", "--model-preset", a.model, "--bf16", "--micro-batch-size", "1",
+                "--global-batch-size", str(gbs), "--train-iters", "1000000", "--lr", "1e-5",
+                "--weight-decay", "1e-2", "--clip-grad", "1.0", "--context-parallel-size", str(cp),
+                "--num-frames", str(frames), "--video-resolution", str(height), str(width), "--synthetic-latents",
+                "--log-interval", "1000000", "--seed", "1234"]
+        if i2v:
+            argv += ["--task-type", "i2v"]
+        if a.init_on_device or "14b" in a.model:
+            argv.append("--init-on-device")
+        if world > 1:
+            argv.append("--use-distributed-optimizer")
+        argv += ["--fused-comm", a.fused_comm]
+        if a.no_overlap:
+            argv.append("--no-overlap-grad-reduce")
+        if a.recompute:
+            argv += ["--recompute-granularity", "full", "--recompute-method", "block", "--recompute-num-layers", "1000"]
+        if a.layers:
+            argv += ["--num-layers", str(a.layers)]
+        targs = parse_args(argv=argv)
+        tr = Trainer(targs, build_data=False)
+        n_mb = targs.num_micro_batches
+        d = mpu.get_data_parallel_rank() if world > 1 else 0
+        host = []
+        for i in range(d * n_mb, (d + 1) * n_mb):
+            host.append({k: v.unsqueeze(0).pin_memory() for k, v in ds[i].items()})
+        dev_pool = [{k: v.to(tr.device) for k, v in b.items()} for b in host]
+        return tr, host, dev_pool
+
+    def teardown(tr):
+        cpx = getattr(getattr(tr.model, "module", tr.model), "cp", None)
+        if cpx is not None:
+            cpx.fused = None
+        tr.model = tr.optimizer = tr.buffer = tr.arena = None
+        mpu.destroy_model_parallel()
+        gc.collect()
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
 
     def cycle(pool):
         i = 0
@@ -165,7 +196,7 @@ def run_ours(a):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(pool, steps, read_loss):
+    def timed(tr, pool, steps, read_loss):
         it = cycle(pool)
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -173,35 +204,92 @@ def run_ours(a):
         e0.record()
         last = None
         for _ in range(steps):
-            loss_dict, _, _, _ = trainer.train_step(fwd, it)
+            loss_dict, _, _, _ = tr.train_step(fwd, it)
             if read_loss:
                 last = float(loss_dict["loss"])  # device -> host read of the step's result
         e1.record()
         sync_all()
         ms = e0.elapsed_time(e1)
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        t = torch.tensor([ms], dtype=torch.float64, device=tr.device)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), _lib.launch_count() - l0, last
 
-    for _ in range(a.warmup):
-        trainer.train_step(fwd, cycle(pool_dev))
-    sync_all()
-    _lib.check_status()
+    def warm(tr, pool, n):
+        """n untimed steps; returns the loss of the first one (the parity value: same weights, same batch)."""
+        first = None
+        for i in range(n):
+            ld, _, _, _ = tr.train_step(fwd, cycle(pool))
+            if i == 0:
+                first = float(ld["loss"])
+        sync_all()
+        _lib.check_status()
+        return first
+
+    cands = candidate_layouts(world, gbs, a.cp)
+    layouts = {}
+    tr = host = dev_pool = None
+    built = None
+    trial_steps, trial_warm = 3, 3
+    for i, cp in enumerate(cands):
+        name = layout_name(world, cp)
+        try:
+            tr, host, dev_pool = build(cp)
+            built = cp
+            if len(cands) == 1:
+                break
+            first = warm(tr, dev_pool, trial_warm)
+            ms, _, _ = timed(tr, dev_pool, trial_steps, read_loss=False)
+            layouts[name] = {"tokens_per_s": gbs * tok_sample * trial_steps / (ms * 1e-3), "ms_per_step": ms / trial_steps,
+                             "steps": trial_steps, "warmup": trial_warm, "loss_first_step": first,
+                             "fused_ulysses": bool(getattr(getattr(getattr(tr.model, "module", tr.model), "cp", None),
+                                                           "fused", None))}
+        except Exception as e:  # a layout that cannot run (memory, unsupported split) is reported, not fatal
+            if len(cands) == 1:
+                raise
+            layouts[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            built = None
+        if i < len(cands) - 1 and tr is not None:
+            teardown(tr)
+            tr = host = dev_pool = None
+    ok = {k: v for k, v in layouts.items() if "tokens_per_s" in v}
+    if len(cands) > 1:
+        if not ok:
+            raise SystemExit(f"no layout ran: {layouts}")
+        best = max(ok, key=lambda k: ok[k]["tokens_per_s"])
+        best_cp = next(c for c in cands if layout_name(world, c) == best)
+        if built != best_cp:
+            if tr is not None:
+                teardown(tr)
+            tr, host, dev_pool = build(best_cp)
+            first_loss = warm(tr, dev_pool, a.warmup)
+        else:
+            first_loss = ok[best]["loss_first_step"]
+            warm(tr, dev_pool, max(0, a.warmup - trial_warm - trial_steps))
+        cp = best_cp
+    else:
+        cp = cands[0]
+        first_loss = warm(tr, dev_pool, a.warmup)
+    dp = world // cp
+    targs = tr.args
+    n_mb = targs.num_micro_batches
+    bytes_h2d_per_mb = sum(v.numel() * v.element_size() for v in host[0].values())
+    torch.cuda.reset_peak_memory_stats()
     clk_path = os.path.join(clock_log_dir(), f"bench_clocks_rank{rank}.csv")
     proc, fh = clock_sampler_start(clk_path) if rank == 0 else (None, None)
-    ms_dev, launches, _ = timed(pool_dev, a.steps, read_loss=False)
+    ms_dev, launches, _ = timed(tr, dev_pool, a.steps, read_loss=False)
     clocks = clock_sampler_stop(proc, fh, clk_path, local) if rank == 0 else {}
-    ms_e2e, _, last_loss = timed(pool_host, a.steps, read_loss=True)
+    ms_e2e, _, last_loss = timed(tr, host, a.steps, read_loss=True)
     _lib.check_status()
-    peak = torch.tensor([torch.cuda.max_memory_allocated(dev) / 2 ** 30], dtype=torch.float64, device=dev)
+    peak = torch.tensor([torch.cuda.max_memory_allocated(tr.device) / 2 ** 30], dtype=torch.float64, device=tr.device)
     if world > 1:
         dist.all_reduce(peak, op=dist.ReduceOp.MAX)
     tokens = gbs * tok_sample * a.steps
     value = tokens / (ms_dev * 1e-3)
     e2e = tokens / (ms_e2e * 1e-3)
     if rank == 0:
-        cfg = getattr(trainer.model, "module", trainer.model).cfg
+        inner = getattr(tr.model, "module", tr.model)
+        cfg = inner.cfg
         desc = (f"{a.model} ({cfg.num_layers} layers, dim {cfg.dim}, {cfg.num_heads}x{cfg.dim // cfg.num_heads} heads, "
                 f"ffn {cfg.ffn_dim})")
         if headline:
@@ -213,6 +301,8 @@ def run_ours(a):
                          (720, 1280, 81): PUBLISHED_720P_TOKENS_PER_S_PER_GPU}.get((height, width, frames))
         if a.layers:
             desc = f"{a.model} truncated to {a.layers} layers (NOT the named config)"
+        fused_opt = bool(getattr(tr.optimizer, "fused", False))
+        fused_cp = bool(getattr(getattr(inner, "cp", None), "fused", None))
         res = {
             "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": ms_dev / a.steps, "higher_is_better": True, "scaling": "strong",
@@ -220,12 +310,13 @@ def run_ours(a):
             "impl": "teletron_b200",
             "config": {"model": desc,
                        "global_batch": gbs, "seq_len": tok_sample,
-                       "parallelism": f"dp{dp}" + (f"xcp{cp}" if cp > 1 else ""), "micro_batches_per_step": n_mb,
+                       "parallelism": layout_name(world, cp), "micro_batches_per_step": n_mb,
+                       "layout_choice": ("the fastest of `layouts` (3 + 3 step trials of every Ulysses size that "
+                                         "divides the GPUs)" if len(cands) > 1 else "only candidate"),
                        "optimizer": "AdamW fp32 master" + (" (sharded)" if world > 1 else ""),
+                       "grad_reduce_overlap": bool(getattr(tr.optimizer, "overlap", False)),
                        "recompute": "full" if a.recompute else "none",
-                       "comm": ("peer-memory fused kernels" if (getattr(trainer.optimizer, "fused", False) or
-                                getattr(getattr(getattr(trainer.model, "module", trainer.model), "cp", None), "fused", None))
-                                else ("nccl" if world > 1 else "none")),
+                       "comm": ("peer-memory fused kernels" if (fused_opt or fused_cp) else ("nccl" if world > 1 else "none")),
                        "l2": "inputs and working set far larger than L2 (each step touches > 50 GB)",
                        "baseline_note": "vs_baseline divides by the tokens/s/GPU read off the reference's H800 chart "
                                         "(1.09k at 480P x 81, 0.57k at 720P x 81; model size not stated there)"},
@@ -233,9 +324,14 @@ def run_ours(a):
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps,
                     "h2d_bytes_per_step": bytes_h2d_per_mb * gbs, "d2h_bytes_per_step": 4 * world,
                     "last_loss": last_loss},
+            "parity": {"loss_first_step": first_loss,
+                       "note": "loss of the first optimizer step: same initial weights and the same 8 samples (data, "
+                               "noise and timestep are functions of the global sample index) at every N and layout"},
             "gpu_launches": launches,
             "peak_mem_gib": round(float(peak.item()), 2),   # torch allocator high-water mark, max over ranks
         }
+        if layouts:
+            res["layouts"] = layouts
         print(json.dumps(res), flush=True)
     if world > 1:
         dist.barrier()
@@ -456,7 +552,9 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", type=str, default="wan2.1-1.3b-t2v")
-    ap.add_argument("--cp", type=int, default=1, help="Ulysses context-parallel size (rest is DP)")
+    ap.add_argument("--cp", type=int, default=0, help="Ulysses context-parallel size, the rest is DP (0: measure every "
+                                                       "size that divides the GPUs, report all, headline = the fastest)")
+    ap.add_argument("--no-overlap", action="store_true", help="reduce gradients after backward instead of during it")
     ap.add_argument("--recompute", action="store_true", help="full activation recompute (not needed at 1.3B)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (invalid as a result)")
     ap.add_argument("--frames", type=int, default=FRAMES)

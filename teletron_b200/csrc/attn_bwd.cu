@@ -1127,14 +1127,19 @@ TT_API int tt_attn_bwd(const void* q, long long ldq, long long q_bs, const void*
 }
 
 // Backward over head-parallel tensors [B, S_pad, Hl, D]; dQ, dK, dV are stored with the Ulysses
-// head -> seq pattern into every peer's [B, S_l, H_total, D] buffers (three peer tables).
+// head -> seq pattern into every peer's [B, S_l, H_total, D] buffers (three peer tables) whose token stride is
+// `dst_ld` elements (0 = H_total * D; larger when the three are column blocks of one [rows, 3 * H_total * D]
+// matrix).  `heads` <= Hl of this rank's head slots hold real heads; lse and scratch are sized for `heads`.
 TT_API int tt_attn_bwd_scatter(const void* q, const void* k, const void* v, const void* o, const void* dout,
                                const float* lse, float* scratch, const long long* dq_peers,
-                               const long long* dk_peers, const long long* dv_peers, const int* kv_lens,
-                               int B, int Hl, int S_pad, int D, float scale, int world, int rank,
-                               unsigned* status, cudaStream_t stream) {
+                               const long long* dk_peers, const long long* dv_peers, long long dst_ld,
+                               const int* kv_lens, int B, int Hl, int heads, int H_total, int S_pad, int D,
+                               float scale, int world, int rank, unsigned* status, cudaStream_t stream) {
   TT_CHECK(world >= 1 && world <= TT_MAX_PEERS && rank >= 0 && rank < world, "attn_bwd_scatter: bad world/rank");
   TT_CHECK(S_pad % world == 0, "attn_bwd_scatter: padded sequence must divide by the group size");
+  TT_CHECK(heads >= 1 && heads <= Hl && rank * Hl + heads <= H_total && H_total <= Hl * world,
+           "attn_bwd_scatter: head slots do not match the head count");
+  TT_CHECK(dst_ld == 0 || (dst_ld >= (long long)H_total * D && dst_ld % 8 == 0), "attn_bwd_scatter: bad destination stride");
   TTScatter sc[3];
   const long long* tabs[3] = {dq_peers, dk_peers, dv_peers};
   for (int t = 0; t < 3; ++t) {
@@ -1143,12 +1148,12 @@ TT_API int tt_attn_bwd_scatter(const void* q, const void* k, const void* v, cons
       sc[t].peer[i] = reinterpret_cast<void*>(tabs[t][i]);
       TT_CHECK(sc[t].peer[i] && ((uintptr_t)sc[t].peer[i] & 15) == 0, "attn_bwd_scatter: bad peer pointer");
     }
-    sc[t].mode = 2; sc[t].S_l = S_pad / world; sc[t].S_pad = S_pad; sc[t].Hl = Hl; sc[t].H = Hl * world;
-    sc[t].D = D; sc[t].rank = rank; sc[t].world = world;
+    sc[t].mode = 2; sc[t].S_l = S_pad / world; sc[t].S_pad = S_pad; sc[t].Hl = Hl; sc[t].H = H_total;
+    sc[t].D = D; sc[t].rank = rank; sc[t].world = world; sc[t].ld = dst_ld;
   }
   const long long ld = (long long)Hl * D, bs = (long long)S_pad * Hl * D;
   // dq/dk/dv local pointers are unused in scatter mode; pass q as an aligned placeholder
   return attn_bwd_impl(q, ld, bs, k, ld, bs, v, ld, bs, o, ld, bs, dout, ld, bs, lse, scratch,
                        const_cast<void*>(q), ld, bs, const_cast<void*>(q), ld, bs, const_cast<void*>(q), ld, bs,
-                       kv_lens, B, Hl, S_pad, S_pad, D, scale, status, &sc[0], &sc[1], &sc[2], stream);
+                       kv_lens, B, heads, S_pad, S_pad, D, scale, status, &sc[0], &sc[1], &sc[2], stream);
 }

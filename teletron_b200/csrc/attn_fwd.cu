@@ -365,22 +365,27 @@ TT_API int tt_attn_fwd(const void* q, long long ldq, long long q_bs, const void*
 
 // Attention over head-parallel tensors [B, S_pad, Hl, D] whose epilogue also stores O with the
 // Ulysses head -> seq pattern into every peer's [B, S_l, H_total, D] buffer (peer_ptrs), in
-// addition to the local head-layout copy `o` that the backward pass needs.
+// addition to the local head-layout copy `o` that the backward pass needs.  `heads` <= Hl is how many of this
+// rank's head slots hold real heads (H_total need not divide by the group size: the last ranks own fewer);
+// lse is [B, heads, S_pad].
 TT_API int tt_attn_fwd_scatter(const void* q, long long ldq, long long q_bs, const void* k, long long ldk,
                                long long k_bs, const void* v, long long ldv, long long v_bs, void* o,
                                long long ldo, long long o_bs, float* lse, const int* kv_lens, int B, int Hl,
-                               int S_pad, int D, float scale, const long long* peer_ptrs, int world,
-                               int rank, unsigned* status, cudaStream_t stream) {
+                               int heads, int H_total, int S_pad, int D, float scale, const long long* peer_ptrs,
+                               int world, int rank, unsigned* status, cudaStream_t stream) {
   TT_CHECK(world >= 1 && world <= TT_MAX_PEERS && rank >= 0 && rank < world, "attn_fwd_scatter: bad world/rank");
   TT_CHECK(S_pad % world == 0, "attn_fwd_scatter: padded sequence must divide by the group size");
+  TT_CHECK(heads >= 1 && heads <= Hl && rank * Hl + heads <= H_total && H_total <= Hl * world,
+           "attn_fwd_scatter: head slots %d x %d ranks do not match %d heads (%d on rank %d)", Hl, world, H_total,
+           heads, rank);
   TTScatter sc;
   memset(&sc, 0, sizeof(sc));
   for (int i = 0; i < world; ++i) {
     sc.peer[i] = reinterpret_cast<void*>(peer_ptrs[i]);
     TT_CHECK(sc.peer[i] && ((uintptr_t)sc.peer[i] & 15) == 0, "attn_fwd_scatter: bad peer pointer %d", i);
   }
-  sc.mode = 2; sc.S_l = S_pad / world; sc.S_pad = S_pad; sc.Hl = Hl; sc.H = Hl * world; sc.D = D;
+  sc.mode = 2; sc.S_l = S_pad / world; sc.S_pad = S_pad; sc.Hl = Hl; sc.H = H_total; sc.D = D;
   sc.rank = rank; sc.world = world;
-  return attn_fwd_impl(q, ldq, q_bs, k, ldk, k_bs, v, ldv, v_bs, o, ldo, o_bs, lse, kv_lens, B, Hl, S_pad,
+  return attn_fwd_impl(q, ldq, q_bs, k, ldk, k_bs, v, ldv, v_bs, o, ldo, o_bs, lse, kv_lens, B, heads, S_pad,
                        S_pad, D, scale, status, sc, stream);
 }

@@ -168,7 +168,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
       bf16* c_row = reinterpret_cast<bf16*>(p.C) + (long long)row * p.ldc;
-      epilogue_tile<BN2>(p, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN2), eg, row, row_ok, c_row, n0);
+      if (p.epi == EPI_QKV_A2A)
+        epilogue_tile_qkv<BN2>(p, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN2), eg, row, row_ok, n0);
+      else
+        epilogue_tile<BN2>(p, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN2), eg, row, row_ok, c_row, n0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty_leader0 + a * 8);
@@ -270,4 +273,51 @@ TT_API int tt_gemm2_bf16(const void* A, long long lda, int a_mn, const void* B, 
   if (!a_mn && b_mn) return launch2<0, 1>(tmA, tmB, p, sms, stream);
   if (a_mn && b_mn) return launch2<1, 1>(tmA, tmB, p, sms, stream);
   return launch2<1, 0>(tmA, tmB, p, sms, stream);
+}
+
+// K-QKV-A2A: [q | k | v] = x W^T + b for this rank's `M = B * S_l` tokens (W: [3C, K] K-major), with the Ulysses
+// seq -> head exchange of v inside the epilogue.  `qk` ([M, 2C], row stride ldqk) receives the q and k blocks,
+// `ssq` ([M, 2 * C / 128] fp32) the sum of squares of each 128-column half tile (tt_rmsrope_fwd_scatter turns them
+// into the full-row statistics without re-reducing the row), and the v block is stored into the head owners'
+// [B, S_pad, ceil(H / world), D] buffers (`v_peer_ptrs`, one device address per rank).  Returns -3 when the shape
+// is outside the CTA-pair kernel's domain (the caller then runs the unfused sequence).
+TT_API int tt_gemm_qkv_a2a(const void* x, long long ldx, const void* W, long long ldw, const void* bias, void* qk,
+                           long long ldqk, float* ssq, const long long* v_peer_ptrs, int world, int rank, int M,
+                           int C, int K, int S_l, int H, int D, unsigned* status, cudaStream_t stream) {
+  if (M < 256) return -3;
+  TT_CHECK(C > 0 && C % 256 == 0 && K > 0 && H * D == C && D % 8 == 0, "gemm_qkv_a2a: bad shape C=%d H=%d D=%d", C, H, D);
+  TT_CHECK(world >= 1 && world <= TT_MAX_PEERS && rank >= 0 && rank < world, "gemm_qkv_a2a: bad world/rank");
+  TT_CHECK(S_l > 0 && M % S_l == 0, "gemm_qkv_a2a: rows must be whole samples of S_l tokens");
+  TT_CHECK(ldx % 8 == 0 && ldw % 8 == 0 && ldqk % 8 == 0 && ((uintptr_t)qk & 15) == 0 && ssq != nullptr,
+           "gemm_qkv_a2a: misaligned operands");
+  if (bias) TT_CHECK(((uintptr_t)bias & 15) == 0, "gemm_qkv_a2a: bias is not 16-byte aligned");
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[2], str[1];
+    uint32_t box[2];
+    dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = 64; box[1] = BM;
+    str[0] = (uint64_t)ldx * 2;
+    if (tt_make_tmap(&tmA, x, 2, 2, dims, str, box, 1)) return -1;
+    dims[0] = (uint64_t)K; dims[1] = (uint64_t)(3 * C); box[0] = 64; box[1] = 128;
+    str[0] = (uint64_t)ldw * 2;
+    if (tt_make_tmap(&tmB, W, 2, 2, dims, str, box, 1)) return -1;
+  }
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = 3 * C; p.K = K;
+  p.C = qk; p.ldc = ldqk; p.c_fp32 = 0;
+  p.bias = (const bf16*)bias; p.epi = EPI_QKV_A2A;
+  p.rows_per_gate = 1; p.alpha = 1.f; p.status = status;
+  p.world = 1;
+  p.qkv_C = C; p.ssq = ssq;
+  for (int i = 0; i < world; ++i) {
+    p.sc.peer[i] = reinterpret_cast<void*>(v_peer_ptrs[i]);
+    TT_CHECK(p.sc.peer[i] && ((uintptr_t)p.sc.peer[i] & 15) == 0, "gemm_qkv_a2a: bad peer pointer %d", i);
+  }
+  p.sc.mode = 1; p.sc.S_l = S_l; p.sc.S_pad = S_l * world; p.sc.Hl = (H + world - 1) / world; p.sc.H = H;
+  p.sc.D = D; p.sc.rank = rank; p.sc.world = world;
+  int dev = 0, sms = 0;
+  TT_CUDA(cudaGetDevice(&dev));
+  TT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  return launch2<0, 0>(tmA, tmB, p, sms, stream);
 }

@@ -14,8 +14,12 @@ constexpr int TP_MAX = 8;  // ranks of a tensor-parallel group
 
 // EPI_GELU_BWD / EPI_SILU_BWD: C = acc * act'(pre), `pre` (the saved pre-activation, bf16) read through `residual`:
 // the input-gradient GEMM of the layer behind an activation produces the gradient of the pre-activation directly.
+// EPI_QKV_A2A: the fused q/k/v projection under Ulysses context parallelism (N = 3 * qkv_C).  The q and k column
+// blocks are stored locally ([M, 2 * qkv_C]) together with the sum of squares of every 128-column half tile of each
+// row (`ssq`, [M, 2 * qkv_C / 128] fp32: the row statistics of the full-row RMSNorm that follows); the v column block
+// is stored straight into the head owner's [B, S_pad, Hl, D] buffer in peer memory (`sc`, the seq -> head exchange).
 enum Epi : int { EPI_NONE = 0, EPI_GELU = 1, EPI_GATE_RES = 2, EPI_ACCUM = 3, EPI_SILU = 4, EPI_GELU_BWD = 5,
-                 EPI_SILU_BWD = 6, EPI_LAST = 6 };
+                 EPI_SILU_BWD = 6, EPI_LAST = 6, EPI_QKV_A2A = 7 };
 
 struct GemmParams {
   int M, N, K;
@@ -39,6 +43,10 @@ struct GemmParams {
   //             [world, seg_rows, ldc] at slot `rank`; tt_tp_reduce_rows then sums the slots
   int tp_mode, seg_rows, world, rank;
   bf16* peer_c[TP_MAX];
+  // EPI_QKV_A2A
+  int qkv_C;
+  float* ssq;
+  TTScatter sc;
 };
 
 struct TmapSet {
@@ -179,6 +187,69 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t acc,
       }
     }
     __syncwarp();  // tcgen05.ld is warp-collective: reconverge before the next chunk
+  }
+}
+
+// EPI_QKV_A2A epilogue of one 128-row x BN accumulator tile (BN = 256, tiles never straddle the q / k / v column
+// blocks because qkv_C is a multiple of 256).  Same ownership as epilogue_tile: one output row per lane, column half
+// `eg` per warp.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile_qkv(const GemmParams& p, uint32_t acc, int eg, int row, bool row_ok,
+                                                  int n0) {
+  const int C = p.qkv_C;
+  const int part = n0 / C;  // 0 = q, 1 = k, 2 = v
+  const int b = row_ok ? row / p.sc.S_l : 0;
+  const int tok = row_ok ? row - b * p.sc.S_l : 0;
+  bf16* c_row = reinterpret_cast<bf16*>(p.C) + (long long)row * p.ldc;
+  float ss = 0.f;
+#pragma unroll 1
+  for (int c = eg * (BN / 64); c < (eg + 1) * (BN / 64); ++c) {
+    uint32_t r[32];
+    tmem_ld32(acc + (uint32_t)(c * 32), r);
+    tmem_ld_wait();
+    const int col0 = n0 + c * 32;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int col = col0 + g * 8;
+      if (!row_ok) break;
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
+      if (p.bias) {
+        uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+        const uint32_t* bu = reinterpret_cast<const uint32_t*>(&bv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = unpack_bf16(bu[j]);
+          v[2 * j] += f.x;
+          v[2 * j + 1] += f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16(v[0], v[1]);
+      o.y = pack_bf16(v[2], v[3]);
+      o.z = pack_bf16(v[4], v[5]);
+      o.w = pack_bf16(v[6], v[7]);
+      if (part < 2) {
+        // statistics of the values as stored (bf16), which is what the norm's backward recomputes from
+        const uint32_t* ou = reinterpret_cast<const uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = unpack_bf16(ou[j]);
+          ss += f.x * f.x + f.y * f.y;
+        }
+        *reinterpret_cast<uint4*>(c_row + col) = o;
+      } else {
+        const int cin = col - 2 * C;
+        const int hd = cin / p.sc.D;
+        *reinterpret_cast<uint4*>(scatter_dst(p.sc, b, tok, hd) + (cin - hd * p.sc.D)) = o;
+      }
+    }
+    __syncwarp();  // tcgen05.ld is warp-collective: reconverge before the next chunk
+  }
+  if (part < 2 && row_ok) {
+    const int halves = C / 128;
+    p.ssq[(long long)row * (2 * halves) + part * halves + (n0 - part * C) / 128 + eg] = ss;
   }
 }
 

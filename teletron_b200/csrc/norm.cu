@@ -359,7 +359,8 @@ rmsrope_kernel(const bf16* __restrict__ in, long long ldi, const bf16* __restric
                long long ldx, bf16* __restrict__ out, long long ldo, const float* __restrict__ w,
                const float2* __restrict__ freqs, int freq_rows, float* __restrict__ rstd_io,
                float* __restrict__ partial, int rows, int C, int D, int per_head, float eps,
-               int rows_per_cta, const TTScatter sc) {
+               int rows_per_cta, const TTScatter sc, const float* __restrict__ ssq = nullptr, int ssq_n = 0,
+               long long ssq_ld = 0) {
   __shared__ float red[NT / 32];
   const int nvec = C >> 3;
   const int vec_per_head = D >> 3;
@@ -415,7 +416,14 @@ rmsrope_kernel(const bf16* __restrict__ in, long long ldi, const bf16* __restric
               rstd_io[(long long)row * H + vec / vec_per_head] = rs[k];
           }
         } else {
-          const float r = rsqrtf(block_sum(tot, red) / (float)C + eps);
+          float full;
+          if (ssq) {  // row statistics from the GEMM that wrote this row; same value in every thread
+            full = 0.f;
+            for (int j = 0; j < ssq_n; ++j) full += ssq[(long long)row * ssq_ld + j];
+          } else {
+            full = block_sum(tot, red);
+          }
+          const float r = rsqrtf(full / (float)C + eps);
 #pragma unroll
           for (int k = 0; k < VPT; ++k) rs[k] = r;
           if (threadIdx.x == 0 && rstd_io) rstd_io[row] = r;
@@ -632,7 +640,8 @@ template <int NV>
 __global__ void __launch_bounds__(NT, 2)
 rmsrope_fwd_warp_kernel(const bf16* __restrict__ in, long long ldi, bf16* __restrict__ out, long long ldo,
                         const float* __restrict__ w, const float2* __restrict__ freqs, int freq_rows,
-                        float* __restrict__ rstd_io, int rows, int D, float eps, const TTScatter sc) {
+                        float* __restrict__ rstd_io, int rows, int D, float eps, const TTScatter sc,
+                        const float* __restrict__ ssq, int ssq_n, long long ssq_ld) {
   constexpr int C = NV * 256;
   __shared__ __align__(16) float w_s[C];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -647,12 +656,18 @@ rmsrope_fwd_warp_kernel(const bf16* __restrict__ in, long long ldi, bf16* __rest
     for (int k = 0; k < NV; ++k) load8(xr + (lane + k * 32) * 8, v[k]);
     float r = 1.f;
     if (w) {
-      float ss = 0.f;
+      float tot = 0.f;
+      if (ssq) {  // row statistics already produced (per 128-column piece) by the GEMM that wrote this row
+        for (int j = 0; j < ssq_n; ++j) tot += ssq[(long long)row * ssq_ld + j];
+      } else {
+        float ss = 0.f;
 #pragma unroll
-      for (int k = 0; k < NV; ++k)
+        for (int k = 0; k < NV; ++k)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ss += v[k][j] * v[k][j];
-      r = rsqrtf(warp_sum(ss) / (float)C + eps);
+          for (int j = 0; j < 8; ++j) ss += v[k][j] * v[k][j];
+        tot = warp_sum(ss);
+      }
+      r = rsqrtf(tot / (float)C + eps);
       if (lane == 0 && rstd_io) rstd_io[row] = r;
     }
 #pragma unroll
@@ -771,7 +786,10 @@ rmsrope_bwd_warp_kernel(const bf16* __restrict__ dy, long long lddy, const bf16*
 // Forward: in = x. Saves rstd ([rows] or [rows, H]) when w != null.
 static int rmsrope_fwd_impl(const void* x, long long ldx, void* y, long long ldy, const float* w,
                             const void* freqs, int freq_rows, float* rstd, int rows, int C, int D,
-                            int per_head, float eps, const TTScatter& sc, cudaStream_t stream) {
+                            int per_head, float eps, const TTScatter& sc, cudaStream_t stream,
+                            const float* ssq = nullptr, int ssq_n = 0, long long ssq_ld = 0) {
+  TT_CHECK(ssq == nullptr || (!per_head && w != nullptr && ssq_n > 0 && ssq_ld >= ssq_n),
+           "rmsrope_fwd: precomputed row statistics go with the full-row norm");
   TT_CHECK(rows > 0 && C % 8 == 0 && C <= 6144 && D > 0 && C % D == 0, "rmsrope_fwd: bad shape");
   TT_CHECK(!per_head || (D == 128 || D == 64), "rmsrope_fwd: per-head norm supports D = 64 or 128");
   TT_CHECK(freqs == nullptr || (D % 8 == 0 && freq_rows > 0), "rmsrope_fwd: bad rotary table");
@@ -782,7 +800,7 @@ static int rmsrope_fwd_impl(const void* x, long long ldx, void* y, long long ldy
     const int wgrid = want < 148 * 8 ? want : 148 * 8;
 #define TT_RMS_FWD_WARP(NVV)                                                                                        \
   rmsrope_fwd_warp_kernel<NVV><<<wgrid, NT, 0, stream>>>((const bf16*)x, ldx, (bf16*)y, ldy, w, (const float2*)freqs, \
-                                                         freq_rows, rstd, rows, D, eps, sc)
+                                                         freq_rows, rstd, rows, D, eps, sc, ssq, ssq_n, ssq_ld)
     switch (C / 256) {
       case 1: TT_RMS_FWD_WARP(1); break;
       case 2: TT_RMS_FWD_WARP(2); break;
@@ -801,7 +819,7 @@ static int rmsrope_fwd_impl(const void* x, long long ldx, void* y, long long ldy
   const int grid = (rows + rpc - 1) / rpc;
   TT_DISPATCH_VPT(vpt_for(C), rmsrope_kernel<VPT, false><<<grid, NT, 0, stream>>>(
       (const bf16*)x, ldx, nullptr, 0, (bf16*)y, ldy, w, (const float2*)freqs, freq_rows, rstd,
-      nullptr, rows, C, D, per_head, eps, rpc, sc));
+      nullptr, rows, C, D, per_head, eps, rpc, sc, ssq, ssq_n, ssq_ld));
   TT_LAUNCH_CHECK();
   return 0;
 }
@@ -816,14 +834,15 @@ TT_API int tt_rmsrope_fwd(const void* x, long long ldx, void* y, long long ldy, 
 
 // Same as tt_rmsrope_fwd, but the result is stored into peer memory with the Ulysses seq -> head
 // pattern (TTScatter mode 1): x is this rank's [B*S_l, H*D] shard, the output lands in every
-// peer's [B, S_pad, H/P, D] buffer. peer_ptrs: `world` device addresses of those buffers.
+// peer's [B, S_pad, ceil(H / world), D] buffer. peer_ptrs: `world` device addresses of those buffers.
+// ssq (optional): [rows, ssq_ld] fp32 whose first ssq_n entries per row add up to the row's sum of squares
+// (written by tt_gemm_qkv_a2a), used instead of reducing the row again.
 TT_API int tt_rmsrope_fwd_scatter(const void* x, long long ldx, const float* w, const void* freqs,
                                   int freq_rows, float* rstd, int rows, int C, int D, int per_head,
                                   float eps, const long long* peer_ptrs, int world, int rank, int S_l,
-                                  int S_pad, cudaStream_t stream) {
+                                  int S_pad, const float* ssq, int ssq_n, long long ssq_ld, cudaStream_t stream) {
   TT_CHECK(world >= 1 && world <= TT_MAX_PEERS && rank >= 0 && rank < world, "rmsrope_fwd_scatter: bad world/rank");
   const int H = C / D;
-  TT_CHECK(H % world == 0, "rmsrope_fwd_scatter: heads (%d) must divide by the group size (%d)", H, world);
   TT_CHECK(S_l > 0 && S_pad == S_l * world && rows % S_l == 0, "rmsrope_fwd_scatter: bad sequence split");
   TTScatter sc;
   memset(&sc, 0, sizeof(sc));
@@ -831,8 +850,10 @@ TT_API int tt_rmsrope_fwd_scatter(const void* x, long long ldx, const float* w, 
     sc.peer[i] = reinterpret_cast<void*>(peer_ptrs[i]);
     TT_CHECK(sc.peer[i] && ((uintptr_t)sc.peer[i] & 15) == 0, "rmsrope_fwd_scatter: bad peer pointer %d", i);
   }
-  sc.mode = 1; sc.S_l = S_l; sc.S_pad = S_pad; sc.Hl = H / world; sc.H = H; sc.D = D; sc.rank = rank; sc.world = world;
-  return rmsrope_fwd_impl(x, ldx, const_cast<void*>(x), ldx, w, freqs, freq_rows, rstd, rows, C, D, per_head, eps, sc, stream);
+  sc.mode = 1; sc.S_l = S_l; sc.S_pad = S_pad; sc.Hl = (H + world - 1) / world; sc.H = H; sc.D = D; sc.rank = rank;
+  sc.world = world;
+  return rmsrope_fwd_impl(x, ldx, const_cast<void*>(x), ldx, w, freqs, freq_rows, rstd, rows, C, D, per_head, eps, sc,
+                          stream, ssq, ssq_n, ssq_ld);
 }
 
 // Backward: dy -> dx, with x (saved forward input) and rstd. partial: fp32 [ctas, C] scratch for

@@ -73,13 +73,17 @@ enum : unsigned {
 //   mode 1 (seq -> head): source [B, S_l, H, D] on rank r  ->  peer h / Hl, [B, S_pad, Hl, D] at
 //                         token r*S_l + s, head h % Hl
 //   mode 2 (head -> seq): source [B, S_pad, Hl, D] on rank r ->  peer t / S_l, [B, S_l, H, D] at
-//                         token t % S_l, head r*Hl + hl
+//                         token t % S_l, head r*Hl + hl; `ld` (elements, 0 = H*D) is the destination's token stride,
+//                         so that the destination may be a column block of a wider matrix
 // mode 0 means "no scatter" (store locally).
+// H need not divide by the group size: Hl = ceil(H / world), the last ranks own fewer (or no) heads and callers
+// run only the heads that exist.
 #define TT_MAX_PEERS 16
 struct TTScatter {
   void* peer[TT_MAX_PEERS];
   int mode;
   int S_l, S_pad, Hl, H, D, rank, world;
+  long long ld;
 };
 
 #ifdef __CUDACC__
@@ -93,7 +97,8 @@ __device__ __forceinline__ bf16* scatter_dst(const TTScatter& sc, int b, int tok
     return reinterpret_cast<bf16*>(sc.peer[p]) + idx;
   }
   const int p = tok / sc.S_l;
-  const long long idx = ((long long)(b * sc.S_l + (tok - p * sc.S_l)) * sc.H + sc.rank * sc.Hl + hd) * sc.D;
+  const long long ld = sc.ld ? sc.ld : (long long)sc.H * sc.D;
+  const long long idx = (long long)(b * sc.S_l + (tok - p * sc.S_l)) * ld + (long long)(sc.rank * sc.Hl + hd) * sc.D;
   return reinterpret_cast<bf16*>(sc.peer[p]) + idx;
 }
 

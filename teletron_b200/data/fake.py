@@ -43,10 +43,15 @@ class FakeDataset(Dataset):
 @DATASETS.register("SyntheticLatentDataset")
 class SyntheticLatentDataset(Dataset):
     def __init__(self, num_frames=81, height=480, width=832, length=10_000_000, text_len=512, text_dim=4096,
-                 i2v=False, clip_tokens=257, clip_dim=1280, dtype=torch.bfloat16, seed=0, **_):
+                 i2v=False, clip_tokens=257, clip_dim=1280, dtype=torch.bfloat16, seed=0, fixed_noise=False,
+                 train_timesteps=1000, **_):
+        """``fixed_noise``: every item also carries its own ``noise`` and ``timestep_id`` (functions of the index),
+        so that the loss of a global batch does not depend on how the batch is split over ranks and micro-batches
+        (parity checks across parallel layouts)."""
         self.grid = latent_grid(num_frames, height, width)
         self.length, self.text_len, self.text_dim = length, text_len, text_dim
         self.i2v, self.clip_tokens, self.clip_dim, self.dtype, self.seed = i2v, clip_tokens, clip_dim, dtype, seed
+        self.fixed_noise, self.train_timesteps = fixed_noise, train_timesteps
 
     def __len__(self):
         return self.length
@@ -62,6 +67,9 @@ class SyntheticLatentDataset(Dataset):
             cond = torch.randn(16, f, h, w, generator=g)
             out["image_emb_y"] = torch.cat([mask, cond], dim=0).to(self.dtype)
             out["clip_feature"] = torch.randn(self.clip_tokens, self.clip_dim, generator=g).to(self.dtype)
+        if self.fixed_noise:
+            out["noise"] = torch.randn(16, f, h, w, generator=g).to(self.dtype)
+            out["timestep_id"] = torch.randint(0, self.train_timesteps, (), generator=g)
         return out
 
 

@@ -184,14 +184,15 @@ class SelfAttention(nn.Module, _FusedStateMixin):
 
     def forward(self, h2d, freqs, batch, cp: Optional[UlyssesContext], residual, gate, rows_per_batch):
         C, H, D = self.dim, self.num_heads, self.head_dim
-        qkv = self.qkv(h2d)  # [rows, 3C]
         fu = cp.fused if (cp is not None and cp.size > 1) else None
         if fu is not None and h2d.is_cuda and fu.supports(H, D):
-            # all-to-alls fused into the norm/rope and attention kernels' stores (peer memory)
+            # all-to-alls fused into the projection GEMM's, the norm/rope kernel's and the attention kernel's stores
+            # (peer memory)
             fu.seq_len = cp.seq_len
-            a2d = fu.attention(qkv[:, 0:C], qkv[:, C:2 * C], qkv[:, 2 * C:3 * C], self.norm_q.weight,
-                               self.norm_k.weight, freqs, batch, rows_per_batch, H, D, self.eps)
+            a2d = fu.attention_qkv(h2d, self.qkv.weight, self.qkv.bias, self.norm_q.weight, self.norm_k.weight,
+                                   freqs, batch, rows_per_batch, H, D, self.eps)
             return ops.linear_residual(a2d, self.o.weight, self.o.bias, residual, gate, rows_per_batch)
+        qkv = self.qkv(h2d)  # [rows, 3C]
         S = rows_per_batch
         if cp is None or cp.size == 1:
             # norm + rope + attention as one autograd node on the three column blocks of qkv

@@ -79,6 +79,9 @@ def _weight_grad(dy, x, w):
     if mg is not None:
         gemm(dy, x, a_mn=True, b_mn=True, out=mg, epi=EPI_ACCUM)
         w.grad_written = True
+        ready = getattr(w, "grad_ready", None)
+        if ready is not None:      # lets the optimizer start this parameter's bucket reduction (parallel/ddp.py)
+            ready()
         return None
     return gemm(dy, x, a_mn=True, b_mn=True, out_dtype=w.dtype)
 

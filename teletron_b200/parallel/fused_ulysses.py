@@ -1,8 +1,10 @@
 """Ulysses attention with the all-to-alls fused into kernel epilogues over NVLink peer memory.
 
 Per self-attention layer, forward:
-  q/k RMSNorm+RoPE kernel and a V copy kernel store their results straight into the owning
-  peer's head-parallel buffers (seq -> head exchange as a store pattern)   -> device barrier
+  the q/k/v projection GEMM stores V straight into the owning peers' head-parallel buffers from its epilogue
+  and leaves q, k (pre-norm) with their per-row sums of squares; the q/k RMSNorm+RoPE kernel takes the row
+  statistics from there and stores its results into the owning peers' head-parallel buffers (seq -> head
+  exchange as store patterns, no copy kernel)                              -> device barrier
   flash attention over [B, S, H/P, D]; its epilogue stores O both locally (kept for backward)
   and into the owning peer's sequence-parallel buffer (head -> seq exchange)  -> device barrier
 backward mirrors it: dO is scattered to the head owners, the attention-backward kernels store
@@ -17,7 +19,8 @@ are dropped (the first pass of a checkpointed range, or no-grad evaluation), and
 reset every micro-batch; gradient staging buffers are reused across layers.  Ordering across ranks
 relies on every rank executing the same kernel sequence; each exchange is fenced by the bounded flag
 barrier of csrc/comm.cu.
-Requirements: heads divisible by the group size, head_dim 128, bf16, one NVLink box.
+Requirements: head_dim 128, bf16, one NVLink box.  The head count need not divide by the group size: every rank
+has ceil(H / P) head slots, the last ranks own fewer heads (or none) and run attention only over the heads they own.
 """
 from __future__ import annotations
 
@@ -74,7 +77,12 @@ class FusedUlysses:
         self.seq_len: Optional[int] = None  # true (un-padded) global sequence length
 
     def supports(self, H: int, D: int) -> bool:
-        return D == 128 and H % self.world == 0
+        return D == 128 and H >= 1
+
+    def head_slots(self, H: int):
+        """(slots per rank, heads this rank owns) for H heads over the group."""
+        hl = (H + self.world - 1) // self.world
+        return hl, max(0, min(hl, H - self.rank * hl))
 
     def begin_microbatch(self, need_elems: int = 0):
         """Call before the first layer of every forward pass: makes sure no peer still reads the slab
@@ -90,8 +98,11 @@ class FusedUlysses:
     @staticmethod
     def slab_elems(layers_alive: int, batch: int, s_pad: int, channels: int, world: int) -> int:
         """bf16 elements one micro-batch needs: per live layer q, k, v in head layout and O in sequence
-        layout (4 tensors of batch * s_pad * channels / world), plus alignment slack."""
-        per_layer = 4 * (batch * s_pad * channels // world + _ALIGN)
+        layout (4 tensors of about batch * s_pad * channels / world; head slots are rounded up when the head count
+        does not divide by the group size), plus alignment slack."""
+        heads = max(channels // 128, 1)
+        slots = (heads + world - 1) // world
+        per_layer = 3 * (batch * s_pad * slots * (channels // heads) + _ALIGN) + (batch * s_pad * channels // world + _ALIGN)
         return int(per_layer * max(layers_alive, 1) * 1.02) + 4 * _ALIGN
 
     def staging(self, name: str, numel: int):
@@ -101,34 +112,39 @@ class FusedUlysses:
             self._staging[name] = t
         return t
 
-    def attention(self, q_pre, k_pre, v, wq, wk, freqs, B, S_l, H, D, eps, scale=None):
-        """q_pre/k_pre/v: [B*S_l, H*D] bf16 views (row stride free). Returns [B*S_l, H*D]."""
+    def attention_qkv(self, x, w_qkv, b_qkv, wq, wk, freqs, B, S_l, H, D, eps, scale=None):
+        """Self-attention of x [B*S_l, K] from the fused projection weight w_qkv [3*H*D, K] on: projection (with
+        the exchange of V in its epilogue), q/k norm + RoPE (exchange in its stores), attention (exchange of O
+        in its epilogue).  Returns [B*S_l, H*D]."""
         # decided here: inside an autograd function's forward the grad mode is always off
         self._keep_for_backward = torch.is_grad_enabled() and not forward_is_discarded()
-        return _FusedUlyssesFn.apply(self, q_pre, k_pre, v, wq, wk, freqs, B, S_l, H, D, eps, scale)
+        return _FusedUlyssesFn.apply(self, x, w_qkv, b_qkv, wq, wk, freqs, B, S_l, H, D, eps, scale)
 
 
-def _scatter_rows(fu: FusedUlysses, x, w, freqs, rstd, rows, C, D, eps, dst_ptrs, S_l, S_pad):
+def _scatter_rows(fu: FusedUlysses, x, w, freqs, rstd, rows, C, D, eps, dst_ptrs, S_l, S_pad, ssq=None):
     L = _lib.lib()
     rc = L.tt_rmsrope_fwd_scatter(
         _lib.ptr(x), _lib.c_ll(x.stride(0)), _lib.ptr(w), _lib.ptr(freqs),
         _lib.c_int(freqs.shape[0] if freqs is not None else 1), _lib.ptr(rstd), _lib.c_int(rows), _lib.c_int(C),
         _lib.c_int(D), _lib.c_int(0), _lib.c_float(eps), dst_ptrs, _lib.c_int(fu.world), _lib.c_int(fu.rank),
-        _lib.c_int(S_l), _lib.c_int(S_pad), _lib.stream())
+        _lib.c_int(S_l), _lib.c_int(S_pad), _lib.ptr(ssq), _lib.c_int(ssq.shape[1] if ssq is not None else 0),
+        _lib.c_ll(ssq.stride(0) if ssq is not None else 0), _lib.stream())
     _lib.check(rc, "tt_rmsrope_fwd_scatter")
 
 
 class _FusedUlyssesFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, fu: FusedUlysses, q_pre, k_pre, v, wq, wk, freqs, B, S_l, H, D, eps, scale):
+    def forward(ctx, fu: FusedUlysses, x, w_qkv, b_qkv, wq, wk, freqs, B, S_l, H, D, eps, scale):
         import math
+
+        from ..ops.gemm import gemm
 
         P, rank = fu.world, fu.rank
         C = H * D
-        Hl = H // P
+        Hl, heads = fu.head_slots(H)
         S_pad = S_l * P
         rows = B * S_l
-        dev = q_pre.device
+        dev = x.device
         scale = scale if scale is not None else 1.0 / math.sqrt(D)
         n_h = B * S_pad * Hl * D
         slab_mark = fu.slab.off
@@ -140,24 +156,45 @@ class _FusedUlyssesFn(torch.autograd.Function):
         wk_f = wk.float().contiguous()
         rstd_q = torch.empty(rows, dtype=torch.float32, device=dev)
         rstd_k = torch.empty(rows, dtype=torch.float32, device=dev)
-        _scatter_rows(fu, q_pre, wq_f, freqs, rstd_q, rows, C, D, eps, qh_p, S_l, S_pad)
-        _scatter_rows(fu, k_pre, wk_f, freqs, rstd_k, rows, C, D, eps, kh_p, S_l, S_pad)
-        _scatter_rows(fu, v, None, None, None, rows, C, D, eps, vh_p, S_l, S_pad)
+        L = _lib.lib()
+        # K-QKV-A2A: projection GEMM whose epilogue stores V into the head owners and leaves the row statistics
+        qk = torch.empty((rows, 2 * C), dtype=torch.bfloat16, device=dev)
+        halves = C // 128
+        ssq = torch.empty((rows, 2 * halves), dtype=torch.float32, device=dev) if C % 256 == 0 else None
+        rc = -3
+        if ssq is not None and x.stride(1) == 1 and w_qkv.stride(1) == 1:
+            rc = L.tt_gemm_qkv_a2a(
+                _lib.ptr(x), _lib.c_ll(x.stride(0)), _lib.ptr(w_qkv), _lib.c_ll(w_qkv.stride(0)), _lib.ptr(b_qkv),
+                _lib.ptr(qk), _lib.c_ll(qk.stride(0)), _lib.ptr(ssq), vh_p, _lib.c_int(P), _lib.c_int(rank),
+                _lib.c_int(rows), _lib.c_int(C), _lib.c_int(x.shape[1]), _lib.c_int(S_l), _lib.c_int(H),
+                _lib.c_int(D), _lib.ptr(_lib.status_word(dev)), _lib.stream())
+        if rc == -3:      # too few rows for the CTA-pair kernel: plain GEMM, V exchanged by a copy kernel
+            qkv = gemm(x, w_qkv, bias=b_qkv)
+            qk, ssq = qkv, None
+            _scatter_rows(fu, qkv[:, 2 * C:], None, None, None, rows, C, D, eps, vh_p, S_l, S_pad)
+        else:
+            _lib.check(rc, "tt_gemm_qkv_a2a")
+        q_pre, k_pre = qk[:, 0:C], qk[:, C:2 * C]
+        _scatter_rows(fu, q_pre, wq_f, freqs, rstd_q, rows, C, D, eps, qh_p, S_l, S_pad,
+                      ssq[:, :halves] if ssq is not None else None)
+        _scatter_rows(fu, k_pre, wk_f, freqs, rstd_k, rows, C, D, eps, kh_p, S_l, S_pad,
+                      ssq[:, halves:] if ssq is not None else None)
         fu.arena.barrier(fu.slot)
-        o_h = torch.empty(n_h, dtype=torch.bfloat16, device=dev)
-        lse = torch.empty((B, Hl, S_pad), dtype=torch.float32, device=dev)
         kv_lens = None
         if fu.seq_len is not None and fu.seq_len != S_pad:
             kv_lens = torch.full((B,), fu.seq_len, dtype=torch.int32, device=dev)
-        ld, bs = Hl * D, S_pad * Hl * D
-        L = _lib.lib()
-        rc = L.tt_attn_fwd_scatter(
-            _lib.ptr(qh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(kh), _lib.c_ll(ld), _lib.c_ll(bs),
-            _lib.ptr(vh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(o_h), _lib.c_ll(ld), _lib.c_ll(bs),
-            _lib.ptr(lse), _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl), _lib.c_int(S_pad), _lib.c_int(D),
-            _lib.c_float(scale), o_p, _lib.c_int(P), _lib.c_int(rank), _lib.ptr(_lib.status_word(dev)),
-            _lib.stream())
-        _lib.check(rc, "tt_attn_fwd_scatter")
+        o_h = lse = None
+        if heads > 0:
+            o_h = torch.empty(n_h, dtype=torch.bfloat16, device=dev)
+            lse = torch.empty((B, heads, S_pad), dtype=torch.float32, device=dev)
+            ld, bs = Hl * D, S_pad * Hl * D
+            rc = L.tt_attn_fwd_scatter(
+                _lib.ptr(qh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(kh), _lib.c_ll(ld), _lib.c_ll(bs),
+                _lib.ptr(vh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(o_h), _lib.c_ll(ld), _lib.c_ll(bs),
+                _lib.ptr(lse), _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl), _lib.c_int(heads), _lib.c_int(H),
+                _lib.c_int(S_pad), _lib.c_int(D), _lib.c_float(scale), o_p, _lib.c_int(P), _lib.c_int(rank),
+                _lib.ptr(_lib.status_word(dev)), _lib.stream())
+            _lib.check(rc, "tt_attn_fwd_scatter")
         fu.arena.barrier(fu.slot)
         if not fu._keep_for_backward:
             # nothing of this layer is read after its own consumers (already enqueued): the next layer may
@@ -167,43 +204,53 @@ class _FusedUlyssesFn(torch.autograd.Function):
             fu.slab.live.append((slab_mark, fu.slab.off))
         ctx.fu = fu
         ctx.meta = (B, S_l, H, D, scale, kv_lens)
-        ctx.save_for_backward(q_pre, k_pre, wq_f, wk_f, freqs, rstd_q, rstd_k, qh, kh, vh, o_h, lse)
+        ctx.save_for_backward(x, w_qkv, q_pre, k_pre, wq_f, wk_f, freqs, rstd_q, rstd_k, qh, kh, vh, o_h, lse)
         ctx.w_dtypes = (wq.dtype, wk.dtype)
+        ctx.bias_ref = b_qkv
         return o_s.view(rows, C)
 
     @staticmethod
     def backward(ctx, do):
+        from ..ops.gemm import gemm
+        from ..ops.linear import _bias_grad, _weight_grad
+
         fu: FusedUlysses = ctx.fu
-        q_pre, k_pre, wq_f, wk_f, freqs, rstd_q, rstd_k, qh, kh, vh, o_h, lse = ctx.saved_tensors
+        x, w_qkv, q_pre, k_pre, wq_f, wk_f, freqs, rstd_q, rstd_k, qh, kh, vh, o_h, lse = ctx.saved_tensors
         B, S_l, H, D, scale, kv_lens = ctx.meta
         P, rank = fu.world, fu.rank
-        C, Hl, S_pad, rows = H * D, H // P, S_l * P, B * S_l
+        C, S_pad, rows = H * D, S_l * P, B * S_l
+        Hl, heads = fu.head_slots(H)
         dev = do.device
         if do.stride(1) != 1:
             do = do.contiguous()
         n_h = B * S_pad * Hl * D
         do_h = fu.staging("do_h", n_h)
-        dq_s = fu.staging("dq_s", rows * C)
-        dk_s = fu.staging("dk_s", rows * C)
-        dv_s = fu.staging("dv_s", rows * C)
+        # dQ, dK, dV land side by side in one [rows, 3C] matrix: the projection's gradient GEMMs read it in place
+        dqkv_s = fu.staging("dqkv_s", rows * 3 * C)
         _scatter_rows(fu, do, None, None, None, rows, C, D, 0.0, do_h.c_ptrs(), S_l, S_pad)
         fu.arena.barrier(fu.slot)
         L = _lib.lib()
-        L.tt_attn_bwd_scratch_floats.restype = _lib.c_ll
-        scratch = torch.empty(L.tt_attn_bwd_scratch_floats(_lib.c_int(B), _lib.c_int(Hl), _lib.c_int(S_pad)),
-                              dtype=torch.float32, device=dev)
-        rc = L.tt_attn_bwd_scatter(
-            _lib.ptr(qh), _lib.ptr(kh), _lib.ptr(vh), _lib.ptr(o_h), _lib.ptr(do_h.tensor), _lib.ptr(lse),
-            _lib.ptr(scratch), dq_s.c_ptrs(), dk_s.c_ptrs(), dv_s.c_ptrs(), _lib.ptr(kv_lens), _lib.c_int(B),
-            _lib.c_int(Hl), _lib.c_int(S_pad), _lib.c_int(D), _lib.c_float(scale), _lib.c_int(P),
-            _lib.c_int(rank), _lib.ptr(_lib.status_word(dev)), _lib.stream())
-        _lib.check(rc, "tt_attn_bwd_scatter")
+        if heads > 0:
+            L.tt_attn_bwd_scratch_floats.restype = _lib.c_ll
+            scratch = torch.empty(L.tt_attn_bwd_scratch_floats(_lib.c_int(B), _lib.c_int(heads), _lib.c_int(S_pad)),
+                                  dtype=torch.float32, device=dev)
+            rc = L.tt_attn_bwd_scatter(
+                _lib.ptr(qh), _lib.ptr(kh), _lib.ptr(vh), _lib.ptr(o_h), _lib.ptr(do_h.tensor), _lib.ptr(lse),
+                _lib.ptr(scratch), dqkv_s.c_ptrs(0), dqkv_s.c_ptrs(C), dqkv_s.c_ptrs(2 * C), _lib.c_ll(3 * C),
+                _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl), _lib.c_int(heads), _lib.c_int(H), _lib.c_int(S_pad),
+                _lib.c_int(D), _lib.c_float(scale), _lib.c_int(P), _lib.c_int(rank),
+                _lib.ptr(_lib.status_word(dev)), _lib.stream())
+            _lib.check(rc, "tt_attn_bwd_scatter")
         fu.arena.barrier(fu.slot)
-        dq_pre, dwq = rmsrope_bwd_raw(dq_s.tensor[:rows * C].view(rows, C), q_pre, wq_f, freqs, rstd_q, D, False)
-        dk_pre, dwk = rmsrope_bwd_raw(dk_s.tensor[:rows * C].view(rows, C), k_pre, wk_f, freqs, rstd_k, D, False)
-        dv = dv_s.tensor[:rows * C].view(rows, C).clone()
+        dqkv = dqkv_s.tensor[:rows * 3 * C].view(rows, 3 * C)
+        # norm + rope backward in place on the q and k column blocks (each thread rewrites only what it has read)
+        _, dwq = rmsrope_bwd_raw(dqkv[:, 0:C], q_pre, wq_f, freqs, rstd_q, D, False, out=dqkv[:, 0:C])
+        _, dwk = rmsrope_bwd_raw(dqkv[:, C:2 * C], k_pre, wk_f, freqs, rstd_k, D, False, out=dqkv[:, C:2 * C])
+        dx = gemm(dqkv, w_qkv, b_mn=True) if ctx.needs_input_grad[1] else None
+        dw = _weight_grad(dqkv, x, w_qkv) if ctx.needs_input_grad[2] else None
+        db = _bias_grad(dqkv, ctx.bias_ref) if (ctx.bias_ref is not None and ctx.needs_input_grad[3]) else None
         # layers run backward in reverse order, so this layer's region is the top of the stack
         if fu.slab.live and fu.slab.live[-1][1] == fu.slab.off:
             fu.slab.release_to(fu.slab.live.pop()[0])
         wdq, wdk = ctx.w_dtypes
-        return (None, dq_pre, dk_pre, dv, dwq.to(wdq), dwk.to(wdk), None, None, None, None, None, None, None)
+        return (None, dx, dw, db, dwq.to(wdq), dwk.to(wdk), None, None, None, None, None, None, None)

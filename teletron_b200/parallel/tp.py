@@ -271,6 +271,17 @@ class TPContext:
         return x.narrow(0, self.rank * n, n)
 
 
+def _init_shard(out_features: int, in_features: int, dim: int, tp: "TPContext") -> torch.Tensor:
+    """This rank's slice along ``dim`` of a freshly initialised FULL [out, in] weight.  Every tensor-parallel rank
+    draws the same full matrix from the shared random stream (all ranks are seeded alike) and keeps its own
+    slice: the shards differ between ranks, the merged weight is distributed exactly like the unsharded layer
+    (fan-in of the full layer), and the random stream stays in step across ranks."""
+    full = torch.empty(out_features, in_features)
+    nn.init.kaiming_uniform_(full, a=math.sqrt(5))
+    n = full.shape[dim] // tp.size
+    return full.narrow(dim, tp.rank * n, n).clone()
+
+
 class ColumnParallelLinear(nn.Module):
     """Holds rows [rank*N/T, (rank+1)*N/T) of a [N, K] weight. Input: row-sharded [M/T, K]."""
 
@@ -278,9 +289,8 @@ class ColumnParallelLinear(nn.Module):
         super().__init__()
         assert out_features % tp.size == 0
         self.tp, self.in_features, self.out_features = tp, in_features, out_features
-        self.weight = nn.Parameter(torch.empty(out_features // tp.size, in_features))
+        self.weight = nn.Parameter(_init_shard(out_features, in_features, 0, tp))
         self.bias = nn.Parameter(torch.zeros(out_features // tp.size)) if bias else None
-        nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
         self.shard_dim = 0
 
     def forward(self, x_rows, act=None, gathered: bool = False):
@@ -298,9 +308,8 @@ class RowParallelLinear(nn.Module):
         super().__init__()
         assert in_features % tp.size == 0
         self.tp, self.in_features, self.out_features = tp, in_features, out_features
-        self.weight = nn.Parameter(torch.empty(out_features, in_features // tp.size))
+        self.weight = nn.Parameter(_init_shard(out_features, in_features, 1, tp))
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
-        nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
         self.shard_dim = 1
 
     def forward(self, x_cols):

@@ -77,7 +77,11 @@ _FLAGS = [
                                    "to initialise in host memory); the random stream then differs from a host-side init")),
     ("--use-distributed-optimizer", dict(action="store_true")),
     ("--use-zero2", dict(action="store_true", help="accepted; maps to the sharded optimizer")),
-    ("--overlap-grad-reduce", dict(action="store_true")),
+    ("--overlap-grad-reduce", dict(action="store_true", default=None,
+                                   help="start each gradient bucket's reduction during the last micro-batch's backward "
+                                        "(default: on for the peer-memory path, off for NCCL)")),
+    ("--no-overlap-grad-reduce", dict(action="store_false", dest="overlap_grad_reduce")),
+    ("--ddp-bucket-size", dict(type=int, default=40_000_000, help="elements per gradient bucket")),
     ("--overlap-param-gather", dict(action="store_true")),
     ("--no-delay-grad-reduce", dict(action="store_false", dest="delay_grad_reduce")),
     ("--delay-param-gather", dict(action="store_true")),

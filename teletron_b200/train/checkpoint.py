@@ -210,17 +210,22 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, strict: bool = 
             args.consumed_valid_samples = getattr(saved, "consumed_valid_samples", 0)
         if optimizer is not None:
             if not args.no_load_optim and "optimizer" in sd:
-                if getattr(optimizer, "sharded", False) and sd["optimizer"].get("sharded"):
+                opt_sd = sd["optimizer"]
+                if opt_sd.get("sharded"):        # the fp32 state lives beside the model file, in buffer order
                     full = torch.load(checkpoint_name(root, iteration, filename=DISTOPT_FILE),
                                       map_location="cpu", weights_only=False)
                     optimizer.scatter_full_state(full)
-                    optimizer.step_count = sd["optimizer"]["step"]
-                    optimizer.param_groups[0].update(sd["optimizer"]["param_groups"][0])
-                elif "master" in sd["optimizer"] and not getattr(optimizer, "sharded", False):
-                    optimizer.load_state_dict(sd["optimizer"])
+                elif "master" in opt_sd:
+                    # a replicated optimizer's regions, one after the other, are the full buffer as well: any
+                    # sharding of this run takes its shares from it
+                    full = {k: torch.cat([t.reshape(-1) for t in opt_sd[k]]) for k in ("master", "exp_avg", "exp_avg_sq")}
+                    full["layout"] = opt_sd.get("layout")
+                    optimizer.scatter_full_state(full)
                 else:
-                    raise RuntimeError("optimizer layout (sharded vs. replicated) differs from the checkpoint; "
+                    raise RuntimeError("the checkpoint's optimizer entry has no state this optimizer can read; "
                                        "use --no-load-optim")
+                optimizer.step_count = opt_sd["step"]
+                optimizer.param_groups[0].update(opt_sd["param_groups"][0])
             else:
                 optimizer.reload_model_params()
         if opt_param_scheduler is not None and not args.no_load_optim and "opt_param_scheduler" in sd:

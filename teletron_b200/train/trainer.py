@@ -193,13 +193,17 @@ class Trainer:
                     if a.fused_comm == "on":
                         raise
                     print(f"WARNING: fused tensor-parallel kernels unavailable ({e}); using NCCL collectives", flush=True)
-        self.buffer = ParamBuffer(inner, shard_world=world if a.use_distributed_optimizer else 1, arena=arena)
+        tp_names = tuple(tp_shard_dims(inner)) if a.tensor_model_parallel_size > 1 else None
+        self.buffer = ParamBuffer(inner, shard_world=world if a.use_distributed_optimizer else 1, arena=arena,
+                                  bucket_size=getattr(a, "ddp_bucket_size", None), tp_sharded_names=tp_names)
+        # the peer-memory path overlaps each bucket's reduction with backward by default; NCCL on request
+        overlap = world > 1 and (a.overlap_grad_reduce or (arena is not None and a.overlap_grad_reduce is not False))
         self.optimizer = DistributedOptimizer(
             self.buffer, group if world > 1 else None, lr=a.lr, betas=(a.adam_beta1, a.adam_beta2),
             eps=a.adam_eps, weight_decay=a.weight_decay, clip_grad=a.clip_grad,
             sharded=a.use_distributed_optimizer, grad_scale=1.0 / max(a.data_parallel_size, 1),
             tp_group=mpu.get_tensor_model_parallel_group() if a.tensor_model_parallel_size > 1 else None,
-            tp_sharded_names=tuple(tp_shard_dims(inner)) if a.tensor_model_parallel_size > 1 else ())
+            tp_sharded_names=tp_names or (), overlap=overlap)
         self.optimizer.log_num_zeros = bool(getattr(a, "log_num_zeros_in_grad", False))
         self.opt_param_scheduler = scheduler_from_args(a, self.optimizer) if (a.train_iters or a.train_samples) else None
         if a.load or a.pretrained_checkpoint:
@@ -268,7 +272,9 @@ class Trainer:
         fine = tm is not None and a.timing_log_level >= 2
         if tm is not None:
             tm.start("forward-backward")
-        for _ in range(n_mb):
+        for mb in range(n_mb):
+            if mb == n_mb - 1:
+                self.optimizer.begin_last_microbatch()     # bucket reductions may start during this backward
             if fine:
                 tm.start("forward-compute")
             output, loss_func = forward_step_func(it, self.model)

@@ -54,7 +54,10 @@ def make_forward_step(shift: float = 5.0, train_timesteps: int = 1000, local_sha
             noise = torch.randn_like(latents)
         tid = torch.randint(0, sched.num_train_timesteps, (1,), generator=timestep_generator)
         trange = batch.get("timestep_range") if isinstance(batch, dict) else None
-        if trange is not None:  # timestep-expert replicas train on a sub-range of the schedule
+        fixed_tid = batch.get("timestep_id") if isinstance(batch, dict) else None
+        if fixed_tid is not None:  # the sample names its own timestep (layout-independent runs)
+            tid = fixed_tid.reshape(-1)[:1].to("cpu", torch.long)
+        elif trange is not None:  # timestep-expert replicas train on a sub-range of the schedule
             lo, hi = int(trange[0] * sched.num_train_timesteps), int(trange[1] * sched.num_train_timesteps)
             tid = torch.randint(lo, max(hi, lo + 1), (1,), generator=timestep_generator)
         tid_dev = tid.to(device)

@@ -223,3 +223,47 @@ def test_hunyuan_tp2_checkpoint_resumes_exactly(tmp_path):
     assert [o[:2] for o in resumed] == [(1, 2), (1, 2)]
     for r in range(2):
         assert torch.allclose(resumed[r][2], full[r][2], atol=1e-6)       # each TP rank's shard
+
+
+def _tp_norm_worker(rank, world):
+    from teletron_b200.parallel.tp import tp_shard_dims
+    from teletron_b200.train import Trainer, make_hunyuan_forward_step
+
+    t = Trainer(_hy_train_args(world, "--tensor-model-parallel-size 2 --clip-grad 0.05"))
+    inner = t.model.module if hasattr(t.model, "module") else t.model
+    sharded = set(tp_shard_dims(inner))
+    gen = torch.Generator().manual_seed(4)
+    fwd = make_hunyuan_forward_step(timestep_generator=gen)
+    norms = []
+    for _ in range(3):
+        _, _, gnorm, _ = t.train_step(fwd)
+        norms.append(float(gnorm))
+    sd = {k: v.detach().float().clone() for k, v in inner.state_dict().items()}
+    return norms, {k: v for k, v in sd.items() if k not in sharded}, {k: v for k, v in sd.items() if k in sharded}
+
+
+def test_tensor_parallel_ranks_share_one_gradient_norm_and_keep_replicated_parameters_identical():
+    """Sharded layers start from different slices of one full weight on each tensor-parallel rank, the squared norm
+    of sharded parameters is summed over the group and that of replicated ones counted once: every rank clips with
+    the same coefficient, so replicated parameters stay bit-identical through clipped steps."""
+    (n0, rep0, sh0), (n1, rep1, sh1) = run_distributed(_tp_norm_worker, 2)
+    assert n0 == n1 and all(x > 0.05 for x in n0)                        # clipping was active on every step
+    assert rep0.keys() == rep1.keys() and len(rep0) > 10
+    for k in rep0:
+        assert torch.equal(rep0[k], rep1[k]), k
+    differing = [k for k in sh0 if k.endswith("weight") and not torch.equal(sh0[k], sh1[k])]
+    assert len(differing) == len([k for k in sh0 if k.endswith("weight")])   # no duplicated weight blocks
+
+
+def test_sharded_layers_initialise_like_the_full_layer():
+    from teletron_b200.parallel.tp import ColumnParallelLinear, RowParallelLinear, TPContext
+
+    for cls, dim in ((ColumnParallelLinear, 0), (RowParallelLinear, 1)):
+        shards = []
+        for r in range(2):
+            torch.manual_seed(3)
+            shards.append(cls(64, 96, TPContext(None, 2, r), bias=False).weight.detach())
+        torch.manual_seed(3)
+        full = torch.nn.Linear(64, 96, bias=False).weight.detach()
+        assert torch.equal(torch.cat(shards, dim=dim), full)             # same stream, full-layer fan-in
+        assert not torch.equal(shards[0], shards[1])

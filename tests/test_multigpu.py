@@ -8,6 +8,8 @@ pytestmark = pytest.mark.gpu
 from dist_utils import run_distributed
 
 needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+needs4 = pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+needs8 = pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
 
 
 def rel(a, b):
@@ -15,7 +17,7 @@ def rel(a, b):
     return (0.5 * (a - b).norm() / (a.norm() + b.norm() + 1e-30)).item()
 
 
-def _opt_worker(rank, world, fused, clip):
+def _opt_worker(rank, world, fused, clip, overlap=False):
     import torch.distributed as dist
 
     from teletron_b200.dist import SymmetricArena
@@ -23,38 +25,67 @@ def _opt_worker(rank, world, fused, clip):
     from teletron_b200.parallel.ddp import DistributedOptimizer, ParamBuffer
 
     torch.manual_seed(0)
-    model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.Linear(512, 264)).cuda().to(torch.bfloat16)
+    model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.Linear(512, 264),
+                                torch.nn.Linear(264, 520)).cuda().to(torch.bfloat16)
     arena = SymmetricArena(dist.group.WORLD) if fused else None
-    buf = ParamBuffer(model, shard_world=world, arena=arena)
+    buf = ParamBuffer(model, shard_world=world, arena=arena, bucket_size=50_000)   # several buckets, ragged last one
+    assert len(buf.buckets) >= 6
     opt = DistributedOptimizer(buf, dist.group.WORLD, lr=1e-2, weight_decay=0.1, clip_grad=clip, sharded=True,
-                               grad_scale=1.0 / world)
+                               grad_scale=1.0 / world, overlap=overlap)
     assert opt.fused == fused
     norms = []
     for step in range(3):
         opt.zero_grad()
         g = torch.Generator(device="cuda").manual_seed(100 * step + rank)
         buf.grads.copy_(torch.randn(buf.numel, device="cuda", generator=g))
+        if overlap:      # what the gradient-ready hooks of a backward pass do, in backward order
+            opt.begin_last_microbatch()
+            for name, p in reversed(buf.named):
+                p.grad_ready()
+            assert opt.fired_in_backward == len(buf.buckets)
         opt.reduce_gradients()
         _, n, _ = opt.step()
         norms.append(float(n))
     torch.cuda.synchronize()
     _lib.check_status()
-    return buf.params.float().cpu(), torch.cat([m.cpu() for m in opt.master]), norms
+    full = opt.gather_full_state()
+    return buf.params.float().cpu(), (full["master"] if full is not None else None), norms
+
+
+def _check_fused_optimizer(world, clip):
+    ref = run_distributed(_opt_worker, world, False, clip, backend="nccl")
+    got = run_distributed(_opt_worker, world, True, clip, backend="nccl")
+    over = run_distributed(_opt_worker, world, True, clip, True, backend="nccl")
+    for r in range(world):
+        assert torch.equal(got[r][0], got[0][0])                      # replicas agree bit for bit
+        assert rel(got[r][0], ref[r][0]) < 1e-3                          # bf16 params
+        assert all(abs(a - b) < 1e-3 * abs(b) for a, b in zip(got[r][2], ref[r][2]))
+        # reductions started bucket by bucket on the side stream: not one bit differs
+        assert torch.equal(over[r][0], got[r][0]) and over[r][2] == got[r][2]
+    assert rel(got[0][1], ref[0][1]) < 1e-5                              # fp32 master weights, whole buffer
+    assert torch.equal(over[0][1], got[0][1])
 
 
 @needs2
 @pytest.mark.parametrize("clip", [0.0, 1.0])
 def test_fused_dp_optimizer_matches_nccl(clip):
-    ref = run_distributed(_opt_worker, 2, False, clip, backend="nccl")
-    got = run_distributed(_opt_worker, 2, True, clip, backend="nccl")
-    for r in range(2):
-        assert torch.equal(got[r][0], got[0][0])                      # replicas agree bit for bit
-        assert rel(got[r][0], ref[r][0]) < 1e-3                          # bf16 params
-        assert rel(got[r][1], ref[r][1]) < 1e-5                          # fp32 master shard
-        assert all(abs(a - b) < 1e-3 * abs(b) for a, b in zip(got[r][2], ref[r][2]))
+    _check_fused_optimizer(2, clip)
 
 
-def _cp_worker(rank, world, fused=False, layers=2, recompute_layers=0):
+@needs8
+@pytest.mark.parametrize("clip", [0.0, 1.0])
+def test_fused_dp_optimizer_matches_nccl_with_eight_peers(clip):
+    _check_fused_optimizer(8, clip)
+
+
+# shapes for the context-parallel tests: (hidden, heads, latent f, h, w) -> f * h/2 * w/2 tokens
+SMALL = (256, 2, 3, 16, 20)            # 240 tokens: below the CTA-pair GEMM's row minimum (copy-kernel exchange of V)
+RAGGED = (512, 4, 3, 34, 42)           # 1,071 tokens: not a multiple of 2, 4 or 8 -> padded tail masked by key length
+UNEVEN = (384, 3, 3, 34, 42)           # 3 heads: do not divide by 2 or 4
+WAN13_HEADS = (1536, 12, 3, 34, 42)    # the 1.3B model's 12 heads (CP = 8: two head slots per rank, two ranks idle)
+
+
+def _cp_worker(rank, world, fused=False, layers=2, recompute_layers=0, shape=SMALL):
     from teletron_b200 import ops
     from teletron_b200.models import WanModel, wan_config
     from teletron_b200.ops import _lib
@@ -71,11 +102,12 @@ def _cp_worker(rank, world, fused=False, layers=2, recompute_layers=0):
     torch.manual_seed(0)
     extra = dict(recompute_granularity="full", recompute_method="block",
                  recompute_num_layers=recompute_layers) if recompute_layers else {}
-    cfg = wan_config("wan-tiny", dim=256, num_heads=2, ffn_dim=512, text_dim=64, freq_dim=64, num_layers=layers,
+    dim, heads, lf, lh, lw = shape
+    cfg = wan_config("wan-tiny", dim=dim, num_heads=heads, ffn_dim=512, text_dim=64, freq_dim=64, num_layers=layers,
                      **extra)
     model = WanModel(cfg, cp).cuda().to(torch.bfloat16)
     g = torch.Generator().manual_seed(5)
-    x = torch.randn(1, 16, 3, 16, 20, generator=g).cuda().bfloat16()   # 3*8*10 = 240 tokens
+    x = torch.randn(1, 16, lf, lh, lw, generator=g).cuda().bfloat16()
     ctx = torch.randn(1, 40, 64, generator=g).cuda().bfloat16()
     t = torch.tensor([400.0]).cuda()
     for _ in range(2 if fused else 1):  # twice: the slab and staging buffers are recycled
@@ -90,14 +122,15 @@ def _cp_worker(rank, world, fused=False, layers=2, recompute_layers=0):
     return out.float().cpu(), {k: v.cpu() for k, v in grads.items()}
 
 
-def _single_gpu_reference(layers=2):
+def _single_gpu_reference(layers=2, shape=SMALL):
     from teletron_b200.models import WanModel, wan_config
 
     torch.manual_seed(0)
-    cfg = wan_config("wan-tiny", dim=256, num_heads=2, ffn_dim=512, text_dim=64, freq_dim=64, num_layers=layers)
+    dim, heads, lf, lh, lw = shape
+    cfg = wan_config("wan-tiny", dim=dim, num_heads=heads, ffn_dim=512, text_dim=64, freq_dim=64, num_layers=layers)
     model = WanModel(cfg).cuda().to(torch.bfloat16)
     g = torch.Generator().manual_seed(5)
-    x = torch.randn(1, 16, 3, 16, 20, generator=g).cuda().bfloat16()
+    x = torch.randn(1, 16, lf, lh, lw, generator=g).cuda().bfloat16()
     ctx = torch.randn(1, 40, 64, generator=g).cuda().bfloat16()
     t = torch.tensor([400.0]).cuda()
     out = model(x, t, ctx)
@@ -114,6 +147,96 @@ def test_ulysses_cp2_matches_single_gpu(fused):
         assert rel(out, ref_out) < 1e-3          # same threshold as the reference's model test
         bad = [(n, rel(grads[n], ref_g[n])) for n in ref_g if ref_g[n].norm() > 2e-4 and rel(grads[n], ref_g[n]) > 2e-2]
         assert not bad, bad
+
+
+def _check_cp(world, shape, fused=True):
+    ref_out, ref_g = _single_gpu_reference(shape=shape)
+    outs = run_distributed(_cp_worker, world, fused, 2, 0, shape, backend="nccl")
+    for out, grads in outs:
+        assert rel(out, ref_out) < 1e-3
+        assert (out - ref_out).abs().max() < 0.05 * ref_out.abs().max()
+        bad = [(n, rel(grads[n], ref_g[n])) for n in ref_g if ref_g[n].norm() > 2e-4 and rel(grads[n], ref_g[n]) > 2e-2]
+        assert not bad, bad
+
+
+@needs2
+@pytest.mark.parametrize("shape", [RAGGED, UNEVEN], ids=["ragged-qkv-epilogue", "three-heads"])
+def test_fused_ulysses_cp2_ragged_tokens_and_uneven_heads(shape):
+    """RAGGED: 536 rows per rank, so the q/k/v projection runs as the GEMM whose epilogue stores V into the head
+    owner and hands the row statistics to the norm kernel; 1,071 tokens leave one padded key that the attention
+    kernel masks.  UNEVEN: three heads over two ranks (two head slots each, the second rank owns one head)."""
+    _check_cp(2, shape)
+
+
+@needs4
+@pytest.mark.parametrize("shape", [RAGGED, UNEVEN], ids=["ragged", "three-heads-one-rank-idle"])
+def test_fused_ulysses_cp4(shape):
+    _check_cp(4, shape)
+
+
+@needs8
+@pytest.mark.parametrize("shape", [WAN13_HEADS], ids=["twelve-heads"])
+def test_fused_ulysses_cp8(shape):
+    _check_cp(8, shape)
+
+
+def _dp_cp_trainer_worker(rank, world, cp, fused):
+    """Two optimizer steps of a small Wan DiT through the Trainer on a fixed global batch of 4 samples (data, noise
+    and timestep are functions of the sample index), in any DP x CP layout."""
+    import os
+
+    from teletron_b200.data import SyntheticLatentDataset
+    from teletron_b200.ops import _lib
+    from teletron_b200.parallel import state as mpu
+    from teletron_b200.train import Trainer, make_forward_step, parse_args
+
+    os.environ["WORLD_SIZE"], os.environ["RANK"], os.environ["LOCAL_RANK"] = str(world), str(rank), str(rank)
+    argv = (f"--model ParallelWanModel --model-preset wan-tiny --hidden-size 512 --num-attention-heads 4 "
+            f"--ffn-hidden-size 1024 --num-layers 2 --bf16 --train-iters 100 --micro-batch-size 1 --global-batch-size 4 "
+            f"--lr 1e-3 --num-frames 9 --video-resolution 272 336 --log-interval 1000 --clip-grad 1.0 --seed 5 "
+            f"--synthetic-latents --context-parallel-size {cp} --fused-comm {'on' if fused else 'off'} "
+            f"--ddp-bucket-size 300000" + (" --use-distributed-optimizer" if world > 1 else "")).split()
+    a = parse_args(argv=argv)
+    t = Trainer(a, build_data=False)
+    ds = SyntheticLatentDataset(9, 272, 336, text_len=32, text_dim=64, seed=7, fixed_noise=True)   # 3*17*21 = 1,071 tokens
+    d = mpu.get_data_parallel_rank() if world > 1 else 0
+    n_mb = a.num_micro_batches
+    pool = [{k: v.unsqueeze(0).cuda() for k, v in ds[i].items()} for i in range(d * n_mb, (d + 1) * n_mb)]
+    fwd = make_forward_step()
+    losses, norms = [], []
+    for _ in range(2):
+        ld, _, gn, _ = t.train_step(fwd, iter(pool))
+        losses.append(float(ld["loss"]))
+        norms.append(float(gn))
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return losses, norms, t.buffer.params[:200000].float().cpu(), bool(t.optimizer.overlap), t.optimizer.fired_in_backward
+
+
+def _check_trainer_layout(world, cp):
+    (l1, n1, p1, _, _), = run_distributed(_dp_cp_trainer_worker, 1, 1, False, backend="nccl")
+    outs = run_distributed(_dp_cp_trainer_worker, world, cp, True, backend="nccl")
+    for losses, norms, params, overlap, fired in outs:
+        assert overlap and fired > 0                       # bucket reductions started from the backward hooks
+        assert all(abs(a - b) < 2e-3 * abs(b) for a, b in zip(losses, l1)), (losses, l1)
+        assert all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(norms, n1)), (norms, n1)
+        assert torch.equal(params, outs[0][2])
+        assert rel(params, p1) < 2e-3
+
+
+@needs2
+def test_trainer_cp2_fused_matches_one_gpu():
+    _check_trainer_layout(2, 2)
+
+
+@needs4
+def test_trainer_dp2_cp2_fused_matches_one_gpu():
+    _check_trainer_layout(4, 2)
+
+
+@needs8
+def test_trainer_dp2_cp4_fused_matches_one_gpu():
+    _check_trainer_layout(8, 4)
 
 
 @needs2

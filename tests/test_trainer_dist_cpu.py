@@ -285,3 +285,67 @@ def test_sigterm_to_the_whole_job_saves_and_leaves_with_the_encoder_rank(tmp_pat
     outs = run_distributed(_sigterm_job_worker, 2, str(tmp_path), timeout=120)
     assert outs == [2, "encoder-rank-done"]
     assert read_tracker(str(tmp_path)) == (2, False)
+
+
+def _overlap_worker(rank, world, overlap, sharded):
+    from teletron_b200.train import Trainer, make_forward_step
+
+    extra = ("--synthetic-latents --global-batch-size 4 --ddp-bucket-size 20000 "
+             + ("--use-distributed-optimizer " if sharded else "")
+             + ("--overlap-grad-reduce" if overlap else "--no-overlap-grad-reduce"))
+    t = Trainer(_args(world, extra))
+    assert t.optimizer.overlap == overlap and len(t.buffer.buckets) > 8
+    gen = torch.Generator().manual_seed(9)
+    norms, fired = [], []
+    for _ in range(2):
+        _, _, gnorm, _ = t.train_step(make_forward_step(timestep_generator=gen))
+        norms.append(float(gnorm))
+        fired.append(t.optimizer.fired_in_backward)
+    return norms, fired, t.buffer.params.clone()
+
+
+def test_bucket_reductions_started_during_backward_change_no_bit():
+    """--overlap-grad-reduce starts most buckets' reductions from the gradient-ready hooks of the last micro-batch;
+    parameters and gradient norm are bit-identical to the run that reduces after backward (plain and sharded)."""
+    for sharded in (False, True):
+        plain = run_distributed(_overlap_worker, 2, False, sharded)
+        over = run_distributed(_overlap_worker, 2, True, sharded)
+        assert plain[0][1] == [0, 0] and min(over[0][1]) > len(over[0][1])      # most buckets fired from the hooks
+        for r in range(2):
+            assert over[r][0] == plain[r][0]
+            assert torch.equal(over[r][2], plain[r][2]) and torch.equal(over[r][2], over[0][2])
+
+
+def _reshard_worker(rank, world, root, mode):
+    from teletron_b200.train import Trainer, make_forward_step
+
+    a = _args(world, f"--synthetic-latents --global-batch-size 2 --use-distributed-optimizer --ddp-bucket-size "
+                     f"{20000 if mode == 'save' else 33000} --save {root} --load {root} --train-iters 3")
+    t = Trainer(a)
+    if mode == "save":
+        gen = torch.Generator().manual_seed(9)
+        for _ in range(2):
+            t.train_step(make_forward_step(timestep_generator=gen))
+        a.iteration = 2
+        t.save(2)
+        full = t.optimizer.gather_full_state()
+        return None if full is None else {k: full[k] for k in ("exp_avg", "exp_avg_sq")} | {"index": full["layout"]["index"]}
+    assert a.iteration == 2
+    full = t.optimizer.gather_full_state()
+    return None if full is None else {k: full[k] for k in ("exp_avg", "exp_avg_sq")} | {"index": full["layout"]["index"]}
+
+
+def test_sharded_optimizer_state_moves_to_another_dp_size_and_bucket_size(tmp_path):
+    """distrib_optim.pt stores the buffer layout, so a run with another data-parallel size (other padding) and
+    another bucket size places every parameter's moments where its own layout wants them."""
+    saved = run_distributed(_reshard_worker, 2, str(tmp_path), "save")[0]
+    loaded = run_distributed(_reshard_worker, 1, str(tmp_path), "load")[0]
+    assert saved["index"].keys() == loaded["index"].keys()
+    moved = 0
+    for k, (o, n) in saved["index"].items():
+        lo, ln = loaded["index"][k]
+        assert ln == n
+        moved += int(lo != o)
+        for key in ("exp_avg", "exp_avg_sq"):
+            assert torch.equal(saved[key][o:o + n], loaded[key][lo:lo + n]), (k, key)
+    assert float(saved["exp_avg_sq"].abs().sum()) > 0
