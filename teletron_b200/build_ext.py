@@ -67,7 +67,6 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     obj_dir.mkdir(exist_ok=True)
     nvcc = find_nvcc()
     flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else [])
-    flags += os.environ.get("TT_NVCC_EXTRA", "").split()  # e.g. -DTT_WAIT_BUDGET_CLOCKS=... for experiments
     hdr_digest = _digest(_headers(), " ".join(flags))
     srcs = _sources()
     if not srcs:

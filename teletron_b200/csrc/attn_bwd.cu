@@ -21,9 +21,6 @@ constexpr int NTHREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 elementwise
 constexpr int BIG = 128 * 128 * 2;     // 128 x 128 bf16 tile (two 64-wide halves of 16 KB)
 constexpr int BIG_HALF = 128 * 128;    // 128 rows x 128 B
 constexpr float LOG2E = 1.4426950408889634f;
-#ifndef TT_BWD_POLY_EVERY
-#define TT_BWD_POLY_EVERY 0  // n > 0: every n-th exponential of phase 1 on the FMA pipe (exp2_fma); 2, 3 and 4 measured slower (22.4 / 21.2 / 20.8 ms against 19.6 at 32,760 tokens), as did 16 elementwise warps (20.1 ms)
-#endif
 constexpr uint32_t HI_K = umma_desc_hi(1024);  // both operand layouts here step 1024 bytes between 8-row groups
 
 struct BwdParams {
@@ -277,10 +274,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
         for (int e = 0; e < 32; e += 4) {
           const float4 a4 = *reinterpret_cast<const float4*>(ls + e);
-          pr[e] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s0[e]), p.scale_log2, -a4.x), e);
-          pr[e + 1] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s0[e + 1]), p.scale_log2, -a4.y), e + 1);
-          pr[e + 2] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s0[e + 2]), p.scale_log2, -a4.z), e + 2);
-          pr[e + 3] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s0[e + 3]), p.scale_log2, -a4.w), e + 3);
+          pr[e] = fast_exp2(fmaf(__uint_as_float(s0[e]), p.scale_log2, -a4.x));
+          pr[e + 1] = fast_exp2(fmaf(__uint_as_float(s0[e + 1]), p.scale_log2, -a4.y));
+          pr[e + 2] = fast_exp2(fmaf(__uint_as_float(s0[e + 2]), p.scale_log2, -a4.z));
+          pr[e + 3] = fast_exp2(fmaf(__uint_as_float(s0[e + 3]), p.scale_log2, -a4.w));
         }
 #pragma unroll
         for (int e = 0; e < 16; ++e) pk[e] = pack_bf16(pr[2 * e], pr[2 * e + 1]);
@@ -288,10 +285,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
         for (int e = 0; e < 32; e += 4) {
           const float4 a4 = *reinterpret_cast<const float4*>(ls + 32 + e);
-          pr[32 + e] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s1[e]), p.scale_log2, -a4.x), e);
-          pr[32 + e + 1] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s1[e + 1]), p.scale_log2, -a4.y), e + 1);
-          pr[32 + e + 2] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s1[e + 2]), p.scale_log2, -a4.z), e + 2);
-          pr[32 + e + 3] = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s1[e + 3]), p.scale_log2, -a4.w), e + 3);
+          pr[32 + e] = fast_exp2(fmaf(__uint_as_float(s1[e]), p.scale_log2, -a4.x));
+          pr[32 + e + 1] = fast_exp2(fmaf(__uint_as_float(s1[e + 1]), p.scale_log2, -a4.y));
+          pr[32 + e + 2] = fast_exp2(fmaf(__uint_as_float(s1[e + 2]), p.scale_log2, -a4.z));
+          pr[32 + e + 3] = fast_exp2(fmaf(__uint_as_float(s1[e + 3]), p.scale_log2, -a4.w));
         }
 #pragma unroll
         for (int e = 0; e < 16; ++e) pk[e] = pack_bf16(pr[32 + 2 * e], pr[32 + 2 * e + 1]);
@@ -587,12 +584,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          const float pe = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s0[e]), p.scale_log2, -lse2), e);
+          const float pe = fast_exp2(fmaf(__uint_as_float(s0[e]), p.scale_log2, -lse2));
           pr[e] = (e < valid) ? pe : 0.f;
         }
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          const float pe = exp2_mixed<TT_BWD_POLY_EVERY>(fmaf(__uint_as_float(s1[e]), p.scale_log2, -lse2), e);
+          const float pe = fast_exp2(fmaf(__uint_as_float(s1[e]), p.scale_log2, -lse2));
           pr[32 + e] = (32 + e < valid) ? pe : 0.f;
         }
       }
@@ -655,282 +652,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, 512);
-}
-
-// ===================================================================== dQ on CTA pairs
-// The same algorithm as attn_bwd_dq_kernel with tcgen05.mma.cta_group::2: a cluster of two CTAs owns 256 queries
-// (128 tensor-memory lanes each), the leader's thread issues 256 x 128 x 16 MMAs for both, so one round of waits and
-// commits serves twice the work.  B operands are split between the CTAs' shared memory: for S = Q K^T and
-// dP = dO V^T along the keys (64 key rows each), for dQ += dS K along the head dimension (all 128 keys x 64 columns
-// each); a CTA therefore loads two different 16 KB pieces of the K tile and one of V.  TMA completions of both CTAs
-// count on the leader's barriers, accumulator-ready / stage-free signals reach both CTAs through tcgen05.commit with
-// a CTA mask, and the elementwise warps of both arrive on the leader's ds_full.
-constexpr int C_KST = 3;                            // K stages (two 16 KB pieces each)
-constexpr int C_VST = 3;                            // V stages (16 KB)
-constexpr int HALF64 = 64 * 128;                    // 64 rows x 128 B
-constexpr int C_SM_Q = 0;
-constexpr int C_SM_DO = C_SM_Q + BIG;
-constexpr int C_SM_K = C_SM_DO + BIG;               // per stage: [keys half: 2 x HALF64][d half: BIG_HALF]
-constexpr int C_SM_V = C_SM_K + C_KST * BIG;
-constexpr int C_SM_BAR = C_SM_V + C_VST * BIG_HALF;
-constexpr int C_SMEM = C_SM_BAR + 256;
-
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
-attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmK64, const __grid_constant__ CUtensorMap tmV64,
-                    const __grid_constant__ CUtensorMap tmdO, const BwdParams p) {
-  extern __shared__ __align__(1024) uint8_t smem[];
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C_SM_BAR);
-  uint64_t* q_full = bars;                 // leader: both CTAs' Q / dO
-  uint64_t* k_full = bars + 1;             // leader, C_KST
-  uint64_t* k_empty = k_full + C_KST;      // both, C_KST
-  uint64_t* v_full = k_empty + C_KST;      // leader, C_VST
-  uint64_t* v_empty = v_full + C_VST;      // both, C_VST
-  uint64_t* s_full = v_empty + C_VST;      // both, 2
-  uint64_t* dp_full = s_full + 2;          // both
-  uint64_t* ds_full = dp_full + 1;         // leader: 16 arrivals (8 warps of each CTA)
-  uint64_t* done_bar = ds_full + 1;        // both
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
-  volatile uint32_t* abort_flag = tmem_slot + 1;
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const uint32_t cta = cluster_ctarank();
-  const int q0 = blockIdx.x * 128;
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
-  int kv_len = p.Skv;
-  if (p.kv_lens) kv_len = min(max(p.kv_lens[b], 1), p.Skv);
-  const int n_it = (kv_len + 127) / 128;
-
-  if ((smem_u32(smem) & 1023u) != 0) {
-    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0u, TT_ST_BAD_SMEM_ALIGN);
-    return;
-  }
-  if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int i = 0; i < C_KST; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
-    for (int i = 0; i < C_VST; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
-    mbar_init(&s_full[0], 1);
-    mbar_init(&s_full[1], 1);
-    mbar_init(dp_full, 1);
-    mbar_init(ds_full, 16);
-    mbar_init(done_bar, 1);
-    *abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 0 && lane == 0) {
-    tma_prefetch_desc(&tmQ);
-    tma_prefetch_desc(&tmK);
-    tma_prefetch_desc(&tmK64);
-    tma_prefetch_desc(&tmV64);
-    tma_prefetch_desc(&tmdO);
-  }
-  if (warp == 1) {
-    tmem_alloc2(tmem_slot, 512);
-    tmem_relinquish2();
-  }
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync_all();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      // every copy of either CTA counts on the leader's barrier; only the leader posts the expected bytes
-      const uint32_t qf = map_to_cta(smem_u32(q_full), 0);
-      if (cta == 0) mbar_expect_tx(q_full, 2 * 2 * BIG);
-      for (int hf = 0; hf < 2; ++hf) {
-        tma2_load_3d(smem + C_SM_Q + hf * BIG_HALF, &tmQ, qf, h * 128 + hf * 64, q0, b);
-        tma2_load_3d(smem + C_SM_DO + hf * BIG_HALF, &tmdO, qf, h * 128 + hf * 64, q0, b);
-      }
-      for (int j = 0; j < n_it; ++j) {
-        const int ks_ = j % C_KST, vs_ = j % C_VST;
-        if (!mbar_wait(&k_empty[ks_], ((j / C_KST) & 1) ^ 1, abort_flag, p.status, TT_ST_TIMEOUT_PRODUCER)) break;
-        if (cta == 0) mbar_expect_tx(&k_full[ks_], 2 * BIG);
-        const uint32_t kf = map_to_cta(smem_u32(&k_full[ks_]), 0);
-        uint8_t* kst = smem + C_SM_K + ks_ * BIG;
-        // this CTA's 64 key rows (all 128 columns) for S, and all 128 key rows x this CTA's 64 columns for dQ
-        for (int hf = 0; hf < 2; ++hf)
-          tma2_load_3d(kst + hf * HALF64, &tmK64, kf, h * 128 + hf * 64, j * 128 + (int)cta * 64, b);
-        tma2_load_3d(kst + 2 * HALF64, &tmK, kf, h * 128 + (int)cta * 64, j * 128, b);
-        if (!mbar_wait(&v_empty[vs_], ((j / C_VST) & 1) ^ 1, abort_flag, p.status, TT_ST_TIMEOUT_PRODUCER + 1)) break;
-        if (cta == 0) mbar_expect_tx(&v_full[vs_], 2 * BIG_HALF);
-        const uint32_t vf = map_to_cta(smem_u32(&v_full[vs_]), 0);
-        for (int hf = 0; hf < 2; ++hf)
-          tma2_load_3d(smem + C_SM_V + vs_ * BIG_HALF + hf * HALF64, &tmV64, vf, h * 128 + hf * 64,
-                       j * 128 + (int)cta * 64, b);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0 && cta == 0) {
-      constexpr uint32_t idesc_s = umma_idesc(256, 128, 0, 0);
-      constexpr uint32_t idesc_o = umma_idesc(256, 128, 0, 1);
-      const uint32_t tm = tmem_base;
-      const uint32_t q_lo = umma_desc_lo(smem_u32(smem + C_SM_Q), 16);
-      const uint32_t do_lo = umma_desc_lo(smem_u32(smem + C_SM_DO), 16);
-      const uint32_t k_base = smem_u32(smem + C_SM_K);
-      const uint32_t v_base = smem_u32(smem + C_SM_V);
-      auto mma_s = [&](uint32_t k_st, uint32_t buf) {
-        const uint32_t kb = umma_desc_lo(k_base + k_st * BIG, 16);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t offA = ((ks >> 2) * BIG_HALF + (ks & 3) * 32) >> 4;
-          const uint32_t offB = ((ks >> 2) * HALF64 + (ks & 3) * 32) >> 4;
-          umma2_ss_lo<HI_K, HI_K>(tm + B_TM_S + buf * 128, q_lo + offA, kb + offB, idesc_s, ks != 0);
-        }
-        tc_commit2(&s_full[buf], 3);
-      };
-      auto mma_dp = [&](uint32_t v_st) {
-        const uint32_t vb = umma_desc_lo(v_base + v_st * BIG_HALF, 16);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t offA = ((ks >> 2) * BIG_HALF + (ks & 3) * 32) >> 4;
-          const uint32_t offB = ((ks >> 2) * HALF64 + (ks & 3) * 32) >> 4;
-          umma2_ss_lo<HI_K, HI_K>(tm + B_TM_DP, do_lo + offA, vb + offB, idesc_s, ks != 0);
-        }
-        tc_commit2(dp_full, 3);
-        tc_commit2(&v_empty[v_st], 3);
-      };
-      auto mma_dq = [&](uint32_t k_st, uint32_t acc0) {
-        const uint32_t kd = umma_desc_lo(k_base + k_st * BIG + 2 * HALF64, BIG_HALF);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma2_ts_lo<HI_K>(tm + B_TM_DQ, tm + B_TM_DP + packed_kstep_col(ks), kd + ks * (2048 >> 4), idesc_o,
-                            ks != 0 ? 1u : acc0);
-        tc_commit2(&k_empty[k_st], 3);
-      };
-      auto wait1 = [&](uint64_t* bar, uint32_t parity, unsigned code) -> bool {
-        return mbar_wait(bar, parity, abort_flag, p.status, code);
-      };
-      uint32_t ks_ = 0, kph = 0, vs_ = 0, vph = 0, kq = 0, eph = 0, sbuf = 0;
-      bool ok = wait1(q_full, 0, TT_ST_TIMEOUT_MMA + 1);
-      if (ok) ok = wait1(&k_full[0], 0, TT_ST_TIMEOUT_MMA + 2);
-      if (ok) ok = wait1(&v_full[0], 0, TT_ST_TIMEOUT_MMA + 3);
-      if (ok && n_it > 1) ok = wait1(&k_full[1], 0, TT_ST_TIMEOUT_MMA + 2);
-      if (ok) {
-        tc_fence_after();
-        mma_s(0, 0);
-        mma_dp(0);
-        ks_ = 1; vs_ = 1; sbuf = 1;
-        if (n_it > 1) {
-          mma_s(1, 1);
-          ks_ = 2; sbuf = 0;
-        }
-      }
-      for (int j = 0; j < n_it && ok; ++j) {
-        if (j + 1 < n_it) ok = wait1(&v_full[vs_], vph, TT_ST_TIMEOUT_MMA + 3);
-        if (ok && j + 2 < n_it) ok = wait1(&k_full[ks_], kph, TT_ST_TIMEOUT_MMA + 2);
-        if (ok) ok = wait1(ds_full, eph, TT_ST_TIMEOUT_MMA + 4);
-        if (!ok) break;
-        tc_fence_after();
-        mma_dq(kq, j > 0 ? 1u : 0u);
-        if (j + 1 < n_it) mma_dp(vs_);
-        if (j + 2 < n_it) mma_s(ks_, sbuf);
-        if (++kq == C_KST) kq = 0;
-        eph ^= 1;
-        if (++vs_ == C_VST) { vs_ = 0; vph ^= 1; }
-        sbuf ^= 1;
-        if (++ks_ == C_KST) { ks_ = 0; kph ^= 1; }
-      }
-      if (ok) tc_commit2(done_bar, 3);
-    }
-  } else {
-    const int q = warp & 3;
-    const int wg = (warp - 2) >> 2;  // which 64 of the tile's 128 key columns
-    const int r = q * 32 + lane;
-    const int row = q0 + r;
-    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const uint32_t ds_full_leader = map_to_cta(smem_u32(ds_full), 0);
-    float lse2 = 1.0e30f, del = 0.f;
-    if (row < p.Sq) {
-      lse2 = p.lse2[((long long)b * p.H + h) * p.Sq_pad + row];
-      del = p.delta[((long long)b * p.H + h) * p.Sq_pad + row];
-    }
-    bool ok = true;
-    for (int j = 0; j < n_it; ++j) {
-      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, p.status, TT_ST_TIMEOUT_SOFTMAX + 1)) { ok = false; break; }
-      __syncwarp();
-      tc_fence_after();
-      const int valid = kv_len - j * 128 - wg * 64;
-      float pr[64];
-      {
-        uint32_t s0[32], s1[32];
-        const uint32_t s_addr = tmem_base + lane_addr + B_TM_S + (j & 1) * 128 + wg * 64;
-        tmem_ld32(s_addr, s0);
-        tmem_ld32(s_addr + 32, s1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const float pe = fast_exp2(fmaf(__uint_as_float(s0[e]), p.scale_log2, -lse2));
-          pr[e] = (e < valid) ? pe : 0.f;
-        }
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const float pe = fast_exp2(fmaf(__uint_as_float(s1[e]), p.scale_log2, -lse2));
-          pr[32 + e] = (32 + e < valid) ? pe : 0.f;
-        }
-      }
-      if (!mbar_wait(dp_full, j & 1, abort_flag, p.status, TT_ST_TIMEOUT_SOFTMAX + 2)) { ok = false; break; }
-      __syncwarp();
-      tc_fence_after();
-      {
-        uint32_t d0[32], d1[32], ds[16];
-        const uint32_t dp_addr = tmem_base + lane_addr + B_TM_DP + wg * 64;
-        tmem_ld32(dp_addr, d0);
-        tmem_ld32(dp_addr + 32, d1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 16; ++e)
-          ds[e] = pack_bf16(pr[2 * e] * (__uint_as_float(d0[2 * e]) - del),
-                            pr[2 * e + 1] * (__uint_as_float(d0[2 * e + 1]) - del));
-        tmem_st16(dp_addr, ds);
-#pragma unroll
-        for (int e = 0; e < 16; ++e)
-          ds[e] = pack_bf16(pr[32 + 2 * e] * (__uint_as_float(d1[2 * e]) - del),
-                            pr[32 + 2 * e + 1] * (__uint_as_float(d1[2 * e + 1]) - del));
-        tmem_st16(dp_addr + 16, ds);
-      }
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(ds_full_leader);
-    }
-    if (ok) ok = mbar_wait(done_bar, 0, abort_flag, p.status, TT_ST_TIMEOUT_SOFTMAX + 3);
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
-      tc_fence_after();
-      bf16* dst = (p.sc0.mode == 2 && row < p.Sq) ? scatter_dst(p.sc0, b, row, h)
-                                                  : p.out0 + (long long)b * p.bs0 + (long long)row * p.ld0 + h * 128;
-#pragma unroll 1
-      for (int c = wg * 2; c < wg * 2 + 2; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tmem_base + lane_addr + B_TM_DQ + c * 32, o);
-        tmem_ld_wait();
-        if (row < p.Sq) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 pk;
-            pk.x = pack_bf16(__uint_as_float(o[g * 8 + 0]) * p.scale, __uint_as_float(o[g * 8 + 1]) * p.scale);
-            pk.y = pack_bf16(__uint_as_float(o[g * 8 + 2]) * p.scale, __uint_as_float(o[g * 8 + 3]) * p.scale);
-            pk.z = pack_bf16(__uint_as_float(o[g * 8 + 4]) * p.scale, __uint_as_float(o[g * 8 + 5]) * p.scale);
-            pk.w = pack_bf16(__uint_as_float(o[g * 8 + 6]) * p.scale, __uint_as_float(o[g * 8 + 7]) * p.scale);
-            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = pk;
-          }
-        }
-        __syncwarp();
-      }
-    }
-  }
-  __syncwarp();
-  if (*abort_flag) {
-    for (int i = 0; i < 200; ++i) __nanosleep(1000);
-  }
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync_all();  // the partner's MMAs may still read this CTA's shared memory
-  if (warp == 1) tmem_dealloc2(tmem_base, 512);
 }
 
 // ===================================================================== preprocess
@@ -1008,14 +729,6 @@ int make_map(CUtensorMap* tm, const void* ptr, long long ld, long long bs, int S
 // All tensors [B, S, H, 128] views (token stride ld*, batch stride *_bs, in elements).
 // lse: fp32 [B,H,Sq] from the forward pass. scratch: fp32 [2, B, H, Sq_pad] with
 // Sq_pad = Sq rounded up to 128 (tt_attn_bwd_scratch_floats gives the element count).
-static int g_use_pair = -1;
-// 1: use the CTA-pair dQ kernel, 0: the one-CTA kernel (default). Returns the previous setting (-1: unset).
-TT_API int tt_attn_bwd_set_pair(int on) {
-  const int old = g_use_pair;
-  g_use_pair = on ? 1 : 0;
-  return old;
-}
-
 TT_API long long tt_attn_bwd_scratch_floats(int B, int H, int Sq) {
   return 2ll * B * H * ((Sq + 127) / 128 * 128);
 }
@@ -1073,33 +786,6 @@ static int attn_bwd_impl(const void* q, long long ldq, long long q_bs, const voi
     dim3 grid((Skv + 127) / 128, H, B);
     attn_bwd_dkdv_kernel<<<grid, NTHREADS, A_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, p);
     TT_LAUNCH_CHECK();
-  }
-  // The CTA-pair dQ kernel is correct but measured 1 ms slower than the one-CTA kernel at 32,760 tokens x 12 heads
-  // (the hand-offs between the leader's MMA thread and sixteen elementwise warps in two CTAs cost more than the
-  // halved number of MMA instructions saves); it runs only on request (TT_ATTN_PAIR=1 or tt_attn_bwd_set_pair).
-  if (g_use_pair < 0) {
-    const char* e = getenv("TT_ATTN_PAIR");
-    g_use_pair = (e && e[0] == '1') ? 1 : 0;
-  }
-  if (g_use_pair) {
-    CUtensorMap tmK64, tmV64;  // 64-row boxes: each CTA of a pair loads its half of the key rows
-    if (make_map(&tmK64, k, ldk, k_bs, Skv, H, B, 64)) return -1;
-    if (make_map(&tmV64, v, ldv, v_bs, Skv, H, B, 64)) return -1;
-    static bool attr2_done = false;
-    if (!attr2_done) {
-      TT_CUDA(cudaFuncSetAttribute(attn_bwd_dq2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_SMEM));
-      attr2_done = true;
-    }
-    p.out0 = (bf16*)dq; p.ld0 = lddq; p.bs0 = dq_bs;
-    p.out1 = nullptr; p.ld1 = 0; p.bs1 = 0;
-    memset(&p.sc0, 0, sizeof(p.sc0));
-    memset(&p.sc1, 0, sizeof(p.sc1));
-    if (scq) p.sc0 = *scq;
-    const int tiles = (Sq + 127) / 128;
-    dim3 grid((tiles + 1) / 2 * 2, H, B);  // pairs of query tiles; a trailing empty tile only sees masked rows
-    attn_bwd_dq2_kernel<<<grid, NTHREADS, C_SMEM, stream>>>(tmQ, tmK, tmK64, tmV64, tmdO, p);
-    TT_LAUNCH_CHECK();
-    return 0;
   }
   {
     p.out0 = (bf16*)dq; p.ld0 = lddq; p.bs0 = dq_bs;

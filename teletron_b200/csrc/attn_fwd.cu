@@ -35,9 +35,6 @@ constexpr int SM_BAR = SM_KV + KV_SLOTS * TILE_BYTES;
 constexpr int SMEM_BYTES = SM_BAR + 256 + 1024;
 constexpr int NTHREADS = 320;
 constexpr float RESCALE_THRESHOLD = 8.0f;
-#ifndef TT_FWD_POLY_EVERY
-#define TT_FWD_POLY_EVERY 0  // n > 0: every n-th even-indexed exponential on the FMA pipe (exp2_fma)
-#endif
 
 struct AttnParams {
   int Sq, Skv, H, B;
@@ -235,7 +232,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int c = 0; c < 4; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float e0 = exp2_mixed<TT_FWD_POLY_EVERY>(fmaf(__uint_as_float(s[c][i]), p.scale_log2, -m_new), i >> 1);
+          const float e0 = fast_exp2(fmaf(__uint_as_float(s[c][i]), p.scale_log2, -m_new));
           const float e1 = fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), p.scale_log2, -m_new));
           ls4[(i >> 1) & 3] += e0 + e1;
           pk[c * 16 + (i >> 1)] = pack_bf16(e0, e1);

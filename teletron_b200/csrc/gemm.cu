@@ -237,8 +237,6 @@ TT_API int tt_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, l
   TT_CHECK(ldc % (c_fp32 ? 4 : 8) == 0, "gemm: ldc (%lld) breaks 16-byte row alignment", ldc);
   TT_CHECK(((uintptr_t)C & 15) == 0, "gemm: C is not 16-byte aligned");
   TT_CHECK(epi >= 0 && epi <= EPI_LAST, "gemm: unknown epilogue %d", epi);
-  if (epi == EPI_GELU_BWD || epi == EPI_SILU_BWD)
-    TT_CHECK(residual && ldr % 8 == 0 && ((uintptr_t)residual & 15) == 0, "gemm: the activation-gradient epilogue needs an aligned pre-activation tensor");
   if (epi == EPI_GATE_RES) {
     TT_CHECK(residual && gate && rows_per_gate > 0, "gemm: gate/residual epilogue needs both tensors");
     TT_CHECK(ldr % 8 == 0 && gate_ld % 4 == 0, "gemm: residual/gate leading dims misaligned");

@@ -21,10 +21,7 @@ namespace {
 
 constexpr int BN2 = 256;
 constexpr int STAGES2 = 6;
-#ifndef TT_GEMM2_ROUND
-#define TT_GEMM2_ROUND 3
-#endif
-constexpr int ROUND2 = TT_GEMM2_ROUND;  // stages consumed per wait / commit round of the MMA thread
+constexpr int ROUND2 = 3;  // stages consumed per wait / commit round of the MMA thread
 constexpr int B_HALF_BYTES = 128 * BK * 2;
 constexpr int STAGE2_BYTES = A_BYTES + B_HALF_BYTES;  // 32 KB per CTA and stage
 constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 256 + 1024;
@@ -236,8 +233,6 @@ TT_API int tt_gemm2_bf16(const void* A, long long lda, int a_mn, const void* B, 
   TT_CHECK(lda % 8 == 0 && ldb % 8 == 0, "gemm2: lda/ldb must be multiples of 8 elements");
   TT_CHECK(ldc % (c_fp32 ? 4 : 8) == 0 && ((uintptr_t)C & 15) == 0, "gemm2: C misaligned");
   TT_CHECK(epi >= 0 && epi <= EPI_LAST, "gemm2: unknown epilogue %d", epi);
-  if (epi == EPI_GELU_BWD || epi == EPI_SILU_BWD)
-    TT_CHECK(residual && ldr % 8 == 0 && ((uintptr_t)residual & 15) == 0, "gemm2: the activation-gradient epilogue needs an aligned pre-activation tensor");
   if (epi == EPI_GATE_RES) {
     TT_CHECK(residual && gate && rows_per_gate > 0, "gemm2: gate/residual epilogue needs both tensors");
     TT_CHECK(ldr % 8 == 0 && gate_ld % 4 == 0 && (((uintptr_t)residual | (uintptr_t)gate) & 15) == 0,

@@ -12,14 +12,12 @@ constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int TP_MAX = 8;  // ranks of a tensor-parallel group
 
-// EPI_GELU_BWD / EPI_SILU_BWD: C = acc * act'(pre), `pre` (the saved pre-activation, bf16) read through `residual`:
-// the input-gradient GEMM of the layer behind an activation produces the gradient of the pre-activation directly.
 // EPI_QKV_A2A: the fused q/k/v projection under Ulysses context parallelism (N = 3 * qkv_C).  The q and k column
 // blocks are stored locally ([M, 2 * qkv_C]) together with the sum of squares of every 128-column half tile of each
 // row (`ssq`, [M, 2 * qkv_C / 128] fp32: the row statistics of the full-row RMSNorm that follows); the v column block
 // is stored straight into the head owner's [B, S_pad, Hl, D] buffer in peer memory (`sc`, the seq -> head exchange).
-enum Epi : int { EPI_NONE = 0, EPI_GELU = 1, EPI_GATE_RES = 2, EPI_ACCUM = 3, EPI_SILU = 4, EPI_GELU_BWD = 5,
-                 EPI_SILU_BWD = 6, EPI_LAST = 6, EPI_QKV_A2A = 7 };
+enum Epi : int { EPI_NONE = 0, EPI_GELU = 1, EPI_GATE_RES = 2, EPI_ACCUM = 3, EPI_SILU = 4, EPI_LAST = 4,
+                 EPI_QKV_A2A = 7 };
 
 struct GemmParams {
   int M, N, K;
@@ -139,20 +137,6 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t acc,
           float2 f = unpack_bf16(ru[j]);
           v[2 * j] = f.x + gg[2 * j] * v[2 * j];
           v[2 * j + 1] = f.y + gg[2 * j + 1] * v[2 * j + 1];
-        }
-      } else if (p.epi == EPI_GELU_BWD || p.epi == EPI_SILU_BWD) {
-        uint4 rv = *reinterpret_cast<const uint4*>(p.residual + (long long)row * p.ldr + col);
-        const uint32_t* ru = reinterpret_cast<const uint32_t*>(&rv);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 f = unpack_bf16(ru[j]);
-          if (p.epi == EPI_GELU_BWD) {
-            v[2 * j] *= gelu_tanh_grad(f.x);
-            v[2 * j + 1] *= gelu_tanh_grad(f.y);
-          } else {
-            v[2 * j] *= silu_grad(f.x);
-            v[2 * j + 1] *= silu_grad(f.y);
-          }
         }
       } else if (p.epi == EPI_ACCUM) {
         if (p.c_fp32) {

@@ -441,28 +441,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x on the FMA pipe (no special-function unit): round-to-nearest split x = n + f with f in [-0.5, 0.5], a degree-4
-// polynomial for 2^f (relative error about 4e-5) and n added to the exponent field.  Ten instructions instead of one
-// MUFU slot: the attention kernels mix both forms, because at four results per clock and sub-core the
-// special-function unit, not the issue slot, bounds their exponential phases.  Inputs below -125 give 2^-125.
-__device__ __forceinline__ float exp2_fma(float x) {
-  x = fmaxf(x, -125.f);
-  const float r = x + 12582912.f;  // 1.5 * 2^23: the sum's low mantissa bits hold round(x)
-  const float f = x - (r - 12582912.f);
-  float p = fmaf(f, 0.0096181291f, 0.0555041087f);
-  p = fmaf(p, f, 0.2402265070f);
-  p = fmaf(p, f, 0.6931471806f);
-  p = fmaf(p, f, 1.0f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
-}
-// POLY_EVERY-th elements (by index) use exp2_fma, the others the special-function unit
-template <int POLY_EVERY>
-__device__ __forceinline__ float exp2_mixed(float x, int idx) {
-  if constexpr (POLY_EVERY > 0) {
-    if ((idx % POLY_EVERY) == POLY_EVERY - 1) return exp2_fma(x);
-  }
-  return fast_exp2(x);
-}
 __device__ __forceinline__ float fast_tanh(float x) {
   float y;
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -5,6 +5,7 @@
 #include <stdarg.h>
 #include <atomic>
 #include <mutex>
+#include <unordered_map>
 
 static thread_local char g_err[1024] = "";
 
@@ -39,8 +40,54 @@ static EncodeTiledFn get_encode() {
   return fn;
 }
 
+// Descriptors are pure functions of their arguments (a descriptor holds an address, not a device), so they are kept
+// by (address, element size, rank, extents, strides, box, swizzle): a training step launches the same few hundred
+// GEMM / attention shapes on the same buffers again and again, and the driver call costs microseconds of host time.
+namespace {
+struct TmapKey {
+  uint64_t w[16];
+  bool operator==(const TmapKey& o) const { return memcmp(w, o.w, sizeof(w)) == 0; }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = 1469598103934665603ull;
+    for (uint64_t x : k.w) {
+      h ^= x;
+      h *= 1099511628211ull;
+    }
+    return (size_t)h;
+  }
+};
+std::mutex g_tmap_mu;
+std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmaps;
+constexpr size_t TMAP_CACHE_MAX = 1 << 16;   // cleared when full; an entry never goes stale (same arguments, same descriptor)
+}  // namespace
+
+TT_API long long tt_tmap_cache_size() {
+  std::lock_guard<std::mutex> lk(g_tmap_mu);
+  return (long long)g_tmaps.size();
+}
+
 int tt_make_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, const uint64_t* dims,
                  const uint64_t* strides_bytes, const uint32_t* box, int swizzle128) {
+  TT_CHECK(rank >= 1 && rank <= 5, "TMA rank %d out of range", rank);
+  TmapKey key;
+  memset(&key, 0, sizeof(key));
+  key.w[0] = (uint64_t)(uintptr_t)base;
+  key.w[1] = (uint64_t)elem_bytes | ((uint64_t)rank << 8) | ((uint64_t)(swizzle128 != 0) << 16);
+  for (int i = 0; i < rank; ++i) {
+    key.w[2 + i] = dims[i];
+    key.w[7 + i] = (i + 1 < rank) ? strides_bytes[i] : 0;
+    key.w[12 + i / 2] |= (uint64_t)box[i] << (32 * (i & 1));
+  }
+  {
+    std::lock_guard<std::mutex> lk(g_tmap_mu);
+    auto it = g_tmaps.find(key);
+    if (it != g_tmaps.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
   EncodeTiledFn enc = get_encode();
   TT_CHECK(enc != nullptr, "cuTensorMapEncodeTiled entry point not available");
   TT_CHECK(((uintptr_t)base & 15) == 0, "TMA base address %p is not 16-byte aligned", base);
@@ -67,6 +114,11 @@ int tt_make_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, c
                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TT_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  {
+    std::lock_guard<std::mutex> lk(g_tmap_mu);
+    if (g_tmaps.size() >= TMAP_CACHE_MAX) g_tmaps.clear();
+    g_tmaps.emplace(key, *out);
+  }
   return 0;
 }
 

@@ -12,17 +12,16 @@ import torch
 
 from . import _lib
 
-EPI_NONE, EPI_GELU, EPI_GATE_RES, EPI_ACCUM, EPI_SILU, EPI_GELU_BWD, EPI_SILU_BWD = 0, 1, 2, 3, 4, 5, 6
+EPI_NONE, EPI_GELU, EPI_GATE_RES, EPI_ACCUM, EPI_SILU = 0, 1, 2, 3, 4
 
 # CTA-pair kernel (csrc/gemm2.cu, tcgen05.mma.cta_group::2) for outputs of at least 256 x 256; the one-CTA kernel
-# (csrc/gemm.cu) takes everything else.  TT_GEMM_PAIR=0 switches the pair kernel off.
-import os as _os
-
-_PAIR = _os.environ.get("TT_GEMM_PAIR", "1") != "0"
+# (csrc/gemm.cu) takes everything else.
+_PAIR = True
 
 
 def set_pair_gemm(on: bool) -> bool:
-    """Enable / disable the CTA-pair GEMM kernel; returns the previous setting."""
+    """Route large GEMMs to the CTA-pair kernel (default) or everything to the one-CTA kernel, which the tests use
+    to cover both; returns the previous setting."""
     global _PAIR
     old, _PAIR = _PAIR, bool(on)
     return old
@@ -51,13 +50,6 @@ def gemm_ref(a, b, *, a_mn=False, b_mn=False, bias=None, epi=EPI_NONE, residual=
         aux = acc.to(torch.bfloat16) if want_aux else None
         g = gate.float().repeat_interleave(rows_per_gate, dim=0)[: acc.shape[0]]
         acc = residual.float() + g * acc
-    elif epi in (EPI_GELU_BWD, EPI_SILU_BWD):
-        pre = residual.float().detach().requires_grad_(True)
-        with torch.enable_grad():
-            act = (torch.nn.functional.gelu(pre, approximate="tanh") if epi == EPI_GELU_BWD
-                   else torch.nn.functional.silu(pre))
-            (dact,) = torch.autograd.grad(act.sum(), pre)
-        acc = acc * dact
     elif epi == EPI_ACCUM:
         acc = out.float() + acc
     if out is not None:
@@ -75,8 +67,7 @@ def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, epi=EPI_NONE, residual=None
     a: [M,K] (or [K,M] when a_mn)   b: [N,K] (or [K,N] when b_mn); both bf16 with a
     contiguous last dim.  ``epi``: EPI_GELU / EPI_SILU (optionally returning the
     pre-activation as aux), EPI_GATE_RES (``residual + gate[row // rows_per_gate] * acc``,
-    gate fp32), EPI_ACCUM (``out += acc``), EPI_GELU_BWD / EPI_SILU_BWD (``acc * act'(residual)``
-    with ``residual`` the saved pre-activation).
+    gate fp32), EPI_ACCUM (``out += acc``).
     """
     if not a.is_cuda:
         return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, epi=epi, residual=residual, gate=gate,
@@ -105,8 +96,6 @@ def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, epi=EPI_NONE, residual=None
         aux = None
     if bias is not None:
         assert bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == N
-    if epi in (EPI_GELU_BWD, EPI_SILU_BWD):
-        assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and residual.stride(1) == 1
     if epi == EPI_GATE_RES:
         assert residual.dtype == torch.bfloat16 and gate.dtype == torch.float32
         assert residual.shape == (M, N) and residual.stride(1) == 1 and gate.stride(-1) == 1

@@ -4,8 +4,7 @@
 ``linear_residual(x, w, b, res, gate, rows_per_gate)``
                                     y = res + gate[row // rows_per_gate] * (x w^T + b)
 ``ffn(x, w1, b1, w2, b2, res, gate, rows_per_gate, act)``
-                                    the two composed; optionally (``set_ffn_fused_backward``) backward multiplies
-                                    by act' inside the epilogue of the second layer's input-gradient GEMM
+                                    the two composed
 
 Backward runs dgrad with the weight read MN-major and wgrad with both operands read
 MN-major (no transposes).  When the weight carries a ``main_grad`` fp32 buffer (set by
@@ -15,36 +14,14 @@ On CPU everything falls back to differentiable PyTorch.
 """
 from __future__ import annotations
 
-import os
-
 import torch
 import torch.nn.functional as F
 
 from . import _lib
-from .gemm import EPI_ACCUM, EPI_GATE_RES, EPI_GELU, EPI_GELU_BWD, EPI_NONE, EPI_SILU, EPI_SILU_BWD, gemm
+from .gemm import EPI_ACCUM, EPI_GATE_RES, EPI_GELU, EPI_NONE, EPI_SILU, gemm
 
 _ACT = {None: EPI_NONE, "gelu": EPI_GELU, "silu": EPI_SILU}
-_ACT_BWD = {"gelu": EPI_GELU_BWD, "silu": EPI_SILU_BWD}
-# Off by default: at K = 1536 the input-gradient GEMM is bound by its epilogue, and the tanh derivative there costs
-# more (+0.35 ms per Wan2.1-1.3B block at 32,760 tokens) than the separate memory-bound pass it removes.
-_FFN_FUSED_BWD = os.environ.get("TT_FFN_FUSED_BWD", "0") == "1"
 
-
-def set_ffn_fused_backward(on: bool) -> None:
-    global _FFN_FUSED_BWD
-    _FFN_FUSED_BWD = bool(on)
-
-
-class _ActLink:
-    """Connects the autograd node of ``act(x w1^T + b1)`` with the node of the layer that consumes its output
-    and nothing else does: the consumer's backward then returns the gradient of the pre-activation (its
-    input-gradient GEMM applies act' in the epilogue) and sets ``done`` so that the producer's backward does
-    not apply it again.  The pre-activation itself travels through ``save_for_backward`` of both nodes, so
-    activation recompute still drops it."""
-    __slots__ = ("pre", "act", "done")
-
-    def __init__(self):
-        self.pre, self.act, self.done = None, None, False
 _COLSUM_CHUNKS = 296
 
 
@@ -94,7 +71,7 @@ def _bias_grad(dy, b):
 
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, b, act, link=None):
+    def forward(ctx, x, w, b, act):
         need_pre = act is not None and any(ctx.needs_input_grad[:3])
         if need_pre:
             y, pre = gemm(x, w, bias=b, epi=_ACT[act], want_aux=True)
@@ -104,9 +81,6 @@ class _Linear(torch.autograd.Function):
         ctx.act = act
         ctx.has_bias = b is not None
         ctx.bias_ref = b
-        ctx.link = link
-        if link is not None:
-            link.pre, link.act = pre, act
         return y
 
     @staticmethod
@@ -114,15 +88,12 @@ class _Linear(torch.autograd.Function):
         x, w, pre = ctx.saved_tensors
         if dy.stride(1) != 1:
             dy = dy.contiguous()
-        link = ctx.link
-        if link is not None and link.done:
-            link.done = False          # dy already is the gradient of the pre-activation
-        elif ctx.act is not None:
+        if ctx.act is not None:
             dy = act_bwd(dy, pre, ctx.act)
         dx = gemm(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
         dw = _weight_grad(dy, x, w) if ctx.needs_input_grad[1] else None
         db = _bias_grad(dy, ctx.bias_ref) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
-        return dx, dw, db, None, None
+        return dx, dw, db, None
 
 
 def linear(x, w, b=None, act=None):
@@ -139,7 +110,7 @@ def linear(x, w, b=None, act=None):
 
 class _LinearResidual(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, b, res, gate, rows_per_gate, link=None):
+    def forward(ctx, x, w, b, res, gate, rows_per_gate):
         rows = x.shape[0]
         has_gate = gate is not None
         if has_gate:
@@ -153,17 +124,13 @@ class _LinearResidual(torch.autograd.Function):
             y, z = gemm(x, w, bias=b, epi=EPI_GATE_RES, residual=res, gate=g, rows_per_gate=rpg, want_aux=True)
         else:
             y, z = gemm(x, w, bias=b, epi=EPI_GATE_RES, residual=res, gate=g, rows_per_gate=rpg), None
-        pre = link.pre if link is not None else None
-        if link is not None:
-            link.pre = None            # from here on only the saved-tensor slots refer to it
-        ctx.save_for_backward(x, w, z, gate if has_gate else None, pre)
+        ctx.save_for_backward(x, w, z, gate if has_gate else None)
         ctx.meta = (rows_per_gate, has_gate, b)
-        ctx.link = link if pre is not None else None
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w, z, gate, pre = ctx.saved_tensors
+        x, w, z, gate = ctx.saved_tensors
         rows_per_gate, has_gate, b = ctx.meta
         if dy.stride(1) != 1:
             dy = dy.contiguous()
@@ -186,20 +153,14 @@ class _LinearResidual(torch.autograd.Function):
             _lib.check(rc, "tt_gate_bwd")
         else:
             dz = dy
-        dx = None
-        if ctx.needs_input_grad[0]:
-            if ctx.link is not None:   # x = act(pre) feeds nothing else: return d(pre) = (dz w) o act'(pre)
-                dx = gemm(dz, w, b_mn=True, epi=_ACT_BWD[ctx.link.act], residual=pre)
-                ctx.link.done = True
-            else:
-                dx = gemm(dz, w, b_mn=True)
+        dx = gemm(dz, w, b_mn=True) if ctx.needs_input_grad[0] else None
         dw = _weight_grad(dz, x, w) if ctx.needs_input_grad[1] else None
         db = _bias_grad(dz, b) if (b is not None and ctx.needs_input_grad[2]) else None
         dres = dy if ctx.needs_input_grad[3] else None
-        return dx, dw, db, dres, dgate, None, None
+        return dx, dw, db, dres, dgate, None
 
 
-def linear_residual(x, w, b, res, gate=None, rows_per_gate=1, _link=None):
+def linear_residual(x, w, b, res, gate=None, rows_per_gate=1):
     """res + gate * (x @ w.T + b); gate fp32 [batch, N] (None = plain residual add)."""
     if not x.is_cuda:
         z = F.linear(x, w, b)
@@ -207,14 +168,10 @@ def linear_residual(x, w, b, res, gate=None, rows_per_gate=1, _link=None):
             g = gate.float().repeat_interleave(rows_per_gate, dim=0)[: z.shape[0]]
             return (res.float() + g * z.float()).to(x.dtype)
         return res + z
-    return _LinearResidual.apply(x, w, b, res, gate, rows_per_gate, _link)
+    return _LinearResidual.apply(x, w, b, res, gate, rows_per_gate)
 
 
 def ffn(x, w1, b1, w2, b2, res, gate=None, rows_per_gate=1, act="gelu"):
     """res + gate * (act(x @ w1.T + b1) @ w2.T + b2): the feed-forward branch of a DiT block
     (teletron/models/wan/wan_model.py:219-223, 264-265 in the reference)."""
-    if not x.is_cuda or not _FFN_FUSED_BWD:
-        return linear_residual(linear(x, w1, b1, act), w2, b2, res, gate, rows_per_gate)
-    link = _ActLink()
-    h = _Linear.apply(x, w1, b1, act, link)
-    return _LinearResidual.apply(h, w2, b2, res, gate, rows_per_gate, link)
+    return linear_residual(linear(x, w1, b1, act), w2, b2, res, gate, rows_per_gate)

@@ -292,7 +292,9 @@ class DistributedOptimizer:
     def _install_hooks(self):
         for n, p in self.buf.named:
             p.grad_ready = (lambda name=n: self._param_ready(name))
-            p.register_post_accumulate_grad_hook(lambda _p, name=n: self._param_ready(name))
+            # autograd runs this hook for every parameter of the graph, also with an undefined gradient when the
+            # wgrad GEMM has already accumulated into main_grad (and reported through grad_ready)
+            p.register_post_accumulate_grad_hook(lambda _p, name=n: self._param_ready(name, _p.grad is not None))
 
     def begin_last_microbatch(self):
         """Arm the gradient-ready hooks: from here on a bucket's reduction starts as soon as every parameter in
@@ -304,11 +306,11 @@ class DistributedOptimizer:
         for bk in self.buf.buckets:
             self._pending_params[bk.gid] = len(bk.params)
 
-    def _param_ready(self, name: str):
+    def _param_ready(self, name: str, has_grad: bool = True):
         if not self._armed:
             return
         if self._param_seen.get(name):
-            if any(self._fired[g] for g in self.buf.param_buckets[name]):
+            if has_grad and any(self._fired[g] for g in self.buf.param_buckets[name]):
                 raise RuntimeError(f"{name} received another gradient after its bucket's reduction had started; "
                                    "parameters used more than once per backward need --no-overlap-grad-reduce")
             return
