@@ -38,6 +38,7 @@ import torch
 import torch.distributed as dist
 
 from .. import ops
+from ..utils.nvtx import nvtx_range
 
 _ALIGN = 8  # elements; keeps every parameter 16-byte aligned in the bf16 buffer
 DEFAULT_BUCKET_ELEMS = 40_000_000
@@ -208,11 +209,13 @@ class DistributedOptimizer:
 
     def __init__(self, buf: ParamBuffer, group=None, *, lr=1e-4, betas=(0.9, 0.999), eps=1e-8,
                  weight_decay=0.01, clip_grad=0.0, sharded=False, grad_scale=1.0, tp_group=None,
-                 tp_sharded_names=(), overlap=False, comm_blocks: int = 0):
+                 tp_sharded_names=(), overlap=False, comm_blocks: int = 0, kind: str = "adam", momentum: float = 0.9):
         """``tp_group``: under tensor parallelism the gradients of the regions that are replicated across
         the TP group are partial sums over that group's row shards and are all-reduced over it before the
         DP x CP reduction; the squared norm of the sharded regions is summed over it.  (The buffer must
         have been built with the same ``tp_sharded_names``.)"""
+        assert kind in ("adam", "sgd"), kind
+        self.kind, self.momentum = kind, momentum      # "sgd": momentum SGD (teletron/train/lr_scheduler.py:373-379)
         self.buf, self.group = buf, group
         self.tp_group = tp_group
         self.tp_world = dist.get_world_size(tp_group) if tp_group is not None else 1
@@ -239,7 +242,8 @@ class DistributedOptimizer:
         self._reduced: Optional[List[torch.Tensor]] = None
         self._p16: Optional[List[torch.Tensor]] = None
         # fused path: peer-memory reduce-scatter + AdamW + parameter scatter (csrc/comm.cu)
-        self.fused = bool(self.sharded and buf.arena is not None and buf.grads.dtype == torch.float32)
+        self.fused = bool(self.sharded and buf.arena is not None and buf.grads.dtype == torch.float32
+                          and kind == "adam")
         self.overlap = bool(overlap) and self.world > 1
         self.comm_blocks = int(comm_blocks)
         self.log_num_zeros = False
@@ -385,7 +389,7 @@ class DistributedOptimizer:
                 cur.wait_stream(self._side)      # keep bucket order: the side stream's buckets come first
                 self._side_used = False
             stream_ctx = contextlib.nullcontext()
-        with stream_ctx:
+        with stream_ctx, nvtx_range(f"dp_reduce_bucket_{bk.gid}"):
             if self.overlap or not self._barrier_done:
                 # every rank's gradients of this bucket (and of all earlier ones) are complete; with overlap one
                 # barrier per bucket, whichever stream it runs on, so that every rank issues the same sequence
@@ -490,6 +494,12 @@ class DistributedOptimizer:
         L = _lib.lib()
         buf, arena = self.buf, self.buf.arena
         self.step_count += 1
+        with nvtx_range("dp_adamw_scatter"):
+            return self._fused_step_body(L, arena)
+
+    def _fused_step_body(self, L, arena):
+        from ..ops import _lib
+
         zeros = self._count_zeros(self._reduced) if self.log_num_zeros else None
         if self.tp_group is None:
             rc = L.tt_dp_norm_exchange(_lib.ptr(self._partials), _lib.c_int(self._partials.numel()),
@@ -558,6 +568,14 @@ class DistributedOptimizer:
             gsh = self._shard_grads[i]
             if gsh.dtype != torch.float32:
                 gsh = gsh.float()
+            if self.kind == "sgd":     # exp_avg is the momentum buffer; weight decay added to the gradient
+                g32 = gsh * (self.grad_scale if coef is None else self.grad_scale * coef)
+                if r.wd and wd_base:
+                    g32 = g32.add(self.master[i], alpha=wd_base)
+                self.exp_avg[i].mul_(self.momentum).add_(g32)
+                self.master[i].add_(self.exp_avg[i], alpha=-lr)
+                p16.copy_(self.master[i])
+                continue
             ops.adamw_step(self.master[i], p16, self.exp_avg[i], self.exp_avg_sq[i], gsh, lr=lr,
                            beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,
                            wd=wd_base if r.wd else 0.0, step=self.step_count, grad_scale=self.grad_scale,

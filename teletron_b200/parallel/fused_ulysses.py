@@ -30,6 +30,7 @@ import torch
 
 from ..ops import _lib
 from ..ops.norm import rmsrope_bwd_raw
+from ..utils.nvtx import nvtx_range
 from .recompute import forward_is_discarded
 
 _ALIGN = 128  # elements (256 bytes)
@@ -163,11 +164,12 @@ class _FusedUlyssesFn(torch.autograd.Function):
         ssq = torch.empty((rows, 2 * halves), dtype=torch.float32, device=dev) if C % 256 == 0 else None
         rc = -3
         if ssq is not None and x.stride(1) == 1 and w_qkv.stride(1) == 1:
-            rc = L.tt_gemm_qkv_a2a(
-                _lib.ptr(x), _lib.c_ll(x.stride(0)), _lib.ptr(w_qkv), _lib.c_ll(w_qkv.stride(0)), _lib.ptr(b_qkv),
-                _lib.ptr(qk), _lib.c_ll(qk.stride(0)), _lib.ptr(ssq), vh_p, _lib.c_int(P), _lib.c_int(rank),
-                _lib.c_int(rows), _lib.c_int(C), _lib.c_int(x.shape[1]), _lib.c_int(S_l), _lib.c_int(H),
-                _lib.c_int(D), _lib.ptr(_lib.status_word(dev)), _lib.stream())
+            with nvtx_range("qkv_gemm_a2a"):
+                rc = L.tt_gemm_qkv_a2a(
+                    _lib.ptr(x), _lib.c_ll(x.stride(0)), _lib.ptr(w_qkv), _lib.c_ll(w_qkv.stride(0)),
+                    _lib.ptr(b_qkv), _lib.ptr(qk), _lib.c_ll(qk.stride(0)), _lib.ptr(ssq), vh_p, _lib.c_int(P),
+                    _lib.c_int(rank), _lib.c_int(rows), _lib.c_int(C), _lib.c_int(x.shape[1]), _lib.c_int(S_l),
+                    _lib.c_int(H), _lib.c_int(D), _lib.ptr(_lib.status_word(dev)), _lib.stream())
         if rc == -3:      # too few rows for the CTA-pair kernel: plain GEMM, V exchanged by a copy kernel
             qkv = gemm(x, w_qkv, bias=b_qkv)
             qk, ssq = qkv, None
@@ -188,12 +190,13 @@ class _FusedUlyssesFn(torch.autograd.Function):
             o_h = torch.empty(n_h, dtype=torch.bfloat16, device=dev)
             lse = torch.empty((B, heads, S_pad), dtype=torch.float32, device=dev)
             ld, bs = Hl * D, S_pad * Hl * D
-            rc = L.tt_attn_fwd_scatter(
-                _lib.ptr(qh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(kh), _lib.c_ll(ld), _lib.c_ll(bs),
-                _lib.ptr(vh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(o_h), _lib.c_ll(ld), _lib.c_ll(bs),
-                _lib.ptr(lse), _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl), _lib.c_int(heads), _lib.c_int(H),
-                _lib.c_int(S_pad), _lib.c_int(D), _lib.c_float(scale), o_p, _lib.c_int(P), _lib.c_int(rank),
-                _lib.ptr(_lib.status_word(dev)), _lib.stream())
+            with nvtx_range("attn_fwd_a2a"):
+                rc = L.tt_attn_fwd_scatter(
+                    _lib.ptr(qh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(kh), _lib.c_ll(ld), _lib.c_ll(bs),
+                    _lib.ptr(vh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(o_h), _lib.c_ll(ld), _lib.c_ll(bs),
+                    _lib.ptr(lse), _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl), _lib.c_int(heads),
+                    _lib.c_int(H), _lib.c_int(S_pad), _lib.c_int(D), _lib.c_float(scale), o_p, _lib.c_int(P),
+                    _lib.c_int(rank), _lib.ptr(_lib.status_word(dev)), _lib.stream())
             _lib.check(rc, "tt_attn_fwd_scatter")
         fu.arena.barrier(fu.slot)
         if not fu._keep_for_backward:
@@ -234,12 +237,13 @@ class _FusedUlyssesFn(torch.autograd.Function):
             L.tt_attn_bwd_scratch_floats.restype = _lib.c_ll
             scratch = torch.empty(L.tt_attn_bwd_scratch_floats(_lib.c_int(B), _lib.c_int(heads), _lib.c_int(S_pad)),
                                   dtype=torch.float32, device=dev)
-            rc = L.tt_attn_bwd_scatter(
-                _lib.ptr(qh), _lib.ptr(kh), _lib.ptr(vh), _lib.ptr(o_h), _lib.ptr(do_h.tensor), _lib.ptr(lse),
-                _lib.ptr(scratch), dqkv_s.c_ptrs(0), dqkv_s.c_ptrs(C), dqkv_s.c_ptrs(2 * C), _lib.c_ll(3 * C),
-                _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl), _lib.c_int(heads), _lib.c_int(H), _lib.c_int(S_pad),
-                _lib.c_int(D), _lib.c_float(scale), _lib.c_int(P), _lib.c_int(rank),
-                _lib.ptr(_lib.status_word(dev)), _lib.stream())
+            with nvtx_range("attn_bwd_a2a"):
+                rc = L.tt_attn_bwd_scatter(
+                    _lib.ptr(qh), _lib.ptr(kh), _lib.ptr(vh), _lib.ptr(o_h), _lib.ptr(do_h.tensor), _lib.ptr(lse),
+                    _lib.ptr(scratch), dqkv_s.c_ptrs(0), dqkv_s.c_ptrs(C), dqkv_s.c_ptrs(2 * C), _lib.c_ll(3 * C),
+                    _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl), _lib.c_int(heads), _lib.c_int(H),
+                    _lib.c_int(S_pad), _lib.c_int(D), _lib.c_float(scale), _lib.c_int(P), _lib.c_int(rank),
+                    _lib.ptr(_lib.status_word(dev)), _lib.stream())
             _lib.check(rc, "tt_attn_bwd_scatter")
         fu.arena.barrier(fu.slot)
         dqkv = dqkv_s.tensor[:rows * 3 * C].view(rows, 3 * C)

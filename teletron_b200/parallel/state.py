@@ -36,6 +36,7 @@ class Topology:
     pp: int = 1
     encoder_ranks: int = 0
     replicas: int = 1
+    ep: int = 1
 
     def __post_init__(self):
         dit = self.world_size - self.encoder_ranks
@@ -47,6 +48,8 @@ class Topology:
         mp = self.tp * self.cp * self.pp
         if per % mp:
             raise ValueError(f"replica world {per} not divisible by tp*cp*pp = {mp}")
+        if (per // mp) % self.ep:
+            raise ValueError(f"data-parallel size {per // mp} not divisible by the expert-parallel size {self.ep}")
 
     # ---- sizes
     @property
@@ -114,6 +117,35 @@ class Topology:
     def replica_groups(self): return [list(range(k * self.replica_world, (k + 1) * self.replica_world)) for k in range(self.replicas)]
     def dit_group(self): return list(range(self.dit_world))
 
+    # expert parallelism lives inside data parallelism (teletron/core/parallel_state.py:596-633): `ep` consecutive
+    # data-parallel ranks hold different experts; ranks with the same expert form the "data modulo expert" group
+    def ep_groups(self) -> List[List[int]]:
+        out = []
+        for g in self._groups(["dp"]):
+            out.extend(g[i:i + self.ep] for i in range(0, len(g), self.ep))
+        return out
+
+    def tp_ep_groups(self) -> List[List[int]]:
+        out = []
+        for g in self._groups(["dp", "tp"]):          # sorted: tp fastest inside each dp index
+            n = self.ep * self.tp
+            out.extend(g[i:i + n] for i in range(0, len(g), n))
+        return out
+
+    def dp_modulo_ep_groups(self) -> List[List[int]]:
+        out = []
+        for g in self._groups(["dp"]):
+            out.extend(g[j::self.ep] for j in range(self.ep))
+        return out
+
+    # first and last pipeline stage share the embedding weights' gradients; the first stage alone holds position
+    # embeddings (parallel_state.py:495-542).  With one stage both groups are the rank itself.
+    def embedding_groups(self) -> List[List[int]]:
+        return [sorted({g[0], g[-1]}) for g in self.pp_groups()]
+
+    def position_embedding_groups(self) -> List[List[int]]:
+        return [[g[0]] for g in self.pp_groups()]
+
     def tp_cp_leaders(self) -> List[int]:
         return [g[0] for g in self.tp_cp_groups()]
 
@@ -156,12 +188,13 @@ def _new_groups(name: str, rank_lists: List[List[int]], rank: int, backend=None,
 
 def initialize_model_parallel(tensor_model_parallel_size: int = 1, pipeline_model_parallel_size: int = 1,
                               context_parallel_size: int = 1, encoder_world_size: int = 0,
-                              consumer_models_num: int = 1, timeout=None, gloo_twins: bool = False) -> Topology:
+                              consumer_models_num: int = 1, timeout=None, gloo_twins: bool = False,
+                              expert_model_parallel_size: int = 1) -> Topology:
     """Create every process group. Must be called by all ranks of the world (encoder ranks too)."""
     assert dist.is_initialized(), "call torch.distributed.init_process_group first"
     world, rank = dist.get_world_size(), dist.get_rank()
     topo = Topology(world, tensor_model_parallel_size, context_parallel_size, pipeline_model_parallel_size,
-                    encoder_world_size, consumer_models_num)
+                    encoder_world_size, consumer_models_num, expert_model_parallel_size)
     _S.topo, _S.rank = topo, rank
     _S.groups, _S.ranks, _S.gloo = {}, {}, {}
     _S.groups["world"] = dist.group.WORLD
@@ -175,6 +208,12 @@ def initialize_model_parallel(tensor_model_parallel_size: int = 1, pipeline_mode
     _new_groups("dp_cp", topo.dp_groups(True), rank, timeout=timeout, gloo_twin=gloo_twins)
     _new_groups("tp_cp", topo.tp_cp_groups(), rank, timeout=timeout)
     _new_groups("mp", topo.model_parallel_groups(), rank, timeout=timeout)
+    _new_groups("embd", topo.embedding_groups(), rank, timeout=timeout)
+    _new_groups("pos_embd", topo.position_embedding_groups(), rank, timeout=timeout)
+    if topo.ep > 1:
+        _new_groups("ep", topo.ep_groups(), rank, timeout=timeout)
+        _new_groups("tp_ep", topo.tp_ep_groups(), rank, timeout=timeout)
+        _new_groups("dp_mod_ep", topo.dp_modulo_ep_groups(), rank, timeout=timeout, gloo_twin=gloo_twins)
     return topo
 
 
@@ -229,6 +268,15 @@ def get_tensor_context_parallel_group(): return _group("tp_cp")
 def get_tensor_context_parallel_world_size(): return _size("tp_cp")
 def get_tensor_context_parallel_rank(): return _rank_in("tp_cp")
 def get_tensor_context_parallel_src_rank(): return _S.ranks["tp_cp"][0] if (_S.topo and "tp_cp" in _S.ranks) else 0
+def get_embedding_group(): return _group("embd")
+def get_position_embedding_group(): return _group("pos_embd")
+def is_rank_in_embedding_group(): return _S.topo is not None and _S.rank in _S.ranks.get("embd", [])
+def get_expert_model_parallel_group(): return _group("ep")
+def get_expert_model_parallel_world_size(): return _size("ep")
+def get_expert_model_parallel_rank(): return _rank_in("ep")
+def get_tensor_and_expert_parallel_group(): return _group("tp_ep")
+def get_data_modulo_expert_parallel_group(): return _group("dp_mod_ep")
+def get_data_modulo_expert_parallel_rank(): return _rank_in("dp_mod_ep")
 def get_group_ranks(name: str) -> List[int]: return list(_S.ranks.get(name, [0]))
 
 

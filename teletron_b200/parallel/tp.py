@@ -24,6 +24,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from .. import ops
+from ..utils.nvtx import nvtx_range
 
 
 def _ag_rows(x, group, world):

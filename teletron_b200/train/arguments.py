@@ -53,7 +53,8 @@ _FLAGS = [
     ("--adam-beta1", dict(type=float, default=0.9)),
     ("--adam-beta2", dict(type=float, default=0.999)),
     ("--adam-eps", dict(type=float, default=1e-8)),
-    ("--optimizer", dict(type=str, default="adam", choices=["adam"])),
+    ("--optimizer", dict(type=str, default="adam", choices=["adam", "sgd"])),
+    ("--sgd-momentum", dict(type=float, default=0.9)),
     ("--bf16", dict(action="store_true")),
     ("--fp16", dict(action="store_true")),
     ("--lr", dict(type=float, default=1e-5)),
@@ -83,9 +84,9 @@ _FLAGS = [
     ("--no-overlap-grad-reduce", dict(action="store_false", dest="overlap_grad_reduce")),
     ("--ddp-bucket-size", dict(type=int, default=40_000_000, help="elements per gradient bucket")),
     ("--overlap-param-gather", dict(action="store_true")),
-    ("--no-delay-grad-reduce", dict(action="store_false", dest="delay_grad_reduce")),
+    ("--no-delay-grad-reduce", dict(action="store_false", dest="delay_grad_reduce", default=None)),
     ("--delay-param-gather", dict(action="store_true")),
-    ("--no-rope-fusion", dict(action="store_false", dest="apply_rope_fusion")),
+    ("--no-rope-fusion", dict(action="store_false", dest="apply_rope_fusion", default=None)),
     ("--distributed-timeout-minutes", dict(type=int, default=10)),
     ("--distributed-backend", dict(type=str, default=None, choices=["nccl", "gloo"])),
     ("--seed", dict(type=int, default=1234)),
@@ -104,6 +105,9 @@ _FLAGS = [
     ("--tensor-model-parallel-size", dict(type=int, default=1)),
     ("--pipeline-model-parallel-size", dict(type=int, default=1)),
     ("--context-parallel-size", dict(type=int, default=1)),
+    ("--expert-model-parallel-size", dict(type=int, default=1,
+                                          help="expert-parallel groups inside data parallelism (the DiTs here have no "
+                                               "expert layers; the groups exist for models that do)")),
     ("--sequence-parallel", dict(action="store_true")),
     ("--distributed-vae", dict(action="store_true")),
     ("--distributed-vae-world-size", dict(type=int, default=0)),
@@ -169,7 +173,7 @@ _FLAGS = [
     ("--producer-profile", dict(action="store_true")),
     ("--profile-path", dict(type=str, default="./profile")),
     ("--show-args", dict(action="store_true")),
-    # LoRA / flow / VAE knobs of the reference's dataclass (accepted, LoRA itself is not implemented there either)
+    # LoRA / flow / VAE knobs of the reference's dataclass (a non-zero LoRA rank raises, as in the reference)
     ("--lora-rank", dict(type=int, default=0)),
     ("--lora-alpha", dict(type=float, default=1.0)),
     ("--flow-shift", dict(type=float, default=5.0)),
@@ -214,6 +218,9 @@ def validate_args(args):
     if args.dit_world_size % denom:
         raise ValueError(f"DiT world {args.dit_world_size} not divisible by tp*pp*cp*replicas = {denom}")
     args.data_parallel_size = args.dit_world_size // denom
+    if args.data_parallel_size % args.expert_model_parallel_size:
+        raise ValueError(f"data-parallel size {args.data_parallel_size} not divisible by "
+                         f"--expert-model-parallel-size {args.expert_model_parallel_size}")
     if args.global_batch_size is None:
         args.global_batch_size = args.micro_batch_size * args.data_parallel_size
     per_step = args.micro_batch_size * args.data_parallel_size
@@ -235,6 +242,7 @@ def validate_args(args):
         args.recompute_method = "block"
     if args.lr_warmup_fraction is not None and (args.lr_warmup_iters or args.lr_warmup_samples):
         raise ValueError("give either --lr-warmup-fraction or --lr-warmup-iters/samples")
+    _flags_without_effect(args)
     args.consumed_train_samples = 0
     args.consumed_valid_samples = 0
     args.iteration = 0
@@ -245,6 +253,33 @@ def validate_args(args):
 
         update_train_iters(args)      # follows the batch-size ramp when there is one
     return args
+
+
+def _flags_without_effect(args):
+    """Flags of the reference's command line that are accepted so its launch lines run, but change nothing here:
+    say so once (rank 0) instead of silently doing nothing; LoRA training raises as it does in the reference
+    (teletron/train/checkpoint/checkpoint.py:226-227)."""
+    if args.lora_rank:
+        raise NotImplementedError("--lora-rank: LoRA training is not implemented (nor in the reference); adapter files "
+                                  "can be folded into the weights at load time with ModelManager.load_lora")
+    notes = []
+    if args.overlap_param_gather or args.delay_param_gather:
+        notes.append("--overlap-param-gather / --delay-param-gather: the parameter all-gather is part of the AdamW "
+                     "kernel (peer-memory path) or follows it directly (NCCL path); there is nothing to overlap or delay")
+    if args.delay_grad_reduce is False:
+        notes.append("--no-delay-grad-reduce: with --overlap-grad-reduce every bucket's reduction already starts as soon "
+                     "as the bucket is complete")
+    if args.apply_rope_fusion is False:
+        notes.append("--no-rope-fusion: RoPE is always applied inside the q/k norm kernel")
+    if args.sequence_parallel and args.tensor_model_parallel_size == 1:
+        notes.append("--sequence-parallel: only meaningful with tensor parallelism (where activations between "
+                     "tensor-parallel regions are always sequence-sharded)")
+    if args.ckpt_fully_parallel_save and not args.use_dist_ckpt:
+        notes.append("--ckpt-fully-parallel-save: only used with --use-dist-ckpt")
+    if notes and args.rank == 0:
+        for n in notes:
+            print(f"NOTE: {n}", flush=True)
+    args.inert_flag_notes = notes
 
 
 def _defaults_from_file(parser: argparse.ArgumentParser, path: str) -> dict:

@@ -31,22 +31,62 @@ def make_torch_profiler(args, role: str):
 
 
 class MemorySnapshot:
-    """Records allocator history while active and dumps ``memory_<time>_iter<i>_rank<r>.pt``."""
+    """Allocator history per training step when the environment names ``MEMORY_SNAPSHOT``: ``begin()`` before the step
+    starts the recording, ``dump(iteration)`` after it writes ``memory_<time>_iter<i>_rank<r>.pt`` under
+    ``PROF_SAVE_PATH`` and stops the recording (teletron/train/trainer.py:549-567).  ``backend`` is the module
+    that provides ``_record_memory_history`` / ``_dump_snapshot`` (``torch.cuda.memory``; a stand-in in tests)."""
 
-    def __init__(self, rank: int):
-        self.enabled = bool(os.environ.get("MEMORY_SNAPSHOT")) and torch.cuda.is_available()
+    def __init__(self, rank: int, backend=None, max_entries: int = 80000):
+        self.backend = backend if backend is not None else (torch.cuda.memory if torch.cuda.is_available() else None)
+        self.enabled = bool(os.environ.get("MEMORY_SNAPSHOT")) and self.backend is not None
         self.dir = os.environ.get("PROF_SAVE_PATH", ".")
         self.rank = rank
+        self.max_entries = max_entries
+
+    def begin(self):
         if self.enabled:
-            torch.cuda.memory._record_memory_history(max_entries=100000)
+            self.backend._record_memory_history(max_entries=self.max_entries)
 
     def dump(self, iteration: int):
         if not self.enabled:
             return None
         os.makedirs(self.dir, exist_ok=True)
-        path = os.path.join(self.dir, f"memory_{int(time.time())}_iter{iteration}_rank{self.rank}.pt")
-        torch.cuda.memory._dump_snapshot(path)
+        stamp = time.strftime("%Y%m%d_%H%M%S", time.localtime())
+        path = os.path.join(self.dir, f"memory_{stamp}_iter{iteration}_rank{self.rank}.pt")
+        self.backend._dump_snapshot(path)
+        self.backend._record_memory_history(enabled=None)
         return path
+
+
+from ..utils.nvtx import nvtx_range, set_nvtx  # noqa: E402,F401  (named ranges around the fused kernels)
+
+
+class ProfileWindow:
+    """``--profile``: on the ranks of ``--profile-ranks``, from ``--profile-step-start`` to ``--profile-step-end``
+    the CUDA profiler API is started (for an external profiler attached with capture range = cudaProfilerApi),
+    autograd emits NVTX ranges for every op and the framework's own ranges around its fused kernels are switched on
+    (teletron/train/trainer.py:527-531, 659-662)."""
+
+    def __init__(self, args, cudart=None):
+        self.on = bool(args.profile) and args.rank in args.profile_ranks and (cudart is not None or torch.cuda.is_available())
+        self.start, self.end = args.profile_step_start, args.profile_step_end
+        self._cudart = cudart
+        self._emit = None
+
+    def before_step(self, iteration: int):
+        if self.on and iteration == self.start and self._emit is None:
+            (self._cudart or torch.cuda.cudart()).cudaProfilerStart()
+            self._emit = torch.autograd.profiler.emit_nvtx(record_shapes=True)
+            self._emit.__enter__()
+            set_nvtx(True)
+
+    def after_step(self, iteration: int):
+        """``iteration``: number of completed steps."""
+        if self.on and iteration == self.end and self._emit is not None:
+            set_nvtx(False)
+            self._emit.__exit__(None, None, None)
+            self._emit = None
+            (self._cudart or torch.cuda.cudart()).cudaProfilerStop()
 
 
 class DeviceTimers:

@@ -120,7 +120,8 @@ class Trainer:
             mpu.initialize_model_parallel(a.tensor_model_parallel_size, a.pipeline_model_parallel_size,
                                           a.context_parallel_size, a.distributed_vae_world_size,
                                           a.consumer_models_num,
-                                          timeout=datetime.timedelta(minutes=a.distributed_timeout_minutes))
+                                          timeout=datetime.timedelta(minutes=a.distributed_timeout_minutes),
+                                          expert_model_parallel_size=getattr(a, "expert_model_parallel_size", 1))
             # agree on the earliest start time for --exit-duration-in-mins (trainer.py:87-92)
             t = torch.tensor([self.start_time], dtype=torch.float64,
                              device="cuda" if backend == "nccl" else "cpu")
@@ -203,7 +204,8 @@ class Trainer:
             eps=a.adam_eps, weight_decay=a.weight_decay, clip_grad=a.clip_grad,
             sharded=a.use_distributed_optimizer, grad_scale=1.0 / max(a.data_parallel_size, 1),
             tp_group=mpu.get_tensor_model_parallel_group() if a.tensor_model_parallel_size > 1 else None,
-            tp_sharded_names=tp_names or (), overlap=overlap)
+            tp_sharded_names=tp_names or (), overlap=overlap, kind=getattr(a, "optimizer", "adam"),
+            momentum=getattr(a, "sgd_momentum", 0.9))
         self.optimizer.log_num_zeros = bool(getattr(a, "log_num_zeros_in_grad", False))
         self.opt_param_scheduler = scheduler_from_args(a, self.optimizer) if (a.train_iters or a.train_samples) else None
         if a.load or a.pretrained_checkpoint:
@@ -365,6 +367,10 @@ class Trainer:
             gc.disable()
             gc.collect()
         use_events = torch.cuda.is_available()
+        from .profiling import MemorySnapshot, ProfileWindow
+
+        window = ProfileWindow(a)
+        mem_snap = MemorySnapshot(a.rank)
         n_mb_prev = a.num_micro_batches
         while iteration < a.train_iters:
             # batch-size ramp-up: a new level starts from a checkpoint, then has to split into micro-batches
@@ -377,8 +383,8 @@ class Trainer:
             n_mb_prev = a.num_micro_batches
             self._set_batch_level(strict=True)
             tokens_per_step = getattr(a, "tokens_per_sample", 0) * a.current_global_batch_size
-            if a.profile and iteration == a.profile_step_start and a.rank in a.profile_ranks and use_events:
-                torch.cuda.cudart().cudaProfilerStart()
+            window.before_step(iteration)
+            mem_snap.begin()
             if use_events:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
@@ -392,6 +398,7 @@ class Trainer:
 
                 if _lib.available():
                     _lib.check_status()
+            mem_snap.dump(iteration)
             iteration += 1
             a.iteration = iteration
             a.consumed_train_samples += a.current_global_batch_size
@@ -401,8 +408,7 @@ class Trainer:
                             tokens=tokens_per_step, device_ms=dev_ms, timers=self.timers, num_zeros_in_grad=num_zeros)
             if prof is not None:
                 prof.step()
-            if a.profile and iteration == a.profile_step_end and a.rank in a.profile_ranks and use_events:
-                torch.cuda.cudart().cudaProfilerStop()
+            window.after_step(iteration)
             if a.manual_gc and a.manual_gc_interval and iteration % a.manual_gc_interval == 0:
                 gc.collect()
             if a.eval_interval and a.eval_iters > 0 and iteration % a.eval_interval == 0:

@@ -487,3 +487,116 @@ def test_load_options_finetune_no_optim_no_rng(tmp_path):
     c = _trainer_args(tmp_path / "full", f"--load {root}")
     t3 = Trainer(c)
     assert c.iteration == 4 and torch.equal(t3.optimizer.exp_avg[0], m_state)
+
+
+def test_sgd_optimizer_matches_torch_sgd():
+    from teletron_b200.parallel.ddp import DistributedOptimizer, ParamBuffer
+
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Linear(16, 4))
+    ref = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Linear(16, 4))
+    ref.load_state_dict(net.state_dict())
+    buf = ParamBuffer(net)
+    opt = DistributedOptimizer(buf, None, lr=0.1, weight_decay=0.0, kind="sgd", momentum=0.9)
+    topt = torch.optim.SGD(ref.parameters(), lr=0.1, momentum=0.9)
+    for step in range(3):
+        x = torch.randn(5, 8)
+        opt.zero_grad()
+        topt.zero_grad()
+        net(x).square().mean().backward()
+        ref(x).square().mean().backward()
+        opt.step()
+        topt.step()
+    for (n, p), (_, q) in zip(net.named_parameters(), ref.named_parameters()):
+        assert torch.allclose(p, q, atol=1e-6), n
+
+
+def test_flags_without_effect_are_reported_and_lora_raises(capsys):
+    import pytest
+
+    from teletron_b200.train import parse_args
+
+    a = parse_args(argv="--overlap-param-gather --no-rope-fusion --sequence-parallel --no-delay-grad-reduce".split())
+    out = capsys.readouterr().out
+    assert len(a.inert_flag_notes) == 4 and out.count("NOTE:") == 4
+    assert parse_args(argv=[]).inert_flag_notes == []
+    with pytest.raises(NotImplementedError):
+        parse_args(argv="--lora-rank 8".split())
+
+
+def test_expert_and_embedding_groups_partition_the_data_parallel_ranks():
+    from teletron_b200.parallel.state import Topology
+
+    t = Topology(16, tp=2, cp=2, ep=2)
+    assert t.dp == 4
+    for groups in (t.ep_groups(), t.dp_modulo_ep_groups()):
+        assert sorted(r for g in groups for r in g) == list(range(16)) and all(len(g) == 2 for g in groups)
+    assert [0, 4] in t.ep_groups() and [0, 8] in t.dp_modulo_ep_groups() and [0, 1, 4, 5] in t.tp_ep_groups()
+    assert all(len(g) == 1 for g in t.embedding_groups())          # one pipeline stage: the rank itself
+    p = Topology(8, pp=2)
+    assert [0, 4] in p.embedding_groups() and [0] in p.position_embedding_groups()
+    import pytest
+    with pytest.raises(ValueError):
+        Topology(8, ep=3)
+
+
+def test_memory_snapshot_and_profile_window_drive_their_backends(tmp_path, monkeypatch):
+    """MEMORY_SNAPSHOT records and dumps once per step; --profile starts the profiler API, NVTX emission and the
+    framework's own ranges at the first profiled step and stops them at the last (fakes stand in for CUDA)."""
+    from argparse import Namespace
+
+    from teletron_b200.train import profiling
+    from teletron_b200.utils import nvtx
+
+    calls = []
+
+    class FakeMem:
+        def _record_memory_history(self, **kw):
+            calls.append(("record", kw))
+
+        def _dump_snapshot(self, path):
+            calls.append(("dump", path))
+            open(path, "w").write("x")
+
+    monkeypatch.setenv("MEMORY_SNAPSHOT", "1")
+    monkeypatch.setenv("PROF_SAVE_PATH", str(tmp_path))
+    snap = profiling.MemorySnapshot(3, backend=FakeMem())
+    snap.begin()
+    path = snap.dump(7)
+    assert path.endswith("_iter7_rank3.pt") and (tmp_path / path.split("/")[-1]).exists()
+    assert [c[0] for c in calls] == ["record", "dump", "record"] and calls[-1][1] == {"enabled": None}
+    monkeypatch.delenv("MEMORY_SNAPSHOT")
+    assert profiling.MemorySnapshot(0, backend=FakeMem()).dump(1) is None
+
+    events = []
+
+    class FakeRt:
+        def cudaProfilerStart(self):
+            events.append("start")
+
+        def cudaProfilerStop(self):
+            events.append("stop")
+
+    class FakeEmit:
+        def __init__(self, **kw):
+            events.append("emit")
+
+        def __enter__(self):
+            events.append("enter")
+
+        def __exit__(self, *a):
+            events.append("exit")
+
+    monkeypatch.setattr(torch.autograd.profiler, "emit_nvtx", FakeEmit)
+    monkeypatch.setattr(nvtx, "set_nvtx", lambda on: events.append(("ranges", on)))
+    monkeypatch.setattr(profiling, "set_nvtx", nvtx.set_nvtx)
+    a = Namespace(profile=True, rank=1, profile_ranks=[1], profile_step_start=2, profile_step_end=4)
+    w = profiling.ProfileWindow(a, cudart=FakeRt())
+    for it in range(6):
+        w.before_step(it)
+        w.after_step(it + 1)
+    assert events == ["start", "emit", "enter", ("ranges", True), ("ranges", False), "exit", "stop"]
+    assert not profiling.ProfileWindow(Namespace(profile=True, rank=0, profile_ranks=[1], profile_step_start=2,
+                                                 profile_step_end=4), cudart=FakeRt()).on
+    with nvtx.nvtx_range("off-by-default"):
+        pass
