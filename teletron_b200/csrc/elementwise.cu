@@ -374,6 +374,7 @@ TT_API int tt_colsum(const void* x, long long ldx, float* partial, int chunks, v
                      int accumulate, int rows, int C, cudaStream_t stream) {
   TT_CHECK(rows > 0 && C > 0 && C % 8 == 0 && chunks > 0, "colsum: bad shape");
   TT_CHECK(ldx % 8 == 0 && al16(x) && al16(partial), "colsum: misaligned");
+  TT_CHECK(ldx >= C, "colsum: row stride %lld is smaller than the row width %d (rows would overlap)", ldx, C);
   const int rpc = (rows + chunks - 1) / chunks;
   dim3 g1((C / 8 + 255) / 256, chunks);
   colsum_stage1_kernel<<<g1, 256, 0, stream>>>((const bf16*)x, ldx, partial, rows, C, rpc);
@@ -475,6 +476,7 @@ TT_API int tt_colsum_noalloc(const void* x, long long ldx, void* out, int out_fp
            "caller-provided scratch instead",
            C, TT_COLSUM_NOALLOC_MAX_C);
   TT_CHECK(ldx % 8 == 0 && al16(x), "colsum_noalloc: input misaligned");
+  TT_CHECK(ldx >= C, "colsum_noalloc: row stride %lld is smaller than the row width %d (rows would overlap)", ldx, C);
   TT_CHECK(out != nullptr, "colsum_noalloc: null output");
   float* partial = nullptr;
   if (noalloc_scratch(&partial)) return -2;

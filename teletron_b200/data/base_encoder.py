@@ -8,7 +8,9 @@ Wire format (one message pair per sample, NCCL/gloo p2p):
   header  int32[HEADER_INTS] = [MAGIC, VERSION, seq_no, n_tensors, flags, then per tensor (ndim, d0..d4)]
   payload flat bf16 = the tensors flattened in schema order
 After an early stop request the producer closes each stream with one header that carries ``FLAG_STOP`` and no payload,
-which completes the header receive the consumer keeps in flight.
+which completes the header receive the consumer keeps in flight.  ``FLAG_NEXT_SAME`` on a header promises that the
+next message is a full sample of the same shapes: the consumer then posts both of its receives (into a second
+buffer) while the current sample trains, which is what makes the hand-off double-buffered.
 A fixed, versioned header replaces the reference's bare int32[16] of concatenated shapes
 (teletron/train/consumer_dataloader.py:106-122), whose length silently disagreed between
 producer and consumer once a fifth tensor (shared noise) was added.
@@ -27,6 +29,8 @@ MAX_TENSORS = 9
 MAX_DIMS = 5
 FLAG_LAST = 1
 FLAG_STOP = 2   # header without a payload: the producer was asked to stop and will send nothing more
+FLAG_NEXT_SAME = 4  # a promise: another full sample with the same shapes follows, whatever happens (also after a stop
+                    # request), so the consumer may post the receives of its header AND payload right away
 
 
 def encode_header(shapes: Sequence[Sequence[int]], seq_no: int, flags: int = 0) -> torch.Tensor:

@@ -3,10 +3,15 @@ on dedicated ranks (teletron/train/consumer_dataloader.py:18-282).
 
 The TP x CP leader receives (header, payload) from its producer with a watchdog (timed polling
 of the receive, producer heartbeat and failure keys in the store, so a dead encoder raises an
-error instead of hanging the job), prefetches the next sample while the current one trains, and
-fans the sample out to its TP x CP group with two broadcasts (header, flat payload) instead of
-pickled metadata plus one broadcast per tensor.  ``timestep_range`` is attached for
-timestep-expert replicas from ``--moe-step-factor-list``.
+error instead of hanging the job) and fans the sample out to its TP x CP group with two broadcasts
+(header, flat payload) instead of pickled metadata plus one broadcast per tensor.
+
+Double buffering: the receive of the next header is always in flight, and when a header promises
+that a sample of the same shapes follows (``FLAG_NEXT_SAME``) the receive of that sample's payload
+is posted into a second buffer at once, so the next sample crosses NVLink while the current one
+trains.  Headers are read on the host through a pinned buffer and a side stream: neither the
+receive nor the fan-out waits for the training kernels already queued on the compute stream.
+``timestep_range`` is attached for timestep-expert replicas from ``--moe-step-factor-list``.
 """
 from __future__ import annotations
 
@@ -17,7 +22,8 @@ import torch
 import torch.distributed as dist
 
 from ..parallel import state as mpu
-from .base_encoder import FLAG_LAST, FLAG_STOP, HEADER_INTS, decode_header, numel_of, unpack_tensors
+from .base_encoder import (FLAG_LAST, FLAG_NEXT_SAME, FLAG_STOP, HEADER_INTS, decode_header, encode_header, numel_of,
+                           unpack_tensors)
 from .encoder_service import PolledWork, store, store_has
 
 WAN_SCHEMA = ["context", "clip_feature", "image_emb_y", "latents", "noise"]
@@ -45,8 +51,11 @@ class DistBatchLoader:
         self.group_size = mpu.get_tensor_context_parallel_world_size()
         self.src = mpu.get_tensor_context_parallel_src_rank()
         self.received = 0
+        self.prefetched = 0          # samples whose payload receive was posted before their header arrived
         self.finished = False
         self._pending = None
+        self._pending_payload = None
+        self._side = None
         factors = getattr(args, "moe_step_factor_list", None)
         self.timestep_range = None
         if factors and len(factors) >= 2:
@@ -59,10 +68,28 @@ class DistBatchLoader:
             self._wait(dist.isend(info, dst=self.pair.producer), "the resume handshake")
             self._post_header()
 
+    # ---- host view of a header without touching the compute stream ---------------------------
+    def _header_to_host(self, hdr: torch.Tensor):
+        if not hdr.is_cuda:
+            return hdr
+        if self._side is None:
+            self._side = torch.cuda.Stream()
+            self._hdr_host = torch.empty(HEADER_INTS, dtype=torch.int32).pin_memory()
+            self._hdr_event = torch.cuda.Event()
+        with torch.cuda.stream(self._side):
+            self._hdr_host.copy_(hdr, non_blocking=True)
+            self._hdr_event.record(self._side)
+        self._hdr_event.synchronize()
+        return self._hdr_host.clone()
+
     # ---- leader-side receive with watchdog ------------------------------------------------
     def _post_header(self):
         hdr = torch.zeros(HEADER_INTS, dtype=torch.int32, device=self.dev)
         self._pending = (PolledWork(dist.irecv(hdr, src=self.pair.producer), self.backend), hdr)
+
+    def _post_payload(self, numel: int):
+        blob = torch.empty(numel, dtype=torch.bfloat16, device=self.dev)
+        return PolledWork(dist.irecv(blob, src=self.pair.producer), self.backend), blob
 
     def _wait(self, work, what: str):
         t0 = time.time()
@@ -86,20 +113,31 @@ class DistBatchLoader:
     def _receive(self):
         work, hdr = self._pending
         self._wait(work, "a sample header")
-        shapes, seq, flags = decode_header(hdr.cpu())
+        shapes, seq, flags = decode_header(self._header_to_host(hdr))
         if flags & FLAG_STOP:                      # the producer closed the stream after a stop request
             self.finished, self._pending = True, None
             return None
         if seq != (self.received & 0x7FFFFFFF):
             raise ValueError(f"encoder stream out of order: got sample {seq}, expected {self.received}")
-        blob = torch.empty(numel_of(shapes), dtype=torch.bfloat16, device=self.dev)
-        self._wait(dist.irecv(blob, src=self.pair.producer), "a sample payload")
-        self.received += 1
+        numel = numel_of(shapes)
+        if self._pending_payload is not None:      # posted when the previous header promised this sample
+            pwork, blob = self._pending_payload
+            self._pending_payload = None
+            if blob.numel() != numel:
+                raise ValueError("encoder stream broke its promise: the sample announced as same-shaped is not")
+            self.prefetched += 1
+        else:
+            pwork, blob = self._post_payload(numel)
+        # receives match the producer's sends in order: header n, payload n, header n+1, payload n+1
         if flags & FLAG_LAST:
             self.finished = True
             self._pending = None
         else:
-            self._post_header()  # prefetch: the next header is already in flight while we train
+            self._post_header()                    # the next header is always in flight while we train
+            if flags & FLAG_NEXT_SAME:
+                self._pending_payload = self._post_payload(numel)      # ... and so is its payload, when promised
+        self._wait(pwork, "a sample payload")
+        self.received += 1
         return hdr, blob, shapes
 
     # ---- iterator -------------------------------------------------------------------------------
@@ -107,22 +145,32 @@ class DistBatchLoader:
         return self
 
     def __next__(self) -> Dict[str, torch.Tensor]:
+        stop = False
         if self.is_leader:
-            if self.finished and self._pending is None and self.received > 0 and self._exhausted():
-                raise StopIteration
-            got = self._receive()
+            got = None
+            if not (self.finished and self._pending is None):
+                got = self._receive()
             if got is None:
-                raise StopIteration
-            hdr, blob, shapes = got
+                stop = True
+                hdr, blob, shapes = encode_header([], self.received, FLAG_STOP).to(self.dev), None, None
+            else:
+                hdr, blob, shapes = got
         else:
             hdr = torch.zeros(HEADER_INTS, dtype=torch.int32, device=self.dev)
             blob, shapes = None, None
         if self.group_size > 1:
+            # the header always goes round first, a stop header when the stream is over, so that followers leave
+            # with the leader instead of waiting in a broadcast that never comes
             dist.broadcast(hdr, self.src, group=self.group)
             if not self.is_leader:
-                shapes, _, _ = decode_header(hdr.cpu())
-                blob = torch.empty(numel_of(shapes), dtype=torch.bfloat16, device=self.dev)
-            dist.broadcast(blob, self.src, group=self.group)
+                shapes, _, flags = decode_header(self._header_to_host(hdr))
+                stop = bool(flags & FLAG_STOP)
+                if not stop:
+                    blob = torch.empty(numel_of(shapes), dtype=torch.bfloat16, device=self.dev)
+            if not stop:
+                dist.broadcast(blob, self.src, group=self.group)
+        if stop:
+            raise StopIteration
         tensors = unpack_tensors(blob, shapes)
         batch = {}
         for name, t in zip(self.schema, tensors):
@@ -151,7 +199,7 @@ class DistBatchLoader:
                     break
             time.sleep(0.005)
         issued = int(st.get(key).decode())
-        while self.received < issued:
+        while self.received < issued and self._pending is not None:
             self._receive()
         if self._pending is not None:              # the prefetched header receive: completed by the stop header
             self._receive()

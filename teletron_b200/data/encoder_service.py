@@ -28,7 +28,7 @@ import torch.distributed as dist
 from ..models.registry import encoder_for_model, get_encoder
 from ..parallel import state as mpu
 from ..parallel.state import CommPair
-from .base_encoder import FLAG_LAST, FLAG_STOP, pack_tensors
+from .base_encoder import FLAG_LAST, FLAG_NEXT_SAME, FLAG_STOP, encode_header, pack_tensors
 
 QUEUE_DEPTH = 2
 MAX_OUTSTANDING_SENDS = 1
@@ -167,12 +167,27 @@ def producer_process(args, encoder=None, dataset=None):
             prof = make_torch_profiler(args, "producer")
             prof.__enter__()
         stopping = False
+        promised = {p.consumer: False for p in pairs}   # the last header sent to this consumer carried FLAG_NEXT_SAME
+
+        def send_next(c, may_promise=True):
+            shapes, blob = queues[c].popleft()
+            flags = FLAG_LAST if issued[c] + 1 >= total else 0
+            # promise the following sample when it is already encoded and looks the same: the consumer then
+            # receives it into its second buffer while this one trains
+            promised[c] = bool(may_promise and not flags and queues[c] and queues[c][0][0] == shapes)
+            if promised[c]:
+                flags |= FLAG_NEXT_SAME
+            hdr = encode_header(shapes, issued[c], flags).to(dev)
+            inflight.append((PolledWork(dist.isend(hdr, dst=c), backend), c, hdr))
+            inflight.append((PolledWork(dist.isend(blob, dst=c), backend), c, blob))
+            issued[c] += 1
+
         while True:
             st.set(f"tt_hb_{rank}", str(time.time()))
             inflight = [x for x in inflight if not x[0].done()]
             if not stopping and store_has("tt_stop"):
                 stopping = True
-            done = all(issued[c] >= total for c in issued) or stopping
+            done = all(issued[c] >= total for c in issued) or (stopping and not any(promised.values()))
             if done and not inflight:
                 break
             if not stopping:
@@ -184,25 +199,18 @@ def producer_process(args, encoder=None, dataset=None):
                         shapes = [tuple(t.shape) for t in tensors]
                         for c in g["consumers"]:
                             queues[c].append((shapes, blob))
-                for p in pairs:
-                    c = p.consumer
-                    if queues[c] and sum(1 for x in inflight if x[1] == c) < MAX_OUTSTANDING_SENDS * 2:
-                        shapes, blob = queues[c].popleft()
-                        last = FLAG_LAST if issued[c] + 1 >= total else 0
-                        from .base_encoder import encode_header
-
-                        hdr = encode_header(shapes, issued[c], last).to(dev)
-                        inflight.append((PolledWork(dist.isend(hdr, dst=c), backend), c, hdr))
-                        inflight.append((PolledWork(dist.isend(blob, dst=c), backend), c, blob))
-                        issued[c] += 1
+            for p in pairs:
+                c = p.consumer
+                if stopping and not promised[c]:
+                    continue                      # after a stop request only promised samples still go out
+                if queues[c] and sum(1 for x in inflight if x[1] == c) < MAX_OUTSTANDING_SENDS * 2:
+                    send_next(c, may_promise=not stopping)   # a sample sent while stopping promises nothing further
             if prof is not None:
                 prof.step()
             time.sleep(POLL_SECONDS)
         if stopping:
             # close every unfinished stream with a payload-less header: the consumer's prefetched header receive
             # completes instead of staying in flight until the process group is torn down
-            from .base_encoder import encode_header
-
             closing = []
             for c, n in issued.items():
                 if n < total:

@@ -50,19 +50,22 @@ def _encoder_fed_worker(rank, world):
     from teletron_b200.train import Trainer, make_forward_step
 
     a = _args(world, "--distributed-vae --distributed-vae-world-size 1 --context-parallel-size 2 "
-                     "--encoder-name synthetic_wan_encoder --dataset-type FakeDataset")
+                     "--encoder-name synthetic_wan_encoder --dataset-type FakeDataset --train-iters 5")
     try:
         t = Trainer(a)
     except SystemExit:
         return "encoder-rank-done"
     t.pretrain(make_forward_step())
-    return float(t.buffer.params.float().abs().sum())
+    return float(t.buffer.params.float().abs().sum()), t.train_data_iterator.received, t.train_data_iterator.prefetched
 
 
 def test_training_fed_by_an_encoder_rank():
     outs = run_distributed(_encoder_fed_worker, 3, timeout=240)
     assert outs[2] == "encoder-rank-done"
-    assert outs[0] == outs[1] and outs[0] > 0
+    assert outs[0][0] == outs[1][0] and outs[0][0] > 0
+    # the TP x CP leader received all five samples, and for some of them the encoder had promised the sample ahead, so
+    # the receive of its payload was posted while the previous sample trained (double buffering)
+    assert outs[0][1] == 5 and outs[0][2] >= 1 and outs[1][1:] == (0, 0)
 
 
 def _resilience_worker(rank, world, root, mode):
