@@ -4,14 +4,18 @@
 Architecture and parameter names follow the reference VAE (teletron/models/wan/encoder/
 wan_video_vae.py:34-598) so its checkpoints load: ``encoder.conv1``, ``encoder.downsamples.N``
 (residual blocks, ``Resample`` with ``resample.1`` / ``time_conv``), ``encoder.middle``, ``encoder.head``,
-``conv1`` / ``conv2`` 1x1x1 convolutions, and the mirrored decoder.  The reference walks the clip in
-temporal chunks with a per-layer feature cache to save memory; with causal convolutions that is the
-same function as one pass over the whole clip, which is what this implementation does (180 GB
-of HBM make the cache unnecessary):
-  * temporal down-sampling keeps the first frame and applies the stride-2, kernel-3 ``time_conv``
-    to the whole sequence without padding;
-  * temporal up-sampling keeps the first frame and, for the following frames, applies the causal
-    ``time_conv`` with a zero history and interleaves its two channel halves in time.
+``conv1`` / ``conv2`` 1x1x1 convolutions, and the mirrored decoder.  Two ways to run it, the same function:
+  * one pass over the whole clip (short clips: the 96-channel full-resolution activations of the first stage cost
+    about 0.19 GB per 480P frame in bf16);
+  * in temporal chunks, as the reference does (wan_video_vae.py:121-173, 215-221, 526-576): the encoder takes the
+    first frame, then ``chunk_frames`` (4) frames at a time, the decoder one latent frame at a time, and every
+    causal convolution keeps the last frames of its input as the history of the next chunk (``StreamState``), so
+    activation memory does not grow with the clip length.
+Temporal resampling:
+  * down-sampling keeps the first frame and applies the stride-2, kernel-3 ``time_conv`` to the sequence without
+    padding (across chunks: the last frame of the previous chunk is the first input of the next);
+  * up-sampling keeps the first frame and, for the following frames, applies the causal ``time_conv`` with a zero
+    history and interleaves its two channel halves in time.
 Latents are normalised with the published per-channel mean / std.  ``tiled`` decoding / encoding
 splits H x W into overlapping tiles blended with linear feathering.
 """
@@ -27,8 +31,32 @@ LATENT_STD = [2.8184, 1.4541, 2.3275, 2.6558, 1.2196, 1.7708, 2.6052, 2.0743,
               3.2687, 2.1526, 2.8652, 1.5579, 1.6382, 1.1253, 2.8251, 1.9160]
 
 
+class StreamState(dict):
+    """Per-layer history of a clip that is fed chunk by chunk: causal convolutions store the last frames of their
+    input here (keyed by the module), resampling layers whether they have seen the first frame."""
+
+
+_STREAM = None  # the StreamState of the chunked pass in progress (None: whole-clip pass)
+
+
+class _streaming:
+    def __init__(self, state: StreamState):
+        self.state = state
+
+    def __enter__(self):
+        global _STREAM
+        self.prev, _STREAM = _STREAM, self.state
+        return self.state
+
+    def __exit__(self, *exc):
+        global _STREAM
+        _STREAM = self.prev
+        return False
+
+
 class CausalConv3d(nn.Conv3d):
-    """Conv3d that pads only the past along time (2 * pad_t frames in front, none behind)."""
+    """Conv3d that pads only the past along time (2 * pad_t frames in front, none behind).  In a chunked pass the
+    "past" of a chunk is the tail of the previous chunk's input instead of zeros."""
 
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)
@@ -36,7 +64,15 @@ class CausalConv3d(nn.Conv3d):
         self.padding = (0, 0, 0)
 
     def forward(self, x):
-        return super().forward(F.pad(x, self._pad))
+        tpad = self._pad[4]
+        if _STREAM is None or tpad == 0:
+            return super().forward(F.pad(x, self._pad))
+        hist = _STREAM.get(self)
+        if hist is None:
+            hist = x.new_zeros(x.shape[0], x.shape[1], tpad, x.shape[3], x.shape[4])
+        xin = torch.cat([hist, x], dim=2)
+        _STREAM[self] = xin[:, :, -tpad:].clone()
+        return super().forward(F.pad(xin, self._pad[:4] + (0, 0)))
 
 
 class RMS_norm(nn.Module):
@@ -78,16 +114,36 @@ class Resample(nn.Module):
 
     def forward(self, x):
         b, c, t, h, w = x.shape
-        if self.mode == "upsample3d" and t > 1:
-            rest = self.time_conv(x[:, :, 1:])                      # zero history for the frames after the first
-            rest = rest.reshape(b, 2, c, t - 1, h, w)
-            rest = torch.stack((rest[:, 0], rest[:, 1]), dim=3).reshape(b, c, 2 * (t - 1), h, w)
-            x = torch.cat([x[:, :, :1], rest], dim=2)
+        st = _STREAM
+        first = st is None or ("seen", self) not in st       # this call holds the clip's first frame
+        if st is not None:
+            st[("seen", self)] = True
+        if self.mode == "upsample3d":
+            keep = 1 if first else 0                          # the clip's first frame is not doubled
+            if t > keep:
+                rest = self.time_conv(x[:, :, keep:])         # zero history for the first frame that goes through
+                rest = rest.reshape(b, 2, c, t - keep, h, w)
+                rest = torch.stack((rest[:, 0], rest[:, 1]), dim=3).reshape(b, c, 2 * (t - keep), h, w)
+                x = torch.cat([x[:, :, :keep], rest], dim=2)
         if self.mode != "none":
             x = _per_frame(lambda y: self.resample(y.float()).to(y.dtype) if isinstance(self.resample[0], nn.Upsample)
                            else self.resample(y), x)
-        if self.mode == "downsample3d" and x.shape[2] > 1:
-            x = torch.cat([x[:, :, :1], nn.Conv3d.forward(self.time_conv, x)], dim=2)  # no padding, stride 2
+        if self.mode == "downsample3d":
+            if st is None:
+                if x.shape[2] > 1:
+                    x = torch.cat([x[:, :, :1], nn.Conv3d.forward(self.time_conv, x)], dim=2)  # no padding, stride 2
+            else:
+                # the stride-2 windows continue across chunks: the previous chunk's last frame opens this chunk's
+                # first window, so a chunk after the first has to bring an even number of frames
+                last = x[:, :, -1:].clone()
+                if first:
+                    if x.shape[2] > 1:
+                        assert (x.shape[2] - 1) % 2 == 0, "the first chunk takes 1 + 2k frames"
+                        x = torch.cat([x[:, :, :1], nn.Conv3d.forward(self.time_conv, x)], dim=2)
+                else:
+                    assert x.shape[2] % 2 == 0, "chunks after the first take an even number of frames per stage"
+                    x = nn.Conv3d.forward(self.time_conv, torch.cat([st[("last", self)], x], dim=2))
+                st[("last", self)] = last
         return x
 
 
@@ -186,15 +242,35 @@ class VideoVAE_(nn.Module):
         self.conv2 = CausalConv3d(z_dim, z_dim, 1)
         self.decoder = Decoder3d(dim, z_dim, dim_mult, num_res_blocks, attn_scales, temperal_downsample[::-1], dropout)
 
-    def encode(self, x, scale):
-        mu, _logvar = self.conv1(self.encoder(x)).chunk(2, dim=1)
+    def encode(self, x, scale, chunk_frames: int = 0):
+        """``chunk_frames`` > 0: the first frame, then that many frames at a time (a multiple of 4), with the
+        convolutions' history carried between chunks."""
+        if chunk_frames and x.shape[2] > 1:
+            assert chunk_frames % 4 == 0 and (x.shape[2] - 1) % 4 == 0, "chunks of 4k frames after the first frame"
+            outs = []
+            with _streaming(StreamState()):
+                outs.append(self.encoder(x[:, :, :1]))
+                for t0 in range(1, x.shape[2], chunk_frames):
+                    outs.append(self.encoder(x[:, :, t0:t0 + chunk_frames]))
+            h = torch.cat(outs, dim=2)
+        else:
+            h = self.encoder(x)
+        mu, _logvar = self.conv1(h).chunk(2, dim=1)
         mean, inv_std = scale
         return (mu - mean.view(1, -1, 1, 1, 1)) * inv_std.view(1, -1, 1, 1, 1)
 
-    def decode(self, z, scale):
+    def decode(self, z, scale, chunk_frames: int = 0):
+        """``chunk_frames`` > 0: that many latent frames at a time (the reference decodes one by one)."""
         mean, inv_std = scale
         z = z / inv_std.view(1, -1, 1, 1, 1) + mean.view(1, -1, 1, 1, 1)
-        return self.decoder(self.conv2(z)).clamp_(-1, 1)
+        x = self.conv2(z)
+        if chunk_frames and x.shape[2] > 1:
+            outs = []
+            with _streaming(StreamState()):
+                for t0 in range(0, x.shape[2], chunk_frames):
+                    outs.append(self.decoder(x[:, :, t0:t0 + chunk_frames]).clamp_(-1, 1))
+            return torch.cat(outs, dim=2)
+        return self.decoder(x).clamp_(-1, 1)
 
 
 class WanVideoVAE(nn.Module):
@@ -261,30 +337,41 @@ class WanVideoVAE(nn.Module):
                 wsum[:, :, :, y0:y0 + oh, x0:x0 + ow] += m
         return (acc / wsum.clamp_min(1e-6)).to(x.dtype)
 
+    # frames per chunk: None = decide by clip length (whole clip up to `whole_clip_frames` frames, chunked beyond),
+    # 0 = always the whole clip, n = chunks of n frames (encoder; multiple of 4) / n latent frames (decoder)
+    whole_clip_frames = 33
+
+    def _chunk(self, frames: int, chunk_frames, default: int) -> int:
+        if chunk_frames is None:
+            return default if frames > self.whole_clip_frames else 0
+        return int(chunk_frames)
+
     @torch.no_grad()
-    def encode(self, videos, device=None, tiled=False, tile_size=(34, 34), tile_stride=(18, 16)):
+    def encode(self, videos, device=None, tiled=False, tile_size=(34, 34), tile_stride=(18, 16), chunk_frames=None):
         outs = []
         for v in videos:
             x = v.unsqueeze(0).to(device or v.device)
             scale = self._scale(x)
+            ck = self._chunk(x.shape[2], chunk_frames, 4)
             if tiled:
                 tile = (tile_size[0] * 8, tile_size[1] * 8)
                 stride = (tile_stride[0] * 8, tile_stride[1] * 8)
-                z = self._tiled(lambda t: self.model.encode(t, scale), x, tile, stride, 1 / 8, self.z_dim)
+                z = self._tiled(lambda t: self.model.encode(t, scale, ck), x, tile, stride, 1 / 8, self.z_dim)
             else:
-                z = self.model.encode(x, scale)
+                z = self.model.encode(x, scale, ck)
             outs.append(z.squeeze(0))
         return torch.stack(outs)
 
     @torch.no_grad()
-    def decode(self, latents, device=None, tiled=False, tile_size=(34, 34), tile_stride=(18, 16)):
+    def decode(self, latents, device=None, tiled=False, tile_size=(34, 34), tile_stride=(18, 16), chunk_frames=None):
         outs = []
         for z in latents:
             z = z.unsqueeze(0).to(device or z.device)
             scale = self._scale(z)
+            ck = self._chunk(4 * (z.shape[2] - 1) + 1, chunk_frames, 1)
             if tiled:
-                v = self._tiled(lambda t: self.model.decode(t, scale), z, tile_size, tile_stride, 8, 3)
+                v = self._tiled(lambda t: self.model.decode(t, scale, ck), z, tile_size, tile_stride, 8, 3)
             else:
-                v = self.model.decode(z, scale)
+                v = self.model.decode(z, scale, ck)
             outs.append(v.squeeze(0))
         return torch.stack(outs)

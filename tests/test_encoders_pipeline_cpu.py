@@ -315,3 +315,118 @@ def test_model_manager_loads_a_published_style_vae_file(tmp_path):
     assert mm.fetch_model("wan_video_vae") is loaded and not any(b.is_meta for b in loaded.buffers())
     x = torch.randn(3, 5, 32, 32)
     assert torch.equal(loaded.encode([x], device="cpu"), vae.encode([x], device="cpu"))
+
+
+# ------------------------------------------------------------------------------ parity with the reference's encoder files
+def _load_reference_module(rel, name, stubs=None):
+    """Load one file of the reference by path (its package imports Megatron on import, its files mostly do not)."""
+    import importlib.util
+    import sys
+    import types
+
+    import pytest
+    from conftest import reference_file
+
+    path = reference_file(rel)
+    if path is None:
+        pytest.skip("reference tree not available")
+    added = []
+    for mod_name, attrs in (stubs or {}).items():
+        parts = mod_name.split(".")
+        for i in range(1, len(parts) + 1):
+            n = ".".join(parts[:i])
+            if n not in sys.modules:
+                sys.modules[n] = types.ModuleType(n)
+                added.append(n)
+        for k, v in attrs.items():
+            setattr(sys.modules[mod_name], k, v)
+    try:
+        spec = importlib.util.spec_from_file_location(name, path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    finally:
+        for n in added:
+            sys.modules.pop(n, None)
+    return mod
+
+
+def test_vae_matches_the_reference_file_whole_clip_and_chunked():
+    """Same state dict in the reference's VideoVAE_ (which walks the clip in chunks with its per-layer cache) and
+    here: encode and decode agree for the whole-clip pass and for the chunked pass, which also agree with each other."""
+    from teletron_b200.models.encoders.wan_vae import WanVideoVAE
+
+    ref = _load_reference_module("teletron/models/wan/encoder/wan_video_vae.py", "ref_wan_vae")
+    torch.manual_seed(0)
+    vae = WanVideoVAE(dim=8).float()
+    for p in vae.model.parameters():
+        torch.nn.init.normal_(p, std=0.15)
+    rv = ref.VideoVAE_(dim=8, z_dim=16).float().eval()
+    missing, unexpected = rv.load_state_dict(vae.model.state_dict(), strict=True)
+    assert not missing and not unexpected
+    x = torch.rand(1, 3, 17, 32, 48) * 2 - 1
+    scale = [vae.mean, vae.inv_std]
+    with torch.no_grad():
+        z_ref = rv.encode(x, scale)
+        v_ref = rv.decode(z_ref, scale).clamp_(-1, 1)
+    z_whole = vae.encode([x[0]], chunk_frames=0)
+    z_chunk = vae.encode([x[0]], chunk_frames=4)
+    z_chunk8 = vae.encode([x[0]], chunk_frames=8)
+    tol = 1e-5 * max(1.0, float(z_ref.abs().max()))
+    assert z_whole.shape == z_ref.shape == (1, 16, 5, 4, 6)
+    assert float((z_whole - z_ref).abs().max()) < tol and float((z_chunk - z_ref).abs().max()) < tol
+    assert float((z_chunk8 - z_whole).abs().max()) < tol
+    v_whole = vae.decode(z_ref, chunk_frames=0)
+    v_chunk = vae.decode(z_ref, chunk_frames=1)
+    v_chunk2 = vae.decode(z_ref, chunk_frames=2)
+    assert v_whole.shape == v_ref.shape == (1, 3, 17, 32, 48)
+    assert float((v_whole - v_ref).abs().max()) < 1e-4 and float((v_chunk - v_ref).abs().max()) < 1e-4
+    assert float((v_chunk2 - v_whole).abs().max()) < 1e-4
+    # long clips switch to chunks by themselves
+    assert vae._chunk(81, None, 4) == 4 and vae._chunk(17, None, 4) == 0 and vae._chunk(81, 0, 4) == 0
+
+
+def test_umt5_encoder_matches_the_reference_file():
+    from teletron_b200.models.encoders.umt5 import UMT5Encoder
+
+    ref = _load_reference_module("teletron/models/wan/encoder/wan_video_text_encoder.py", "ref_wan_t5")
+    torch.manual_seed(0)
+    kw = dict(vocab=200, dim=64, dim_attn=64, dim_ffn=160, num_heads=4, num_layers=3, num_buckets=32, shared_pos=False)
+    rm = ref.WanTextEncoder(dropout=0.0, **kw).float().eval()
+    m = UMT5Encoder(**kw).float().eval()
+    missing, unexpected = m.load_state_dict(rm.state_dict(), strict=True)
+    assert not missing and not unexpected
+    ids = torch.randint(0, 200, (2, 24))
+    mask = torch.ones(2, 24, dtype=torch.long)
+    mask[0, 17:] = 0
+    mask[1, 9:] = 0
+    with torch.no_grad():
+        a, b = rm(ids, mask), m(ids, mask)
+    assert a.shape == b.shape == (2, 24, 64)
+    assert float((a - b).abs().max()) < 1e-4 * max(1.0, float(a.abs().max()))
+
+
+def test_clip_vision_tower_matches_the_reference_file():
+    """The reference's ViT (open-CLIP ViT-H/14 layout: pre-norm, GELU MLP, class token) with the same weights: the
+    tokens after the second-to-last block are the i2v conditioning features."""
+    import torch.nn.functional as F
+    from einops import rearrange
+
+    from teletron_b200.models.encoders.clip_vit import VisionTransformer
+
+    def flash_attention(q, k, v, num_heads, compatibility_mode=False):   # what wan_model.py does in that mode
+        q, k, v = (rearrange(t, "b s (n d) -> b n s d", n=num_heads) for t in (q, k, v))
+        return rearrange(F.scaled_dot_product_attention(q, k, v), "b n s d -> b s (n d)")
+
+    ref = _load_reference_module("teletron/models/wan/encoder/wan_video_image_encoder.py", "ref_wan_clip",
+                                 stubs={"teletron.models.wan.wan_model": {"flash_attention": flash_attention}})
+    torch.manual_seed(0)
+    rm = ref.VisionTransformer(image_size=56, patch_size=14, dim=64, mlp_ratio=4, out_dim=32, num_heads=4, num_layers=4,
+                               pool_type="token", pre_norm=True, post_norm=False, activation="gelu").float().eval()
+    m = VisionTransformer(image_size=56, patch=14, dim=64, heads=4, layers=4, mlp_ratio=4, out_dim=32).float().eval()
+    missing, unexpected = m.load_state_dict(rm.state_dict(), strict=True)
+    assert not missing and not unexpected
+    x = torch.randn(2, 3, 56, 56)
+    with torch.no_grad():
+        a, b = rm(x, use_31_block=True), m(x, use_31_block=True)
+    assert a.shape == b.shape == (2, 17, 64)
+    assert float((a - b).abs().max()) < 1e-4 * max(1.0, float(a.abs().max()))
