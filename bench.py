@@ -106,18 +106,19 @@ def dist_env():
 
 
 # ------------------------------------------------------------------------------ ours
-def candidate_layouts(world: int, gbs: int, cp_flag: int):
+def candidate_layouts(world: int, gbs: int, cp_flag: int, tp: int = 1):
     """Ulysses sizes to measure at `world` GPUs: the one asked for, or every power of two that divides the world and
     leaves a data-parallel size that divides the global batch; data parallelism only (cp = 1) comes last."""
     if cp_flag > 0:
         return [cp_flag]
+    world //= tp
     out = [cp for cp in (8, 4, 2, 1) if cp <= world and world % cp == 0 and gbs % (world // cp) == 0]
     return out or [world]
 
 
-def layout_name(world: int, cp: int) -> str:
-    dp = world // cp
-    return f"dp{dp}" + (f"xcp{cp}" if cp > 1 else "")
+def layout_name(world: int, cp: int, tp: int = 1) -> str:
+    dp = world // (cp * tp)
+    return f"dp{dp}" + (f"xtp{tp}" if tp > 1 else "") + (f"xcp{cp}" if cp > 1 else "")
 
 
 def run_ours(a):
@@ -130,6 +131,7 @@ def run_ours(a):
     from teletron_b200.ops import _lib
     from teletron_b200.parallel import state as mpu
     from teletron_b200.train import Trainer, make_forward_step, parse_args
+    from teletron_b200.train.hunyuan_step import make_hunyuan_forward_step
 
     rank, world, local = dist_env()
     assert world == a.gpus, f"WORLD_SIZE {world} != --gpus {a.gpus} (launch N > 1 under torchrun)"
@@ -139,22 +141,30 @@ def run_ours(a):
     headline = (a.model == "wan2.1-1.3b-t2v" and (frames, height, width, gbs) == (FRAMES, HEIGHT, WIDTH, GLOBAL_BATCH))
     tok_sample = tokens_per_sample(frames, height, width)
     i2v = "i2v" in a.model
+    hunyuan = a.model.startswith("hunyuan")
+    tp = a.tp
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    fwd = make_forward_step()
+    fwd = make_hunyuan_forward_step() if hunyuan else make_forward_step()
     # the same global batch at every N and in every layout: sample i (latents, text, noise, timestep) is a function
     # of i alone, and data-parallel rank d takes samples [d * n_mb, (d + 1) * n_mb)
-    ds = SyntheticLatentDataset(frames, height, width, i2v=i2v, seed=1234, fixed_noise=True)
+    if hunyuan:
+        from teletron_b200.data.fake import SyntheticHunyuanDataset
+
+        ds = SyntheticHunyuanDataset(frames, height, width, i2v=i2v, seed=1234)
+    else:
+        ds = SyntheticLatentDataset(frames, height, width, i2v=i2v, seed=1234, fixed_noise=True)
 
     def build(cp):
-        argv = ["--model", "ParallelWanModel", "--model-preset", a.model, "--bf16", "--micro-batch-size", "1",
+        argv = ["--model", "ParallelHunyuanVideoModel" if hunyuan else "ParallelWanModel", "--model-preset", a.model,
+                "--tensor-model-parallel-size", str(tp), "--bf16", "--micro-batch-size", "1",
                 "--global-batch-size", str(gbs), "--train-iters", "1000000", "--lr", "1e-5",
                 "--weight-decay", "1e-2", "--clip-grad", "1.0", "--context-parallel-size", str(cp),
                 "--num-frames", str(frames), "--video-resolution", str(height), str(width), "--synthetic-latents",
                 "--log-interval", "1000000", "--seed", "1234"]
         if i2v:
             argv += ["--task-type", "i2v"]
-        if a.init_on_device or "14b" in a.model:
+        if a.init_on_device or "14b" in a.model or "13b" in a.model:
             argv.append("--init-on-device")
         if world > 1:
             argv.append("--use-distributed-optimizer")
@@ -226,13 +236,13 @@ def run_ours(a):
         _lib.check_status()
         return first
 
-    cands = candidate_layouts(world, gbs, a.cp)
+    cands = candidate_layouts(world, gbs, a.cp, tp)
     layouts = {}
     tr = host = dev_pool = None
     built = None
     trial_steps, trial_warm = 3, 3
     for i, cp in enumerate(cands):
-        name = layout_name(world, cp)
+        name = layout_name(world, cp, tp)
         try:
             tr, host, dev_pool = build(cp)
             built = cp
@@ -257,7 +267,7 @@ def run_ours(a):
         if not ok:
             raise SystemExit(f"no layout ran: {layouts}")
         best = max(ok, key=lambda k: ok[k]["tokens_per_s"])
-        best_cp = next(c for c in cands if layout_name(world, c) == best)
+        best_cp = next(c for c in cands if layout_name(world, c, tp) == best)
         if built != best_cp:
             if tr is not None:
                 teardown(tr)
@@ -270,7 +280,6 @@ def run_ours(a):
     else:
         cp = cands[0]
         first_loss = warm(tr, dev_pool, a.warmup)
-    dp = world // cp
     targs = tr.args
     n_mb = targs.num_micro_batches
     bytes_h2d_per_mb = sum(v.numel() * v.element_size() for v in host[0].values())
@@ -290,8 +299,12 @@ def run_ours(a):
     if rank == 0:
         inner = getattr(tr.model, "module", tr.model)
         cfg = inner.cfg
-        desc = (f"{a.model} ({cfg.num_layers} layers, dim {cfg.dim}, {cfg.num_heads}x{cfg.dim // cfg.num_heads} heads, "
-                f"ffn {cfg.ffn_dim})")
+        if hunyuan:
+            desc = (f"{a.model} ({cfg.num_layers} dual + {cfg.num_single_layers} single blocks, hidden {cfg.hidden_size}, "
+                    f"{cfg.num_attention_heads}x{cfg.attention_head_dim} heads)")
+        else:
+            desc = (f"{a.model} ({cfg.num_layers} layers, dim {cfg.dim}, {cfg.num_heads}x{cfg.dim // cfg.num_heads} "
+                    f"heads, ffn {cfg.ffn_dim})")
         if headline:
             metric, published = METRIC, PUBLISHED_TOKENS_PER_S_PER_GPU
             desc = "Wan2.1-1.3B t2v (30 layers, dim 1536, 12x128 heads, ffn 8960)"
@@ -310,7 +323,7 @@ def run_ours(a):
             "impl": "teletron_b200",
             "config": {"model": desc,
                        "global_batch": gbs, "seq_len": tok_sample,
-                       "parallelism": layout_name(world, cp), "micro_batches_per_step": n_mb,
+                       "parallelism": layout_name(world, cp, tp), "micro_batches_per_step": n_mb,
                        "layout_choice": ("the fastest of `layouts` (3 + 3 step trials of every Ulysses size that "
                                          "divides the GPUs)" if len(cands) > 1 else "only candidate"),
                        "optimizer": "AdamW fp32 master" + (" (sharded)" if world > 1 else ""),
@@ -554,6 +567,7 @@ def main(argv=None):
     ap.add_argument("--model", type=str, default="wan2.1-1.3b-t2v")
     ap.add_argument("--cp", type=int, default=0, help="Ulysses context-parallel size, the rest is DP (0: measure every "
                                                        "size that divides the GPUs, report all, headline = the fastest)")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (HunyuanVideo)")
     ap.add_argument("--no-overlap", action="store_true", help="reduce gradients after backward instead of during it")
     ap.add_argument("--recompute", action="store_true", help="full activation recompute (not needed at 1.3B)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (invalid as a result)")

@@ -343,10 +343,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int which = 0; which < 2; ++which) {  // 0: dV, 1: dK
         bf16* dst;
         if (which == 0)
-          dst = (p.sc1.mode == 2 && row < p.Skv) ? scatter_dst(p.sc1, b, row, h)
+          dst = scatter_row(p.sc1, row, p.Skv) ? scatter_dst(p.sc1, b, row, h)
                                                  : p.out1 + (long long)b * p.bs1 + (long long)row * p.ld1 + h * 128;
         else
-          dst = (p.sc0.mode == 2 && row < p.Skv) ? scatter_dst(p.sc0, b, row, h)
+          dst = scatter_row(p.sc0, row, p.Skv) ? scatter_dst(p.sc0, b, row, h)
                                                  : p.out0 + (long long)b * p.bs0 + (long long)row * p.ld0 + h * 128;
         const float mul = which == 0 ? 1.f : p.scale;
 #pragma unroll 1
@@ -623,7 +623,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
-      bf16* dst = (p.sc0.mode == 2 && row < p.Sq) ? scatter_dst(p.sc0, b, row, h)
+      bf16* dst = scatter_row(p.sc0, row, p.Sq) ? scatter_dst(p.sc0, b, row, h)
                                                   : p.out0 + (long long)b * p.bs0 + (long long)row * p.ld0 + h * 128;
 #pragma unroll 1
       for (int c = wg * 2; c < wg * 2 + 2; ++c) {
@@ -812,20 +812,25 @@ TT_API int tt_attn_bwd(const void* q, long long ldq, long long q_bs, const void*
                        status, nullptr, nullptr, nullptr, stream);
 }
 
-// Backward over head-parallel tensors [B, S_pad, Hl, D]; dQ, dK, dV are stored with the Ulysses
-// head -> seq pattern into every peer's [B, S_l, H_total, D] buffers (three peer tables) whose token stride is
-// `dst_ld` elements (0 = H_total * D; larger when the three are column blocks of one [rows, 3 * H_total * D]
-// matrix).  `heads` <= Hl of this rank's head slots hold real heads; lse and scratch are sized for `heads`.
+// Backward over head-parallel tensors [B, S_total, Hl, D]; dQ, dK, dV of the first S_pad rows of every sample are
+// stored with the Ulysses head -> seq pattern into every peer's [B, S_l, H_total, D] buffers (three peer tables) whose
+// token stride is `dst_ld` elements (0 = H_total * D; larger when the three are column blocks of one
+// [rows, 3 * H_total * D] matrix).  Rows S_pad .. S_total (the replicated text tokens of a joint sequence; none when
+// S_total == S_pad) stay local: their dQ / dK / dV go to `dq_local` / `dk_local` / `dv_local` ([B, S_total, Hl, D],
+// may be null when there are none).  `heads` <= Hl of this rank's head slots hold real heads; lse and scratch are
+// sized for `heads` and S_total.
 TT_API int tt_attn_bwd_scatter(const void* q, const void* k, const void* v, const void* o, const void* dout,
                                const float* lse, float* scratch, const long long* dq_peers,
                                const long long* dk_peers, const long long* dv_peers, long long dst_ld,
-                               const int* kv_lens, int B, int Hl, int heads, int H_total, int S_pad, int D,
-                               float scale, int world, int rank, unsigned* status, cudaStream_t stream) {
+                               void* dq_local, void* dk_local, void* dv_local, const int* kv_lens, int B, int Hl,
+                               int heads, int H_total, int S_pad, int S_total, int D, float scale, int world,
+                               int rank, unsigned* status, cudaStream_t stream) {
   TT_CHECK(world >= 1 && world <= TT_MAX_PEERS && rank >= 0 && rank < world, "attn_bwd_scatter: bad world/rank");
-  TT_CHECK(S_pad % world == 0, "attn_bwd_scatter: padded sequence must divide by the group size");
+  TT_CHECK(S_pad % world == 0 && S_total >= S_pad, "attn_bwd_scatter: padded sequence must divide by the group size");
   TT_CHECK(heads >= 1 && heads <= Hl && rank * Hl + heads <= H_total && H_total <= Hl * world,
            "attn_bwd_scatter: head slots do not match the head count");
   TT_CHECK(dst_ld == 0 || (dst_ld >= (long long)H_total * D && dst_ld % 8 == 0), "attn_bwd_scatter: bad destination stride");
+  TT_CHECK(S_total == S_pad || (dq_local && dk_local && dv_local), "attn_bwd_scatter: rows that stay local need local outputs");
   TTScatter sc[3];
   const long long* tabs[3] = {dq_peers, dk_peers, dv_peers};
   for (int t = 0; t < 3; ++t) {
@@ -835,11 +840,13 @@ TT_API int tt_attn_bwd_scatter(const void* q, const void* k, const void* v, cons
       TT_CHECK(sc[t].peer[i] && ((uintptr_t)sc[t].peer[i] & 15) == 0, "attn_bwd_scatter: bad peer pointer");
     }
     sc[t].mode = 2; sc[t].S_l = S_pad / world; sc[t].S_pad = S_pad; sc[t].Hl = Hl; sc[t].H = H_total;
-    sc[t].D = D; sc[t].rank = rank; sc[t].world = world; sc[t].ld = dst_ld;
+    sc[t].D = D; sc[t].rank = rank; sc[t].world = world; sc[t].ld = dst_ld; sc[t].n_rows = S_pad;
   }
-  const long long ld = (long long)Hl * D, bs = (long long)S_pad * Hl * D;
-  // dq/dk/dv local pointers are unused in scatter mode; pass q as an aligned placeholder
-  return attn_bwd_impl(q, ld, bs, k, ld, bs, v, ld, bs, o, ld, bs, dout, ld, bs, lse, scratch,
-                       const_cast<void*>(q), ld, bs, const_cast<void*>(q), ld, bs, const_cast<void*>(q), ld, bs,
-                       kv_lens, B, heads, S_pad, S_pad, D, scale, status, &sc[0], &sc[1], &sc[2], stream);
+  const long long ld = (long long)Hl * D, bs = (long long)S_total * Hl * D;
+  // without local rows the local output pointers are never used; q is an aligned placeholder then
+  void* lq = dq_local ? dq_local : const_cast<void*>(q);
+  void* lk = dk_local ? dk_local : const_cast<void*>(q);
+  void* lv = dv_local ? dv_local : const_cast<void*>(q);
+  return attn_bwd_impl(q, ld, bs, k, ld, bs, v, ld, bs, o, ld, bs, dout, ld, bs, lse, scratch, lq, ld, bs, lk, ld, bs,
+                       lv, ld, bs, kv_lens, B, heads, S_total, S_total, D, scale, status, &sc[0], &sc[1], &sc[2], stream);
 }

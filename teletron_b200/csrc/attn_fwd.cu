@@ -272,7 +272,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int row = q0 + t * TILE + r;
       const float inv = 1.f / l;
       bf16* orow = p.O + (long long)b * p.o_batch_stride + (long long)row * p.ldo + h * 128;
-      bf16* prow = (p.sc.mode == 2 && row < p.Sq) ? scatter_dst(p.sc, b, row, h) : nullptr;
+      bf16* prow = scatter_row(p.sc, row, p.Sq) ? scatter_dst(p.sc, b, row, h) : nullptr;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
@@ -360,18 +360,20 @@ TT_API int tt_attn_fwd(const void* q, long long ldq, long long q_bs, const void*
                        scale, status, sc, stream);
 }
 
-// Attention over head-parallel tensors [B, S_pad, Hl, D] whose epilogue also stores O with the
-// Ulysses head -> seq pattern into every peer's [B, S_l, H_total, D] buffer (peer_ptrs), in
-// addition to the local head-layout copy `o` that the backward pass needs.  `heads` <= Hl is how many of this
-// rank's head slots hold real heads (H_total need not divide by the group size: the last ranks own fewer);
-// lse is [B, heads, S_pad].
+// Attention over head-parallel tensors [B, S_total, Hl, D] whose epilogue also stores the first S_pad rows of O of
+// every sample with the Ulysses head -> seq pattern into every peer's [B, S_l, H_total, D] buffer (peer_ptrs), in
+// addition to the local head-layout copy `o` that the backward pass needs (and that is the only copy of rows
+// S_pad .. S_total, the replicated text tokens of a joint sequence).  `heads` <= Hl is how many of this rank's head
+// slots hold real heads (H_total need not divide by the group size: the last ranks own fewer); lse is
+// [B, heads, S_total].
 TT_API int tt_attn_fwd_scatter(const void* q, long long ldq, long long q_bs, const void* k, long long ldk,
                                long long k_bs, const void* v, long long ldv, long long v_bs, void* o,
                                long long ldo, long long o_bs, float* lse, const int* kv_lens, int B, int Hl,
-                               int heads, int H_total, int S_pad, int D, float scale, const long long* peer_ptrs,
-                               int world, int rank, unsigned* status, cudaStream_t stream) {
+                               int heads, int H_total, int S_pad, int S_total, int D, float scale,
+                               const long long* peer_ptrs, int world, int rank, unsigned* status,
+                               cudaStream_t stream) {
   TT_CHECK(world >= 1 && world <= TT_MAX_PEERS && rank >= 0 && rank < world, "attn_fwd_scatter: bad world/rank");
-  TT_CHECK(S_pad % world == 0, "attn_fwd_scatter: padded sequence must divide by the group size");
+  TT_CHECK(S_pad % world == 0 && S_total >= S_pad, "attn_fwd_scatter: padded sequence must divide by the group size");
   TT_CHECK(heads >= 1 && heads <= Hl && rank * Hl + heads <= H_total && H_total <= Hl * world,
            "attn_fwd_scatter: head slots %d x %d ranks do not match %d heads (%d on rank %d)", Hl, world, H_total,
            heads, rank);
@@ -382,7 +384,7 @@ TT_API int tt_attn_fwd_scatter(const void* q, long long ldq, long long q_bs, con
     TT_CHECK(sc.peer[i] && ((uintptr_t)sc.peer[i] & 15) == 0, "attn_fwd_scatter: bad peer pointer %d", i);
   }
   sc.mode = 2; sc.S_l = S_pad / world; sc.S_pad = S_pad; sc.Hl = Hl; sc.H = H_total; sc.D = D;
-  sc.rank = rank; sc.world = world;
-  return attn_fwd_impl(q, ldq, q_bs, k, ldk, k_bs, v, ldv, v_bs, o, ldo, o_bs, lse, kv_lens, B, heads, S_pad,
-                       S_pad, D, scale, status, sc, stream);
+  sc.rank = rank; sc.world = world; sc.n_rows = S_pad;
+  return attn_fwd_impl(q, ldq, q_bs, k, ldk, k_bs, v, ldv, v_bs, o, ldo, o_bs, lse, kv_lens, B, heads, S_total,
+                       S_total, D, scale, status, sc, stream);
 }

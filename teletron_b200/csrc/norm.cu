@@ -836,11 +836,14 @@ TT_API int tt_rmsrope_fwd(const void* x, long long ldx, void* y, long long ldy, 
 // pattern (TTScatter mode 1): x is this rank's [B*S_l, H*D] shard, the output lands in every
 // peer's [B, S_pad, ceil(H / world), D] buffer. peer_ptrs: `world` device addresses of those buffers.
 // ssq (optional): [rows, ssq_ld] fp32 whose first ssq_n entries per row add up to the row's sum of squares
-// (written by tt_gemm_qkv_a2a), used instead of reducing the row again.
+// (written by tt_gemm_qkv_a2a), used instead of reducing the row again.  dst_rows (0 = S_pad): rows per sample of the
+// peers' buffers when they hold more than the exchanged tokens (joint video + text sequences).
 TT_API int tt_rmsrope_fwd_scatter(const void* x, long long ldx, const float* w, const void* freqs,
                                   int freq_rows, float* rstd, int rows, int C, int D, int per_head,
                                   float eps, const long long* peer_ptrs, int world, int rank, int S_l,
-                                  int S_pad, const float* ssq, int ssq_n, long long ssq_ld, cudaStream_t stream) {
+                                  int S_pad, const float* ssq, int ssq_n, long long ssq_ld, int dst_rows,
+                                  cudaStream_t stream) {
+  TT_CHECK(dst_rows == 0 || dst_rows >= S_pad, "rmsrope_fwd_scatter: destination holds fewer rows than the sequence");
   TT_CHECK(world >= 1 && world <= TT_MAX_PEERS && rank >= 0 && rank < world, "rmsrope_fwd_scatter: bad world/rank");
   const int H = C / D;
   TT_CHECK(S_l > 0 && S_pad == S_l * world && rows % S_l == 0, "rmsrope_fwd_scatter: bad sequence split");
@@ -851,7 +854,7 @@ TT_API int tt_rmsrope_fwd_scatter(const void* x, long long ldx, const float* w, 
     TT_CHECK(sc.peer[i] && ((uintptr_t)sc.peer[i] & 15) == 0, "rmsrope_fwd_scatter: bad peer pointer %d", i);
   }
   sc.mode = 1; sc.S_l = S_l; sc.S_pad = S_pad; sc.Hl = (H + world - 1) / world; sc.H = H; sc.D = D; sc.rank = rank;
-  sc.world = world;
+  sc.world = world; sc.dst_rows = dst_rows;
   return rmsrope_fwd_impl(x, ldx, const_cast<void*>(x), ldx, w, freqs, freq_rows, rstd, rows, C, D, per_head, eps, sc,
                           stream, ssq, ssq_n, ssq_ld);
 }

@@ -78,12 +78,16 @@ enum : unsigned {
 // mode 0 means "no scatter" (store locally).
 // H need not divide by the group size: Hl = ceil(H / world), the last ranks own fewer (or no) heads and callers
 // run only the heads that exist.
+// Joint sequences (video tokens followed by replicated text tokens): the head-parallel buffers hold `dst_rows` rows per
+// sample (0 = S_pad) of which only the first `n_rows` (0 = all) take part in the exchange; a kernel that scatters
+// (mode 2) stores rows >= n_rows to its local output instead.
 #define TT_MAX_PEERS 16
 struct TTScatter {
   void* peer[TT_MAX_PEERS];
   int mode;
   int S_l, S_pad, Hl, H, D, rank, world;
   long long ld;
+  int dst_rows, n_rows;
 };
 
 #ifdef __CUDACC__
@@ -93,13 +97,19 @@ namespace tt {
 __device__ __forceinline__ bf16* scatter_dst(const TTScatter& sc, int b, int tok, int hd) {
   if (sc.mode == 1) {
     const int p = hd / sc.Hl;
-    const long long idx = ((long long)(b * sc.S_pad + sc.rank * sc.S_l + tok) * sc.Hl + (hd - p * sc.Hl)) * sc.D;
+    const int rows = sc.dst_rows ? sc.dst_rows : sc.S_pad;
+    const long long idx = ((long long)b * rows + sc.rank * sc.S_l + tok) * sc.Hl * sc.D + (long long)(hd - p * sc.Hl) * sc.D;
     return reinterpret_cast<bf16*>(sc.peer[p]) + idx;
   }
   const int p = tok / sc.S_l;
   const long long ld = sc.ld ? sc.ld : (long long)sc.H * sc.D;
   const long long idx = (long long)(b * sc.S_l + (tok - p * sc.S_l)) * ld + (long long)(sc.rank * sc.Hl + hd) * sc.D;
   return reinterpret_cast<bf16*>(sc.peer[p]) + idx;
+}
+
+// whether row `row` of a kernel that scatters its output (mode 2) goes to a peer (else: to the local output)
+__device__ __forceinline__ bool scatter_row(const TTScatter& sc, int row, int rows_total) {
+  return sc.mode == 2 && row < rows_total && (sc.n_rows == 0 || row < sc.n_rows);
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

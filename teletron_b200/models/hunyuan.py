@@ -300,6 +300,28 @@ class HunyuanAttention(nn.Module):
         n = xg.shape[0] // B
         return tuple(t.reshape(B, n, self.heads_local, self.D) for t in (q, k, v))
 
+    def attend(self, hv, ht, freqs, B, cp, text_lens):
+        """Joint attention of the (modulated) video rows ``hv`` and text rows ``ht``; returns the attention outputs
+        (video [B, S_l, H_local, D], text [B, T, H_local, D]).  On one NVLink box the context-parallel exchanges of
+        the video q / k / v and of the output are stores of the norm and attention kernels into peer memory
+        (``parallel.fused_ulysses``); otherwise all-to-alls."""
+        fu = cp.fused if (cp is not None and cp.size > 1) else None
+        if (fu is not None and hv.is_cuda and fu.supports(self.heads_local, self.D)
+                and self.heads_local % cp.size == 0):
+            xg = self.tp.gather_rows(hv)
+            q_pre = self.to_q(xg, gathered=True)
+            k_pre = self.to_k(xg, gathered=True)
+            v = self.to_v(xg, gathered=True)
+            qt, kt, vt = self.qkv(ht, None, True, B)
+            S_l = xg.shape[0] // B
+            ov, ot = fu.joint_attention(q_pre, k_pre, v, self.norm_q.weight, self.norm_k.weight, freqs, qt, kt, vt,
+                                        text_lens, B, S_l, self.heads_local, self.D, self.eps)
+            ot = _GatherHeads.apply(ot.contiguous(), cp.group, cp.size, cp.rank)
+            return ov.view(B, S_l, self.heads_local, self.D), ot
+        qv, kv, vv = self.qkv(hv, freqs, False, B)
+        qt, kt, vt = self.qkv(ht, None, True, B)
+        return joint_attention(qv, kv, vv, qt, kt, vt, cp, text_lens)
+
 
 def _gated_residual(y_rows, residual, gate, rows_per_batch):
     """residual + gate[batch] * y for row matrices (used where the projection ends in a reduce-scatter)."""
@@ -341,9 +363,7 @@ class DualStreamBlock(nn.Module):
         # the norm's backward kernel instead of by a separate add
         hv, xv = ops.adaln_res(xv, ev[:, 1], ev[:, 0], rv, self.eps)
         ht, xt = ops.adaln_res(xt, et[:, 1], et[:, 0], rt, self.eps)
-        qv, kv, vv = self.attn.qkv(hv, freqs, False, B)
-        qt, kt, vt = self.attn.qkv(ht, None, True, B)
-        ov, ot = joint_attention(qv, kv, vv, qt, kt, vt, cp, text_lens)
+        ov, ot = self.attn.attend(hv, ht, freqs, B, cp, text_lens)
         xv = _project_out(self.attn.to_out[0], ov.reshape(-1, ov.shape[2] * ov.shape[3]), xv, ev[:, 2], rv)
         xt = _project_out(self.attn.to_add_out, ot.reshape(-1, ot.shape[2] * ot.shape[3]), xt, et[:, 2], rt)
         hv, xv = ops.adaln_res(xv, ev[:, 4], ev[:, 3], rv, self.eps)
@@ -378,9 +398,7 @@ class SingleStreamBlock(nn.Module):
         e = self.norm(temb)  # shift, scale, gate
         hv, xv = ops.adaln_res(xv, e[:, 1], e[:, 0], rv, self.eps)
         ht, xt = ops.adaln_res(xt, e[:, 1], e[:, 0], rt, self.eps)
-        qv, kv, vv = self.attn.qkv(hv, freqs, False, B)
-        qt, kt, vt = self.attn.qkv(ht, None, False, B)
-        ov, ot = joint_attention(qv, kv, vv, qt, kt, vt, cp, text_lens)
+        ov, ot = self.attn.attend(hv, ht, freqs, B, cp, text_lens)
         mv = self.proj_mlp(hv, act="gelu")
         mt = self.proj_mlp(ht, act="gelu")
         cv = torch.cat([ov.reshape(mv.shape[0], -1), mv], dim=1)
@@ -475,6 +493,22 @@ class HunyuanVideoModel(nn.Module):
             assert S % cp.size == 0, "video tokens must divide by the context-parallel size"
             xv = cp.split_tokens(xv.view(B, S, C)).reshape(-1, C)
             freqs = cp.split_rows(freqs)
+            fu = cp.fused
+            if fu is not None and xv.is_cuda:
+                # symmetric slab for the joint q / k / v (head layout) and the video output of every live layer
+                alive = cfg.num_layers + cfg.num_single_layers
+                if self.training and cfg.recompute_granularity == "full":
+                    # checkpointed blocks give their region back at once; the others keep theirs until backward
+                    k = cfg.recompute_num_layers or 0
+                    if (cfg.recompute_method or "block") == "block":
+                        alive = (cfg.num_layers - min(k, cfg.num_layers)
+                                 + cfg.num_single_layers - min(k, cfg.num_single_layers) + 2)
+                    else:
+                        alive = max(k, 1) + 1
+                heads_local = cfg.num_attention_heads // self.tp.size
+                per_layer = (3 * B * (S + (T + 7) // 8 * 8) * (heads_local // cp.size) * cfg.attention_head_dim
+                             + B * (S // cp.size) * heads_local * cfg.attention_head_dim + 4 * 128)
+                fu.begin_microbatch(int(per_layer * alive * 1.02) + 512)
         if self.tp.size > 1:  # sequence-sharded activations between tensor-parallel regions
             xv, xt = self.tp.split_rows(xv), self.tp.split_rows(xt)
             freqs_attn = freqs  # attention sees the TP-gathered rows

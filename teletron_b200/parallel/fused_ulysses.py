@@ -121,15 +121,31 @@ class FusedUlysses:
         self._keep_for_backward = torch.is_grad_enabled() and not forward_is_discarded()
         return _FusedUlyssesFn.apply(self, x, w_qkv, b_qkv, wq, wk, freqs, B, S_l, H, D, eps, scale)
 
+    def joint_attention(self, q_pre, k_pre, v, wq, wk, freqs, qt, kt, vt, text_lens, B, S_l, H, D, eps, scale=None):
+        """Attention over [video tokens | replicated text tokens] (HunyuanVideo,
+        teletron/models/hunyuan/parallel_model.py:84-118).  Video q_pre / k_pre / v: this rank's [B*S_l, H*D]
+        projections before the per-head norm (wq / wk: [D]) and RoPE; they are normalised, rotated and stored into
+        the head owners' joint buffers by the norm kernel.  Text qt / kt / vt: [B, T, H, D], already normalised and
+        identical on every rank; each rank attends with its own heads of them.  text_lens [B] masks the padded
+        text tail.  Returns (video output [B*S_l, H*D], this rank's heads of the text output [B, T, head slots, D]).
+        The video token count must divide by the group size (no padding inside a joint sequence)."""
+        self._keep_for_backward = torch.is_grad_enabled() and not forward_is_discarded()
+        return _FusedJointFn.apply(self, q_pre, k_pre, v, wq, wk, freqs, qt, kt, vt, text_lens, B, S_l, H, D, eps,
+                                   scale)
 
-def _scatter_rows(fu: FusedUlysses, x, w, freqs, rstd, rows, C, D, eps, dst_ptrs, S_l, S_pad, ssq=None):
+
+def _scatter_rows(fu: FusedUlysses, x, w, freqs, rstd, rows, C, D, eps, dst_ptrs, S_l, S_pad, ssq=None,
+                  per_head=False, dst_rows=0):
+    """norm (full row, or per head) + RoPE of x [rows, C] (either may be skipped: w / freqs None), stored with the
+    seq -> head pattern into the peers' [B, dst_rows or S_pad, head slots, D] buffers."""
     L = _lib.lib()
     rc = L.tt_rmsrope_fwd_scatter(
         _lib.ptr(x), _lib.c_ll(x.stride(0)), _lib.ptr(w), _lib.ptr(freqs),
         _lib.c_int(freqs.shape[0] if freqs is not None else 1), _lib.ptr(rstd), _lib.c_int(rows), _lib.c_int(C),
-        _lib.c_int(D), _lib.c_int(0), _lib.c_float(eps), dst_ptrs, _lib.c_int(fu.world), _lib.c_int(fu.rank),
-        _lib.c_int(S_l), _lib.c_int(S_pad), _lib.ptr(ssq), _lib.c_int(ssq.shape[1] if ssq is not None else 0),
-        _lib.c_ll(ssq.stride(0) if ssq is not None else 0), _lib.stream())
+        _lib.c_int(D), _lib.c_int(int(per_head)), _lib.c_float(eps), dst_ptrs, _lib.c_int(fu.world),
+        _lib.c_int(fu.rank), _lib.c_int(S_l), _lib.c_int(S_pad), _lib.ptr(ssq),
+        _lib.c_int(ssq.shape[1] if ssq is not None else 0), _lib.c_ll(ssq.stride(0) if ssq is not None else 0),
+        _lib.c_int(dst_rows), _lib.stream())
     _lib.check(rc, "tt_rmsrope_fwd_scatter")
 
 
@@ -195,8 +211,8 @@ class _FusedUlyssesFn(torch.autograd.Function):
                     _lib.ptr(qh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(kh), _lib.c_ll(ld), _lib.c_ll(bs),
                     _lib.ptr(vh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(o_h), _lib.c_ll(ld), _lib.c_ll(bs),
                     _lib.ptr(lse), _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl), _lib.c_int(heads),
-                    _lib.c_int(H), _lib.c_int(S_pad), _lib.c_int(D), _lib.c_float(scale), o_p, _lib.c_int(P),
-                    _lib.c_int(rank), _lib.ptr(_lib.status_word(dev)), _lib.stream())
+                    _lib.c_int(H), _lib.c_int(S_pad), _lib.c_int(S_pad), _lib.c_int(D), _lib.c_float(scale), o_p,
+                    _lib.c_int(P), _lib.c_int(rank), _lib.ptr(_lib.status_word(dev)), _lib.stream())
             _lib.check(rc, "tt_attn_fwd_scatter")
         fu.arena.barrier(fu.slot)
         if not fu._keep_for_backward:
@@ -241,9 +257,9 @@ class _FusedUlyssesFn(torch.autograd.Function):
                 rc = L.tt_attn_bwd_scatter(
                     _lib.ptr(qh), _lib.ptr(kh), _lib.ptr(vh), _lib.ptr(o_h), _lib.ptr(do_h.tensor), _lib.ptr(lse),
                     _lib.ptr(scratch), dqkv_s.c_ptrs(0), dqkv_s.c_ptrs(C), dqkv_s.c_ptrs(2 * C), _lib.c_ll(3 * C),
-                    _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl), _lib.c_int(heads), _lib.c_int(H),
-                    _lib.c_int(S_pad), _lib.c_int(D), _lib.c_float(scale), _lib.c_int(P), _lib.c_int(rank),
-                    _lib.ptr(_lib.status_word(dev)), _lib.stream())
+                    None, None, None, _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl), _lib.c_int(heads),
+                    _lib.c_int(H), _lib.c_int(S_pad), _lib.c_int(S_pad), _lib.c_int(D), _lib.c_float(scale),
+                    _lib.c_int(P), _lib.c_int(rank), _lib.ptr(_lib.status_word(dev)), _lib.stream())
             _lib.check(rc, "tt_attn_bwd_scatter")
         fu.arena.barrier(fu.slot)
         dqkv = dqkv_s.tensor[:rows * 3 * C].view(rows, 3 * C)
@@ -258,3 +274,124 @@ class _FusedUlyssesFn(torch.autograd.Function):
             fu.slab.release_to(fu.slab.live.pop()[0])
         wdq, wdk = ctx.w_dtypes
         return (None, dx, dw, db, dwq.to(wdq), dwk.to(wdk), None, None, None, None, None, None, None)
+
+
+class _FusedJointFn(torch.autograd.Function):
+    """Joint video + text attention with the video exchanges in the kernels' stores; the text tokens never leave
+    the rank (every rank holds them and uses its own heads)."""
+
+    @staticmethod
+    def forward(ctx, fu: FusedUlysses, q_pre, k_pre, v, wq, wk, freqs, qt, kt, vt, text_lens, B, S_l, H, D, eps, scale):
+        import math
+
+        P, rank = fu.world, fu.rank
+        C = H * D
+        Hl, heads = fu.head_slots(H)
+        assert heads == Hl, "joint attention needs the head count to divide by the group size"
+        S_pad = S_l * P
+        T = qt.shape[1]
+        Tp = (T + 7) // 8 * 8
+        S_tot = S_pad + Tp
+        rows = B * S_l
+        dev = q_pre.device
+        scale = scale if scale is not None else 1.0 / math.sqrt(D)
+        n_h = B * S_tot * Hl * D
+        slab_mark = fu.slab.off
+        qh, qh_p = fu.slab.take(n_h)
+        kh, kh_p = fu.slab.take(n_h)
+        vh, vh_p = fu.slab.take(n_h)
+        o_s, o_p = fu.slab.take(rows * C)
+        wq_f, wk_f = wq.float().contiguous(), wk.float().contiguous()
+        rstd_q = torch.empty((rows, H), dtype=torch.float32, device=dev)
+        rstd_k = torch.empty((rows, H), dtype=torch.float32, device=dev)
+        with nvtx_range("joint_qkv_a2a"):
+            _scatter_rows(fu, q_pre, wq_f, freqs, rstd_q, rows, C, D, eps, qh_p, S_l, S_pad, per_head=True, dst_rows=S_tot)
+            _scatter_rows(fu, k_pre, wk_f, freqs, rstd_k, rows, C, D, eps, kh_p, S_l, S_pad, per_head=True, dst_rows=S_tot)
+            _scatter_rows(fu, v, None, None, None, rows, C, D, eps, vh_p, S_l, S_pad, dst_rows=S_tot)
+        # this rank's heads of the text tokens go behind the video rows of the same buffers (no concatenation)
+        hs = slice(rank * Hl, (rank + 1) * Hl)
+        for buf, t in ((qh, qt), (kh, kt), (vh, vt)):
+            b4 = buf.view(B, S_tot, Hl, D)
+            b4[:, S_pad:S_pad + T].copy_(t[:, :, hs])
+            if Tp > T:
+                b4[:, S_pad + T:].zero_()
+        fu.arena.barrier(fu.slot)
+        kv_lens = (text_lens.to(device=dev, dtype=torch.int32) + S_pad) if text_lens is not None else \
+            torch.full((B,), S_pad + T, dtype=torch.int32, device=dev)
+        o_h = torch.empty(n_h, dtype=torch.bfloat16, device=dev)
+        lse = torch.empty((B, Hl, S_tot), dtype=torch.float32, device=dev)
+        ld, bs = Hl * D, S_tot * Hl * D
+        L = _lib.lib()
+        with nvtx_range("joint_attn_fwd_a2a"):
+            rc = L.tt_attn_fwd_scatter(
+                _lib.ptr(qh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(kh), _lib.c_ll(ld), _lib.c_ll(bs),
+                _lib.ptr(vh), _lib.c_ll(ld), _lib.c_ll(bs), _lib.ptr(o_h), _lib.c_ll(ld), _lib.c_ll(bs),
+                _lib.ptr(lse), _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl), _lib.c_int(Hl), _lib.c_int(H),
+                _lib.c_int(S_pad), _lib.c_int(S_tot), _lib.c_int(D), _lib.c_float(scale), o_p, _lib.c_int(P),
+                _lib.c_int(rank), _lib.ptr(_lib.status_word(dev)), _lib.stream())
+        _lib.check(rc, "tt_attn_fwd_scatter")
+        fu.arena.barrier(fu.slot)
+        ot = o_h.view(B, S_tot, Hl, D)[:, S_pad:S_pad + T].clone()
+        if not fu._keep_for_backward:
+            fu.slab.release_to(slab_mark)
+        else:
+            fu.slab.live.append((slab_mark, fu.slab.off))
+        ctx.fu = fu
+        ctx.meta = (B, S_l, H, D, T, Tp, scale)
+        ctx.save_for_backward(q_pre, k_pre, wq_f, wk_f, freqs, rstd_q, rstd_k, qh, kh, vh, o_h, lse, kv_lens)
+        ctx.w_dtypes = (wq.dtype, wk.dtype)
+        ctx.text_shape = tuple(qt.shape)
+        return o_s.view(rows, C), ot
+
+    @staticmethod
+    def backward(ctx, do, dot):
+        fu: FusedUlysses = ctx.fu
+        q_pre, k_pre, wq_f, wk_f, freqs, rstd_q, rstd_k, qh, kh, vh, o_h, lse, kv_lens = ctx.saved_tensors
+        B, S_l, H, D, T, Tp, scale = ctx.meta
+        P, rank = fu.world, fu.rank
+        C, S_pad, rows = H * D, S_l * P, B * S_l
+        Hl = H // P
+        S_tot = S_pad + Tp
+        dev = do.device
+        if do.stride(1) != 1:
+            do = do.contiguous()
+        n_h = B * S_tot * Hl * D
+        do_h = fu.staging("do_h", n_h)
+        dqkv_s = fu.staging("dqkv_s", rows * 3 * C)
+        _scatter_rows(fu, do, None, None, None, rows, C, D, 0.0, do_h.c_ptrs(), S_l, S_pad, dst_rows=S_tot)
+        d4 = do_h.tensor[:n_h].view(B, S_tot, Hl, D)
+        d4[:, S_pad:S_pad + T].copy_(dot)
+        if Tp > T:
+            d4[:, S_pad + T:].zero_()
+        fu.arena.barrier(fu.slot)
+        L = _lib.lib()
+        L.tt_attn_bwd_scratch_floats.restype = _lib.c_ll
+        scratch = torch.empty(L.tt_attn_bwd_scratch_floats(_lib.c_int(B), _lib.c_int(Hl), _lib.c_int(S_tot)),
+                              dtype=torch.float32, device=dev)
+        # gradients of the rows that stay local (text): head-layout buffers of the joint length
+        dql, dkl, dvl = (torch.empty(n_h, dtype=torch.bfloat16, device=dev) for _ in range(3))
+        with nvtx_range("joint_attn_bwd_a2a"):
+            rc = L.tt_attn_bwd_scatter(
+                _lib.ptr(qh), _lib.ptr(kh), _lib.ptr(vh), _lib.ptr(o_h), _lib.ptr(do_h.tensor), _lib.ptr(lse),
+                _lib.ptr(scratch), dqkv_s.c_ptrs(0), dqkv_s.c_ptrs(C), dqkv_s.c_ptrs(2 * C), _lib.c_ll(3 * C),
+                _lib.ptr(dql), _lib.ptr(dkl), _lib.ptr(dvl), _lib.ptr(kv_lens), _lib.c_int(B), _lib.c_int(Hl),
+                _lib.c_int(Hl), _lib.c_int(H), _lib.c_int(S_pad), _lib.c_int(S_tot), _lib.c_int(D),
+                _lib.c_float(scale), _lib.c_int(P), _lib.c_int(rank), _lib.ptr(_lib.status_word(dev)), _lib.stream())
+        _lib.check(rc, "tt_attn_bwd_scatter")
+        fu.arena.barrier(fu.slot)
+        dqkv = dqkv_s.tensor[:rows * 3 * C].view(rows, 3 * C)
+        dq_pre, dwq = rmsrope_bwd_raw(dqkv[:, 0:C], q_pre, wq_f, freqs, rstd_q, D, True)
+        dk_pre, dwk = rmsrope_bwd_raw(dqkv[:, C:2 * C], k_pre, wk_f, freqs, rstd_k, D, True)
+        dv = dqkv[:, 2 * C:].clone()
+        # text gradients: this rank's heads only, the other heads' slots are zero (their owners contribute them)
+        hs = slice(rank * Hl, (rank + 1) * Hl)
+        outs = []
+        for g in (dql, dkl, dvl):
+            full = torch.zeros(ctx.text_shape, dtype=torch.bfloat16, device=dev)
+            full[:, :, hs] = g.view(B, S_tot, Hl, D)[:, S_pad:S_pad + T]
+            outs.append(full)
+        if fu.slab.live and fu.slab.live[-1][1] == fu.slab.off:
+            fu.slab.release_to(fu.slab.live.pop()[0])
+        wdq, wdk = ctx.w_dtypes
+        return (None, dq_pre, dk_pre, dv, dwq.to(wdq), dwk.to(wdk), None, outs[0], outs[1], outs[2], None,
+                None, None, None, None, None, None)
