@@ -1,9 +1,9 @@
 """Small, self-contained workloads for profiling single kernels (``ncu -k regex:<kernel> -c 1 ...``).
 
-    python -m teletron_b200.ops.profile_cases gemm  [--m 32760 --n 8960 --k 1536 --epi gelu]
-    python -m teletron_b200.ops.profile_cases attn  [--seq 16384 --heads 12] [--bwd]
-    python -m teletron_b200.ops.profile_cases norm  [--rows 32760 --c 1536]
-    python -m teletron_b200.ops.profile_cases layers [--layers 2]     Wan2.1-1.3B blocks, one 480P x 81 sample, fwd + bwd
+    python examples/profiling/profile_cases.py gemm  [--m 32760 --n 8960 --k 1536 --epi gelu]
+    python examples/profiling/profile_cases.py attn  [--seq 16384 --heads 12] [--bwd]
+    python examples/profiling/profile_cases.py norm  [--rows 32760 --c 1536]
+    python examples/profiling/profile_cases.py layers [--layers 2]     Wan2.1-1.3B blocks, one 480P x 81 sample, fwd + bwd
 
 Each case runs one warm-up and then a few timed launches (CUDA events) and prints the achieved
 rate, so the same command serves both as the plain run and as the profiled run.
@@ -12,13 +12,17 @@ from __future__ import annotations
 
 import argparse
 import json
+import sys
+from pathlib import Path
 
 import torch
 
-from . import _lib
-from .attention import attention_bwd, attention_fwd
-from .gemm import EPI_GELU, EPI_NONE, gemm
-from .norm import adaln
+sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+
+from teletron_b200.ops import _lib  # noqa: E402
+from teletron_b200.ops.attention import attention_bwd, attention_fwd  # noqa: E402
+from teletron_b200.ops.gemm import EPI_GELU, EPI_NONE, gemm  # noqa: E402
+from teletron_b200.ops.norm import adaln  # noqa: E402
 
 
 def _time(fn, iters=3):
@@ -40,8 +44,8 @@ def _tp_case(a):
 
     import torch.distributed as dist
 
-    from ..dist import SymmetricArena
-    from ..parallel.tp import ColumnParallelLinear, FusedTP, RowParallelLinear, TPContext
+    from teletron_b200.dist import SymmetricArena
+    from teletron_b200.parallel.tp import ColumnParallelLinear, FusedTP, RowParallelLinear, TPContext
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -83,8 +87,8 @@ def _dpopt_case(a):
 
     import torch.distributed as dist
 
-    from ..dist import SymmetricArena
-    from ..parallel.ddp import DistributedOptimizer, ParamBuffer
+    from teletron_b200.dist import SymmetricArena
+    from teletron_b200.parallel.ddp import DistributedOptimizer, ParamBuffer
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -94,7 +98,7 @@ def _dpopt_case(a):
     rows = n // 4096
     holder.w = torch.nn.Parameter(torch.zeros(rows, 4096, device="cuda", dtype=torch.bfloat16))
     arena = SymmetricArena(dist.group.WORLD) if a.fused else None
-    buf = ParamBuffer(holder, shard_world=world, arena=arena)
+    buf = ParamBuffer(holder, shard_world=world, arena=arena, bucket_size=40_000_000)
     opt = DistributedOptimizer(buf, dist.group.WORLD, lr=1e-4, weight_decay=0.01, clip_grad=1.0, sharded=True,
                                grad_scale=1.0 / world)
     buf.grads.normal_()
@@ -173,9 +177,9 @@ def main():
             ms = _time(lambda: attention_fwd(q, k, v), a.iters)
             res.update(seq=a.seq, kv=kv, heads=a.heads, bwd=False, ms=ms, tflops=flops / ms / 1e9)
     elif a.case == "layers":
-        from ..models import WanModel, wan_config
-        from ..parallel.ddp import ParamBuffer
-        from .flow import flow_mse
+        from teletron_b200.models import WanModel, wan_config
+        from teletron_b200.parallel.ddp import ParamBuffer
+        from teletron_b200.ops.flow import flow_mse
 
         model = WanModel(wan_config("wan2.1-1.3b-t2v", num_layers=a.layers)).to(dev).to(torch.bfloat16).train()
         buf = ParamBuffer(model)

@@ -19,6 +19,40 @@ using namespace tt_gemm;
 
 namespace {
 
+// all-gather -> GEMM in this one kernel (K-AG-GEMM): the A operand is the concatenation of one row segment per rank.
+// Two extra warps per CTA copy it, 128-row block by block, from the ranks' buffers (plain loads over NVLink for the
+// remote segments) into a local gathered matrix `G`, and publish one flag per block; the TMA producer of a tile waits
+// for the flags of its rows and then loads A from `G`.  Tiles are visited starting with the local segment, blocks are
+// copied in the same order, so the remote rows arrive while the local rows are multiplied and every remote element
+// crosses NVLink exactly once.  `G` stays behind for the weight-gradient GEMM.
+struct AgParams {
+  const bf16* src[TP_MAX];  // rank s's segment [seg_rows, K] (its own included)
+  bf16* G;                  // [world * seg_rows, K]
+  unsigned* flags;          // one per 128-row block of G; a block is complete when its flag equals `epoch`
+  unsigned epoch;
+  int seg_rows, n_blocks, rot_tiles;  // rot_tiles: first 256-row tile that holds local rows
+};
+
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// bounded wait for a block flag; false (and the abort flag raised) when it runs out
+__device__ __forceinline__ bool flag_wait(const unsigned* f, unsigned epoch, volatile uint32_t* abort_flag,
+                                          unsigned* status, unsigned code) {
+  const long long t0 = clock64();
+  unsigned v;
+  while (true) {
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    if (v == epoch) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > TT_WAIT_BUDGET_CLOCKS) {
+      *abort_flag = 1;
+      if (status) atomicCAS(status, 0u, code);
+      return false;
+    }
+    __nanosleep(100);
+  }
+}
+
 constexpr int BN2 = 256;
 constexpr int STAGES2 = 6;
 constexpr int ROUND2 = 3;  // stages consumed per wait / commit round of the MMA thread
@@ -26,9 +60,10 @@ constexpr int B_HALF_BYTES = 128 * BK * 2;
 constexpr int STAGE2_BYTES = A_BYTES + B_HALF_BYTES;  // 32 KB per CTA and stage
 constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 256 + 1024;
 
-template <int A_MN, int B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
-gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+template <int A_MN, int B_MN, bool AG>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AG ? 384 : 320, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
+             const AgParams ag) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -48,6 +83,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   const int tiles_n = (p.N + BN2 - 1) / BN2;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
+  // row tile of the i-th tile this cluster visits: with the gathered A operand the local segment comes first
+  auto tile_m = [&](int tile) { return AG ? (tile / tiles_n + ag.rot_tiles) % tiles_m : tile / tiles_n; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) {
@@ -81,8 +118,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       int it = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int m0 = (tile / tiles_n) * 2 * BM + (int)cta * BM;
+        const int m0 = tile_m(tile) * 2 * BM + (int)cta * BM;
         const int n0 = (tile % tiles_n) * BN2 + (int)cta * 128;  // this CTA's half of the B tile
+        if (AG && m0 < p.M) {
+          // this CTA's 128 rows of the gathered operand have to be in place (copied by some CTA's copier warps)
+          if (!flag_wait(ag.flags + m0 / BM, ag.epoch, abort_flag, p.status, TT_ST_TIMEOUT_PRODUCER + 2)) break;
+          fence_proxy_async_all();  // the copy was written with ordinary stores, the TMA engine reads it
+        }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES2;
           const uint32_t ph = (it / STAGES2) & 1;
@@ -149,6 +191,41 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         if (ok) tc_commit2(&tfull[a], 3);
       }
     }
+  } else if (AG && warp >= 10) {
+    // ------------------------------------------------------------ copier warps (all-gather of the A operand)
+    const int t = threadIdx.x - 320;          // 0..63
+    const int vec_per_row = p.K >> 3;         // 16-byte vectors per row
+    for (int j = blockIdx.x; j < ag.n_blocks; j += gridDim.x) {
+      const int blk = (j + 2 * ag.rot_tiles) % ag.n_blocks;   // same order as the tiles are visited
+      const int r0 = blk * BM;
+      const int nrows = min(BM, p.M - r0);
+      const long long nvec = (long long)nrows * vec_per_row;
+      for (long long v0 = t; v0 < nvec; v0 += 64 * 8) {
+        uint4 buf[8];
+        long long dsts[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const long long v = v0 + (long long)u * 64;
+          dsts[u] = -1;
+          if (v < nvec) {
+            const int row = r0 + (int)(v / vec_per_row);
+            const int col = (int)(v % vec_per_row) << 3;
+            const int seg = row / ag.seg_rows;
+            buf[u] = *reinterpret_cast<const uint4*>(ag.src[seg] + (long long)(row - seg * ag.seg_rows) * p.K + col);
+            dsts[u] = (long long)row * p.K + col;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (dsts[u] >= 0) *reinterpret_cast<uint4*>(ag.G + dsts[u]) = buf[u];
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 64;" ::: "memory");   // both copier warps have written and fenced their part
+      if (t == 0) {
+        fence_proxy_async_all();
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ag.flags + blk), "r"(ag.epoch) : "memory");
+      }
+    }
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs)
     const int q = warp & 3;
@@ -160,7 +237,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       const uint32_t aph = (tcount >> 1) & 1;
       if (!mbar_wait(&tfull[a], aph, abort_flag, p.status, TT_ST_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
-      const int m0 = (tile / tiles_n) * 2 * BM + (int)cta * BM;
+      const int m0 = tile_m(tile) * 2 * BM + (int)cta * BM;
       const int n0 = (tile % tiles_n) * BN2;
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
@@ -186,9 +263,14 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   if (warp == 1) tmem_dealloc2(tmem_base, 512);
 }
 
-template <int A_MN, int B_MN>
-int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms, cudaStream_t stream) {
-  auto kern = gemm2_kernel<A_MN, B_MN>;
+template <int A_MN, int B_MN, bool AG = false>
+int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms, cudaStream_t stream,
+            const AgParams* agp = nullptr) {
+  auto kern = gemm2_kernel<A_MN, B_MN, AG>;
+  constexpr int NT2 = AG ? 384 : 320;
+  AgParams ag;
+  memset(&ag, 0, sizeof(ag));
+  if (agp) ag = *agp;
   static bool attr_done = false;
   if (!attr_done) {
     TT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES));
@@ -200,7 +282,7 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
   if (max_clusters == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sms, 1, 1);
-    cfg.blockDim = dim3(320, 1, 1);
+    cfg.blockDim = dim3(NT2, 1, 1);
     cfg.dynamicSmemBytes = SMEM2_BYTES;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -215,7 +297,7 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
   }
   int clusters = max_clusters < sms / 2 ? max_clusters : sms / 2;
   if (tiles < clusters) clusters = tiles;
-  kern<<<2 * clusters, 320, SMEM2_BYTES, stream>>>(tmA, tmB, p);
+  kern<<<2 * clusters, NT2, SMEM2_BYTES, stream>>>(tmA, tmB, p, ag);
   TT_LAUNCH_CHECK();
   return 0;
 }
@@ -315,4 +397,56 @@ TT_API int tt_gemm_qkv_a2a(const void* x, long long ldx, const void* W, long lon
   TT_CUDA(cudaGetDevice(&dev));
   TT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   return launch2<0, 0>(tmA, tmB, p, sms, stream);
+}
+
+// K-AG-GEMM: C = epilogue([A_0; A_1; ...] B^T) where segment s of A ([seg_rows, K], row stride K) lives in rank s's
+// buffer at device address a_ptrs[s] (peer memory; a_ptrs[rank] is this rank's own).  The kernel gathers the segments
+// into `G` ([world * seg_rows, K], local, left filled for the caller) while it multiplies: see AgParams.  `flags`:
+// uint32[ceil(world * seg_rows / 128)] that held no value equal to `epoch` before the call (zero-initialised once,
+// then epoch = 1, 2, ... per call).  The caller has put a cross-rank barrier between the writes of the segments and
+// this call.  Returns -3 for shapes outside the CTA-pair kernel's domain.
+TT_API int tt_gemm2_bf16_ag(const long long* a_ptrs, const void* B, long long ldb, int b_mn, void* C, long long ldc,
+                            void* G, unsigned* flags, unsigned epoch, int seg_rows, int world, int rank, int N, int K,
+                            const void* bias, int epi, void* aux_out, unsigned* status, cudaStream_t stream) {
+  const long long M = (long long)seg_rows * world;
+  if (N < 256 || M < 256) return -3;
+  TT_CHECK(world >= 1 && world <= TP_MAX && rank >= 0 && rank < world && seg_rows > 0, "gemm2_ag: bad world/rank");
+  TT_CHECK(N % 8 == 0 && K % 8 == 0 && M < (1ll << 31), "gemm2_ag: bad shape");
+  TT_CHECK(ldb % 8 == 0 && ldc % 8 == 0 && ((uintptr_t)C & 15) == 0 && ((uintptr_t)G & 15) == 0 && flags != nullptr,
+           "gemm2_ag: misaligned operands");
+  TT_CHECK(epi == EPI_NONE || epi == EPI_GELU || epi == EPI_SILU, "gemm2_ag: epilogue %d not supported", epi);
+  if (bias) TT_CHECK(((uintptr_t)bias & 15) == 0, "gemm2_ag: bias is not 16-byte aligned");
+  AgParams ag;
+  memset(&ag, 0, sizeof(ag));
+  for (int i = 0; i < world; ++i) {
+    ag.src[i] = reinterpret_cast<const bf16*>(a_ptrs[i]);
+    TT_CHECK(ag.src[i] && ((uintptr_t)ag.src[i] & 15) == 0, "gemm2_ag: bad segment pointer %d", i);
+  }
+  ag.G = (bf16*)G; ag.flags = flags; ag.epoch = epoch; ag.seg_rows = seg_rows;
+  ag.n_blocks = (int)((M + BM - 1) / BM);
+  ag.rot_tiles = (int)(((long long)rank * seg_rows) / (2 * BM));
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[2], str[1];
+    uint32_t box[2];
+    dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = 64; box[1] = BM;
+    str[0] = (uint64_t)K * 2;
+    if (tt_make_tmap(&tmA, G, 2, 2, dims, str, box, 1)) return -1;
+    if (b_mn) { dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 64; box[1] = 64; }
+    else      { dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = 64; box[1] = 128; }
+    str[0] = (uint64_t)ldb * 2;
+    if (tt_make_tmap(&tmB, B, 2, 2, dims, str, box, 1)) return -1;
+  }
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = (int)M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc; p.c_fp32 = 0;
+  p.bias = (const bf16*)bias; p.epi = epi;
+  p.rows_per_gate = 1; p.aux_out = (bf16*)aux_out; p.alpha = 1.f; p.status = status;
+  p.world = 1;
+  int dev = 0, sms = 0;
+  TT_CUDA(cudaGetDevice(&dev));
+  TT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (b_mn) return launch2<0, 1, true>(tmA, tmB, p, sms, stream, &ag);
+  return launch2<0, 0, true>(tmA, tmB, p, sms, stream, &ag);
 }

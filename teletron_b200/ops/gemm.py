@@ -146,6 +146,28 @@ def gemm_ag(a_peer_ptrs, seg_rows: int, k: int, b, *, b_mn=False, bias=None, epi
     return (out, aux) if want_aux else out
 
 
+def gemm_ag_gather(a_peer_ptrs, seg_rows: int, k: int, b, flags, epoch: int, rank: int, *, b_mn=False, bias=None,
+                   epi=EPI_NONE, want_aux=False, device=None):
+    """all-gather -> GEMM in one kernel that gathers as it multiplies (csrc/gemm2.cu, tt_gemm2_bf16_ag): segment s of
+    A is read once from rank s's buffer by the kernel's copier warps into a local gathered matrix, which is returned
+    as the third result.  ``flags``: int32 [>= ceil(world * seg_rows / 128)] holding no value equal to ``epoch``."""
+    world = len(a_peer_ptrs)
+    n = b.shape[1] if b_mn else b.shape[0]
+    assert b.dtype == torch.bfloat16 and b.stride(1) == 1
+    dev = device or b.device
+    out = torch.empty((world * seg_rows, n), dtype=torch.bfloat16, device=dev)
+    aux = torch.empty_like(out) if want_aux else None
+    gathered = torch.empty((world * seg_rows, k), dtype=torch.bfloat16, device=dev)
+    ptrs = (_lib.c_ll * world)(*[int(p) for p in a_peer_ptrs])
+    rc = _lib.lib().tt_gemm2_bf16_ag(ptrs, _lib.ptr(b), _lib.c_ll(b.stride(0)), _lib.c_int(int(b_mn)), _lib.ptr(out),
+                                     _lib.c_ll(out.stride(0)), _lib.ptr(gathered), _lib.ptr(flags), _lib.c_uint(epoch),
+                                     _lib.c_int(seg_rows), _lib.c_int(world), _lib.c_int(rank), _lib.c_int(n),
+                                     _lib.c_int(k), _lib.ptr(bias), _lib.c_int(epi), _lib.ptr(aux),
+                                     _lib.ptr(_lib.status_word(dev)), _lib.stream())
+    _lib.check(rc, "tt_gemm2_bf16_ag")
+    return out, aux, gathered
+
+
 def gemm_rs_scatter(a, b, c_peer_ptrs, seg_rows: int, rank: int, *, b_mn=False):
     """First half of GEMM -> reduce-scatter: the partial product ``a @ b^T`` ([world * seg_rows, n]) is stored,
     tile by tile, into slot ``rank`` of the staging buffer ([world, seg_rows, n]) of the rank that owns the rows

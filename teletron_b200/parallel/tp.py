@@ -90,9 +90,9 @@ class GatherRowsKeepLocalGrad(torch.autograd.Function):
 class FusedTP:
     """Peer-memory buffers and call order for the fused tensor-parallel kernels of one TP group on one box:
 
-      all-gather -> GEMM    each rank copies its rows into a symmetric buffer, a device barrier follows, and the
-                            remote segments are pulled over NVLink while the GEMM of the local segment runs
-                            (or, ``one_kernel``, the GEMM's TMA loads read the peers' buffers: ``ops.gemm_ag``)
+      all-gather -> GEMM    each rank copies its rows into a symmetric buffer, a device barrier follows, and one
+                            GEMM kernel pulls the remote segments over NVLink with its copier warps while its
+                            tensor-core tiles start on the local segment (``ops.gemm_ag_gather``)
       GEMM -> reduce-scatter  the GEMM epilogue stores each tile of partial sums into the staging buffer of the rank
                             that owns the rows (``ops.gemm_rs_scatter``); after a barrier every rank sums its
                             ``world`` slots (``ops.tp_reduce_rows``)
@@ -110,7 +110,8 @@ class FusedTP:
         self._st_cap = 0
         self._n_ag = 0
         self._n_rs = 0
-        self._side = None
+        self._ag_flags = None      # one flag per 128-row block of the gathered operand, epoch-valued
+        self._ag_epoch = 0
 
     def _x_buf(self, numel):
         if numel > self._x_cap:  # collective: every rank grows at the same call
@@ -126,54 +127,36 @@ class FusedTP:
         self._n_rs += 1
         return self._st[self._n_rs & 1]
 
-    def ag_gemm(self, x_rows, w, *, b_mn=False, bias=None, epi=0, want_aux=False, one_kernel=False):
-        """epilogue(all_gather_rows(x_rows) @ W^T): x_rows [rows, k] bf16, W [n, k] (or [k, n] when b_mn).
-        Returns (y, pre-activation or None, gathered x or None).
+    def ag_gemm(self, x_rows, w, *, b_mn=False, bias=None, epi=0, want_aux=False):
+        """epilogue(all_gather_rows(x_rows) @ W^T) in one kernel: x_rows [rows, k] bf16, W [n, k] (or [k, n] when
+        b_mn).  Returns (y, pre-activation or None, gathered x or None).
 
-        Default: every remote segment is pulled once into a local gathered buffer by a copy on a side stream
-        while the GEMM of the local segment runs, and the GEMM of segment s starts when its copy has landed
-        (events, no kernel waits on another kernel).  ``one_kernel`` uses ``ops.gemm_ag`` instead, whose TMA
-        loads read the peers directly: one launch and no gathered copy, but every remote A tile crosses NVLink
-        once per column tile of the output (24 times for a 6,144-wide shard), which measured twice as slow as
-        NCCL on an MLP pair at 2 x 16,384 rows; it is kept for narrow outputs."""
+        Every rank puts its rows into a symmetric buffer; after a device barrier the GEMM kernel itself gathers the
+        operand (``ops.gemm_ag_gather``, csrc/gemm2.cu): two copier warps per CTA pull the segments, 128 rows at a
+        time, into a local gathered matrix and flag them, the tiles of the local segment are multiplied first and
+        the others as their rows land, so each remote element crosses NVLink once and the gathered matrix is left
+        for the weight gradient.  Outputs narrower than 256 columns (or fewer than 256 rows) use ``ops.gemm_ag``,
+        whose TMA loads read the peers' buffers directly (no gathered copy; fine when there are few column tiles)."""
         rows, k = x_rows.shape
         buf = self._x_buf(rows * k)
         mine = buf.tensor[: rows * k].view(rows, k)
         mine.copy_(x_rows)
         self.arena.barrier(0)
-        if one_kernel:
-            res = ops.gemm_ag(buf.peer_ptrs, rows, k, w, b_mn=b_mn, bias=bias, epi=epi, want_aux=want_aux,
-                              device=x_rows.device)
-            return (res[0], res[1], None) if want_aux else (res, None, None)
         n = w.shape[1] if b_mn else w.shape[0]
-        world, rank = self.world, self.rank
-        gathered = torch.empty((world * rows, k), dtype=torch.bfloat16, device=x_rows.device)
-        out = torch.empty((world * rows, n), dtype=torch.bfloat16, device=x_rows.device)
-        aux = torch.empty_like(out) if want_aux else None
-        cur = torch.cuda.current_stream()
-        if self._side is None:
-            self._side = torch.cuda.Stream()
-        side = self._side
-        side.wait_stream(cur)  # behind the barrier: the peers' rows are complete
-        events = {}
-        with torch.cuda.stream(side):
-            for i in range(1, world):
-                s_ = (rank + i) % world
-                peer = buf.handle.get_buffer(s_, (rows, k), torch.bfloat16)
-                gathered[s_ * rows:(s_ + 1) * rows].copy_(peer, non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record(side)
-                events[s_] = ev
-        gathered.record_stream(side)
-        gathered[rank * rows:(rank + 1) * rows].copy_(mine)
-        for i in range(world):
-            s_ = (rank + i) % world
-            if i > 0:
-                cur.wait_event(events[s_])
-            sl = slice(s_ * rows, (s_ + 1) * rows)
-            ops.gemm(gathered[sl], w, b_mn=b_mn, bias=bias, epi=epi, out=out[sl], want_aux=want_aux,
-                     aux=aux[sl] if want_aux else None)
-        return out, aux, gathered
+        if n >= 256 and rows * self.world >= 256:
+            with nvtx_range("ag_gemm"):
+                blocks = (rows * self.world + 127) // 128
+                if self._ag_flags is None or self._ag_flags.numel() < blocks:
+                    self._ag_flags = torch.zeros(blocks, dtype=torch.int32, device=x_rows.device)
+                    self._ag_epoch = 0
+                self._ag_epoch = (self._ag_epoch % 0x7FFFFFF0) + 1
+                y, aux, gathered = ops.gemm_ag_gather(buf.peer_ptrs, rows, k, w, self._ag_flags, self._ag_epoch,
+                                                      self.rank, b_mn=b_mn, bias=bias, epi=epi, want_aux=want_aux,
+                                                      device=x_rows.device)
+            return y, aux, gathered
+        res = ops.gemm_ag(buf.peer_ptrs, rows, k, w, b_mn=b_mn, bias=bias, epi=epi, want_aux=want_aux,
+                          device=x_rows.device)
+        return (res[0], res[1], None) if want_aux else (res, None, None)
 
     def gemm_rs(self, x, w, *, b_mn=False):
         """reduce_scatter_rows(x @ W^T): x [world * rows, k]; returns this rank's [rows, n] of the sum."""

@@ -278,11 +278,15 @@ def _tp_worker(rank, world, fused):
         y.backward(dy_full[rank * rows:(rank + 1) * rows])
         outs = [y.detach(), x.grad, col.weight.grad, col.bias.grad, row.weight.grad]
     if fused:
-        # the one-kernel variant (TMA loads straight from the peers' buffers) against the pull-and-overlap default
+        # the gathering GEMM kernel (400 gathered rows, 384 columns) against the variant whose TMA loads read the peers
+        from teletron_b200 import ops
+
         xd = x.detach()
-        y1 = tp.fused.ag_gemm(xd, col.weight.detach(), bias=col.bias.detach(), one_kernel=True)[0]
-        y2 = tp.fused.ag_gemm(xd, col.weight.detach(), bias=col.bias.detach())[0]
+        y1, _, g1 = tp.fused.ag_gemm(xd, col.weight.detach(), bias=col.bias.detach())
+        buf = tp.fused._x[tp.fused._n_ag & 1]
+        y2 = ops.gemm_ag(buf.peer_ptrs, rows, C, col.weight.detach(), bias=col.bias.detach(), device=xd.device)
         torch.cuda.synchronize()
+        assert g1 is not None and torch.equal(g1, x_full), "the kernel's gathered operand is not the all-gather"
         assert rel(y1, y2) < 1e-3, rel(y1, y2)
     torch.cuda.synchronize()
     _lib.check_status()
