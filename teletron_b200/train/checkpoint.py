@@ -5,6 +5,14 @@
     <save>/iter_0000100/mp_rank_00/model_optim_rng.pt   one directory per tensor-parallel rank
     <save>/iter_0000100/mp_rank_00/distrib_optim.pt     fp32 optimizer state when it is sharded
 
+With ``--use-dist-ckpt`` the iteration directory holds a distributed checkpoint instead (the reference hands this
+case to Megatron's ``dist_checkpointing.save(state_dict, dir, (format, 1))``, checkpoint.py:61-106,154-179):
+``metadata.json`` (``sharded_backend`` = ``--dist-ckpt-format``), ``common.pt`` (everything that is not a tensor)
+and the tensors written by every rank in parallel through ``torch.distributed.checkpoint`` — replicated model
+tensors once (spread over the ranks with ``--ckpt-fully-parallel-save``), tensor-parallel shards and each rank's
+share of the optimizer state under rank-qualified keys, so nothing is gathered to one rank.  On load the format is
+taken from the flag or, with ``--auto-detect-ckpt-format``, from the presence of ``metadata.json``.
+
 ``model_optim_rng.pt`` is a ``torch.save`` dict with the keys ``args`` (argparse.Namespace),
 ``checkpoint_version`` (3.0), ``iteration``, ``model`` (bare parameter names such as
 ``blocks.0.self_attn.q.weight``, bf16), ``optimizer``, ``opt_param_scheduler``, ``rng_state`` and
@@ -123,11 +131,123 @@ def _plain_namespace(args) -> Namespace:
     return Namespace(**keep)
 
 
+# ----------------------------------------------------------------------------- distributed format
+DIST_META = "metadata.json"
+DIST_COMMON = "common.pt"
+
+
+def is_dist_checkpoint(root: str, iteration, release: bool = False) -> bool:
+    return os.path.exists(os.path.join(checkpoint_dir(root, iteration, release), DIST_META))
+
+
+def _dist_tensor_dict(model, optimizer, args, with_optim: bool):
+    """The tensors this rank contributes / expects, keyed so that equal keys mean equal (replicated) tensors:
+    tensor-parallel shards carry the TP rank in their key, optimizer shares the rank in the DP x CP group too."""
+    from ..parallel.tp import tp_shard_dims
+
+    inner = model.module if hasattr(model, "module") else model
+    tp_size = mpu.get_tensor_model_parallel_world_size()
+    tp_rank = mpu.get_tensor_model_parallel_rank()
+    sharded = set(tp_shard_dims(inner)) if tp_size > 1 else set()
+    out = {}
+    for k, v in inner.state_dict().items():
+        key = f"model.{k}" + (f"@tp{tp_rank}of{tp_size}" if k in sharded else "")
+        out[key] = v.detach()
+    if with_optim and optimizer is not None:
+        r = optimizer.rank if optimizer.sharded else 0
+        w = optimizer.world if optimizer.sharded else 1
+        for kind in ("master", "exp_avg", "exp_avg_sq"):
+            for i, t in enumerate(getattr(optimizer, kind)):
+                out[f"optimizer.{kind}.region{i}@tp{tp_rank}of{tp_size}@dp{r}of{w}"] = t
+    return out
+
+
+def _save_dist(iteration, model, optimizer, opt_param_scheduler, args, flops) -> str:
+    import json
+
+    import torch.distributed.checkpoint as dcp
+    from torch.distributed.checkpoint.default_planner import DefaultSavePlanner
+
+    d = checkpoint_dir(args.save, iteration)
+    multi = dist.is_initialized() and dist.get_world_size() > 1
+    rank0 = (not dist.is_initialized()) or dist.get_rank() == 0
+    with_optim = not args.no_save_optim
+    per_rank_rng = bool(getattr(args, "data_parallel_random_init", False)) and not args.no_save_rng
+    rng_states = get_rng_state(per_dp_rank=True) if per_rank_rng else None      # collective
+    if rank0:
+        os.makedirs(d, exist_ok=True)
+        common = dict(args=_plain_namespace(args), checkpoint_version=3.0, iteration=iteration,
+                      num_floating_point_operations_so_far=flops)
+        if with_optim and optimizer is not None:
+            common["optimizer"] = dict(step=optimizer.step_count, param_groups=optimizer.param_groups,
+                                       sharded=optimizer.sharded, world=optimizer.world, layout=optimizer.layout())
+            if opt_param_scheduler is not None:
+                common["opt_param_scheduler"] = opt_param_scheduler.state_dict()
+        if not args.no_save_rng:
+            common["rng_state"] = rng_states if rng_states is not None else get_rng_state()
+        _atomic_save(common, os.path.join(d, DIST_COMMON))
+        with open(os.path.join(d, DIST_META + ".tmp"), "w") as f:
+            json.dump(dict(sharded_backend=args.dist_ckpt_format, sharded_backend_version=1, common_backend="torch",
+                           common_backend_version=1), f)
+        os.replace(os.path.join(d, DIST_META + ".tmp"), os.path.join(d, DIST_META))
+    _barrier()
+    tensors = _dist_tensor_dict(model, optimizer, args, with_optim)
+    # replicated tensors are written once: by the lowest rank that holds them, or spread over all holders
+    planner = DefaultSavePlanner(dedup_save_to_lowest_rank=not args.ckpt_fully_parallel_save)
+    group = mpu.get_transformer_model_group() if multi else None
+    dcp.save(tensors, checkpoint_id=d, planner=planner, process_group=group, no_dist=not multi)
+    return d
+
+
+def _load_dist(d, model, optimizer, args, want_optim: bool):
+    import torch.distributed.checkpoint as dcp
+
+    multi = dist.is_initialized() and dist.get_world_size() > 1
+    common = torch.load(os.path.join(d, DIST_COMMON), map_location="cpu", weights_only=False)
+    opt_meta = common.get("optimizer")
+    load_optim = bool(want_optim and optimizer is not None and opt_meta is not None)
+    if load_optim:
+        if opt_meta["layout"] != optimizer.layout() or opt_meta.get("world") != optimizer.world or \
+                bool(opt_meta.get("sharded")) != bool(optimizer.sharded):
+            raise RuntimeError("the distributed checkpoint's optimizer shares were written under another layout "
+                               "(data-parallel size, bucket size or model); resume with the same layout, convert "
+                               "through a non-distributed checkpoint, or use --no-load-optim")
+    inner = model.module if hasattr(model, "module") else model
+    want = _dist_tensor_dict(model, optimizer, args, load_optim)
+    target = {k: torch.empty_like(v, device="cpu") for k, v in want.items()}
+    dcp.load(target, checkpoint_id=d, process_group=mpu.get_transformer_model_group() if multi else None,
+             no_dist=not multi)
+    sd = {}
+    for k, v in target.items():
+        if k.startswith("model."):
+            sd[k[len("model."):].split("@tp")[0]] = v
+    inner.load_state_dict(sd, strict=True)
+    if load_optim:
+        for k, v in target.items():
+            if k.startswith("optimizer."):
+                _, kind, rest = k.split(".", 2)
+                i = int(rest.split("@")[0][len("region"):])
+                getattr(optimizer, kind)[i].copy_(v)
+        optimizer.step_count = opt_meta["step"]
+        optimizer.param_groups[0].update(opt_meta["param_groups"][0])
+    return common, load_optim
+
+
 # ----------------------------------------------------------------------------- save
 def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
                     num_floating_point_operations_so_far: float = 0.0) -> Optional[str]:
     root = args.save
     assert root, "--save is not set"
+    if getattr(args, "use_dist_ckpt", False):
+        path = _save_dist(iteration, model, optimizer, opt_param_scheduler, args, num_floating_point_operations_so_far)
+        _barrier()
+        if (not dist.is_initialized()) or dist.get_rank() == 0:
+            tmp = tracker_filename(root) + ".tmp"
+            with open(tmp, "w") as f:
+                f.write(str(iteration))
+            os.replace(tmp, tracker_filename(root))
+        _barrier()
+        return path
     dp_rank = mpu.get_data_parallel_rank(with_context_parallel=True)
     sharded_opt = optimizer is not None and getattr(optimizer, "sharded", False) and not args.no_save_optim
     full_opt = optimizer.gather_full_state() if sharded_opt else None  # collective: every rank calls it
@@ -188,15 +308,26 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, strict: bool = 
         return 0, 0.0
     if args.ckpt_step is not None:
         iteration, release = args.ckpt_step, False
-    path = checkpoint_name(root, iteration, release)
-    if not os.path.exists(path):
-        raise FileNotFoundError(f"checkpoint file {path} is missing or incomplete")
-    try:
-        sd = torch.load(path, map_location="cpu", weights_only=False)
-    except Exception as e:
-        raise RuntimeError(f"could not read checkpoint {path}: {e}") from e
-    inner = model.module if hasattr(model, "module") else model
-    inner.load_state_dict(sd["model"], strict=strict)
+    dist_fmt = is_dist_checkpoint(root, iteration, release)
+    if dist_fmt and not (getattr(args, "use_dist_ckpt", False) or getattr(args, "auto_detect_ckpt_format", False)):
+        raise RuntimeError(f"{checkpoint_dir(root, iteration, release)} holds a distributed checkpoint; pass "
+                           "--use-dist-ckpt or --auto-detect-ckpt-format")
+    if dist_fmt:
+        want_optim = not (finetune or release or args.no_load_optim)
+        sd, optim_loaded = _load_dist(checkpoint_dir(root, iteration, release), model, optimizer, args, want_optim)
+        if optim_loaded:
+            sd.pop("optimizer", None)              # already placed; what is left is read like the plain format
+            sd["_optimizer_placed"] = True
+    else:
+        path = checkpoint_name(root, iteration, release)
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"checkpoint file {path} is missing or incomplete")
+        try:
+            sd = torch.load(path, map_location="cpu", weights_only=False)
+        except Exception as e:
+            raise RuntimeError(f"could not read checkpoint {path}: {e}") from e
+        inner = model.module if hasattr(model, "module") else model
+        inner.load_state_dict(sd["model"], strict=strict)
     flops = float(sd.get("num_floating_point_operations_so_far", 0.0))
     if finetune or release:
         iteration = 0
@@ -209,7 +340,9 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, strict: bool = 
             args.consumed_train_samples = getattr(saved, "consumed_train_samples", 0)
             args.consumed_valid_samples = getattr(saved, "consumed_valid_samples", 0)
         if optimizer is not None:
-            if not args.no_load_optim and "optimizer" in sd:
+            if sd.get("_optimizer_placed"):
+                pass                               # a distributed checkpoint: every rank has read its own shares
+            elif not args.no_load_optim and "optimizer" in sd:
                 opt_sd = sd["optimizer"]
                 if opt_sd.get("sharded"):        # the fp32 state lives beside the model file, in buffer order
                     full = torch.load(checkpoint_name(root, iteration, filename=DISTOPT_FILE),

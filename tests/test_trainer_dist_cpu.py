@@ -352,3 +352,43 @@ def test_sharded_optimizer_state_moves_to_another_dp_size_and_bucket_size(tmp_pa
         for key in ("exp_avg", "exp_avg_sq"):
             assert torch.equal(saved[key][o:o + n], loaded[key][lo:lo + n]), (k, key)
     assert float(saved["exp_avg_sq"].abs().sum()) > 0
+
+
+def _dist_ckpt_worker(rank, world, root, mode):
+    from teletron_b200.train import Trainer, make_forward_step
+
+    flags = "--use-dist-ckpt --ckpt-fully-parallel-save" if mode != "auto" else "--auto-detect-ckpt-format"
+    a = _args(world, f"--synthetic-latents --global-batch-size 2 --use-distributed-optimizer --ddp-bucket-size 20000 "
+                     f"--save {root} --load {root} --train-iters 4 {flags}")
+    t = Trainer(a)
+    gen = torch.Generator().manual_seed(9)
+    fwd = make_forward_step(timestep_generator=gen)
+    def step():
+        t.train_step(fwd)
+        a.iteration += 1
+        a.consumed_train_samples += a.global_batch_size
+
+    if mode == "save":
+        step(), step()
+        t.save(2)
+        step(), step()
+        return t.buffer.params.clone(), torch.cat([m.reshape(-1) for m in t.optimizer.exp_avg]), sorted(os.listdir(
+            os.path.join(root, "iter_0000002")))
+    assert a.iteration == 2 and t.optimizer.step_count == 2 and a.consumed_train_samples == 4
+    for _ in range(2):       # the generator restarts, so replay its first two draws to stay on the saved run's stream
+        torch.randint(0, 1000, (1,), generator=gen)
+    step(), step()
+    return t.buffer.params.clone(), torch.cat([m.reshape(-1) for m in t.optimizer.exp_avg]), []
+
+
+def test_distributed_checkpoint_resumes_exactly(tmp_path):
+    """--use-dist-ckpt: every rank writes its own shares (no gather), replicated tensors once; resuming from the
+    directory (named by the flag or detected from metadata.json) continues bit for bit."""
+    saved = run_distributed(_dist_ckpt_worker, 2, str(tmp_path), "save")
+    files = saved[0][2]
+    assert "metadata.json" in files and "common.pt" in files and ".metadata" in files
+    assert sum(f.endswith(".distcp") for f in files) == 2 and "mp_rank_00" not in files
+    for mode in ("load", "auto"):
+        got = run_distributed(_dist_ckpt_worker, 2, str(tmp_path), mode)
+        for r in range(2):
+            assert torch.equal(got[r][0], saved[r][0]) and torch.equal(got[r][1], saved[r][1])
