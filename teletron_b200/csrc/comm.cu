@@ -109,9 +109,13 @@ dp_bucket_kernel(PeerPtrs grads, PeerPtrs params16, BucketGeom geo, int b0, int 
           g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
         }
         ss += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
+        // the sum replaces this rank's own copy of its share (nobody else reads that part of this rank's buffer),
+        // or goes to a separate owned-flat buffer when the caller gave one
         if (reduced) reinterpret_cast<float4*>(reduced)[fl] = g;
+        else if (!ADAM) *reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[geo.rank]) + off) = g;
       } else {
-        g = reinterpret_cast<const float4*>(reduced)[fl];
+        g = reduced ? reinterpret_cast<const float4*>(reduced)[fl]
+                    : ld4(reinterpret_cast<const float*>(grads.p[geo.rank]) + off);
       }
       if (ADAM) {
         float4 pp = reinterpret_cast<float4*>(master)[fl];
@@ -212,8 +216,9 @@ TT_API int tt_peer_barrier(const long long* flag_ptrs, int world, int rank, int 
 
 // One region of the flat buffers cut into `n_buckets` uniform buckets of `bucket_elems` elements (the last one
 // `last_elems` long); works on buckets [b0, b1).
-//   mode 0: pull-reduce each owned share from every peer into `reduced` (owned-flat order) + sum-of-squares partials
-//   mode 1: AdamW from `reduced` + bf16 parameter store into every peer
+//   mode 0: pull-reduce each owned share from every peer + sum-of-squares partials; the sum goes to `reduced`
+//           (owned-flat order) or, when `reduced` is null, over this rank's own copy of the share in its gradient buffer
+//   mode 1: AdamW from `reduced` (or from that in-place sum) + bf16 parameter store into every peer
 //   mode 2: both in one pass (no global-norm clipping)
 // The clip coefficient is `*clip_coef` when given; otherwise, when `ss_slots` is given, the kernel sums that array's
 // `world` entries (every rank's share of the squared norm, see tt_dp_norm_exchange), writes the norm to `norm_out`
@@ -230,11 +235,10 @@ TT_API int tt_dp_bucket_step(int mode, const long long* grad_ptrs, const long lo
                last_elems % (4ll * world) == 0 && region_start % 4 == 0,
            "dp_bucket_step: buckets must split into 16-byte aligned shares");
   PeerPtrs g, p;
-  if (mode != 1) {
+  if (mode != 1 || reduced == nullptr) {
     if (fill_peers(&g, grad_ptrs, world)) return -1;
   } else {
     for (int i = 0; i < MAX_PEERS; ++i) g.p[i] = nullptr;
-    TT_CHECK(reduced != nullptr, "dp_bucket_step: mode 1 reads the reduced gradient");
   }
   if (mode != 0) {
     if (fill_peers(&p, param_ptrs, world)) return -1;

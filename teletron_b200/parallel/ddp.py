@@ -375,9 +375,6 @@ class DistributedOptimizer:
         from ..ops import _lib
 
         buf, arena, r = self.buf, self.buf.arena, self.regions[bk.region]
-        if self._reduced is None:
-            self._reduced = [torch.empty(self.owned_len(x), dtype=torch.float32, device=buf.grads.device)
-                             for x in self.regions]
         cur = torch.cuda.current_stream()
         if self._side is None:
             self._side = torch.cuda.Stream()
@@ -399,7 +396,7 @@ class DistributedOptimizer:
                 _lib.c_int(0), buf.symm_grads.c_ptrs(), buf.symm_params.c_ptrs(), _lib.c_int(self.world),
                 _lib.c_int(self.rank), _lib.c_ll(r.start), _lib.c_ll(r.bucket_elems), _lib.c_ll(r.last_elems),
                 _lib.c_int(r.n_buckets), _lib.c_int(bk.index), _lib.c_int(bk.index + 1),
-                _lib.ptr(self._reduced[bk.region]), None, None, None, _lib.c_float(self.grad_scale), None, None,
+                None, None, None, None, _lib.c_float(self.grad_scale), None, None,
                 _lib.c_float(0.0), None, _lib.c_float(0.0), _lib.c_float(0.0), _lib.c_float(0.0), _lib.c_float(0.0),
                 _lib.c_float(0.0), _lib.c_int(1), _lib.ptr(self._partials[bk.gid]), _lib.c_int(self._blocks),
                 _lib.stream())
@@ -428,7 +425,9 @@ class DistributedOptimizer:
         if self.fused and self._side_used:
             torch.cuda.current_stream().wait_stream(self._side)
             self._side_used = False
-        if self.world > 1 and self.sharded:
+        if self.fused:
+            self._shard_grads = ["in place"] * len(self.regions)    # each share's sum sits in this rank's gradient buffer
+        elif self.world > 1 and self.sharded:
             self._shard_grads = list(self._reduced)
         else:
             self._shard_grads = [g[r.start:r.end] for r in self.regions]
@@ -475,7 +474,7 @@ class DistributedOptimizer:
             _lib.c_int(mode), buf.symm_grads.c_ptrs(), buf.symm_params.c_ptrs(), _lib.c_int(self.world),
             _lib.c_int(self.rank), _lib.c_ll(r.start), _lib.c_ll(r.bucket_elems), _lib.c_ll(r.last_elems),
             _lib.c_int(r.n_buckets), _lib.c_int(b0), _lib.c_int(r.n_buckets if b1 is None else b1),
-            _lib.ptr(self._reduced[ri] if self._reduced is not None else None), _lib.ptr(self.master[ri]),
+            None, _lib.ptr(self.master[ri]),
             _lib.ptr(self.exp_avg[ri]), _lib.ptr(self.exp_avg_sq[ri]), _lib.c_float(self.grad_scale),
             _lib.ptr(coef), _lib.ptr(ss_slots), _lib.c_float(self.clip_grad or 0.0),
             _lib.ptr(self._norm_out if ss_slots is not None else None), _lib.c_float(lr),
@@ -500,7 +499,10 @@ class DistributedOptimizer:
     def _fused_step_body(self, L, arena):
         from ..ops import _lib
 
-        zeros = self._count_zeros(self._reduced) if self.log_num_zeros else None
+        buf = self.buf
+        zeros = None
+        if self.log_num_zeros:
+            zeros = self._count_zeros([self._owned(buf.grads, r) for r in self.regions])
         if self.tp_group is None:
             rc = L.tt_dp_norm_exchange(_lib.ptr(self._partials), _lib.c_int(self._partials.numel()),
                                        self._ss_slots.c_ptrs(), _lib.c_int(self.world), _lib.c_int(self.rank),

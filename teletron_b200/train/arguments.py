@@ -243,6 +243,9 @@ def validate_args(args):
     if args.lr_warmup_fraction is not None and (args.lr_warmup_iters or args.lr_warmup_samples):
         raise ValueError("give either --lr-warmup-fraction or --lr-warmup-iters/samples")
     _flags_without_effect(args)
+    # video tokens per sample (8x VAE, 4x temporal compression, 2 x 2 spatial patches): throughput is logged in tokens/s
+    h, w = args.video_resolution
+    args.tokens_per_sample = ((args.num_frames - 1) // 4 + 1) * (h // 16) * (w // 16)
     args.consumed_train_samples = 0
     args.consumed_valid_samples = 0
     args.iteration = 0

@@ -54,6 +54,12 @@ def checkpoint_name(root: str, iteration, release=False, tp_rank: Optional[int] 
     return os.path.join(checkpoint_dir(root, iteration, release), sub, filename)
 
 
+def zero2_shard_name(root: str, iteration, release: bool = False) -> str:
+    """``zero2_optim_dp{d}_cp{c}.pt`` of this rank, beside its tensor-parallel rank's model file."""
+    return checkpoint_name(root, iteration, release,
+                           filename=f"zero2_optim_dp{mpu.get_data_parallel_rank()}_cp{mpu.get_context_parallel_rank()}.pt")
+
+
 def tracker_filename(root: str) -> str:
     return os.path.join(root, TRACKER)
 
@@ -250,7 +256,12 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
         return path
     dp_rank = mpu.get_data_parallel_rank(with_context_parallel=True)
     sharded_opt = optimizer is not None and getattr(optimizer, "sharded", False) and not args.no_save_optim
-    full_opt = optimizer.gather_full_state() if sharded_opt else None  # collective: every rank calls it
+    zero2 = sharded_opt and bool(getattr(args, "use_zero2", False))
+    if zero2:
+        # --use-zero2: every rank writes its own optimizer shares, nothing is gathered
+        # (zero2_optim_dp{d}_cp{c}.pt beside the model file, teletron/train/checkpoint/utils.py:88-95)
+        _atomic_save(optimizer.state_dict(), zero2_shard_name(root, iteration))
+    full_opt = optimizer.gather_full_state() if (sharded_opt and not zero2) else None  # collective: every rank calls it
     per_rank_rng = bool(getattr(args, "data_parallel_random_init", False)) and not args.no_save_rng
     rng_states = get_rng_state(per_dp_rank=True) if per_rank_rng else None  # collective too
     path = None
@@ -264,7 +275,7 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
                 sd["optimizer"] = optimizer.state_dict()
             elif optimizer is not None:
                 sd["optimizer"] = dict(step=optimizer.step_count, param_groups=optimizer.param_groups,
-                                       sharded=True)
+                                       sharded=True, zero2=zero2)
             if opt_param_scheduler is not None:
                 sd["opt_param_scheduler"] = opt_param_scheduler.state_dict()
         if not args.no_save_rng:
@@ -344,7 +355,13 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, strict: bool = 
                 pass                               # a distributed checkpoint: every rank has read its own shares
             elif not args.no_load_optim and "optimizer" in sd:
                 opt_sd = sd["optimizer"]
-                if opt_sd.get("sharded"):        # the fp32 state lives beside the model file, in buffer order
+                if opt_sd.get("zero2"):          # one file per DP x CP rank, each rank reads its own
+                    shard = zero2_shard_name(root, iteration)
+                    if not os.path.exists(shard):
+                        raise FileNotFoundError(f"{shard} is missing: ZeRO-2 optimizer shards can only be read by a "
+                                                "run with the same data- and context-parallel sizes")
+                    optimizer.load_state_dict(torch.load(shard, map_location="cpu", weights_only=False))
+                elif opt_sd.get("sharded"):      # the fp32 state lives beside the model file, in buffer order
                     full = torch.load(checkpoint_name(root, iteration, filename=DISTOPT_FILE),
                                       map_location="cpu", weights_only=False)
                     optimizer.scatter_full_state(full)

@@ -334,3 +334,135 @@ def test_gemm_pair_kernel_epilogues(epi):
     _lib.check_status()
     for x, y in zip(outs[0], outs[1]):
         assert rel(x, y) < 1e-3
+
+
+# ------------------------------------------------------------------------------ real sizes, max-abs bounds, odd shapes
+def _max_abs_ok(got, ref, frac):
+    """Largest element-wise error relative to the reference's largest magnitude."""
+    return (got.float() - ref.float()).abs().max().item() <= frac * ref.float().abs().max().item()
+
+
+@pytest.mark.parametrize("M,N_,K,b_mn", [(2048, 1536, 8960, False), (1024, 5120, 13824, False), (2048, 8960, 1536, True)])
+def test_gemm_at_the_models_reduction_depths(M, N_, K, b_mn):
+    """K = 8,960 and 13,824 (the second feed-forward layer of the 1.3B / 14B models) accumulate 140 / 216 k-blocks
+    per tile: normalised-L2 and max-abs error against the fp32 product."""
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((K, N_) if b_mn else (N_, K), device=DEV, dtype=torch.bfloat16)
+    kw = dict(b_mn=b_mn, alpha=1.0 / math.sqrt(K))
+    ref = G.gemm_ref(a, b, out_dtype=torch.float32, **kw)
+    for pair in (True, False):
+        old = G.set_pair_gemm(pair)
+        try:
+            got = G.gemm(a, b, **kw)
+        finally:
+            G.set_pair_gemm(old)
+        assert rel(got, ref) < 2e-3, (pair, rel(got, ref))
+        assert _max_abs_ok(got, ref, 8e-3), pair      # bf16 output rounding of values up to ~5 sigma
+
+
+def test_attention_at_the_benchmark_shape_rows_against_fp32():
+    """32,760 tokens x 12 heads (the 480P x 81-frame sample): a few hundred query rows of the forward output, and
+    dK / dV rows of the backward, against an fp32 softmax over all 32,760 keys."""
+    S, H, D = 32760, 12, 128
+    q, k, v = (torch.randn(1, S, H, D, device=DEV).to(torch.bfloat16) for _ in range(3))
+    o, lse = attention_fwd(q, k, v)
+    rows = torch.cat([torch.arange(0, 64), torch.arange(16300, 16364), torch.arange(S - 120, S)]).to(DEV)
+    scale = 1.0 / math.sqrt(D)
+    for h in (0, 7, 11):
+        s = (q[0, rows, h].float() @ k[0, :, h].float().t()) * scale
+        p = torch.softmax(s, dim=-1)
+        ref = p @ v[0, :, h].float()
+        got = o[0, rows, h]
+        assert rel(got, ref) < 2e-3 and _max_abs_ok(got, ref, 2e-2), h
+        assert (lse[0, h, rows] - torch.logsumexp(s, -1)).abs().max().item() < 2e-3
+    # backward: dV = P^T dO and dK = dS^T Q for a slice of keys, with the probabilities of ALL queries of one head
+    do = torch.randn_like(o)
+    dq, dk, dv = attention_bwd(q, k, v, o, lse, do)
+    h = 5
+    keys = torch.arange(20000, 20128, device=DEV)
+    s = (q[0, :, h].float() @ k[0, keys, h].float().t()) * scale                     # [S, 128]
+    p = torch.exp(s - lse[0, h].unsqueeze(1))
+    dv_ref = p.t() @ do[0, :, h].float()
+    dp = do[0, :, h].float() @ v[0, keys, h].float().t()
+    delta = (do[0, :, h].float() * o[0, :, h].float()).sum(-1, keepdim=True)
+    dk_ref = (p * (dp - delta)).t() @ q[0, :, h].float() * scale
+    assert rel(dv[0, keys, h], dv_ref) < 3e-3 and rel(dk[0, keys, h], dk_ref) < 5e-3
+    assert _max_abs_ok(dv[0, keys, h], dv_ref, 3e-2) and _max_abs_ok(dk[0, keys, h], dk_ref, 3e-2)
+
+
+@pytest.mark.parametrize("rows,C", [(65, 1536), (1, 256), (1027, 8960), (333, 72)])
+def test_colsum_odd_shapes(rows, C):
+    from teletron_b200.ops.linear import colsum
+
+    x = torch.randn(rows, C, device=DEV).to(torch.bfloat16)
+    ref = x.float().sum(0)
+    got = colsum(x)
+    assert (got - ref).abs().max().item() <= 1e-4 * max(1.0, ref.abs().max().item())
+    wide = torch.randn(rows, 2 * C + 8, device=DEV).to(torch.bfloat16)      # strided view
+    assert (colsum(wide[:, 8:8 + C]) - wide[:, 8:8 + C].float().sum(0)).abs().max().item() <= \
+        1e-4 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("n", [4, 1028, 999_996, 40_000_004])
+def test_grad_norm_odd_lengths(n):
+    from teletron_b200.ops.optim import grad_norm
+
+    g = torch.randn(n, device=DEV)
+    out = grad_norm(g, max_norm=1.0)
+    ref = g.double().norm().item()
+    assert abs(out[0].item() - ref) < 1e-5 * ref and abs(out[2].item() - ref * ref) < 1e-5 * ref * ref
+    assert abs(out[1].item() - min(1.0, 1.0 / (ref + 1e-6))) < 1e-6
+
+
+@pytest.mark.parametrize("B,S,C", [(1, 77, 1536), (2, 301, 256), (3, 64, 5120)])
+def test_gate_backward_odd_shapes(B, S, C):
+    """residual + gate * z: dz = gate * dy, dgate[b] = sum over the sample's rows of dy * z (two-stage column sums)."""
+    rows = B * S
+    mk = lambda *sh, s=1.0: (torch.randn(*sh, device=DEV) * s).to(torch.bfloat16)
+    x, w, b, res = mk(rows, 128, s=0.5), mk(C, 128, s=0.1), mk(C), mk(rows, C)
+    gate = torch.randn(B, C, device=DEV)
+    dy = mk(rows, C)
+    ts = [t.detach().clone().requires_grad_(True) for t in (x, w, b, res, gate)]
+    ops.linear_residual(ts[0], ts[1], ts[2], ts[3], ts[4], S).backward(dy)
+    rs = [t.detach().float().requires_grad_(True) for t in (x, w, b, res, gate)]
+    z = torch.nn.functional.linear(rs[0], rs[1], rs[2])
+    (rs[3] + rs[4].repeat_interleave(S, 0) * z).backward(dy.float())
+    for name, u, v in zip("x w b res gate".split(), ts, rs):
+        assert rel(u.grad, v.grad) < 8e-3, (name, rel(u.grad, v.grad))
+    assert _max_abs_ok(ts[4].grad, rs[4].grad, 3e-2)
+
+
+def test_multi_tensor_fold_matches_add():
+    """Gradients of many small bf16 tensors folded into fp32 slices of a flat buffer in one launch per 48 tensors."""
+    from teletron_b200.parallel.ddp import ParamBuffer
+
+    torch.manual_seed(1)
+    sizes = [7, 1536, 3, 9216, 128, 1] * 20                      # 120 tensors, odd lengths
+    mod = torch.nn.ParameterList([torch.nn.Parameter(torch.randn(n, device=DEV).to(torch.bfloat16)) for n in sizes])
+    buf = ParamBuffer(mod)
+    buf.grads.normal_()
+    before = buf.grads.clone()
+    for p in mod:
+        p.grad = torch.randn_like(p)
+    grads = {n: p.grad.clone() for n, p in buf.named}
+    count0 = _lib.launch_count()
+    buf.collect_grads()
+    assert _lib.launch_count() - count0 == 3                      # ceil(120 / 48) launches
+    for n, p in buf.named:
+        o, cnt, _ = buf.index[n]
+        assert torch.equal(buf.grads[o:o + cnt], before[o:o + cnt] + grads[n].float()), n
+        assert p.grad is None
+
+
+def test_tensor_map_cache_reuses_descriptors():
+    L = _lib.lib()
+    L.tt_tmap_cache_size.restype = _lib.c_ll
+    a = torch.randn(512, 256, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(512, 256, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(512, 512, device=DEV, dtype=torch.bfloat16)
+    G.gemm(a, b, out=out)
+    n1 = L.tt_tmap_cache_size()
+    for _ in range(5):
+        G.gemm(a, b, out=out)
+    assert L.tt_tmap_cache_size() == n1 and n1 >= 2
+    assert rel(out, G.gemm_ref(a, b)) < 2e-3

@@ -392,3 +392,29 @@ def test_distributed_checkpoint_resumes_exactly(tmp_path):
         got = run_distributed(_dist_ckpt_worker, 2, str(tmp_path), mode)
         for r in range(2):
             assert torch.equal(got[r][0], saved[r][0]) and torch.equal(got[r][1], saved[r][1])
+
+
+def _zero2_worker(rank, world, root, mode):
+    from teletron_b200.train import Trainer, make_forward_step
+
+    a = _args(world, f"--synthetic-latents --global-batch-size 2 --use-zero2 --context-parallel-size 2 "
+                     f"--save {root} --load {root} --train-iters 3")
+    t = Trainer(a)
+    assert t.optimizer.sharded
+    if mode == "save":
+        gen = torch.Generator().manual_seed(9)
+        t.train_step(make_forward_step(timestep_generator=gen))
+        a.iteration = 1
+        t.save(1)
+        return sorted(os.listdir(os.path.join(root, "iter_0000001", "mp_rank_00"))), [m.clone() for m in t.optimizer.exp_avg_sq]
+    assert a.iteration == 1 and t.optimizer.step_count == 1
+    return [], [m.clone() for m in t.optimizer.exp_avg_sq]
+
+
+def test_zero2_flag_writes_one_optimizer_shard_per_rank(tmp_path):
+    saved = run_distributed(_zero2_worker, 2, str(tmp_path), "save")
+    assert saved[0][0] == ["model_optim_rng.pt", "zero2_optim_dp0_cp0.pt", "zero2_optim_dp0_cp1.pt"]
+    loaded = run_distributed(_zero2_worker, 2, str(tmp_path), "load")
+    for r in range(2):
+        for a_, b_ in zip(saved[r][1], loaded[r][1]):
+            assert torch.equal(a_, b_) and float(a_.abs().sum()) > 0
