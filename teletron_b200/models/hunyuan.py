@@ -33,7 +33,7 @@ import torch.nn.functional as F
 
 from .. import ops
 from ..parallel import recompute as rc
-from ..parallel.tp import ColumnParallelLinear, RowParallelLinear, TPContext
+from ..parallel.tp import ColumnParallelLinear, FusedColumnParallel, RowParallelLinear, TPContext
 from ..parallel.ulysses import UlyssesContext, _HeadToSeq, _SeqToHead
 from .registry import MODELS
 
@@ -280,24 +280,26 @@ class HunyuanAttention(nn.Module):
         C, D = cfg.hidden_size, cfg.attention_head_dim
         self.tp, self.D, self.eps, self.dual = tp, D, cfg.eps, dual
         self.heads_local = cfg.num_attention_heads // tp.size
-        self.to_q, self.to_k, self.to_v = (ColumnParallelLinear(C, C, tp) for _ in range(3))
+        # q / k / v as one column-parallel GEMM (one all-gather -> GEMM under TP); checkpoints keep to_q / to_k / to_v
+        self.to_qkv = FusedColumnParallel(C, C, ("to_q", "to_k", "to_v"), tp)
+        FusedColumnParallel.install_state_hooks(self, "to_qkv")
         self.norm_q, self.norm_k = HeadNorm(D), HeadNorm(D)
         if dual:
             self.to_out = nn.ModuleList([RowParallelLinear(C, C, tp)])
-            self.add_q_proj, self.add_k_proj, self.add_v_proj = (ColumnParallelLinear(C, C, tp) for _ in range(3))
+            self.add_qkv_proj = FusedColumnParallel(C, C, ("add_q_proj", "add_k_proj", "add_v_proj"), tp)
+            FusedColumnParallel.install_state_hooks(self, "add_qkv_proj")
             self.norm_added_q, self.norm_added_k = HeadNorm(D), HeadNorm(D)
             self.to_add_out = RowParallelLinear(C, C, tp)
 
     def qkv(self, x_rows, freqs, text: bool, B: int):
         """x_rows: TP-row-sharded [rows/T, C]. Returns q, k, v as [B, tokens, H_local, D]."""
-        xg = self.tp.gather_rows(x_rows)
         use_add = text and self.dual
-        lq, lk, lv = (self.add_q_proj, self.add_k_proj, self.add_v_proj) if use_add else (self.to_q, self.to_k, self.to_v)
+        proj = self.add_qkv_proj if use_add else self.to_qkv
         nq, nk = (self.norm_added_q, self.norm_added_k) if use_add else (self.norm_q, self.norm_k)
-        q = ops.rmsnorm_rope(lq(xg, gathered=True), nq.weight, freqs, self.D, True, self.eps)
-        k = ops.rmsnorm_rope(lk(xg, gathered=True), nk.weight, freqs, self.D, True, self.eps)
-        v = lv(xg, gathered=True)
-        n = xg.shape[0] // B
+        q_pre, k_pre, v = proj.split(proj(x_rows))
+        q = ops.rmsnorm_rope(q_pre, nq.weight, freqs, self.D, True, self.eps)
+        k = ops.rmsnorm_rope(k_pre, nk.weight, freqs, self.D, True, self.eps)
+        n = q_pre.shape[0] // B
         return tuple(t.reshape(B, n, self.heads_local, self.D) for t in (q, k, v))
 
     def attend(self, hv, ht, freqs, B, cp, text_lens):
@@ -308,12 +310,9 @@ class HunyuanAttention(nn.Module):
         fu = cp.fused if (cp is not None and cp.size > 1) else None
         if (fu is not None and hv.is_cuda and fu.supports(self.heads_local, self.D)
                 and self.heads_local % cp.size == 0):
-            xg = self.tp.gather_rows(hv)
-            q_pre = self.to_q(xg, gathered=True)
-            k_pre = self.to_k(xg, gathered=True)
-            v = self.to_v(xg, gathered=True)
+            q_pre, k_pre, v = self.to_qkv.split(self.to_qkv(hv))
             qt, kt, vt = self.qkv(ht, None, True, B)
-            S_l = xg.shape[0] // B
+            S_l = q_pre.shape[0] // B
             ov, ot = fu.joint_attention(q_pre, k_pre, v, self.norm_q.weight, self.norm_k.weight, freqs, qt, kt, vt,
                                         text_lens, B, S_l, self.heads_local, self.D, self.eps)
             ot = _GatherHeads.apply(ot.contiguous(), cp.group, cp.size, cp.rank)

@@ -285,6 +285,52 @@ class ColumnParallelLinear(nn.Module):
         return ops.linear(x, self.weight, self.bias, act)
 
 
+class FusedColumnParallel(ColumnParallelLinear):
+    """Several column-parallel projections of the same input as ONE GEMM (q / k / v): the local weight is
+    ``[n * out / T, in]`` with one row block per projection, so a single all-gather -> GEMM serves all of them.  In
+    state dicts the projections appear under their own names (``names``: sibling keys ``<name>.weight`` /
+    ``<name>.bias`` beside this module's key), each holding this rank's shard, so checkpoints keep the per-projection
+    layout of the unfused model.  The module that owns this one calls ``install_state_hooks(owner, attribute)``:
+    ``load_state_dict`` hands a child only the keys under its own prefix, so the renaming has to happen one level up."""
+
+    def __init__(self, in_features: int, out_features: int, names, tp: TPContext, bias: bool = True):
+        nn.Module.__init__(self)
+        assert out_features % tp.size == 0
+        self.tp, self.in_features, self.out_features, self.names = tp, in_features, out_features, tuple(names)
+        self.out_local = out_features // tp.size
+        self.weight = nn.Parameter(torch.cat([_init_shard(out_features, in_features, 0, tp) for _ in self.names]))
+        self.bias = nn.Parameter(torch.zeros(len(self.names) * self.out_local)) if bias else None
+        self.shard_dim = 0
+        self.col_groups = tuple(out_features for _ in self.names)     # of the merged (all TP ranks) weight
+
+    @staticmethod
+    def install_state_hooks(owner: nn.Module, attr: str):
+        def save_hook(module, state, prefix, _local):
+            fp = getattr(module, attr)
+            for kind in ("weight", "bias"):
+                key = f"{prefix}{attr}.{kind}"
+                if key in state:
+                    t = state.pop(key)
+                    for i, n in enumerate(fp.names):
+                        state[f"{prefix}{n}.{kind}"] = t[i * fp.out_local:(i + 1) * fp.out_local]
+            return state
+
+        def load_hook(module, state, prefix, *_):
+            fp = getattr(module, attr)
+            for kind in ("weight", "bias"):
+                keys = [f"{prefix}{n}.{kind}" for n in fp.names]
+                if all(k in state for k in keys):
+                    state[f"{prefix}{attr}.{kind}"] = torch.cat([state.pop(k) for k in keys], dim=0)
+
+        owner._register_state_dict_hook(save_hook)
+        owner.register_load_state_dict_pre_hook(load_hook)
+
+    def split(self, y):
+        """The projections' column blocks of the fused output."""
+        n = self.out_local
+        return tuple(y[:, i * n:(i + 1) * n] for i in range(len(self.names)))
+
+
 class RowParallelLinear(nn.Module):
     """Holds columns [rank*K/T, (rank+1)*K/T) of a [N, K] weight. Output: row-sharded [M/T, N]."""
 
@@ -355,10 +401,24 @@ def tp_merge_state_dicts(shards: List[Dict[str, torch.Tensor]], shard_dims: Dict
     return out
 
 
-def tp_shard_dims(module: nn.Module) -> Dict[str, int]:
+def tp_shard_dims(module: nn.Module, params: bool = False) -> Dict[str, object]:
+    """Which tensors are tensor-parallel shards, and along which dim (or ``(dim, column groups)``).  Keys are
+    state-dict names by default; with ``params`` they are parameter names (they differ for fused projections,
+    which state dicts list per projection)."""
     dims = {}
     for name, m in module.named_modules():
-        if isinstance(m, (ColumnParallelLinear, RowParallelLinear)):
+        if isinstance(m, FusedColumnParallel):
+            if params:
+                dims[f"{name}.weight"] = (0, m.col_groups)
+                if m.bias is not None:
+                    dims[f"{name}.bias"] = (0, m.col_groups)
+            else:
+                parent = name.rsplit(".", 1)[0] + "." if "." in name else ""
+                for n in m.names:
+                    dims[f"{parent}{n}.weight"] = 0
+                    if m.bias is not None:
+                        dims[f"{parent}{n}.bias"] = 0
+        elif isinstance(m, (ColumnParallelLinear, RowParallelLinear)):
             groups = getattr(m, "col_groups", None)
             dims[f"{name}.weight"] = (m.shard_dim, tuple(groups)) if groups else m.shard_dim
             if isinstance(m, ColumnParallelLinear) and m.bias is not None:

@@ -75,11 +75,11 @@ def _tp_worker(rank, world, full_sd):
     mpu.initialize_model_parallel(tensor_model_parallel_size=world)
     tp = TPContext(mpu.get_tensor_model_parallel_group(), world, rank)
     m = HunyuanVideoModel(_cfg(), None, tp)
-    dims = tp_shard_dims(m)
-    m.load_state_dict(tp_shard_state_dict(full_sd, dims, rank, world))
+    m.load_state_dict(tp_shard_state_dict(full_sd, tp_shard_dims(m), rank, world))   # state-dict names
+    pdims = tp_shard_dims(m, params=True)                                           # parameter names
     out, grads = _run(m)
     for n, g in grads.items():
-        if n not in dims:
+        if n not in pdims:
             torch.distributed.all_reduce(g)        # replicated parameters see only this rank's rows
     return out, grads, m.state_dict()
 
@@ -88,9 +88,10 @@ def test_tensor_parallel_matches_single_rank_and_shards_round_trip():
     m, (ref_out, ref_g) = _single()
     full_sd = {k: v.clone() for k, v in m.state_dict().items()}
     outs = run_distributed(_tp_worker, 2, full_sd)
-    dims = tp_shard_dims(HunyuanVideoModel(_cfg(), None, TPContext(None, 2, 0)))
-    merged_g = tp_merge_state_dicts([o[1] for o in outs], dims)
-    merged_sd = tp_merge_state_dicts([o[2] for o in outs], dims)
+    probe = HunyuanVideoModel(_cfg(), None, TPContext(None, 2, 0))
+    merged_g = tp_merge_state_dicts([o[1] for o in outs], tp_shard_dims(probe, params=True))
+    merged_sd = tp_merge_state_dicts([o[2] for o in outs], tp_shard_dims(probe))
+    assert any(k.endswith("attn.to_q.weight") for k in full_sd) and not any("to_qkv" in k for k in full_sd)
     for out, _, _ in outs:
         assert (out - ref_out).abs().max() < 1e-5
     for n, g in ref_g.items():
@@ -231,7 +232,7 @@ def _tp_norm_worker(rank, world):
 
     t = Trainer(_hy_train_args(world, "--tensor-model-parallel-size 2 --clip-grad 0.05"))
     inner = t.model.module if hasattr(t.model, "module") else t.model
-    sharded = set(tp_shard_dims(inner))
+    sharded = set(tp_shard_dims(inner))          # state-dict names: fused projections listed per projection
     gen = torch.Generator().manual_seed(4)
     fwd = make_hunyuan_forward_step(timestep_generator=gen)
     norms = []

@@ -332,8 +332,8 @@ def _hy_tp_worker(rank, world, full_sd, fused):
     if fused:
         tp.fused = FusedTP(SymmetricArena(dist.group.WORLD))
     m = HunyuanVideoModel(hunyuan_config("hunyuan-tiny"), None, tp)
-    dims = tp_shard_dims(m)
-    m.load_state_dict(tp_shard_state_dict(full_sd, dims, rank, world))
+    m.load_state_dict(tp_shard_state_dict(full_sd, tp_shard_dims(m), rank, world))
+    dims = tp_shard_dims(m, params=True)
     m = m.cuda().to(torch.bfloat16)
     out, grads = _hy_run(m)
     for n, g in grads.items():
@@ -361,7 +361,7 @@ def test_hunyuan_tp2_matches_single_gpu(fused):
     full_sd = {k: v.clone() for k, v in ref.state_dict().items()}
     ref_out, ref_g = _hy_run(copy.deepcopy(ref).cuda().to(torch.bfloat16))
     outs = run_distributed(_hy_tp_worker, 2, full_sd, fused, backend="nccl")
-    dims = tp_shard_dims(HunyuanVideoModel(hunyuan_config("hunyuan-tiny"), None, TPContext(None, 2, 0)))
+    dims = tp_shard_dims(HunyuanVideoModel(hunyuan_config("hunyuan-tiny"), None, TPContext(None, 2, 0)), params=True)
     merged = tp_merge_state_dicts([o[1] for o in outs], dims)
     for out, _ in outs:
         assert rel(out, ref_out) < 1e-2
@@ -391,8 +391,8 @@ def _hy_cp_worker(rank, world, full_sd, tp_size, fused):
             tp.fused = FusedTP(SymmetricArena(mpu.get_tensor_model_parallel_group()))
     cfg = hunyuan_config("hunyuan-tiny", hidden_size=512, num_attention_heads=4)
     m = HunyuanVideoModel(cfg, cp, tp)
-    dims = tp_shard_dims(m)
-    m.load_state_dict(tp_shard_state_dict(full_sd, dims, tp.rank, tp_size))
+    m.load_state_dict(tp_shard_state_dict(full_sd, tp_shard_dims(m), tp.rank, tp_size))
+    dims = tp_shard_dims(m, params=True)
     m = m.cuda().to(torch.bfloat16)
     for _ in range(2):                          # twice: slab and staging buffers are recycled
         m.zero_grad(set_to_none=True)
@@ -421,7 +421,7 @@ def _check_hunyuan_layout(world, tp_size):
     full_sd = {k: v.clone() for k, v in ref.state_dict().items()}
     ref_out, ref_g = _hy_run(copy.deepcopy(ref).cuda().to(torch.bfloat16))
     outs = run_distributed(_hy_cp_worker, world, full_sd, tp_size, True, backend="nccl")
-    dims = tp_shard_dims(HunyuanVideoModel(cfg, None, TPContext(None, tp_size, 0)))
+    dims = tp_shard_dims(HunyuanVideoModel(cfg, None, TPContext(None, tp_size, 0)), params=True)
     by_tp = {}
     for out, grads, tpr in outs:
         assert rel(out, ref_out) < 1e-2
