@@ -309,12 +309,15 @@ class _FusedJointFn(torch.autograd.Function):
             _scatter_rows(fu, k_pre, wk_f, freqs, rstd_k, rows, C, D, eps, kh_p, S_l, S_pad, per_head=True, dst_rows=S_tot)
             _scatter_rows(fu, v, None, None, None, rows, C, D, eps, vh_p, S_l, S_pad, dst_rows=S_tot)
         # this rank's heads of the text tokens go behind the video rows of the same buffers (no concatenation)
+        # (every slab view shares one version counter with the slab; these writes, like the kernels' own, must not
+        # look to autograd like changes to the earlier layers' saved q / k / v)
         hs = slice(rank * Hl, (rank + 1) * Hl)
-        for buf, t in ((qh, qt), (kh, kt), (vh, vt)):
-            b4 = buf.view(B, S_tot, Hl, D)
-            b4[:, S_pad:S_pad + T].copy_(t[:, :, hs])
-            if Tp > T:
-                b4[:, S_pad + T:].zero_()
+        with torch.autograd._unsafe_preserve_version_counter(fu.slab.buf.tensor):
+            for buf, t in ((qh, qt), (kh, kt), (vh, vt)):
+                b4 = buf.view(B, S_tot, Hl, D)
+                b4[:, S_pad:S_pad + T].copy_(t[:, :, hs])
+                if Tp > T:
+                    b4[:, S_pad + T:].zero_()
         fu.arena.barrier(fu.slot)
         kv_lens = (text_lens.to(device=dev, dtype=torch.int32) + S_pad) if text_lens is not None else \
             torch.full((B,), S_pad + T, dtype=torch.int32, device=dev)
