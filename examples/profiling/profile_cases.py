@@ -125,9 +125,178 @@ def _dpopt_case(a):
     dist.destroy_process_group()
 
 
+def _cp_case(a):
+    """One self-attention layer of a Wan-shaped model under fused Ulysses CP = world (under torchrun on the ranks of one
+    box): device time of every fused compute + exchange kernel (CUDA events around each launch, max over ranks), with
+    the bytes each sends over NVLink and its roofline = max(FLOPs / measured GEMM peak, NVLink bytes / link rate)."""
+    import os
+
+    import torch.distributed as dist
+
+    from teletron_b200.dist import SymmetricArena
+    from teletron_b200.parallel.fused_ulysses import FusedUlysses
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dist.init_process_group("nccl")
+    fu = FusedUlysses(SymmetricArena(dist.group.WORLD))
+    H, D = a.heads, 128
+    C = H * D
+    S = a.seq
+    S_l = (S + world - 1) // world
+    fu.seq_len = S
+    torch.manual_seed(rank)
+    x = torch.randn(S_l, C, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(3 * C, C, device="cuda") / C ** 0.5).to(torch.bfloat16).requires_grad_(True)
+    b = torch.zeros(3 * C, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    wq = torch.ones(C, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    wk = torch.ones(C, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    freqs = torch.randn(S_l, D // 2, 2, device="cuda")
+    freqs = freqs / freqs.norm(dim=-1, keepdim=True)
+    do = torch.randn(S_l, C, device="cuda", dtype=torch.bfloat16)
+    L = _lib.lib()
+    names = ["tt_gemm_qkv_a2a", "tt_rmsrope_fwd_scatter", "tt_attn_fwd_scatter", "tt_attn_bwd_scatter", "tt_peer_barrier"]
+    events = {n: [] for n in names}
+
+    def wrap(name):
+        fn = getattr(L, name)
+
+        def timed(*args):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            rc = fn(*args)
+            e1.record()
+            events[name].append((e0, e1))
+            return rc
+
+        setattr(L, name, timed)
+
+    for n in names:
+        wrap(n)
+
+    def step():
+        fu.begin_microbatch(fu.slab_elems(1, 1, S_l * world, C, world))
+        fu.attention_qkv(x, w, b, wq, wk, freqs, 1, S_l, H, D, 1e-6).backward(do)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    for n in names:
+        events[n].clear()
+    for _ in range(a.iters):
+        step()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    per_step = {n: sum(e0.elapsed_time(e1) for e0, e1 in ev) / a.iters for n, ev in events.items()}
+    calls = {n: len(ev) // a.iters for n, ev in events.items()}
+    t = torch.tensor([per_step[n] for n in names], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        P = world
+        tile = S_l * C * 2                                  # one [S_l, C] bf16 tensor
+        out_frac = (P - 1) / P                              # share of a rank's rows that leaves the GPU
+        Hl = (H + P - 1) // P
+        attn_flops = 4.0 * Hl * (S_l * P) ** 2 * D
+        rows = {
+            "tt_gemm_qkv_a2a": dict(flops=2.0 * S_l * C * 3 * C, nvlink_bytes=out_frac * tile),          # V
+            "tt_rmsrope_fwd_scatter": dict(flops=0.0, nvlink_bytes=3 * out_frac * tile),                  # q, k, dO
+            "tt_attn_fwd_scatter": dict(flops=attn_flops, nvlink_bytes=out_frac * tile),                  # O
+            "tt_attn_bwd_scatter": dict(flops=3.5 * attn_flops, nvlink_bytes=3 * out_frac * tile),        # dQ, dK, dV
+            "tt_peer_barrier": dict(flops=0.0, nvlink_bytes=0.0),
+        }
+        out = dict(case="cp", world=world, seq=S, heads=H, rows_per_rank=S_l, kernels={})
+        for i, n in enumerate(names):
+            ms = float(t[i].item())
+            r = rows[n]
+            floor_ms = max(r["flops"] / a.peak_tflops / 1e9, r["nvlink_bytes"] / a.link_gbs / 1e6)
+            out["kernels"][n] = dict(ms_per_layer=ms, launches_per_layer=calls[n], nvlink_mb=r["nvlink_bytes"] / 1e6,
+                                     tflops=r["flops"] / ms / 1e9 if ms else 0.0,
+                                     roofline_ms=floor_ms, fraction_of_roofline=(floor_ms / ms) if ms and floor_ms else None)
+        print(json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _single_rank_fused_cases(a):
+    """The fused compute + exchange kernels with a group of one (the "peer" buffers are this GPU's own), so that a
+    single-process profiler run can capture them: ``qkv1`` = tt_gemm_qkv_a2a, ``ag1`` = tt_gemm2_bf16_ag,
+    ``dp1`` = tt_dp_bucket_step (reduce pass and AdamW pass).  Times are CUDA events; the exchanges cost no NVLink
+    bytes here, the kernels' instruction streams are the multi-rank ones."""
+    dev = "cuda"
+    L = _lib.lib()
+    res = dict(case=a.case)
+    if a.case == "qkv1":
+        H, D = a.heads, 128
+        C, M = H * D, a.m
+        x = torch.randn(M, C, device=dev, dtype=torch.bfloat16)
+        w = (torch.randn(3 * C, C, device=dev) / C ** 0.5).to(torch.bfloat16)
+        b = torch.zeros(3 * C, device=dev, dtype=torch.bfloat16)
+        qk = torch.empty(M, 2 * C, device=dev, dtype=torch.bfloat16)
+        ssq = torch.empty(M, 2 * (C // 128), device=dev, dtype=torch.float32)
+        vh = torch.empty(M * C, device=dev, dtype=torch.bfloat16)
+        ptrs = (_lib.c_ll * 1)(vh.data_ptr())
+
+        def run():
+            rc = L.tt_gemm_qkv_a2a(_lib.ptr(x), _lib.c_ll(C), _lib.ptr(w), _lib.c_ll(C), _lib.ptr(b), _lib.ptr(qk),
+                                   _lib.c_ll(2 * C), _lib.ptr(ssq), ptrs, _lib.c_int(1), _lib.c_int(0), _lib.c_int(M),
+                                   _lib.c_int(C), _lib.c_int(C), _lib.c_int(M), _lib.c_int(H), _lib.c_int(D),
+                                   _lib.ptr(_lib.status_word(torch.device(dev))), _lib.stream())
+            _lib.check(rc, "tt_gemm_qkv_a2a")
+
+        ms = _time(run, a.iters)
+        ref = (x.float() @ w.float().t())
+        err = (qk.float() - ref[:, :2 * C]).norm() / ref[:, :2 * C].norm()
+        res.update(m=M, c=C, ms=ms, tflops=2.0 * M * C * 3 * C / ms / 1e9, rel_err_qk=float(err),
+                   rel_err_ssq=float((ssq[:, :C // 128].sum(1) - qk[:, :C].float().pow(2).sum(1)).abs().max()
+                                     / qk[:, :C].float().pow(2).sum(1).max()))
+    elif a.case == "ag1":
+        M, K, N = a.m, a.k, a.n
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = (torch.randn(N, K, device=dev) / K ** 0.5).to(torch.bfloat16)
+        flags = torch.zeros((M + 127) // 128, dtype=torch.int32, device=dev)
+        from teletron_b200 import ops
+
+        state = dict(epoch=0)
+
+        def run():
+            state["epoch"] += 1
+            return ops.gemm_ag_gather([x.data_ptr()], M, K, w, flags, state["epoch"], 0, device=torch.device(dev))
+
+        ms = _time(run, a.iters)
+        y, _, g = run()
+        ms_plain = _time(lambda: gemm(x, w), a.iters)
+        res.update(m=M, n=N, k=K, ms=ms, ms_plain_gemm=ms_plain, tflops=2.0 * M * N * K / ms / 1e9,
+                   gathered_ok=bool(torch.equal(g, x)), rel_err=float((y.float() - gemm(x, w).float()).norm() / y.float().norm()))
+    else:  # dp1
+        n = a.params * 1_000_000 // 128 * 128
+        grads = torch.randn(n, device=dev)
+        params = torch.zeros(n, device=dev, dtype=torch.bfloat16)
+        master, m1, v1 = (torch.zeros(n, device=dev) for _ in range(3))
+        blocks = L.tt_comm_blocks()
+        partial = torch.zeros(blocks, device=dev)
+        gp, pp = (_lib.c_ll * 1)(grads.data_ptr()), (_lib.c_ll * 1)(params.data_ptr())
+
+        def run(mode):
+            rc = L.tt_dp_bucket_step(_lib.c_int(mode), gp, pp, _lib.c_int(1), _lib.c_int(0), _lib.c_ll(0), _lib.c_ll(n),
+                                     _lib.c_ll(n), _lib.c_int(1), _lib.c_int(0), _lib.c_int(1), None, _lib.ptr(master),
+                                     _lib.ptr(m1), _lib.ptr(v1), _lib.c_float(1.0), None, None, _lib.c_float(0.0), None,
+                                     _lib.c_float(1e-4), _lib.c_float(0.9), _lib.c_float(0.999), _lib.c_float(1e-8),
+                                     _lib.c_float(0.01), _lib.c_int(1), _lib.ptr(partial), _lib.c_int(0), _lib.stream())
+            _lib.check(rc, "tt_dp_bucket_step")
+
+        ms0 = _time(lambda: run(0), a.iters)
+        ms1 = _time(lambda: run(1), a.iters)
+        res.update(params=n, ms_reduce_pass=ms0, ms_adamw_pass=ms1, reduce_gbs=n * 8 / ms0 / 1e6,
+                   adamw_gbs=n * (4 * 4 + 3 * 4 + 2) / ms1 / 1e6)
+    _lib.check_status()
+    print(json.dumps(res), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "attn", "norm", "layers", "tp", "dpopt"])
+    ap.add_argument("case", choices=["gemm", "attn", "norm", "layers", "tp", "dpopt", "cp", "qkv1", "ag1", "dp1"])
+    ap.add_argument("--peak-tflops", type=float, default=1636.2, help="cp case: measured bf16 GEMM burst of the box")
+    ap.add_argument("--link-gbs", type=float, default=770.0, help="cp case: measured NVLink peer copy, GB/s per direction")
     ap.add_argument("--params", type=int, default=1400, help="dpopt case: millions of parameters")
     ap.add_argument("--inner", type=int, default=12288, help="tp case: full inner width of the MLP")
     ap.add_argument("--fused", action="store_true", help="tp case: peer-memory kernels instead of NCCL")
@@ -150,6 +319,10 @@ def main():
         return _tp_case(a)
     if a.case == "dpopt":
         return _dpopt_case(a)
+    if a.case == "cp":
+        return _cp_case(a)
+    if a.case in ("qkv1", "ag1", "dp1"):
+        return _single_rank_fused_cases(a)
     dev = "cuda"
     torch.manual_seed(0)
     res = dict(case=a.case)

@@ -75,6 +75,10 @@ class FusedUlysses:
         self.slot = barrier_slot
         self.slab = SymmSlab(arena, slab_bytes // 2) if slab_bytes else None
         self._staging = {}
+        # debugging aid (--poison-comm-buffers): before every micro-batch the slab and the gradient staging buffers are
+        # filled with NaN, so a kernel that reads a peer's data before it has arrived produces NaN instead of stale,
+        # plausible values (the race check that compute-sanitizer would otherwise do)
+        self.poison = False
         self.seq_len: Optional[int] = None  # true (un-padded) global sequence length
 
     def supports(self, H: int, D: int) -> bool:
@@ -95,6 +99,12 @@ class FusedUlysses:
             self.slab = None
             self.slab = SymmSlab(self.arena, int(need_elems))
         self.slab.reset()
+        if self.poison:
+            with torch.autograd._unsafe_preserve_version_counter(self.slab.buf.tensor):
+                self.slab.buf.tensor.fill_(float("nan"))
+            for t in self._staging.values():
+                t.tensor.fill_(float("nan"))
+            self.arena.barrier(self.slot)      # nobody writes into a peer that is still poisoning
 
     @staticmethod
     def slab_elems(layers_alive: int, batch: int, s_pad: int, channels: int, world: int) -> int:

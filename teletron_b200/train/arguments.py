@@ -99,6 +99,9 @@ _FLAGS = [
     ("--no-manual-gc-eval", dict(action="store_false", dest="manual_gc_eval")),
     ("--empty-unused-memory-level", dict(type=int, default=0, choices=[0, 1, 2])),
     ("--check-for-nan-in-loss-and-grad", dict(action="store_true")),
+    ("--poison-comm-buffers", dict(action="store_true",
+                                   help="debugging: fill the peer-memory activation buffers with NaN before every "
+                                        "micro-batch, so that a read before the data has arrived shows up as NaN")),
     ("--fused-comm", dict(type=str, default="auto", choices=["auto", "on", "off"],
                           help="peer-memory fused collectives (auto: on when every rank shares one NVLink box)")),
     # parallelism

@@ -177,6 +177,7 @@ class Trainer:
             if symmetric_memory_available():
                 try:
                     cp_ctx.fused = FusedUlysses(SymmetricArena(mpu.get_context_parallel_group()))
+                    cp_ctx.fused.poison = bool(getattr(a, "poison_comm_buffers", False))
                 except Exception as e:
                     if a.fused_comm == "on":
                         raise

@@ -99,6 +99,7 @@ def _cp_worker(rank, world, fused=False, layers=2, recompute_layers=0, shape=SMA
         from teletron_b200.parallel.fused_ulysses import FusedUlysses
 
         cp.fused = FusedUlysses(SymmetricArena(mpu.get_context_parallel_group()))
+        cp.fused.poison = True      # NaN-filled peer buffers: a read before arrival would show in the comparison
     torch.manual_seed(0)
     extra = dict(recompute_granularity="full", recompute_method="block",
                  recompute_num_layers=recompute_layers) if recompute_layers else {}
