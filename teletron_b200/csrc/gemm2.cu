@@ -24,13 +24,16 @@ namespace {
 // remote segments) into a local gathered matrix `G`, and publish one flag per block; the TMA producer of a tile waits
 // for the flags of its rows and then loads A from `G`.  Tiles are visited starting with the local segment, blocks are
 // copied in the same order, so the remote rows arrive while the local rows are multiplied and every remote element
-// crosses NVLink exactly once.  `G` stays behind for the weight-gradient GEMM.
+// crosses NVLink exactly once.  Rows inside the rank's own segment are loaded straight from where they are (a second
+// tensor map), without waiting for anything; their copy into `G`, which stays behind for the weight-gradient GEMM,
+// is made last.
 struct AgParams {
   const bf16* src[TP_MAX];  // rank s's segment [seg_rows, K] (its own included)
   bf16* G;                  // [world * seg_rows, K]
   unsigned* flags;          // one per 128-row block of G; a block is complete when its flag equals `epoch`
   unsigned epoch;
   int seg_rows, n_blocks, rot_tiles;  // rot_tiles: first 256-row tile that holds local rows
+  int local_row0;                     // first row of this rank's own segment in G
 };
 
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
@@ -63,7 +66,7 @@ constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 256 + 1024;
 template <int A_MN, int B_MN, bool AG>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AG ? 384 : 320, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
-             const AgParams ag) {
+             const AgParams ag, const __grid_constant__ CUtensorMap tmL) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -120,8 +123,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const int m0 = tile_m(tile) * 2 * BM + (int)cta * BM;
         const int n0 = (tile % tiles_n) * BN2 + (int)cta * 128;  // this CTA's half of the B tile
-        if (AG && m0 < p.M) {
-          // this CTA's 128 rows of the gathered operand have to be in place (copied by some CTA's copier warps)
+        // rows that lie entirely inside this rank's own segment are read where they are (tmL), at once; the others
+        // come from the gathered matrix once some CTA's copier warps have put them there
+        const int l0 = m0 - ag.local_row0;
+        const bool a_local = AG && l0 >= 0 && l0 + BM <= ag.seg_rows;
+        if (AG && !a_local && m0 < p.M) {
           if (!flag_wait(ag.flags + m0 / BM, ag.epoch, abort_flag, p.status, TT_ST_TIMEOUT_PRODUCER + 2)) break;
           fence_proxy_async_all();  // the copy was written with ordinary stores, the TMA engine reads it
         }
@@ -140,6 +146,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           if (A_MN) {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i) tma2_load_2d(sa + i * 8192, &tmA, bar, m0 + i * 64, k0);
+          } else if (a_local) {
+            tma2_load_2d(sa, &tmL, bar, k0, l0);
           } else {
             tma2_load_2d(sa, &tmA, bar, k0, m0);
           }
@@ -195,8 +203,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     // ------------------------------------------------------------ copier warps (all-gather of the A operand)
     const int t = threadIdx.x - 320;          // 0..63
     const int vec_per_row = p.K >> 3;         // 16-byte vectors per row
+    // remote blocks first, in the order the tiles need them (the block after the local segment, onwards, wrapping);
+    // the local segment's blocks, which gate nothing, fill the gathered matrix last
+    const int first_remote = min((ag.local_row0 + ag.seg_rows) / BM, ag.n_blocks - 1);
     for (int j = blockIdx.x; j < ag.n_blocks; j += gridDim.x) {
-      const int blk = (j + 2 * ag.rot_tiles) % ag.n_blocks;   // same order as the tiles are visited
+      const int blk = (j + first_remote) % ag.n_blocks;
       const int r0 = blk * BM;
       const int nrows = min(BM, p.M - r0);
       const long long nvec = (long long)nrows * vec_per_row;
@@ -265,7 +276,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 
 template <int A_MN, int B_MN, bool AG = false>
 int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms, cudaStream_t stream,
-            const AgParams* agp = nullptr) {
+            const AgParams* agp = nullptr, const CUtensorMap* tmLp = nullptr) {
   auto kern = gemm2_kernel<A_MN, B_MN, AG>;
   constexpr int NT2 = AG ? 384 : 320;
   AgParams ag;
@@ -297,7 +308,7 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
   }
   int clusters = max_clusters < sms / 2 ? max_clusters : sms / 2;
   if (tiles < clusters) clusters = tiles;
-  kern<<<2 * clusters, NT2, SMEM2_BYTES, stream>>>(tmA, tmB, p, ag);
+  kern<<<2 * clusters, NT2, SMEM2_BYTES, stream>>>(tmA, tmB, p, ag, tmLp ? *tmLp : tmA);
   TT_LAUNCH_CHECK();
   return 0;
 }
@@ -425,13 +436,16 @@ TT_API int tt_gemm2_bf16_ag(const long long* a_ptrs, const void* B, long long ld
   ag.G = (bf16*)G; ag.flags = flags; ag.epoch = epoch; ag.seg_rows = seg_rows;
   ag.n_blocks = (int)((M + BM - 1) / BM);
   ag.rot_tiles = (int)(((long long)rank * seg_rows) / (2 * BM));
-  CUtensorMap tmA, tmB;
+  ag.local_row0 = rank * seg_rows;
+  CUtensorMap tmA, tmB, tmL;
   {
     uint64_t dims[2], str[1];
     uint32_t box[2];
     dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = 64; box[1] = BM;
     str[0] = (uint64_t)K * 2;
     if (tt_make_tmap(&tmA, G, 2, 2, dims, str, box, 1)) return -1;
+    dims[1] = (uint64_t)seg_rows;
+    if (tt_make_tmap(&tmL, ag.src[rank], 2, 2, dims, str, box, 1)) return -1;
     if (b_mn) { dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 64; box[1] = 64; }
     else      { dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = 64; box[1] = 128; }
     str[0] = (uint64_t)ldb * 2;
@@ -447,6 +461,6 @@ TT_API int tt_gemm2_bf16_ag(const long long* a_ptrs, const void* B, long long ld
   int dev = 0, sms = 0;
   TT_CUDA(cudaGetDevice(&dev));
   TT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  if (b_mn) return launch2<0, 1, true>(tmA, tmB, p, sms, stream, &ag);
-  return launch2<0, 0, true>(tmA, tmB, p, sms, stream, &ag);
+  if (b_mn) return launch2<0, 1, true>(tmA, tmB, p, sms, stream, &ag, &tmL);
+  return launch2<0, 0, true>(tmA, tmB, p, sms, stream, &ag, &tmL);
 }
