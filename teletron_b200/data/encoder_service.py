@@ -167,6 +167,7 @@ def producer_process(args, encoder=None, dataset=None):
             prof = make_torch_profiler(args, "producer")
             prof.__enter__()
         stopping = False
+        encoded, encode_seconds, t_loop = 0, 0.0, time.time()
         promised = {p.consumer: False for p in pairs}   # the last header sent to this consumer carried FLAG_NEXT_SAME
 
         def send_next(c, may_promise=True):
@@ -194,8 +195,13 @@ def producer_process(args, encoder=None, dataset=None):
                 for g, it in zip(groups, iters):
                     first = g["consumers"][0]
                     if issued[first] + len(queues[first]) < total and len(queues[first]) < QUEUE_DEPTH:
+                        t_enc = time.time()
                         tensors, _ = encoder.encode(next(it))
                         blob = pack_tensors(tensors).to(dev)
+                        if dev.type == "cuda":
+                            torch.cuda.synchronize()      # the sample is complete before it is queued (and timed)
+                        encode_seconds += time.time() - t_enc
+                        encoded += 1
                         shapes = [tuple(t.shape) for t in tensors]
                         for c in g["consumers"]:
                             queues[c].append((shapes, blob))
@@ -226,6 +232,11 @@ def producer_process(args, encoder=None, dataset=None):
                 st.set(f"tt_issued_{rank}_{c}", str(n))
         if prof is not None:
             prof.__exit__(None, None, None)
+        if encoded:
+            wall = max(time.time() - t_loop, 1e-9)
+            print(f"[encoder rank {rank}] encoded {encoded} samples in {wall:.1f} s: {encode_seconds / encoded:.3f} s per "
+                  f"sample of encoder time ({encoded / max(encode_seconds, 1e-9):.2f} samples/s when busy), "
+                  f"{sum(issued.values())} messages sent", flush=True)
         return sum(issued.values())
     except Exception:
         msg = traceback.format_exc()
