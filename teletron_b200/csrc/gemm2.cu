@@ -253,6 +253,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
       bf16* c_row = reinterpret_cast<bf16*>(p.C) + (long long)row * p.ldc;
+      if (p.tp_mode == 2 && row_ok) {
+        // GEMM -> reduce-scatter: this row of partial sums goes to the rank that owns it, into this rank's slot
+        // of that rank's staging buffer [world, seg_rows, ldc]
+        const int seg = row / p.seg_rows;
+        c_row = p.peer_c[seg] + ((long long)p.rank * p.seg_rows + (row - seg * p.seg_rows)) * p.ldc;
+      }
       if (p.epi == EPI_QKV_A2A)
         epilogue_tile_qkv<BN2>(p, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN2), eg, row, row_ok, n0);
       else
@@ -463,4 +469,44 @@ TT_API int tt_gemm2_bf16_ag(const long long* a_ptrs, const void* B, long long ld
   TT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   if (b_mn) return launch2<0, 1, true>(tmA, tmB, p, sms, stream, &ag, &tmL);
   return launch2<0, 0, true>(tmA, tmB, p, sms, stream, &ag, &tmL);
+}
+
+// K-GEMM-RS on CTA pairs, first half: the partial product A B^T ([world * seg_rows, N]) is stored row by row into slot
+// `rank` of the staging buffer [world, seg_rows, ldc] of the rank that owns the row (c_peers: one device address per
+// rank, peer memory); after a cross-rank barrier tt_tp_reduce_rows sums the slots.  Returns -3 for shapes outside
+// the pair kernel's domain (the one-CTA kernel, tt_gemm_bf16_rs, takes those).
+TT_API int tt_gemm2_bf16_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn,
+                            const long long* c_peers, long long ldc, int seg_rows, int world, int rank, int N, int K,
+                            unsigned* status, cudaStream_t stream) {
+  const long long M = (long long)seg_rows * world;
+  if (N < 256 || M < 256) return -3;
+  TT_CHECK(world >= 1 && world <= TP_MAX && rank >= 0 && rank < world && seg_rows > 0, "gemm2_rs: bad world/rank");
+  TT_CHECK(N % 8 == 0 && K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0 && M < (1ll << 31), "gemm2_rs: bad shape");
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[2], str[1];
+    uint32_t box[2];
+    dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = 64; box[1] = BM;
+    str[0] = (uint64_t)lda * 2;
+    if (tt_make_tmap(&tmA, A, 2, 2, dims, str, box, 1)) return -1;
+    if (b_mn) { dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 64; box[1] = 64; }
+    else      { dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = 64; box[1] = 128; }
+    str[0] = (uint64_t)ldb * 2;
+    if (tt_make_tmap(&tmB, B, 2, 2, dims, str, box, 1)) return -1;
+  }
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = (int)M; p.N = N; p.K = K;
+  p.ldc = ldc; p.c_fp32 = 0; p.epi = EPI_NONE;
+  p.rows_per_gate = 1; p.alpha = 1.f; p.status = status;
+  p.tp_mode = 2; p.seg_rows = seg_rows; p.world = world; p.rank = rank;
+  for (int s = 0; s < world; ++s) {
+    TT_CHECK(c_peers[s] != 0 && (c_peers[s] & 15) == 0, "gemm2_rs: bad peer pointer %d", s);
+    p.peer_c[s] = reinterpret_cast<bf16*>(c_peers[s]);
+  }
+  p.C = p.peer_c[rank];
+  int dev = 0, sms = 0;
+  TT_CUDA(cudaGetDevice(&dev));
+  TT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  return b_mn ? launch2<0, 1>(tmA, tmB, p, sms, stream) : launch2<0, 0>(tmA, tmB, p, sms, stream);
 }

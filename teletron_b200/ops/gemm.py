@@ -171,12 +171,20 @@ def gemm_ag_gather(a_peer_ptrs, seg_rows: int, k: int, b, flags, epoch: int, ran
 def gemm_rs_scatter(a, b, c_peer_ptrs, seg_rows: int, rank: int, *, b_mn=False):
     """First half of GEMM -> reduce-scatter: the partial product ``a @ b^T`` ([world * seg_rows, n]) is stored,
     tile by tile, into slot ``rank`` of the staging buffer ([world, seg_rows, n]) of the rank that owns the rows
-    (csrc/gemm.cu, tt_gemm_bf16_rs)."""
+    (csrc/gemm2.cu, tt_gemm2_bf16_rs on CTA pairs; csrc/gemm.cu, tt_gemm_bf16_rs for small shapes)."""
     world = len(c_peer_ptrs)
     n = b.shape[1] if b_mn else b.shape[0]
     m, k = a.shape
     assert m == world * seg_rows and a.stride(1) == 1 and b.stride(1) == 1
     ptrs = (_lib.c_ll * world)(*[int(p) for p in c_peer_ptrs])
+    if _PAIR:
+        rc = _lib.lib().tt_gemm2_bf16_rs(_lib.ptr(a), _lib.c_ll(a.stride(0)), _lib.ptr(b), _lib.c_ll(b.stride(0)),
+                                         _lib.c_int(int(b_mn)), ptrs, _lib.c_ll(n), _lib.c_int(seg_rows),
+                                         _lib.c_int(world), _lib.c_int(rank), _lib.c_int(n), _lib.c_int(k),
+                                         _lib.ptr(_lib.status_word(a.device)), _lib.stream())
+        if rc != -3:
+            _lib.check(rc, "tt_gemm2_bf16_rs")
+            return
     rc = _lib.lib().tt_gemm_bf16_rs(_lib.ptr(a), _lib.c_ll(a.stride(0)), _lib.ptr(b), _lib.c_ll(b.stride(0)),
                                     _lib.c_int(int(b_mn)), ptrs, _lib.c_ll(n), _lib.c_int(seg_rows), _lib.c_int(world),
                                     _lib.c_int(rank), _lib.c_int(n), _lib.c_int(k),

@@ -254,7 +254,8 @@ def test_gemm_ag_segments_on_one_device(world, seg, K, N, b_mn):
     assert rel(y, ref) < 4e-3
 
 
-@pytest.mark.parametrize("world,seg,K,N,b_mn", [(2, 200, 192, 320, False), (3, 128, 256, 136, True)])
+@pytest.mark.parametrize("world,seg,K,N,b_mn", [(2, 200, 192, 320, False), (3, 128, 256, 136, True),
+                                                (2, 300, 128, 512, True), (4, 130, 320, 264, False)])
 def test_gemm_rs_segments_on_one_device(world, seg, K, N, b_mn):
     """GEMM -> reduce-scatter: every emulated rank scatters its partial product into the owners' staging buffers,
     then each owner sums its slots."""
