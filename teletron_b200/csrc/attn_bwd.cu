@@ -339,35 +339,35 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       int kv_len = p.Skv;
       if (p.kv_lens) kv_len = min(max(p.kv_lens[b], 1), p.Skv);
       const bool live = row < kv_len;
+      // every operand tile has been consumed: the first Q stage stages the output rows, 4 KB per warp
+      uint8_t* stage = smem + A_SM_Q + (warp - 2) * (32 * 128);
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {  // 0: dV, 1: dK
-        bf16* dst;
+        bf16* dst = nullptr;
         if (which == 0)
           dst = scatter_row(p.sc1, row, p.Skv) ? scatter_dst(p.sc1, b, row, h)
                                                  : p.out1 + (long long)b * p.bs1 + (long long)row * p.ld1 + h * 128;
         else
           dst = scatter_row(p.sc0, row, p.Skv) ? scatter_dst(p.sc0, b, row, h)
                                                  : p.out0 + (long long)b * p.bs0 + (long long)row * p.ld0 + h * 128;
-        const float mul = which == 0 ? 1.f : p.scale;
+        dst = row < p.Skv ? dst + wg * 64 : nullptr;
+        const float m2 = live ? (which == 0 ? 1.f : p.scale) : 0.f;
 #pragma unroll 1
-        for (int c = wg * 2; c < wg * 2 + 2; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t o[32];
-          tmem_ld32(tmem_base + lane_addr + A_TM_DV + which * 128 + c * 32, o);
+          tmem_ld32(tmem_base + lane_addr + A_TM_DV + which * 128 + (wg * 2 + c) * 32, o);
           tmem_ld_wait();
-          if (row < p.Skv) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 pk;
-              const float m2 = live ? mul : 0.f;
-              pk.x = pack_bf16(__uint_as_float(o[g * 8 + 0]) * m2, __uint_as_float(o[g * 8 + 1]) * m2);
-              pk.y = pack_bf16(__uint_as_float(o[g * 8 + 2]) * m2, __uint_as_float(o[g * 8 + 3]) * m2);
-              pk.z = pack_bf16(__uint_as_float(o[g * 8 + 4]) * m2, __uint_as_float(o[g * 8 + 5]) * m2);
-              pk.w = pack_bf16(__uint_as_float(o[g * 8 + 6]) * m2, __uint_as_float(o[g * 8 + 7]) * m2);
-              *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = pk;
-            }
+          for (int g = 0; g < 4; ++g) {
+            uint4 pk;
+            pk.x = pack_bf16(__uint_as_float(o[g * 8 + 0]) * m2, __uint_as_float(o[g * 8 + 1]) * m2);
+            pk.y = pack_bf16(__uint_as_float(o[g * 8 + 2]) * m2, __uint_as_float(o[g * 8 + 3]) * m2);
+            pk.z = pack_bf16(__uint_as_float(o[g * 8 + 4]) * m2, __uint_as_float(o[g * 8 + 5]) * m2);
+            pk.w = pack_bf16(__uint_as_float(o[g * 8 + 6]) * m2, __uint_as_float(o[g * 8 + 7]) * m2);
+            stage_put<8>(stage, lane, c * 4 + g, pk);
           }
-          __syncwarp();
         }
+        stage_flush<8>(stage, lane, dst, nullptr);
       }
     }
   }
@@ -625,24 +625,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       bf16* dst = scatter_row(p.sc0, row, p.Sq) ? scatter_dst(p.sc0, b, row, h)
                                                   : p.out0 + (long long)b * p.bs0 + (long long)row * p.ld0 + h * 128;
+      dst = row < p.Sq ? dst + wg * 64 : nullptr;
+      // every operand tile has been consumed: the first K stage stages the output rows, 4 KB per warp
+      uint8_t* stage = smem + B_SM_K + (warp - 2) * (32 * 128);
 #pragma unroll 1
-      for (int c = wg * 2; c < wg * 2 + 2; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t o[32];
-        tmem_ld32(tmem_base + lane_addr + B_TM_DQ + c * 32, o);
+        tmem_ld32(tmem_base + lane_addr + B_TM_DQ + (wg * 2 + c) * 32, o);
         tmem_ld_wait();
-        if (row < p.Sq) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 pk;
-            pk.x = pack_bf16(__uint_as_float(o[g * 8 + 0]) * p.scale, __uint_as_float(o[g * 8 + 1]) * p.scale);
-            pk.y = pack_bf16(__uint_as_float(o[g * 8 + 2]) * p.scale, __uint_as_float(o[g * 8 + 3]) * p.scale);
-            pk.z = pack_bf16(__uint_as_float(o[g * 8 + 4]) * p.scale, __uint_as_float(o[g * 8 + 5]) * p.scale);
-            pk.w = pack_bf16(__uint_as_float(o[g * 8 + 6]) * p.scale, __uint_as_float(o[g * 8 + 7]) * p.scale);
-            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = pk;
-          }
+        for (int g = 0; g < 4; ++g) {
+          uint4 pk;
+          pk.x = pack_bf16(__uint_as_float(o[g * 8 + 0]) * p.scale, __uint_as_float(o[g * 8 + 1]) * p.scale);
+          pk.y = pack_bf16(__uint_as_float(o[g * 8 + 2]) * p.scale, __uint_as_float(o[g * 8 + 3]) * p.scale);
+          pk.z = pack_bf16(__uint_as_float(o[g * 8 + 4]) * p.scale, __uint_as_float(o[g * 8 + 5]) * p.scale);
+          pk.w = pack_bf16(__uint_as_float(o[g * 8 + 6]) * p.scale, __uint_as_float(o[g * 8 + 7]) * p.scale);
+          stage_put<8>(stage, lane, c * 4 + g, pk);
         }
-        __syncwarp();
       }
+      stage_flush<8>(stage, lane, dst, nullptr);
     }
   }
   __syncwarp();

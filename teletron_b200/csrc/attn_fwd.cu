@@ -271,27 +271,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       const int row = q0 + t * TILE + r;
       const float inv = 1.f / l;
-      bf16* orow = p.O + (long long)b * p.o_batch_stride + (long long)row * p.ldo + h * 128;
+      // the group's Q tile is no longer read (its last S and P*V have completed): it stages the output rows
+      uint8_t* stage = smem + SM_Q + t * TILE_BYTES + q * (32 * 256);
+      bf16* orow = row < p.Sq ? p.O + (long long)b * p.o_batch_stride + (long long)row * p.ldo + h * 128 : nullptr;
       bf16* prow = scatter_row(p.sc, row, p.Sq) ? scatter_dst(p.sc, b, row, h) : nullptr;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
         tmem_ld32(o_addr + c * 32, o);
         tmem_ld_wait();
-        if (row < p.Sq) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 pk;
-            pk.x = pack_bf16(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
-            pk.y = pack_bf16(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
-            pk.z = pack_bf16(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
-            pk.w = pack_bf16(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = pk;
-            if (prow) *reinterpret_cast<uint4*>(prow + c * 32 + g * 8) = pk;
-          }
+        for (int g = 0; g < 4; ++g) {
+          uint4 pk;
+          pk.x = pack_bf16(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
+          pk.y = pack_bf16(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
+          pk.z = pack_bf16(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
+          pk.w = pack_bf16(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
+          stage_put<16>(stage, lane, c * 4 + g, pk);
         }
-        __syncwarp();
       }
+      stage_flush<16>(stage, lane, orow, prow);
       if (row < p.Sq && p.lse)
         p.lse[((long long)b * p.H + h) * p.Sq + row] = (m_used + log2f(l)) * 0.6931471805599453f;
     }

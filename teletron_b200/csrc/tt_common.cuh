@@ -115,6 +115,36 @@ __device__ __forceinline__ bool scatter_row(const TTScatter& sc, int row, int ro
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
+
+// Row staging for epilogues whose accumulator comes out of tensor memory one row per lane.  Written from the
+// registers as they are, a warp's store instruction touches 32 rows with 16 bytes each: fine for the local L2,
+// wasteful over NVLink, where every 16-byte piece travels as a packet of its own.  The warp instead parks its
+// 32 x (CH x 16 B) block in its own shared-memory area (chunks XOR-swizzled by the row, so neither the writes nor
+// the reads conflict) and writes it out with CH lanes per row: each row leaves as one contiguous piece of
+// CH x 16 bytes.  Only the warp itself touches the area: __syncwarp() is the only synchronisation.
+template <int CH>
+__device__ __forceinline__ void stage_put(uint8_t* stage, int lane, int chunk, const uint4& v) {
+  *reinterpret_cast<uint4*>(stage + lane * (CH * 16) + ((chunk ^ (lane & (CH - 1))) << 4)) = v;
+}
+// dst0 / dst1: this lane's row in up to two destinations (nullptr: skip that destination for the row)
+template <int CH>
+__device__ __forceinline__ void stage_flush(const uint8_t* stage, int lane, bf16* dst0, bf16* dst1) {
+  constexpr int RPI = 32 / CH;  // rows per store instruction
+  const int chunk = lane & (CH - 1);
+  const unsigned long long a0 = reinterpret_cast<unsigned long long>(dst0);
+  const unsigned long long a1 = reinterpret_cast<unsigned long long>(dst1);
+  __syncwarp();
+#pragma unroll 4
+  for (int i = 0; i < 32 / RPI; ++i) {
+    const int row = i * RPI + lane / CH;
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + row * (CH * 16) + ((chunk ^ (row & (CH - 1))) << 4));
+    const unsigned long long r0 = __shfl_sync(0xffffffffu, a0, row);
+    const unsigned long long r1 = __shfl_sync(0xffffffffu, a1, row);
+    if (r0) *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(r0) + chunk * 8) = v;
+    if (r1) *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(r1) + chunk * 8) = v;
+  }
+  __syncwarp();
+}
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 
 // ---------------------------------------------------------------- mbarrier
