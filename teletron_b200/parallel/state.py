@@ -222,6 +222,27 @@ def destroy_model_parallel():
     _S.groups, _S.ranks, _S.gloo = {}, {}, {}
 
 
+def warm_up_groups(names=("dit", "replica", "dp_cp", "dp", "tp_cp", "cp", "tp")) -> None:
+    """Creates the communicators of the groups the training loop uses, now, with one tiny all-reduce each.
+
+    NCCL builds a group's communicator at the group's first collective and allocates its buffers with the driver's
+    own allocator.  When that first use comes late (the timer summary of the first log line, for one) the caching
+    allocator may already hold every free byte of a large model's GPU, and the communicator fails with an
+    out-of-memory error that no amount of cached memory can satisfy.  Groups of one rank and groups this rank is
+    not part of are skipped; every rank walks the names in the same order, and groups of one kind are disjoint, so
+    the collectives pair up."""
+    if _S.topo is None or not dist.is_initialized():
+        return
+    dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
+    for name in names:
+        g = _S.groups.get(name)
+        if g is None or len(_S.ranks.get(name, ())) <= 1:
+            continue
+        dist.all_reduce(torch.zeros(1, device=dev), group=g)
+    if dev == "cuda":
+        torch.cuda.synchronize()
+
+
 def model_parallel_is_initialized() -> bool:
     return _S.topo is not None
 

@@ -13,6 +13,12 @@ import torch
 import torch.distributed as dist
 
 
+def _log_rank(args) -> int:
+    """The rank that prints: the last one that runs the transformer (encoder ranks sit behind it and never log)."""
+    enc = int(getattr(args, "distributed_vae_world_size", 0) or 0) if getattr(args, "distributed_vae", False) else 0
+    return args.world_size - 1 - enc
+
+
 class _TeeWriter:
     """``add_scalar`` to TensorBoard (when present) and to a Weights & Biases run."""
 
@@ -52,7 +58,7 @@ class TrainLogger:
         """Scalar writer on the last rank only (teletron/utils/config.py:59-70): a TensorBoard ``SummaryWriter``
         when ``--tensorboard-dir`` is given, mirrored to Weights & Biases when ``--wandb-project`` is given and the
         package is installed (the reference declares that mirror but never creates it, utils/config.py:42-45)."""
-        if args.rank != args.world_size - 1:
+        if args.rank != _log_rank(args):
             return None
         tb = wb = None
         if args.tensorboard_dir:
@@ -140,7 +146,7 @@ class TrainLogger:
                 w.add_scalar("tokens-per-second", tps, iteration)
         parts.append(f"number of skipped iterations: {self.counts[self.SKIP]:3d}")
         parts.append(f"number of nan iterations: {self.counts[self.NAN]:3d}")
-        if a.rank == a.world_size - 1:
+        if a.rank == _log_rank(a):
             print(" | ".join(parts), flush=True)
         if timers is not None:
             n_it = max(self.counts[self.ADV] + self.counts[self.SKIP], 1)
@@ -149,7 +155,7 @@ class TrainLogger:
             grp = mpu.get_transformer_model_group() if mpu.model_parallel_is_initialized() else None
             per_it = {k: v / n_it for k, v in timers.summary(group=grp).items()}   # encoder ranks take no part
             self.last_timings = per_it
-            if a.rank == a.world_size - 1 and per_it:
+            if a.rank == _log_rank(a) and per_it:
                 print("    time (ms) | " + " | ".join(f"{k}: {v:.2f}" for k, v in per_it.items()), flush=True)
             if w is not None and a.log_timers_to_tensorboard:
                 for k, v in per_it.items():
@@ -157,7 +163,7 @@ class TrainLogger:
         report_mem = not self.reported_memory and torch.cuda.is_available()
         if report_mem:
             self.reported_memory = True
-            if a.rank == a.world_size - 1:
+            if a.rank == _log_rank(a):
                 mb = 1024.0 * 1024.0
                 print(f"[rank {a.rank}] memory (MB) | allocated: {torch.cuda.memory_allocated() / mb:.0f}"
                       f" | max allocated: {torch.cuda.max_memory_allocated() / mb:.0f}"
@@ -172,7 +178,7 @@ class TrainLogger:
         """Framed console line on the last rank (each value with its perplexity ``exp(min(20, value))``, as the
         reference prints, teletron/train/trainer.py:776-795) and the validation scalars (telelogger.py:256-262)."""
         a = self.args
-        if a.rank == a.world_size - 1 and loss_dict:
+        if a.rank == _log_rank(a) and loss_dict:
             line = f" validation loss at {prefix or f'iteration {iteration}'} | "
             for k, v in loss_dict.items():
                 line += f"{k} value: {float(v):.6E} | {k} PPL: {math.exp(min(20.0, float(v))):.6E} | "

@@ -122,6 +122,8 @@ class Trainer:
                                           a.consumer_models_num,
                                           timeout=datetime.timedelta(minutes=a.distributed_timeout_minutes),
                                           expert_model_parallel_size=getattr(a, "expert_model_parallel_size", 1))
+            if not mpu.is_encoder_rank():
+                mpu.warm_up_groups()       # communicators exist before the model takes the memory
             # agree on the earliest start time for --exit-duration-in-mins (trainer.py:87-92)
             t = torch.tensor([self.start_time], dtype=torch.float64,
                              device="cuda" if backend == "nccl" else "cpu")
@@ -373,6 +375,7 @@ class Trainer:
         window = ProfileWindow(a)
         mem_snap = MemorySnapshot(a.rank)
         n_mb_prev = a.num_micro_batches
+        first_step = True
         while iteration < a.train_iters:
             # batch-size ramp-up: a new level starts from a checkpoint, then has to split into micro-batches
             self._set_batch_level(strict=False)
@@ -400,6 +403,12 @@ class Trainer:
                 if _lib.available():
                     _lib.check_status()
             mem_snap.dump(iteration)
+            if first_step and self.device.type == "cuda":
+                # the first step's one-off allocations leave cached blocks that nothing reuses: hand them back once,
+                # so that allocations outside the caching allocator (NCCL buffers made at a group's or a peer's first
+                # use, growth of the symmetric arena) still find memory next to a model that fills the GPU
+                torch.cuda.empty_cache()
+            first_step = False
             iteration += 1
             a.iteration = iteration
             a.consumed_train_samples += a.current_global_batch_size

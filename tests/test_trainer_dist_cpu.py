@@ -1,4 +1,6 @@
 """Trainer on CPU/gloo ranks: DP + CP with the sharded optimizer, and training fed by an encoder rank."""
+import contextlib
+import io
 import os
 
 import torch
@@ -50,13 +52,17 @@ def _encoder_fed_worker(rank, world):
     from teletron_b200.train import Trainer, make_forward_step
 
     a = _args(world, "--distributed-vae --distributed-vae-world-size 1 --context-parallel-size 2 "
-                     "--encoder-name synthetic_wan_encoder --dataset-type FakeDataset --train-iters 5")
+                     "--encoder-name synthetic_wan_encoder --dataset-type FakeDataset --train-iters 5 "
+                     "--log-interval 1 --timing-log-level 1")
     try:
         t = Trainer(a)
     except SystemExit:
         return "encoder-rank-done"
-    t.pretrain(make_forward_step())
-    return float(t.buffer.params.float().abs().sum()), t.train_data_iterator.received, t.train_data_iterator.prefetched
+    out = io.StringIO()
+    with contextlib.redirect_stdout(out):
+        t.pretrain(make_forward_step())
+    return (float(t.buffer.params.float().abs().sum()), t.train_data_iterator.received, t.train_data_iterator.prefetched,
+            out.getvalue().count(" iteration "), bool(t.logger.last_timings))
 
 
 def test_training_fed_by_an_encoder_rank():
@@ -65,7 +71,10 @@ def test_training_fed_by_an_encoder_rank():
     assert outs[0][0] == outs[1][0] and outs[0][0] > 0
     # the TP x CP leader received all five samples, and for some of them the encoder had promised the sample ahead, so
     # the receive of its payload was posted while the previous sample trained (double buffering)
-    assert outs[0][1] == 5 and outs[0][2] >= 1 and outs[1][1:] == (0, 0)
+    assert outs[0][1] == 5 and outs[0][2] >= 1 and outs[1][1:3] == (0, 0)
+    # the log lines come from the last rank that trains (the encoder rank behind it never logs), one per iteration,
+    # and the timer summary runs over the training ranks only
+    assert outs[0][3] == 0 and outs[1][3] == 5 and outs[0][4] and outs[1][4]
 
 
 def _resilience_worker(rank, world, root, mode):
