@@ -189,6 +189,20 @@ def _cp_case(a):
     _lib.check_status()
     per_step = {n: sum(e0.elapsed_time(e1) for e0, e1 in ev) / a.iters for n, ev in events.items()}
     calls = {n: len(ev) // a.iters for n, ev in events.items()}
+    # the same attention on this GPU without any exchange (the rank's heads over the full sequence, local tensors),
+    # and with all heads over the rank's share of the work (what a data-parallel rank does in the same time share)
+    Hl_own = fu.head_slots(H)[1]
+    local = {}
+    for tag, hh in (("own_heads", max(Hl_own, 1)), ("all_heads", H)):
+        ql = torch.randn(1, S_l * world, hh, D, device="cuda", dtype=torch.bfloat16)
+        kl, vl = torch.randn_like(ql), torch.randn_like(ql)
+        ol, lsel = attention_fwd(ql, kl, vl)
+        dol = torch.randn_like(ol)
+        local[tag] = (_time(lambda: attention_fwd(ql, kl, vl), a.iters),
+                      _time(lambda: attention_bwd(ql, kl, vl, ol, lsel, dol), a.iters))
+        del ql, kl, vl, ol, lsel, dol
+    tl = torch.tensor([x for tag in ("own_heads", "all_heads") for x in local[tag]], device="cuda", dtype=torch.float64)
+    dist.all_reduce(tl, op=dist.ReduceOp.MAX)
     t = torch.tensor([per_step[n] for n in names], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
@@ -212,6 +226,9 @@ def _cp_case(a):
             out["kernels"][n] = dict(ms_per_layer=ms, launches_per_layer=calls[n], nvlink_mb=r["nvlink_bytes"] / 1e6,
                                      tflops=r["flops"] / ms / 1e9 if ms else 0.0,
                                      roofline_ms=floor_ms, fraction_of_roofline=(floor_ms / ms) if ms and floor_ms else None)
+        out["local_attention_ms"] = {"own_heads_fwd": float(tl[0]), "own_heads_bwd": float(tl[1]),
+                                     "all_heads_fwd_per_rank_share": float(tl[2]) / world,
+                                     "all_heads_bwd_per_rank_share": float(tl[3]) / world}
         print(json.dumps(out), flush=True)
     dist.barrier()
     dist.destroy_process_group()

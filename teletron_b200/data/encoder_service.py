@@ -182,6 +182,7 @@ def producer_process(args, encoder=None, dataset=None):
             inflight.append((PolledWork(dist.isend(hdr, dst=c), backend), c, hdr))
             inflight.append((PolledWork(dist.isend(blob, dst=c), backend), c, blob))
             issued[c] += 1
+            st.add(f"tt_sent_{rank}_{c}", 1)       # the consumer posts its receives only now: they never idle on a GPU
 
         while True:
             st.set(f"tt_hb_{rank}", str(time.time()))
@@ -222,6 +223,7 @@ def producer_process(args, encoder=None, dataset=None):
                 if n < total:
                     hdr = encode_header([], n, FLAG_STOP).to(dev)
                     closing.append((PolledWork(dist.isend(hdr, dst=c), backend), hdr))
+                    st.add(f"tt_sent_{rank}_{c}", 1)
             for c, n in issued.items():
                 st.set(f"tt_issued_{rank}_{c}", str(n))
             t_end = time.time() + 60.0

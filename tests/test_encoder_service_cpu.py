@@ -103,6 +103,58 @@ def test_encoder_failure_reaches_the_consumer():
     assert out[2] == "failed-as-planned" and out[0] == "consumer-saw-failure"
 
 
+def _slow_encoder_body(rank, world):
+    """An encoder that takes longer per sample than the consumer: the consumer must never have a receive posted for
+    a sample whose sends the producer has not announced (on a GPU such a receive is a kernel that holds an SM while
+    it waits), and when the encoder is ahead the next sample is posted before the consumer asks for it."""
+    import time
+
+    from teletron_b200.data.batch_loader import WanDistBatchLoader
+    from teletron_b200.data.encoder_service import producer_process
+    from teletron_b200.models.registry import get_encoder
+    from teletron_b200.parallel import state as mpu
+
+    args = _args(train_iters=4)
+    mpu.initialize_model_parallel(encoder_world_size=1)      # rank 0 trains, rank 1 encodes
+    if mpu.is_encoder_rank():
+        enc = get_encoder("synthetic_wan_encoder", device=torch.device("cpu"), args=args)
+        inner = enc.encode
+
+        def slow(sample):
+            time.sleep(0.4)
+            return inner(sample)
+
+        enc.encode = slow
+        return producer_process(args, encoder=enc)
+    loader = WanDistBatchLoader(args, timeout_s=30.0)
+    seen = []
+    for i in range(args.train_iters):
+        next(loader)
+        ahead = loader._pending is not None
+        assert loader._posted <= loader._announced()          # nothing posted that is not on its way
+        assert loader._posted == loader.received + int(ahead)
+        seen.append(ahead)
+        if i == 1:
+            time.sleep(1.2)                                    # let the encoder get ahead once
+    return seen, loader.received
+
+
+def _slow_encoder_worker(rank, world):
+    import torch.distributed as dist
+
+    try:
+        return _slow_encoder_body(rank, world)
+    finally:
+        dist.barrier()
+
+
+def test_receives_are_posted_only_for_announced_samples():
+    out = run_distributed(_slow_encoder_worker, 2, timeout=120)
+    seen, received = out[0]
+    assert received == 4 and out[1] == 4
+    assert seen[0] is False                 # the encoder needs 0.4 s per sample: nothing is on its way right after the first
+
+
 def test_items_needed_follows_the_batch_size_ramp():
     from argparse import Namespace
 
