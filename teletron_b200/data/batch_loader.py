@@ -7,7 +7,7 @@ error instead of hanging the job) and fans the sample out to its TP x CP group w
 (header, flat payload) instead of pickled metadata plus one broadcast per tensor.
 
 Double buffering without idle receive kernels: a receive is posted only once the producer has announced (a
-counter in the store) that the matching sends are issued, so an NCCL receive kernel never sits on the GPU waiting
+counter in the store, bumped right before it issues the sends) the sample, so an NCCL receive kernel never sits on the GPU waiting
 for an encoder that is still encoding (such a kernel holds an SM for as long as it waits, and a persistent GEMM
 that counts on every SM then runs at half speed: measured 795 against 680 ms per step).  When the following
 sample is already on its way at the end of a receive, its header and, if the header before promised the same
@@ -88,7 +88,7 @@ class DistBatchLoader:
 
     # ---- leader-side receive with watchdog ------------------------------------------------
     def _announced(self) -> int:
-        """Samples (and stop headers) whose sends the producer has issued to this rank."""
+        """Samples (and stop headers) the producer has announced to this rank: encoded, their sends being issued."""
         return int(store().add(f"tt_sent_{self.pair.producer}_{self.rank}", 0))
 
     def _post_header(self):

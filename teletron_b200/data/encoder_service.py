@@ -179,10 +179,13 @@ def producer_process(args, encoder=None, dataset=None):
             if promised[c]:
                 flags |= FLAG_NEXT_SAME
             hdr = encode_header(shapes, issued[c], flags).to(dev)
+            # announced first, then sent: the consumer posts its receives only for announced samples (they never idle
+            # on its GPU while a sample is still being encoded), and the first NCCL send to a peer may block until
+            # that peer joins with its receive, which it only does once it has seen the announcement
+            st.add(f"tt_sent_{rank}_{c}", 1)
             inflight.append((PolledWork(dist.isend(hdr, dst=c), backend), c, hdr))
             inflight.append((PolledWork(dist.isend(blob, dst=c), backend), c, blob))
             issued[c] += 1
-            st.add(f"tt_sent_{rank}_{c}", 1)       # the consumer posts its receives only now: they never idle on a GPU
 
         while True:
             st.set(f"tt_hb_{rank}", str(time.time()))
@@ -222,8 +225,8 @@ def producer_process(args, encoder=None, dataset=None):
             for c, n in issued.items():
                 if n < total:
                     hdr = encode_header([], n, FLAG_STOP).to(dev)
-                    closing.append((PolledWork(dist.isend(hdr, dst=c), backend), hdr))
                     st.add(f"tt_sent_{rank}_{c}", 1)
+                    closing.append((PolledWork(dist.isend(hdr, dst=c), backend), hdr))
             for c, n in issued.items():
                 st.set(f"tt_issued_{rank}_{c}", str(n))
             t_end = time.time() + 60.0
