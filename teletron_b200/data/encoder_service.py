@@ -203,7 +203,10 @@ def producer_process(args, encoder=None, dataset=None):
                         tensors, _ = encoder.encode(next(it))
                         blob = pack_tensors(tensors).to(dev)
                         if dev.type == "cuda":
-                            torch.cuda.synchronize()      # the sample is complete before it is queued (and timed)
+                            # the sample is complete before it is queued (and timed).  Only the encoder's own stream:
+                            # a device-wide wait would also wait for sends the consumer has not picked up yet, and
+                            # the encoder could never get more than one sample ahead
+                            torch.cuda.current_stream().synchronize()
                         encode_seconds += time.time() - t_enc
                         encoded += 1
                         shapes = [tuple(t.shape) for t in tensors]
