@@ -222,17 +222,20 @@ def destroy_model_parallel():
     _S.groups, _S.ranks, _S.gloo = {}, {}, {}
 
 
-def warm_up_groups(names=("dit", "replica", "dp_cp", "dp", "tp_cp", "cp", "tp")) -> None:
-    """Creates the communicators of the groups the training loop uses, now, with one tiny all-reduce each.
+def warm_up_groups(names=None) -> None:
+    """Creates the communicators of groups whose first collective comes late, now, with one tiny all-reduce each.
 
     NCCL builds a group's communicator at the group's first collective and allocates its buffers with the driver's
-    own allocator.  When that first use comes late (the timer summary of the first log line, for one) the caching
-    allocator may already hold every free byte of a large model's GPU, and the communicator fails with an
-    out-of-memory error that no amount of cached memory can satisfy.  Groups of one rank and groups this rank is
-    not part of are skipped; every rank walks the names in the same order, and groups of one kind are disjoint, so
-    the collectives pair up."""
+    own allocator.  The groups of the training step itself meet theirs in the first step; the group of all
+    transformer ranks is first used by the timer summary of the first log line, when the caching allocator may
+    already hold every free byte of a large model's GPU, and the communicator then fails with an out-of-memory error
+    that no amount of cached memory can satisfy.  ``names`` defaults to that group.  Groups of one rank and groups
+    this rank is not part of are skipped; every rank walks the names in the same order, and groups of one kind are
+    disjoint, so the collectives pair up."""
     if _S.topo is None or not dist.is_initialized():
         return
+    if names is None:
+        names = ("replica",) if _S.topo.replicas > 1 else ("dit",)
     dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
     for name in names:
         g = _S.groups.get(name)
