@@ -50,8 +50,15 @@ def act_bwd(dact: torch.Tensor, pre: torch.Tensor, kind: str) -> torch.Tensor:
     return out
 
 
-def _weight_grad(dy, x, w):
-    """dW = dy^T x. Accumulates into w.main_grad when present (returns None), else returns bf16."""
+def _weight_grad(dy, x, w, owner=None):
+    """dW = dy^T x. Accumulates into the parameter's main_grad when present (returns None), else returns bf16.
+
+    ``owner`` is the parameter object the forward pass was called with.  The tensor that comes back from
+    ``ctx.saved_tensors`` is not always that object: inside a non-reentrant checkpoint the recompute pass hands
+    back a detached alias without the parameter's Python attributes, and the gradient would silently take the
+    bf16 ``.grad`` route (2 more bytes per parameter until the end of backward, and bf16 accumulation)."""
+    if owner is not None:
+        w = owner
     mg = getattr(w, "main_grad", None)
     if mg is not None:
         gemm(dy, x, a_mn=True, b_mn=True, out=mg, epi=EPI_ACCUM)
@@ -81,6 +88,7 @@ class _Linear(torch.autograd.Function):
         ctx.act = act
         ctx.has_bias = b is not None
         ctx.bias_ref = b
+        ctx.w_param = w
         return y
 
     @staticmethod
@@ -91,7 +99,7 @@ class _Linear(torch.autograd.Function):
         if ctx.act is not None:
             dy = act_bwd(dy, pre, ctx.act)
         dx = gemm(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
-        dw = _weight_grad(dy, x, w) if ctx.needs_input_grad[1] else None
+        dw = _weight_grad(dy, x, w, ctx.w_param) if ctx.needs_input_grad[1] else None
         db = _bias_grad(dy, ctx.bias_ref) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
         return dx, dw, db, None
 
@@ -126,6 +134,7 @@ class _LinearResidual(torch.autograd.Function):
             y, z = gemm(x, w, bias=b, epi=EPI_GATE_RES, residual=res, gate=g, rows_per_gate=rpg), None
         ctx.save_for_backward(x, w, z, gate if has_gate else None)
         ctx.meta = (rows_per_gate, has_gate, b)
+        ctx.w_param = w
         return y
 
     @staticmethod
@@ -154,7 +163,7 @@ class _LinearResidual(torch.autograd.Function):
         else:
             dz = dy
         dx = gemm(dz, w, b_mn=True) if ctx.needs_input_grad[0] else None
-        dw = _weight_grad(dz, x, w) if ctx.needs_input_grad[1] else None
+        dw = _weight_grad(dz, x, w, ctx.w_param) if ctx.needs_input_grad[1] else None
         db = _bias_grad(dz, b) if (b is not None and ctx.needs_input_grad[2]) else None
         dres = dy if ctx.needs_input_grad[3] else None
         return dx, dw, db, dres, dgate, None

@@ -235,6 +235,7 @@ class _FusedUlyssesFn(torch.autograd.Function):
         ctx.meta = (B, S_l, H, D, scale, kv_lens)
         ctx.save_for_backward(x, w_qkv, q_pre, k_pre, wq_f, wk_f, freqs, rstd_q, rstd_k, qh, kh, vh, o_h, lse)
         ctx.w_dtypes = (wq.dtype, wk.dtype)
+        ctx.w_param = w_qkv
         ctx.bias_ref = b_qkv
         return o_s.view(rows, C)
 
@@ -277,7 +278,7 @@ class _FusedUlyssesFn(torch.autograd.Function):
         _, dwq = rmsrope_bwd_raw(dqkv[:, 0:C], q_pre, wq_f, freqs, rstd_q, D, False, out=dqkv[:, 0:C])
         _, dwk = rmsrope_bwd_raw(dqkv[:, C:2 * C], k_pre, wk_f, freqs, rstd_k, D, False, out=dqkv[:, C:2 * C])
         dx = gemm(dqkv, w_qkv, b_mn=True) if ctx.needs_input_grad[1] else None
-        dw = _weight_grad(dqkv, x, w_qkv) if ctx.needs_input_grad[2] else None
+        dw = _weight_grad(dqkv, x, w_qkv, ctx.w_param) if ctx.needs_input_grad[2] else None
         db = _bias_grad(dqkv, ctx.bias_ref) if (ctx.bias_ref is not None and ctx.needs_input_grad[3]) else None
         # layers run backward in reverse order, so this layer's region is the top of the stack
         if fu.slab.live and fu.slab.live[-1][1] == fu.slab.off:

@@ -183,7 +183,7 @@ class _FusedColumnLinear(torch.autograd.Function):
         # the gathered activations are kept for the weight gradient when the gather produced them
         ctx.save_for_backward(x_rows if gathered is None else gathered, w, pre)
         ctx.have_gathered = gathered is not None
-        ctx.act, ctx.tp, ctx.bias_ref = act, tp, b
+        ctx.act, ctx.tp, ctx.bias_ref, ctx.w_param = act, tp, b, w
         return y
 
     @staticmethod
@@ -200,7 +200,7 @@ class _FusedColumnLinear(torch.autograd.Function):
         dw = None
         if ctx.needs_input_grad[1]:
             xg = x_rows if ctx.have_gathered else _ag_rows(x_rows, tp.group, tp.size)
-            dw = _weight_grad(dy, xg, w)
+            dw = _weight_grad(dy, xg, w, ctx.w_param)
         db = _bias_grad(dy, ctx.bias_ref) if (ctx.bias_ref is not None and ctx.needs_input_grad[2]) else None
         return dx, dw, db, None, None
 
@@ -212,7 +212,7 @@ class _FusedRowLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_cols, w, tp):
         ctx.save_for_backward(x_cols, w)
-        ctx.tp = tp
+        ctx.tp, ctx.w_param = tp, w
         return tp.fused.gemm_rs(x_cols, w)
 
     @staticmethod
@@ -230,7 +230,7 @@ class _FusedRowLinear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             if dyg is None:
                 dyg = _ag_rows(dy_rows, tp.group, tp.size)
-            dw = _weight_grad(dyg, x_cols, w)
+            dw = _weight_grad(dyg, x_cols, w, ctx.w_param)
         return dx, dw, None
 
 

@@ -186,6 +186,37 @@ def test_linear_residual_gate_and_main_grad():
     assert w.grad is None and rel(w.main_grad - 0.5, wr.grad) < 6e-3
 
 
+def test_weight_gradient_reaches_main_grad_under_activation_checkpointing():
+    """Inside a non-reentrant checkpoint the backward pass gets a detached alias of the weight from its saved
+    tensors, without the parameter's attributes.  The weight gradient must still be accumulated (fp32) into the
+    parameter's main_grad and report through grad_ready, not come back as a bf16 ``.grad``."""
+    from torch.utils.checkpoint import checkpoint
+
+    B, S, K, F_, N_ = 2, 100, 256, 512, 256
+    rows = B * S
+    mk = lambda *sh, s=1.0: (torch.randn(*sh, device=DEV) * s).to(torch.bfloat16)
+    x = mk(rows, K, s=0.5).requires_grad_(True)
+    w1, b1 = torch.nn.Parameter(mk(F_, K, s=0.06)), torch.nn.Parameter(mk(F_))
+    w2, b2 = torch.nn.Parameter(mk(N_, F_, s=0.04)), torch.nn.Parameter(mk(N_))
+    res = mk(rows, N_)
+    gate = torch.randn(B, N_, device=DEV)
+    seen = []
+    for name, w in (("w1", w1), ("w2", w2)):
+        w.main_grad = torch.zeros(w.shape, device=DEV)
+        w.grad_ready = (lambda n=name: seen.append(n))
+    y = checkpoint(lambda t: ops.ffn(t, w1, b1, w2, b2, res, gate, S, act="gelu"), x, use_reentrant=False)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xx, a1, c1, a2, c2 = (t.detach().float().requires_grad_(True) for t in (x, w1, b1, w2, b2))
+    h = torch.nn.functional.gelu(torch.nn.functional.linear(xx, a1, c1), approximate="tanh")
+    yr = res.float() + gate.repeat_interleave(S, 0) * torch.nn.functional.linear(h, a2, c2)
+    yr.backward(dy.float())
+    assert w1.grad is None and w2.grad is None
+    assert sorted(seen) == ["w1", "w2"]
+    assert rel(w1.main_grad, a1.grad) < 8e-3 and rel(w2.main_grad, a2.grad) < 8e-3
+    assert rel(x.grad, xx.grad) < 8e-3
+
+
 @pytest.mark.parametrize("act", ["gelu", "silu"])
 def test_ffn_matches_fp32_autograd(act):
     B, S, C, F_ = 2, 150, 256, 640
