@@ -218,6 +218,10 @@ class Trainer:
             # identical initial weights on every replica (DDP.broadcast_params in the reference)
             dist.broadcast(self.buffer.params, src=mpu.get_group_ranks("dp_cp")[0], group=group)
             self.optimizer.reload_model_params()
+        if self.device.type == "cuda":
+            # the parameters moved into the flat buffer: their first storages (30 GiB for a 16 B-parameter model) sit in
+            # the allocator's cache as odd-sized blocks; hand them back before the first step sizes its own
+            torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ data
     def build_data_iterators(self):
