@@ -130,6 +130,17 @@ class DistBatchLoader:
                     raise EncoderTimeout(f"encoder rank {prod} stopped sending heartbeats {now - hb:.0f}s ago")
             time.sleep(0.001)
 
+    def _wait_group(self, work, what: str):
+        """A follower's wait for a collective of its TP x CP group, on the host and bounded."""
+        polled = PolledWork(work, self.backend)
+        t0 = time.time()
+        while not polled.done():
+            if time.time() - t0 > self.timeout_s:
+                raise EncoderTimeout(f"timed out after {self.timeout_s:.0f}s waiting for {what} from rank {self.src}")
+            time.sleep(0.0005)
+        if polled.thread is None:
+            polled.work.wait()
+
     def _receive(self):
         if self._pending is None:
             self._wait_until(lambda: self._announced() > self._posted, "the next sample")
@@ -182,8 +193,12 @@ class DistBatchLoader:
         if self.group_size > 1:
             # the header always goes round first, a stop header when the stream is over, so that followers leave
             # with the leader instead of waiting in a broadcast that never comes
-            dist.broadcast(hdr, self.src, group=self.group)
-            if not self.is_leader:
+            if self.is_leader:
+                dist.broadcast(hdr, self.src, group=self.group)
+            else:
+                # the header is read on the host through a side stream, which does not wait for the broadcast by
+                # itself: poll the collective's completion first (reading early returned zeros, a "bad magic number")
+                self._wait_group(dist.broadcast(hdr, self.src, group=self.group, async_op=True), "the sample header")
                 shapes, _, flags = decode_header(self._header_to_host(hdr))
                 stop = bool(flags & FLAG_STOP)
                 if not stop:
