@@ -97,7 +97,7 @@ class DistBatchLoader:
         self._posted += 1
 
     def _prefetch(self):
-        """Posts the receives of the following sample if the producer has already issued its sends."""
+        """Posts the receives of the following sample if the producer has already announced it."""
         if self._pending is not None or self.finished or self._announced() <= self._posted:
             return
         self._post_header()
