@@ -54,6 +54,16 @@ def checkpoint_name(root: str, iteration, release=False, tp_rank: Optional[int] 
     return os.path.join(checkpoint_dir(root, iteration, release), sub, filename)
 
 
+def _load_mapped(path: str):
+    """``torch.load`` of a file every rank opens but reads only a part of (the gathered optimizer state: 12 bytes
+    per parameter): memory-mapped, so a rank pages in its own shares instead of holding a private copy of the
+    whole file; plain loading for files written in the legacy (non-zip) format."""
+    try:
+        return torch.load(path, map_location="cpu", weights_only=False, mmap=True)
+    except (RuntimeError, ValueError):
+        return torch.load(path, map_location="cpu", weights_only=False)
+
+
 def zero2_shard_name(root: str, iteration, release: bool = False) -> str:
     """``zero2_optim_dp{d}_cp{c}.pt`` of this rank, beside its tensor-parallel rank's model file."""
     return checkpoint_name(root, iteration, release,
@@ -362,8 +372,7 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, strict: bool = 
                                                 "run with the same data- and context-parallel sizes")
                     optimizer.load_state_dict(torch.load(shard, map_location="cpu", weights_only=False))
                 elif opt_sd.get("sharded"):      # the fp32 state lives beside the model file, in buffer order
-                    full = torch.load(checkpoint_name(root, iteration, filename=DISTOPT_FILE),
-                                      map_location="cpu", weights_only=False)
+                    full = _load_mapped(checkpoint_name(root, iteration, filename=DISTOPT_FILE))
                     optimizer.scatter_full_state(full)
                 elif "master" in opt_sd:
                     # a replicated optimizer's regions, one after the other, are the full buffer as well: any
