@@ -198,6 +198,8 @@ class Trainer:
                         raise
                     print(f"WARNING: fused tensor-parallel kernels unavailable ({e}); using NCCL collectives", flush=True)
         tp_names = tuple(tp_shard_dims(inner, params=True)) if a.tensor_model_parallel_size > 1 else None
+        if arena is not None:
+            torch.cuda.empty_cache()     # the fp32 blocks of the initialisation: the arena is allocated outside this cache
         self.buffer = ParamBuffer(inner, shard_world=world if a.use_distributed_optimizer else 1, arena=arena,
                                   bucket_size=getattr(a, "ddp_bucket_size", None), tp_sharded_names=tp_names)
         # the peer-memory path overlaps each bucket's reduction with backward by default; NCCL on request
