@@ -77,6 +77,48 @@ def test_training_fed_by_an_encoder_rank():
     assert outs[0][3] == 0 and outs[1][3] == 5 and outs[0][4] and outs[1][4]
 
 
+def _replica_worker(rank, world):
+    """Two timestep-expert replicas of one rank each, fed by one encoder rank (the reference's "consumer models",
+    teletron/core/parallel_state.py:192-204): each replica draws its timesteps from its own range, averages
+    nothing with the other replica, and the two end up with different weights."""
+    from teletron_b200.parallel import state as mpu
+    from teletron_b200.train import Trainer, make_forward_step
+
+    a = _args(world, "--distributed-vae --distributed-vae-world-size 1 --consumer-models-num 2 "
+                     "--encoder-name synthetic_wan_encoder --dataset-type FakeDataset --train-iters 3 --log-interval 1")
+    a.moe_step_factor_list = [0.0, 0.5, 1.0]
+    try:
+        t = Trainer(a)
+    except SystemExit:
+        return "encoder-rank-done"
+    assert mpu.get_data_parallel_world_size(with_context_parallel=True) == 1      # replicas are not data-parallel peers
+    seen = []
+    inner = make_forward_step()
+
+    def fwd(it, model):
+        class Tap:
+            def __iter__(self_):
+                return self_
+
+            def __next__(self_):
+                b = next(it)
+                seen.append(b.get("timestep_range"))
+                return b
+
+        return inner(Tap(), model)
+
+    t.pretrain(fwd)
+    return seen, float(t.buffer.params.float().abs().sum()), t.train_data_iterator.received
+
+
+def test_timestep_expert_replicas_train_apart():
+    outs = run_distributed(_replica_worker, 3, timeout=240)
+    assert outs[2] == "encoder-rank-done"
+    (r0, w0, n0), (r1, w1, n1) = outs[0], outs[1]
+    assert r0 == [(0.0, 0.5)] * 3 and r1 == [(0.5, 1.0)] * 3
+    assert n0 == 3 and n1 == 3 and w0 != w1 and w0 > 0 and w1 > 0
+
+
 def _resilience_worker(rank, world, root, mode):
     """mode "full": 3 uninterrupted iterations.  "fail": rank 1 leaves after iteration 1 (between steps, nothing
     of its own in flight); rank 0 finds out at its next collective.  "resume": continue from the last checkpoint."""
