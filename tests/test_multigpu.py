@@ -482,3 +482,56 @@ def test_training_fed_by_an_encoder_rank_over_nccl():
     assert outs[1] == "encoder-rank-done"
     iters, moved = outs[0]
     assert iters == 3 and moved > 0
+
+
+def _ckpt_nccl_worker(rank, world, root, mode, backend="nccl"):
+    """DP2 with the sharded optimizer on the peer-memory path: "full" = three steps; "save" = two steps and a
+    checkpoint; "resume" = load it and take the third step."""
+    import os
+
+    from teletron_b200.ops import _lib
+    from teletron_b200.train import Trainer, make_forward_step, parse_args
+
+    os.environ["WORLD_SIZE"], os.environ["RANK"] = str(world), str(rank)
+    argv = ("--model ParallelWanModel --model-preset wan-tiny --hidden-size 256 --num-attention-heads 2 "
+            "--ffn-hidden-size 512 --num-layers 2 --train-iters 3 --micro-batch-size 1 --global-batch-size 2 "
+            "--lr 1e-3 --num-frames 5 --video-resolution 64 64 --log-interval 100 --clip-grad 1.0 --seed 5 "
+            f"--distributed-backend {backend} --use-distributed-optimizer --synthetic-latents --ddp-bucket-size 20000 "
+            f"--save {root}/{'full' if mode == 'full' else 'run'}").split()
+    if backend == "nccl":
+        argv.append("--bf16")
+    if mode == "resume":
+        argv += ["--load", f"{root}/run"]
+
+    def extra_args(p):
+        p.add_argument("--text-dim", type=int, default=64)
+        p.add_argument("--text-len", type=int, default=16)
+        return p
+
+    a = parse_args(extra_args, argv)
+    t = Trainer(a)
+    start = a.iteration
+    for it in range(start, 2 if mode == "save" else 3):
+        g = torch.Generator().manual_seed(100 + it)     # the timestep stream is a function of the iteration
+        t.train_step(make_forward_step(timestep_generator=g))
+        a.iteration = it + 1
+        a.consumed_train_samples += a.global_batch_size
+    if mode == "save":
+        t.save(2)
+    if backend == "nccl":
+        torch.cuda.synchronize()
+        _lib.check_status()
+    full = t.optimizer.gather_full_state()
+    return start, t.buffer.params.float().cpu(), None if full is None else full["exp_avg_sq"]
+
+
+@needs2
+def test_sharded_optimizer_checkpoint_round_trip_over_nccl(tmp_path):
+    """The optimizer shares travel to rank 0 bucket by bucket (``gather`` over NCCL), the file is memory-mapped
+    on load, and the resumed run continues bit for bit."""
+    full = run_distributed(_ckpt_nccl_worker, 2, str(tmp_path), "full", backend="nccl", timeout=150)
+    run_distributed(_ckpt_nccl_worker, 2, str(tmp_path), "save", backend="nccl", timeout=150)
+    res = run_distributed(_ckpt_nccl_worker, 2, str(tmp_path), "resume", backend="nccl", timeout=150)
+    assert res[0][0] == 2 and full[0][0] == 0
+    assert torch.equal(res[0][1], full[0][1]) and torch.equal(res[1][1], full[1][1])
+    assert torch.equal(res[0][2], full[0][2]) and float(full[0][2].abs().sum()) > 0
