@@ -229,13 +229,15 @@ def warm_up_groups(names=None) -> None:
     own allocator.  The groups of the training step itself meet theirs in the first step; the group of all
     transformer ranks is first used by the timer summary of the first log line, when the caching allocator may
     already hold every free byte of a large model's GPU, and the communicator then fails with an out-of-memory error
-    that no amount of cached memory can satisfy.  ``names`` defaults to that group.  Groups of one rank and groups
+    that no amount of cached memory can satisfy.  ``names`` defaults to that group and the data x context parallel one.  Groups of one rank and groups
     this rank is not part of are skipped; every rank walks the names in the same order, and groups of one kind are
     disjoint, so the collectives pair up."""
     if _S.topo is None or not dist.is_initialized():
         return
     if names is None:
-        names = ("replica",) if _S.topo.replicas > 1 else ("dit",)
+        # ... and the data x context parallel group: with the peer-memory optimizer its first NCCL use may be the
+        # gather of the optimizer state at the first checkpoint
+        names = ("replica" if _S.topo.replicas > 1 else "dit", "dp_cp")
     dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
     for name in names:
         g = _S.groups.get(name)
