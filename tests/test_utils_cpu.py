@@ -321,3 +321,32 @@ def test_status_word_values_are_described():
     assert describe_status(0x503) == "a peer barrier waiting for rank 3 ran out of its time budget"
     assert "MMA-issuing warp" in describe_status(0x202) and "wait #2" in describe_status(0x202)
     assert "misaligned" in describe_status(0x600) and describe_status(0x7ff).startswith("unknown status")
+
+
+def test_epilogue_staging_swizzle_is_a_conflict_free_bijection():
+    """Index arithmetic of ``stage_put`` / ``stage_flush`` (csrc/tt_common.cuh), restated on the host: a warp parks
+    32 rows of CH 16-byte chunks (row = lane) and reads them back with CH lanes per row.  Every (row, chunk) must land
+    in a slot of its own, the reader must find what the writer put there, and neither side may have two lanes of a
+    quarter warp (the unit in which 16-byte shared-memory accesses are served) in the same 16-byte bank group."""
+    for CH in (8, 16):
+        put = lambda lane, chunk: lane * CH * 16 + ((chunk ^ (lane & (CH - 1))) << 4)
+        slots = {put(l, c) for l in range(32) for c in range(CH)}
+        assert len(slots) == 32 * CH and max(slots) == 32 * CH * 16 - 16
+        # writer: one instruction = 32 lanes, same chunk index; served quarter warp by quarter warp
+        for c in range(CH):
+            for q in range(4):
+                banks = {(put(l, c) % 128) // 16 for l in range(q * 8, q * 8 + 8)}
+                assert len(banks) == 8
+        # reader: lane -> (row = i * (32 // CH) + lane // CH, chunk = lane % CH); it reads the slot of (row, chunk)
+        rpi = 32 // CH
+        seen = set()
+        for i in range(32 // rpi):
+            addr = []
+            for lane in range(32):
+                row, chunk = i * rpi + lane // CH, lane % CH
+                addr.append(row * CH * 16 + ((chunk ^ (row & (CH - 1))) << 4))
+                assert addr[-1] == put(row, chunk)
+                seen.add((row, chunk))
+            for q in range(4):
+                assert len({(a % 128) // 16 for a in addr[q * 8:q * 8 + 8]}) == 8
+        assert len(seen) == 32 * CH
